@@ -1,0 +1,452 @@
+// CUDA-core ("SIMT") engine of the block-sparse attention: a plain fp32-FMA implementation
+// of the key-chunk-major main kernels.  It exists to validate the tensor-core engine on the
+// GPU (same workspace contract, same combine kernels) and to serve shapes the tensor-core
+// engine does not cover.  Mathematics follows the reference kernels
+// (csrc/flash_moba/src/flash_fwd_kernel.h:535-640, flash_bwd_kernel.h:552-803,
+//  softmax.h:259-319, mask.h:139-176); the tiling is this library's own.
+#include "fmb_attn.cuh"
+
+namespace fmb {
+
+constexpr int kSimtM = 64;          // gathered query rows per tile
+constexpr int kSimtThreads = 256;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct SimtParams {
+  const void *q, *k, *v, *dout;
+  int64_t q_rs, q_hs, k_rs, k_hs, v_rs, v_hs, do_rs, do_hs;
+  void *dk, *dv; int64_t dk_rs, dk_hs, dv_rs, dv_hs;
+  const float *lse, *softmax_d;
+  const int64_t* col_offsets; const int32_t* col_nnz; const int32_t* indices; int64_t n_indices;
+  const int32_t *cu_q, *cu_k;
+  void* part_o; float* part_lse;
+  int heads, heads_k, ncol; int64_t total_q;
+  float scale; int causal;
+};
+
+// stage `rows_valid` gathered rows (ids in sRow, -1 = padding) transposed: dst[dd][m]
+template <typename T, int D>
+__device__ __forceinline__ void stage_rows_transposed(T* dst, const T* base, int64_t row_stride,
+                                                      const int* sRow, int rows_valid) {
+  constexpr int G = D / 8;
+  for (int e = threadIdx.x; e < kSimtM * G; e += blockDim.x) {
+    const int r = e % kSimtM, g = e / kSimtM;
+    uint4 u = make_uint4(0, 0, 0, 0);
+    if (r < rows_valid && sRow[r] >= 0) u = ldg_nc_16(base + (int64_t)sRow[r] * row_stride + g * 8);
+    const T* x = reinterpret_cast<const T*>(&u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dst[(g * 8 + i) * kSimtM + r] = x[i];
+  }
+}
+// natural layout dst[m][D]
+template <typename T, int D>
+__device__ __forceinline__ void stage_rows(T* dst, const T* base, int64_t row_stride, const int* sRow,
+                                           int rows_valid) {
+  constexpr int G = D / 8;
+  for (int e = threadIdx.x; e < kSimtM * G; e += blockDim.x) {
+    const int r = e / G, g = e % G;
+    uint4 u = make_uint4(0, 0, 0, 0);
+    if (r < rows_valid && sRow[r] >= 0) u = ldg_nc_16(base + (int64_t)sRow[r] * row_stride + g * 8);
+    *reinterpret_cast<uint4*>(dst + r * D + g * 8) = u;
+  }
+}
+// key chunk: natural dst[key][D] and/or transposed dstT[dd][C]
+template <typename T, int C, int D>
+__device__ __forceinline__ void stage_keys(T* dst, T* dstT, const T* base, int64_t row_stride, int keys_valid) {
+  constexpr int G = D / 8;
+  for (int e = threadIdx.x; e < C * G; e += blockDim.x) {
+    const int r = e % C, g = e / C;
+    uint4 u = make_uint4(0, 0, 0, 0);
+    if (r < keys_valid) u = ldg_nc_16(base + (int64_t)r * row_stride + g * 8);
+    if (dst) *reinterpret_cast<uint4*>(dst + r * D + g * 8) = u;
+    if (dstT) {
+      const T* x = reinterpret_cast<const T*>(&u);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dstT[(g * 8 + i) * C + r] = x[i];
+    }
+  }
+}
+
+// acc[4][C/16] += At^T Bt : rows ty*4.., cols tx*(C/16)..   (At [D][64], Bt [D][C])
+template <typename T, int C, int D>
+__device__ __forceinline__ void gemm_rows_keys(const T* At, const T* Bt, float (&acc)[4][C / 16]) {
+  constexpr int TN = C / 16;
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+#pragma unroll 4
+  for (int dd = 0; dd < D; ++dd) {
+    float a[4], b[TN];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) a[i] = Elem<T>::to_f(At[dd * kSimtM + ty * 4 + i]);
+#pragma unroll
+    for (int j = 0; j < TN; ++j) b[j] = Elem<T>::to_f(Bt[dd * C + tx * TN + j]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+  }
+}
+
+// ======================================================================== forward
+template <typename T, int C, int D>
+__global__ void __launch_bounds__(kSimtThreads) fwd_main_simt_kernel(SimtParams p) {
+  constexpr int TN = C / 16, TD = D / 16, SS = C + 4;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* sKt = reinterpret_cast<T*>(smem_raw);          // [D][C]
+  T* sV = sKt + D * C;                              // [C][D]
+  T* sQt = sV + C * D;                              // [D][64]
+  float* sS = reinterpret_cast<float*>(sQt + D * kSimtM);   // [64][C+4]
+  int* sRow = reinterpret_cast<int*>(sS + kSimtM * SS);     // [64]
+  float* sInv = reinterpret_cast<float*>(sRow + kSimtM);    // [64]
+
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int64_t ci = ((int64_t)b * p.heads + h) * p.ncol + c;
+  const int nnz = p.col_nnz[ci];
+  if (nnz <= 0) return;
+  const int64_t off = p.col_offsets[ci];
+  if (off < 0 || off + nnz > p.n_indices) return;
+  const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
+  const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
+  const int key0 = c * C;
+  const int keys_valid = max(0, min(C, len_k - key0));
+  const int hk = h / (p.heads / p.heads_k);
+  const int shift = len_k - len_q;
+  const float scale_log2 = p.scale * kLog2e;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+
+  const T* kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + key0) * p.k_rs + (int64_t)hk * p.k_hs;
+  const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
+  const T* qbase = static_cast<const T*>(p.q) + (int64_t)q0 * p.q_rs + (int64_t)h * p.q_hs;
+  stage_keys<T, C, D>(nullptr, sKt, kbase, p.k_rs, keys_valid);
+  stage_keys<T, C, D>(sV, nullptr, vbase, p.v_rs, keys_valid);
+  T* part_o = static_cast<T*>(p.part_o);
+
+  for (int t0 = 0; t0 < nnz; t0 += kSimtM) {
+    const int rows = min(kSimtM, nnz - t0);
+    __syncthreads();
+    if (threadIdx.x < kSimtM) {
+      int r = -1;
+      if (threadIdx.x < rows) {
+        r = p.indices[off + t0 + threadIdx.x];
+        if (r < 0 || r >= len_q) r = -1;
+      }
+      sRow[threadIdx.x] = r;
+    }
+    __syncthreads();
+    stage_rows_transposed<T, D>(sQt, qbase, p.q_rs, sRow, rows);
+    __syncthreads();
+    float acc[4][TN];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+    gemm_rows_keys<T, C, D>(sQt, sKt, acc);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) sS[(ty * 4 + i) * SS + tx * TN + j] = acc[i][j];
+    __syncthreads();
+    // chunk-local softmax: warp w owns rows w*8..w*8+7
+    for (int rr = 0; rr < 8; ++rr) {
+      const int m = warp * 8 + rr;
+      const int r = sRow[m];
+      const int lim = p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid;  // visible keys: j < lim
+      float mx = -CUDART_INF_F;
+      for (int j = lane; j < C; j += 32) {
+        const float s = (r >= 0 && j < lim) ? sS[m * SS + j] : -CUDART_INF_F;
+        mx = fmaxf(mx, s);
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      float sum = 0.f;
+      for (int j = lane; j < C; j += 32) {
+        float pr = 0.f;
+        if (r >= 0 && j < lim) pr = exp2f((sS[m * SS + j] - mx) * scale_log2);
+        sS[m * SS + j] = pr;
+        sum += pr;
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      if (lane == 0) {
+        sInv[m] = sum > 0.f ? 1.f / sum : 0.f;
+        if (m < rows) p.part_lse[off + t0 + m] = sum > 0.f ? mx * p.scale + logf(sum) : -CUDART_INF_F;
+      }
+    }
+    __syncthreads();
+    // partial O = P.V / l
+    float o[4][TD];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < TD; ++j) o[i][j] = 0.f;
+    for (int j = 0; j < C; ++j) {
+      float pr[4], vv[TD];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pr[i] = sS[(ty * 4 + i) * SS + j];
+#pragma unroll
+      for (int x = 0; x < TD; ++x) vv[x] = Elem<T>::to_f(sV[j * D + tx * TD + x]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int x = 0; x < TD; ++x) o[i][x] = fmaf(pr[i], vv[x], o[i][x]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int m = ty * 4 + i;
+      if (m < rows) {
+        const float inv = sInv[m];
+        T* dst = part_o + (off + t0 + m) * D + tx * TD;
+#pragma unroll
+        for (int x = 0; x < TD; ++x) dst[x] = Elem<T>::from_f(o[i][x] * inv);
+      }
+    }
+  }
+}
+
+// ======================================================================== backward
+template <typename T, int C, int D>
+__global__ void __launch_bounds__(kSimtThreads) bwd_main_simt_kernel(SimtParams p) {
+  constexpr int TN = C / 16, TD = D / 16, SS = C + 4;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* sKt = reinterpret_cast<T*>(smem_raw);          // [D][C]
+  T* sVt = sKt + D * C;                             // [D][C]
+  T* sK = sVt + D * C;                              // [C][D]
+  T* sQt = sK + C * D;                              // [D][64]
+  T* sdOt = sQt + D * kSimtM;                       // [D][64]
+  T* sQ = sdOt + D * kSimtM;                        // [64][D]
+  T* sdO = sQ + kSimtM * D;                         // [64][D]
+  float* sP = reinterpret_cast<float*>(sdO + kSimtM * D);   // [64][C+4]
+  float* sdS = sP + kSimtM * SS;                            // [64][C+4]
+  int* sRow = reinterpret_cast<int*>(sdS + kSimtM * SS);    // [64]
+  float* sLse = reinterpret_cast<float*>(sRow + kSimtM);    // [64]
+  float* sD = sLse + kSimtM;                                // [64]
+
+  const int c = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
+  const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
+  const int key0 = c * C;
+  if (key0 >= len_k) return;
+  const int keys_valid = min(C, len_k - key0);
+  const int group = p.heads / p.heads_k;
+  const int shift = len_k - len_q;
+  const float scale_log2 = p.scale * kLog2e;
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+
+  const T* kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + key0) * p.k_rs + (int64_t)hk * p.k_hs;
+  const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
+  stage_keys<T, C, D>(sK, sKt, kbase, p.k_rs, keys_valid);
+  stage_keys<T, C, D>(nullptr, sVt, vbase, p.v_rs, keys_valid);
+  float* part_dq = static_cast<float*>(p.part_o);
+
+  // dK/dV accumulators: keys ty*TN.., dims tx*TD..
+  float dk[TN][TD], dv[TN][TD];
+#pragma unroll
+  for (int i = 0; i < TN; ++i)
+#pragma unroll
+    for (int j = 0; j < TD; ++j) { dk[i][j] = 0.f; dv[i][j] = 0.f; }
+
+  for (int hg = 0; hg < group; ++hg) {
+    const int h = hk * group + hg;
+    if (c >= p.ncol) break;
+    const int64_t ci = ((int64_t)b * p.heads + h) * p.ncol + c;
+    const int nnz = p.col_nnz[ci];
+    const int64_t off = p.col_offsets[ci];
+    if (nnz <= 0 || off < 0 || off + nnz > p.n_indices) continue;
+    const T* qbase = static_cast<const T*>(p.q) + (int64_t)q0 * p.q_rs + (int64_t)h * p.q_hs;
+    const T* dobase = static_cast<const T*>(p.dout) + (int64_t)q0 * p.do_rs + (int64_t)h * p.do_hs;
+    const float* lse = p.lse + (int64_t)h * p.total_q + q0;
+    const float* dsum = p.softmax_d + (int64_t)h * p.total_q + q0;
+
+    for (int t0 = 0; t0 < nnz; t0 += kSimtM) {
+      const int rows = min(kSimtM, nnz - t0);
+      __syncthreads();
+      if (threadIdx.x < kSimtM) {
+        int r = -1;
+        float l = CUDART_INF_F, dd = 0.f;
+        if (threadIdx.x < rows) {
+          r = p.indices[off + t0 + threadIdx.x];
+          if (r < 0 || r >= len_q) r = -1;
+          else { l = lse[r]; dd = dsum[r]; }
+        }
+        sRow[threadIdx.x] = r; sLse[threadIdx.x] = l; sD[threadIdx.x] = dd;
+      }
+      __syncthreads();
+      stage_rows_transposed<T, D>(sQt, qbase, p.q_rs, sRow, rows);
+      stage_rows_transposed<T, D>(sdOt, dobase, p.do_rs, sRow, rows);
+      stage_rows<T, D>(sQ, qbase, p.q_rs, sRow, rows);
+      stage_rows<T, D>(sdO, dobase, p.do_rs, sRow, rows);
+      __syncthreads();
+      {
+        float s[4][TN], dp[4][TN];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < TN; ++j) { s[i][j] = 0.f; dp[i][j] = 0.f; }
+        gemm_rows_keys<T, C, D>(sQt, sKt, s);
+        gemm_rows_keys<T, C, D>(sdOt, sVt, dp);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int m = ty * 4 + i;
+          const int r = sRow[m];
+          const int lim = p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid;
+          const float l2 = sLse[m] * kLog2e, dd = sD[m];
+#pragma unroll
+          for (int j = 0; j < TN; ++j) {
+            const int col = tx * TN + j;
+            float pr = 0.f;
+            if (r >= 0 && col < lim) pr = exp2f(s[i][j] * scale_log2 - l2);
+            sP[m * SS + col] = pr;
+            sdS[m * SS + col] = pr * (dp[i][j] - dd);
+          }
+        }
+      }
+      __syncthreads();
+      // dV += P^T dO ; dK += dS^T Q        (keys ty*TN.., dims tx*TD..)
+      for (int m = 0; m < kSimtM; ++m) {
+        float pv[TN], ds[TN], dov[TD], qv[TD];
+#pragma unroll
+        for (int i = 0; i < TN; ++i) { pv[i] = sP[m * SS + ty * TN + i]; ds[i] = sdS[m * SS + ty * TN + i]; }
+#pragma unroll
+        for (int j = 0; j < TD; ++j) {
+          dov[j] = Elem<T>::to_f(sdO[m * D + tx * TD + j]);
+          qv[j] = Elem<T>::to_f(sQ[m * D + tx * TD + j]);
+        }
+#pragma unroll
+        for (int i = 0; i < TN; ++i)
+#pragma unroll
+          for (int j = 0; j < TD; ++j) {
+            dv[i][j] = fmaf(pv[i], dov[j], dv[i][j]);
+            dk[i][j] = fmaf(ds[i], qv[j], dk[i][j]);
+          }
+      }
+      // partial dQ = dS . K  (rows ty*4.., dims tx*TD..), unscaled
+      {
+        float dq[4][TD];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < TD; ++j) dq[i][j] = 0.f;
+        for (int key = 0; key < C; ++key) {
+          float ds[4], kv[TD];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) ds[i] = sdS[(ty * 4 + i) * SS + key];
+#pragma unroll
+          for (int j = 0; j < TD; ++j) kv[j] = Elem<T>::to_f(sK[key * D + tx * TD + j]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < TD; ++j) dq[i][j] = fmaf(ds[i], kv[j], dq[i][j]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int m = ty * 4 + i;
+          if (m < rows) {
+            float* dst = part_dq + (off + t0 + m) * D + tx * TD;
+#pragma unroll
+            for (int j = 0; j < TD; ++j) dst[j] = dq[i][j];
+          }
+        }
+      }
+    }
+  }
+  // write dK (scaled) and dV of this chunk
+  T* dkp = static_cast<T*>(p.dk) + (int64_t)(k0 + key0) * p.dk_rs + (int64_t)hk * p.dk_hs;
+  T* dvp = static_cast<T*>(p.dv) + (int64_t)(k0 + key0) * p.dv_rs + (int64_t)hk * p.dv_hs;
+#pragma unroll
+  for (int i = 0; i < TN; ++i) {
+    const int key = ty * TN + i;
+    if (key < keys_valid) {
+#pragma unroll
+      for (int j = 0; j < TD; ++j) {
+        dkp[(int64_t)key * p.dk_rs + tx * TD + j] = Elem<T>::from_f(dk[i][j] * p.scale);
+        dvp[(int64_t)key * p.dv_rs + tx * TD + j] = Elem<T>::from_f(dv[i][j]);
+      }
+    }
+  }
+}
+
+// pairs whose chunk lies beyond the keys of the sequence: empty partials
+__global__ void __launch_bounds__(256) fwd_dead_columns_kernel(SimtParams p, int chunk, int d, int elem_bytes) {
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int len_k = p.cu_k[b + 1] - p.cu_k[b];
+  if (c * chunk < len_k) return;
+  const int64_t ci = ((int64_t)b * p.heads + h) * p.ncol + c;
+  const int nnz = p.col_nnz[ci];
+  const int64_t off = p.col_offsets[ci];
+  if (nnz <= 0 || off < 0 || off + nnz > p.n_indices) return;
+  for (int j = threadIdx.x; j < nnz; j += blockDim.x) p.part_lse[off + j] = -CUDART_INF_F;
+  const int64_t words = (int64_t)nnz * d * elem_bytes / 4;
+  uint32_t* dst = reinterpret_cast<uint32_t*>(static_cast<char*>(p.part_o) + off * d * elem_bytes);
+  for (int64_t i = threadIdx.x; i < words; i += blockDim.x) dst[i] = 0u;
+}
+
+static SimtParams make_params(const AttnArgs& a, const AttnWorkspace& w) {
+  SimtParams p;
+  p.q = a.q; p.k = a.k; p.v = a.v; p.dout = a.dout;
+  p.q_rs = a.q_rs; p.q_hs = a.q_hs; p.k_rs = a.k_rs; p.k_hs = a.k_hs; p.v_rs = a.v_rs; p.v_hs = a.v_hs;
+  p.do_rs = a.do_rs; p.do_hs = a.do_hs;
+  p.dk = a.dk; p.dv = a.dv; p.dk_rs = a.dk_rs; p.dk_hs = a.dk_hs; p.dv_rs = a.dv_rs; p.dv_hs = a.dv_hs;
+  p.lse = a.lse; p.softmax_d = a.softmax_d;
+  p.col_offsets = a.col_offsets; p.col_nnz = a.col_nnz; p.indices = a.indices; p.n_indices = a.n_indices;
+  p.cu_q = a.cu_q; p.cu_k = a.cu_k; p.part_o = w.part_o; p.part_lse = w.part_lse;
+  p.heads = a.heads; p.heads_k = a.heads_k; p.ncol = a.ncol; p.total_q = a.total_q;
+  p.scale = a.scale; p.causal = a.causal;
+  return p;
+}
+
+int launch_fwd_dead_columns(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+  if (a.ncol == 0 || a.batch == 0) return FMB_OK;
+  SimtParams p = make_params(a, w);
+  fwd_dead_columns_kernel<<<dim3(a.ncol, a.heads, a.batch), 256, 0, s>>>(p, a.chunk, a.d, 2);
+  FMB_LAUNCH_CHECK("fwd_dead_columns_kernel");
+  return FMB_OK;
+}
+
+template <typename T, int C, int D>
+static int fwd_launch(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+  SimtParams p = make_params(a, w);
+  const size_t smem = (size_t)(2 * C * D + D * kSimtM) * sizeof(T) + (size_t)kSimtM * (C + 4) * 4 + kSimtM * 8;
+  auto kern = fwd_main_simt_kernel<T, C, D>;
+  FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<dim3(a.ncol, a.heads, a.batch), kSimtThreads, smem, s>>>(p);
+  FMB_LAUNCH_CHECK("fwd_main_simt_kernel");
+  return FMB_OK;
+}
+template <typename T, int C, int D>
+static int bwd_launch(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+  SimtParams p = make_params(a, w);
+  const size_t smem = (size_t)(3 * C * D + 4 * D * kSimtM) * sizeof(T) + (size_t)2 * kSimtM * (C + 4) * 4 +
+                      kSimtM * 12;
+  auto kern = bwd_main_simt_kernel<T, C, D>;
+  FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int nchunk = max(a.ncol, ceil_div(a.max_k, C));
+  kern<<<dim3(nchunk, a.heads_k, a.batch), kSimtThreads, smem, s>>>(p);
+  FMB_LAUNCH_CHECK("bwd_main_simt_kernel");
+  return FMB_OK;
+}
+
+#define FMB_SIMT_DISPATCH(FN)                                                               \
+  if (a.dtype == FMB_BF16) {                                                                \
+    if (a.chunk == 64 && a.d == 64) return FN<__nv_bfloat16, 64, 64>(a, w, s);              \
+    if (a.chunk == 64 && a.d == 128) return FN<__nv_bfloat16, 64, 128>(a, w, s);            \
+    if (a.chunk == 128 && a.d == 64) return FN<__nv_bfloat16, 128, 64>(a, w, s);            \
+    if (a.chunk == 128 && a.d == 128) return FN<__nv_bfloat16, 128, 128>(a, w, s);          \
+  } else {                                                                                  \
+    if (a.chunk == 64 && a.d == 64) return FN<__half, 64, 64>(a, w, s);                     \
+    if (a.chunk == 64 && a.d == 128) return FN<__half, 64, 128>(a, w, s);                   \
+    if (a.chunk == 128 && a.d == 64) return FN<__half, 128, 64>(a, w, s);                   \
+    if (a.chunk == 128 && a.d == 128) return FN<__half, 128, 128>(a, w, s);                 \
+  }                                                                                         \
+  return fail(FMB_ERR_UNSUPPORTED, "attention (CUDA-core engine): chunk %d / head_dim %d not built "  \
+              "(chunk in {64,128}, head_dim in {64,128})", a.chunk, a.d);
+
+int launch_fwd_main_simt(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+  if (a.ncol == 0 || a.batch == 0 || a.heads == 0) return FMB_OK;
+  FMB_SIMT_DISPATCH(fwd_launch)
+}
+int launch_bwd_main_simt(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+  if (a.batch == 0 || a.heads == 0) return FMB_OK;
+  FMB_SIMT_DISPATCH(bwd_launch)
+}
+
+}  // namespace fmb

@@ -1,0 +1,208 @@
+"""Thin PyTorch wrappers over the C ABI: allocate outputs and workspaces with the torch
+caching allocator, pass raw device pointers + the current CUDA stream.  One function per
+stage; `flash_moba_b200.interface` composes them into the reference's public API.
+
+The arithmetic lives entirely in libflashmoba_b200.so; nothing here computes on tensors.
+"""
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import check, lib
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return _lib.FMB_BF16
+    if t.dtype == torch.float16:
+        return _lib.FMB_FP16
+    raise RuntimeError("FlashMoBA only supports fp16 and bf16 data type")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("flash_moba_b200: all tensors must be on a CUDA device (there is no CPU path)")
+
+
+def _i32c(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.dtype != torch.int32:
+        raise RuntimeError(f"{name} must have dtype int32")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    return t
+
+
+def _last_contig(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.stride(-1) != 1:
+        raise RuntimeError(f"{name} must have contiguous last dimension")
+    return t
+
+
+def ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def set_engine(engine: int) -> int:
+    """0 = CUDA-core validation kernels, 1 = tcgen05 kernels.  Returns the engine in use."""
+    return lib.fmb_set_engine(int(engine))
+
+
+# ------------------------------------------------------------------------------- stage P
+def mean_pool(k: torch.Tensor, cu_seqlens_k: torch.Tensor, max_seqlen_k: int, chunk: int
+              ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Centroids of every chunk.  No host sync: km is allocated with an upper bound of
+    ceil(total_k/chunk) + batch rows; rows [0, cu_seqlens_km[-1]) are valid."""
+    _require_cuda(k, cu_seqlens_k)
+    _last_contig(k, "k")
+    _i32c(cu_seqlens_k, "cu_seqlens_k")
+    total_k, hk, d = k.shape
+    batch = cu_seqlens_k.numel() - 1
+    rows_ub = (total_k + chunk - 1) // chunk + batch
+    with torch.cuda.device(k.device):
+        km = torch.empty((rows_ub, hk, d), dtype=k.dtype, device=k.device)
+        cu_km = torch.empty((batch + 1,), dtype=torch.int32, device=k.device)
+        check(lib.fmb_chunk_offsets(ptr(cu_seqlens_k), batch, chunk, ptr(cu_km), _stream()))
+        check(lib.fmb_mean_pool(ptr(k), k.stride(0), k.stride(1), ptr(cu_seqlens_k), ptr(cu_km), ptr(km),
+                                batch, hk, d, int(max_seqlen_k), chunk, _dtype_code(k), _stream()))
+    return km, cu_km
+
+
+# ------------------------------------------------------------------------------- stage G
+def gate_topk(q, km, cu_seqlens_q, cu_seqlens_k, cu_seqlens_km, max_seqlen_q: int, max_seqlen_k: int,
+              topk: int, chunk: int, causal: bool, return_values: bool = False):
+    """Per-row top-k chunk lists.  Returns idx as a (total_q, heads, topk) VIEW of a
+    head-major (heads, total_q, topk) buffer (the layout the pattern builder streams), and
+    the scores in the same layout (or None)."""
+    _require_cuda(q, km)
+    _last_contig(q, "q")
+    if not km.is_contiguous():
+        raise RuntimeError("km must be contiguous")
+    total_q, h, d = q.shape
+    hk = km.shape[1]
+    batch = cu_seqlens_q.numel() - 1
+    with torch.cuda.device(q.device):
+        idx = torch.empty((h, total_q, topk), dtype=torch.int32, device=q.device)
+        val = torch.empty((h, total_q, topk), dtype=torch.float32, device=q.device) if return_values else None
+        check(lib.fmb_gate_topk(ptr(q), q.stride(0), q.stride(1), ptr(km), ptr(_i32c(cu_seqlens_q, "cu_seqlens_q")),
+                                ptr(_i32c(cu_seqlens_k, "cu_seqlens_k")), ptr(_i32c(cu_seqlens_km, "cu_seqlens_km")),
+                                ptr(idx), ptr(val), topk, total_q * topk, batch, h, hk, d, int(max_seqlen_q),
+                                int(max_seqlen_k), int(topk), int(chunk), int(bool(causal)), _dtype_code(q),
+                                _stream()))
+    return idx.permute(1, 0, 2), (val.permute(1, 0, 2) if val is not None else None)
+
+
+# --------------------------------------------------------------------------- stages O/E/S
+def build_csc(topk_idx: torch.Tensor, cu_seqlens_q: torch.Tensor, max_seqlen_q: int, ncol: int):
+    """(col_offsets i64 (B,H,ncol), col_nnz i32 (B,H,ncol), indices i32 (T*H*topk))."""
+    _require_cuda(topk_idx)
+    if topk_idx.dtype != torch.int32 or topk_idx.stride(-1) != 1:
+        raise RuntimeError("topk_idx must be int32 with contiguous last dimension")
+    total_q, h, topk = topk_idx.shape
+    batch = cu_seqlens_q.numel() - 1
+    dev = topk_idx.device
+    with torch.cuda.device(dev):
+        col_offsets = torch.empty((batch, h, ncol), dtype=torch.int64, device=dev)
+        col_nnz = torch.empty((batch, h, ncol), dtype=torch.int32, device=dev)
+        indices = torch.empty((total_q * h * topk,), dtype=torch.int32, device=dev)
+        nbytes = lib.fmb_build_csc_workspace_bytes(batch, h, int(max_seqlen_q), ncol)
+        ws = torch.empty((max(nbytes, 1),), dtype=torch.uint8, device=dev)
+        check(lib.fmb_build_csc(ptr(topk_idx), topk_idx.stride(0), topk_idx.stride(1),
+                                ptr(_i32c(cu_seqlens_q, "cu_seqlens_q")), ptr(col_offsets), ptr(col_nnz),
+                                ptr(indices), ptr(ws), nbytes, batch, h, topk, int(max_seqlen_q), ncol, _stream()))
+    return col_offsets, col_nnz, indices
+
+
+def varlen_sort(starts: torch.Tensor, ends: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    _require_cuda(starts, ends, src)
+    if starts.dtype != torch.int64 or ends.dtype != torch.int64 or src.dtype != torch.int32:
+        raise RuntimeError("varlen_sort: offsets must be int64 and keys int32")
+    starts, ends, src = starts.contiguous(), ends.contiguous(), src.contiguous()
+    with torch.cuda.device(src.device):
+        dst = torch.empty_like(src)
+        check(lib.fmb_varlen_sort(ptr(starts), ptr(ends), ptr(src), ptr(dst), starts.numel(), src.numel(), _stream()))
+    return dst
+
+
+# ------------------------------------------------------------------------------- stage F
+def _check_pattern(col_offsets, col_nnz, indices):
+    if col_offsets.dtype != torch.int64:
+        raise RuntimeError("moba_col_offsets must have dtype torch.int64")
+    if col_nnz.dtype != torch.int32:
+        raise RuntimeError("moba_col_nnz must have dtype torch.int32")
+    if indices.dtype != torch.int32:
+        raise RuntimeError("moba_row_indices must have dtype torch.int32")
+    for t, n in ((col_offsets, "moba_col_offsets"), (col_nnz, "moba_col_nnz"), (indices, "moba_row_indices")):
+        if not t.is_contiguous():
+            raise RuntimeError(f"{n} must be contiguous")
+    if col_offsets.shape != col_nnz.shape or col_offsets.dim() != 3:
+        raise RuntimeError("moba_col_offsets / moba_col_nnz must both be (batch, heads, ncol)")
+
+
+def attn_fwd(q, k, v, col_offsets, col_nnz, indices, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int,
+             max_seqlen_k: int, chunk: int, softmax_scale: float, causal: bool, out: Optional[torch.Tensor] = None):
+    """Block-sparse forward.  Returns (out (T,H,d), lse (H,T) fp32)."""
+    _require_cuda(q, k, v, col_offsets, col_nnz, indices)
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _last_contig(t, n)
+    if not (q.dtype == k.dtype == v.dtype):
+        raise RuntimeError("query, key and value must have the same dtype")
+    _check_pattern(col_offsets, col_nnz, indices)
+    total_q, h, d = q.shape
+    hk = k.shape[1]
+    batch = cu_seqlens_q.numel() - 1
+    if col_offsets.shape[0] != batch or col_offsets.shape[1] != h:
+        raise RuntimeError("pattern shape does not match (batch, heads)")
+    ncol_needed = (int(max_seqlen_k) + chunk - 1) // chunk
+    if col_offsets.shape[2] != ncol_needed:
+        raise RuntimeError(f"pattern has {col_offsets.shape[2]} columns, expected ceil(max_seqlen_k/lg_block_n) = {ncol_needed}")
+    dev = q.device
+    with torch.cuda.device(dev):
+        if out is None:
+            out = torch.empty_like(q)
+        lse = torch.empty((h, total_q), dtype=torch.float32, device=dev)
+        nbytes = lib.fmb_attn_fwd_workspace_bytes(total_q, h, d, indices.numel())
+        ws = torch.empty((max(nbytes, 1),), dtype=torch.uint8, device=dev)
+        check(lib.fmb_attn_fwd(ptr(q), q.stride(0), q.stride(1), ptr(k), k.stride(0), k.stride(1),
+                               ptr(v), v.stride(0), v.stride(1), ptr(out), out.stride(0), out.stride(1), ptr(lse),
+                               ptr(col_offsets), ptr(col_nnz), ptr(indices), indices.numel(),
+                               ptr(_i32c(cu_seqlens_q, "cu_seqlens_q")), ptr(_i32c(cu_seqlens_k, "cu_seqlens_k")),
+                               ptr(ws), nbytes, batch, h, hk, d, total_q, int(max_seqlen_q), int(max_seqlen_k),
+                               int(chunk), float(softmax_scale), int(bool(causal)), _dtype_code(q), _stream()))
+    return out, lse
+
+
+# ------------------------------------------------------------------------------- stage B
+def attn_bwd(dout, q, k, v, out, lse, dq, dk, dv, col_offsets, col_nnz, indices, cu_seqlens_q, cu_seqlens_k,
+             max_seqlen_q: int, max_seqlen_k: int, chunk: int, softmax_scale: float, causal: bool) -> torch.Tensor:
+    """Block-sparse backward into caller-allocated dq/dk/dv.  Returns softmax_d (H,T) fp32."""
+    _require_cuda(dout, q, k, v, out, lse, dq, dk, dv)
+    for t, n in ((dout, "dout"), (q, "q"), (k, "k"), (v, "v"), (out, "out"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+        _last_contig(t, n)
+    _check_pattern(col_offsets, col_nnz, indices)
+    total_q, h, d = q.shape
+    total_k, hk, _ = k.shape
+    batch = cu_seqlens_q.numel() - 1
+    dev = q.device
+    if lse.dtype != torch.float32 or not lse.is_contiguous() or tuple(lse.shape) != (h, total_q):
+        raise RuntimeError("softmax_lse must be a contiguous float32 (heads, total_q) tensor")
+    with torch.cuda.device(dev):
+        softmax_d = torch.empty((h, total_q), dtype=torch.float32, device=dev)
+        nbytes = lib.fmb_attn_bwd_workspace_bytes(total_q, h, d, indices.numel())
+        ws = torch.empty((max(nbytes, 1),), dtype=torch.uint8, device=dev)
+        check(lib.fmb_attn_bwd(ptr(dout), dout.stride(0), dout.stride(1), ptr(q), q.stride(0), q.stride(1),
+                               ptr(k), k.stride(0), k.stride(1), ptr(v), v.stride(0), v.stride(1),
+                               ptr(out), out.stride(0), out.stride(1), ptr(lse),
+                               ptr(dq), dq.stride(0), dq.stride(1), ptr(dk), dk.stride(0), dk.stride(1),
+                               ptr(dv), dv.stride(0), dv.stride(1), ptr(softmax_d),
+                               ptr(col_offsets), ptr(col_nnz), ptr(indices), indices.numel(),
+                               ptr(_i32c(cu_seqlens_q, "cu_seqlens_q")), ptr(_i32c(cu_seqlens_k, "cu_seqlens_k")),
+                               ptr(ws), nbytes, batch, h, hk, d, total_q, total_k, int(max_seqlen_q),
+                               int(max_seqlen_k), int(chunk), float(softmax_scale), int(bool(causal)),
+                               _dtype_code(q), _stream()))
+    return softmax_d

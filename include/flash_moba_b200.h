@@ -1,0 +1,164 @@
+/*
+ * flash_moba_b200 — C ABI of the B200 (sm_100a) MoBA sparse-attention kernels.
+ *
+ * One shared library, libflashmoba_b200.so.  Every entry point takes plain device
+ * pointers, sizes and a CUDA stream; it never allocates or frees device memory, never
+ * synchronises the host with the device and keeps no state between calls.  All outputs
+ * and workspaces are allocated by the caller; `*_workspace_bytes` tells how much.
+ * All work is enqueued on `stream` of the CURRENT device (the caller sets the device).
+ *
+ * Return value: 0 on success, otherwise one of FMB_ERR_*; `fmb_last_error()` then
+ * returns a thread-local, human readable message.
+ *
+ * Each function names the entry point of the reference project (mit-han-lab/flash-moba)
+ * whose work it replaces, as `file:line` inside that project.
+ *
+ * Conventions
+ *   - q/k/v/out/dout/dq/dk/dv are (tokens, heads, head_dim) with head_dim contiguous;
+ *     `*_row_stride` / `*_head_stride` are in ELEMENTS.
+ *   - cu_seqlens_* are int32[batch+1] on the device.
+ *   - dtype: FMB_BF16 or FMB_FP16.
+ *   - pattern ("CSC"): col_offsets int64[batch][heads][ncol], col_nnz int32[batch][heads][ncol],
+ *     indices int32[n_indices]; column (b,h,c) lists, ascending, the sequence-local query
+ *     rows that attend key chunk c:  indices[col_offsets[b,h,c] .. + col_nnz[b,h,c]).
+ */
+#ifndef FLASH_MOBA_B200_H_
+#define FLASH_MOBA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* fmb_stream_t; /* a cudaStream_t */
+
+enum { FMB_BF16 = 0, FMB_FP16 = 1 };
+
+enum {
+  FMB_OK = 0,
+  FMB_ERR_BAD_ARG = 1,      /* shape / stride / size rule violated            */
+  FMB_ERR_UNSUPPORTED = 2,  /* valid in the reference, not built here          */
+  FMB_ERR_WORKSPACE = 3,    /* workspace pointer null or too small             */
+  FMB_ERR_CUDA = 4,         /* a CUDA runtime call or kernel launch failed     */
+  FMB_ERR_TIMEOUT = 5       /* a bounded device-side wait expired              */
+};
+
+/* Library version (major*10000 + minor*100 + patch). */
+int fmb_version(void);
+
+/* Message of the last failing call made by this thread ("" if none). */
+const char* fmb_last_error(void);
+
+/* ------------------------------------------------------------------ stage P: mean-pool
+ * cu_seqlens_km[b] = sum_{b'<b} ceil(len_k[b'] / chunk); one tiny launch, no host sync.
+ * Replaces the ATen prologue of flash_moba/triton_mean_pool.py:134-138 (which syncs with
+ * `.item()` at :140). */
+int fmb_chunk_offsets(const int32_t* cu_seqlens_k, int batch, int chunk,
+                      int32_t* cu_seqlens_km, fmb_stream_t stream);
+
+/* km[cu_seqlens_km[b] + n, hk, :] = mean over the rows of chunk n of sequence b of k[:, hk, :]
+ * (fp32 accumulation, divided by the true length of a short last chunk, rounded to dtype).
+ * km is contiguous (km_rows, heads_k, head_dim); rows of km that belong to no chunk are
+ * not written.  Replaces mean_pool_kernel / flash_topk_mean_pool,
+ * flash_moba/triton_mean_pool.py:41-109, 112-157. */
+int fmb_mean_pool(const void* k, int64_t k_row_stride, int64_t k_head_stride,
+                  const int32_t* cu_seqlens_k, const int32_t* cu_seqlens_km, void* km,
+                  int batch, int heads_k, int head_dim, int max_seqlen_k, int chunk,
+                  int dtype, fmb_stream_t stream);
+
+/* ------------------------------------------------------------------ stage G: gating top-k
+ * For every query row and q head: scores q . km (fp32, unscaled) against the centroids of
+ * its sequence (kv head = h / (heads/heads_k)), causal chunk rule, top-k.
+ *   topk_idx int32 [row][head][topk]: chunk ids by descending score, -1 = unused; entry
+ *            (row, h, j) lives at row*topk_row_stride + h*topk_head_stride + j (elements),
+ *            so both (total_q, heads, topk) and (heads, total_q, topk) storage work.
+ *   topk_val float, same addressing, or NULL: the scores (+inf for the own chunk).
+ * Rule under `causal`, p = row + len_k - len_q: chunk p/chunk is always selected first;
+ * chunk n competes only if (n+1)*chunk-1 < p; rows with p < 0 select nothing.  Equal
+ * scores: the higher chunk id ranks first.  1 <= topk <= 64.
+ * Replaces moba_fused_topk's main kernel, csrc/flash_topk/flash_topk_api.cpp:130-258 and
+ * csrc/flash_topk/src/flash_topk_kernel.h:31-357. */
+int fmb_gate_topk(const void* q, int64_t q_row_stride, int64_t q_head_stride,
+                  const void* km, /* contiguous (km_rows, heads_k, head_dim) */
+                  const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                  const int32_t* cu_seqlens_km, int32_t* topk_idx, float* topk_val,
+                  int64_t topk_row_stride, int64_t topk_head_stride,
+                  int batch, int heads, int heads_k, int head_dim, int max_seqlen_q,
+                  int max_seqlen_k, int topk, int chunk, int causal, int dtype,
+                  fmb_stream_t stream);
+
+/* ------------------------------------------------------------------ stages O/E/S: pattern
+ * Bytes of scratch `fmb_build_csc` needs. */
+size_t fmb_build_csc_workspace_bytes(int batch, int heads, int max_seqlen_q, int ncol);
+
+/* Top-k lists -> CSC pattern, deterministic, columns come out sorted (no sort pass).
+ *   col_offsets[b,h,c] = (cu_q[b]*heads + len_q[b]*h)*topk + sum_{c'<c} col_nnz[b,h,c']
+ *   indices has total_q*heads*topk entries; the unused tail of each (b,h) region is 0.
+ * Replaces compute_topk_offset + compute_topk_epilogue_1rowblock
+ * (csrc/flash_topk/src/flash_topk_kernel.h:376-402, 407-478) and varlen_sort
+ * (csrc/flash_topk/src/varlen_sort.cu:127-162). */
+int fmb_build_csc(const int32_t* topk_idx, int64_t topk_row_stride, int64_t topk_head_stride,
+                  const int32_t* cu_seqlens_q, int64_t* col_offsets,
+                  int32_t* col_nnz, int32_t* indices, void* workspace, size_t workspace_bytes,
+                  int batch, int heads, int topk, int max_seqlen_q, int ncol,
+                  fmb_stream_t stream);
+
+/* Ascending sort of int32 keys inside each segment [starts[i], ends[i]) of src into dst
+ * (dst is first filled with 0).  Kept for callers of the reference's stand-alone
+ * varlen_sort, csrc/flash_topk/src/varlen_sort.cu:127-162. */
+int fmb_varlen_sort(const int64_t* starts, const int64_t* ends, const int32_t* src, int32_t* dst,
+                    int64_t num_segments, int64_t num_items, fmb_stream_t stream);
+
+/* ------------------------------------------------------------------ stage F: forward
+ * Bytes of scratch for fmb_attn_fwd / fmb_attn_bwd (n_indices = entries of `indices`). */
+size_t fmb_attn_fwd_workspace_bytes(int64_t total_q, int heads, int head_dim, int64_t n_indices);
+size_t fmb_attn_bwd_workspace_bytes(int64_t total_q, int heads, int head_dim, int64_t n_indices);
+
+/* out[row,h] = softmax over the visible keys (scale * q.k) . v, where key col of the row's
+ * sequence is visible iff chunk col/chunk is in the row's pattern, col < len_k and, if
+ * causal, col <= row + len_k - len_q.  lse float (heads, total_q) = log-sum-exp of the
+ * scaled scores; rows without visible keys give out = 0, lse = +inf.
+ * Replaces moba_varlen_fwd, csrc/flash_moba/flash_moba_api.cpp:375-596 and
+ * csrc/flash_moba/src/flash_fwd_kernel.h:232-769. */
+int fmb_attn_fwd(const void* q, int64_t q_row_stride, int64_t q_head_stride,
+                 const void* k, int64_t k_row_stride, int64_t k_head_stride,
+                 const void* v, int64_t v_row_stride, int64_t v_head_stride,
+                 void* out, int64_t o_row_stride, int64_t o_head_stride, float* lse,
+                 const int64_t* col_offsets, const int32_t* col_nnz, const int32_t* indices,
+                 int64_t n_indices, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                 void* workspace, size_t workspace_bytes, int batch, int heads, int heads_k,
+                 int head_dim, int64_t total_q, int max_seqlen_q, int max_seqlen_k, int chunk,
+                 float softmax_scale, int causal, int dtype, fmb_stream_t stream);
+
+/* ------------------------------------------------------------------ stage B: backward
+ * dq/dk/dv for the forward above (dk/dv summed over the q heads of a kv head).
+ * softmax_d float (heads, total_q) receives rowsum(dout*out).  Atomics-free and
+ * deterministic.  Replaces moba_varlen_bwd, csrc/flash_moba/flash_moba_api.cpp:610-848,
+ * csrc/flash_moba/src/flash_bwd_kernel.h:99-874 and
+ * csrc/flash_moba/src/flash_bwd_preprocess_kernel.h:59-140, 146-232. */
+int fmb_attn_bwd(const void* dout, int64_t do_row_stride, int64_t do_head_stride,
+                 const void* q, int64_t q_row_stride, int64_t q_head_stride,
+                 const void* k, int64_t k_row_stride, int64_t k_head_stride,
+                 const void* v, int64_t v_row_stride, int64_t v_head_stride,
+                 const void* out, int64_t o_row_stride, int64_t o_head_stride,
+                 const float* lse, void* dq, int64_t dq_row_stride, int64_t dq_head_stride,
+                 void* dk, int64_t dk_row_stride, int64_t dk_head_stride,
+                 void* dv, int64_t dv_row_stride, int64_t dv_head_stride, float* softmax_d,
+                 const int64_t* col_offsets, const int32_t* col_nnz, const int32_t* indices,
+                 int64_t n_indices, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                 void* workspace, size_t workspace_bytes, int batch, int heads, int heads_k,
+                 int head_dim, int64_t total_q, int64_t total_k, int max_seqlen_q,
+                 int max_seqlen_k, int chunk, float softmax_scale, int causal, int dtype,
+                 fmb_stream_t stream);
+
+/* Selects the attention engine for this process: 0 = CUDA-core validation kernels,
+ * 1 = tcgen05 tensor-core kernels (default when built).  Testing aid; returns the
+ * engine now in use. */
+int fmb_set_engine(int engine);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASH_MOBA_B200_H_ */
