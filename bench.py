@@ -1,0 +1,322 @@
+#!/usr/bin/env python
+"""Benchmark of the MoBA hot path (pattern + block-sparse forward + backward).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload 64k|c2|c3]
+
+A step = one pass of the hot path over one batch of synthetic input through the public API
+(`flash_moba_varlen_func` forward, autograd backward): mean-pool -> gating top-k -> pattern
+-> block-sparse forward -> backward (dQ, dK, dV).  Prints ONE JSON line (rank 0).
+
+metric  : selected-block TFLOP/s of fwd+bwd attention (FLOPs counted over selected blocks
+          only, see flash_moba_b200/accounting.py); ms_per_step beside it.
+value   : device-timed, inputs resident in HBM.   e2e: the same through the public API with
+          q/k/v/dO copied from pinned host memory and out/dq/dk/dv copied back each step.
+N > 1   : query heads are split across ranks (no collective on the data path); value is the
+          whole job's FLOPs / max-over-ranks time ("strong": the 64K problem is fixed).
+--impl reference : the reference's pure-PyTorch MoBA restated in oracle/ (the reference has
+          no CPU build of its CUDA path), timed on the host cores over a bounded sample.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (seqlens, heads, heads_k, d, chunk, topk, backward, input scale)
+    "64k": ([65536], 32, 32, 128, 128, 8, True, 1.0),
+    "c2": ([32768], 16, 16, 128, 128, 8, False, 0.5),
+    "c3": ([8192] * 8, 32, 32, 128, 128, 8, True, 1.0),
+    "small": ([4096], 8, 8, 128, 128, 8, True, 1.0),
+}
+
+
+def _load_accounting():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("fmb_accounting", os.path.join(ROOT, "flash_moba_b200", "accounting.py"))
+    m = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(m)
+    return m
+
+
+ACC = _load_accounting()
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_sample(seqlens, d, chunk, topk, rows=4096, threads=None):
+    """The oracle (pure-PyTorch MoBA restated from the reference) on the host cores over a
+    bounded sample of the workload: the LAST `rows` query rows of one head against all keys of
+    the first sequence (pattern + forward + backward).  Returns (seconds, flops)."""
+    from oracle import moba_oracle as O
+    threads = threads or os.cpu_count()
+    torch.set_num_threads(threads)
+    S = seqlens[0]
+    rows = min(rows, S)
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(rows, 1, d, generator=g).bfloat16().float().requires_grad_(True)
+    k = torch.randn(S, 1, d, generator=g).bfloat16().float().requires_grad_(True)
+    v = torch.randn(S, 1, d, generator=g).bfloat16().float().requires_grad_(True)
+    do = torch.randn(rows, 1, d, generator=g)
+    cq = torch.tensor([0, rows], dtype=torch.int32)
+    ck = torch.tensor([0, S], dtype=torch.int32)
+    t0 = time.perf_counter()
+    km, cu_km = O.mean_pool(k.detach(), ck, chunk)
+    idx, _ = O.gate_topk(q.detach(), km, cq, ck, cu_km, topk, chunk, True)
+    out, _ = O.attention_blocked(q, k, v, cq, ck, idx, chunk, True)
+    torch.autograd.grad(out, (q, k, v), do)
+    dt = time.perf_counter() - t0
+    # pairs of those rows (bottom-right aligned): row r sits at position S-rows+r
+    pairs = 0
+    for r in range(rows):
+        p = S - rows + r
+        sel = min(topk, p // chunk + 1)
+        pairs += (sel - 1) * chunk + (p % chunk + 1)
+    return dt, 3.5 * 4 * d * pairs, rows, threads
+
+
+def run_reference(args, wl):
+    seqlens, H, Hk, d, chunk, topk, backward, scale = WORKLOADS[wl]
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows = 2048
+    for _ in range(max(args.warmup, 1)):
+        cpu_sample(seqlens, d, chunk, topk, rows=256)
+    times, flops, threads = [], 0, 0
+    for _ in range(args.steps):
+        dt, flops, rows, threads = cpu_sample(seqlens, d, chunk, topk, rows=rows)
+        times.append(dt)
+    t = sum(times) / len(times)
+    val = flops / t / 1e12
+    line = {
+        "impl": "reference", "metric": "moba_fwd_bwd_selected_block_tflops", "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wl, "seqlens": seqlens, "heads": H, "heads_k": Hk, "head_dim": d, "chunk": chunk,
+                   "topk": topk, "causal": True},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": f"pattern+fwd+bwd of the last {rows} query rows of 1 head vs all {seqlens[0]} keys, "
+                                   "fp32 PyTorch oracle (oracle/moba_oracle.py), per step"},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="64k", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--engine", type=int, default=1)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    wl = args.workload
+    if args.impl == "reference":
+        return run_reference(args, wl)
+
+    seqlens, H, Hk, d, chunk, topk, backward, scale = WORKLOADS[wl]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    import flash_moba_b200 as F
+    from flash_moba_b200 import _lib, ops
+    ops.set_engine(args.engine)
+
+    # shard: q heads (and their kv heads) split across ranks; no data-path collective
+    assert H % world == 0 and Hk % world == 0, "heads must divide across ranks"
+    h_loc, hk_loc = H // world, Hk // world
+    T = sum(seqlens)
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    mk = lambda h: (torch.randn(T, h, d, generator=g, device=dev, dtype=torch.float32) * scale).to(torch.bfloat16)
+    q, k, v, do = mk(h_loc).requires_grad_(True), mk(hk_loc).requires_grad_(True), mk(hk_loc).requires_grad_(True), mk(h_loc)
+    cu = torch.tensor([0] + list(__import__("itertools").accumulate(seqlens)), dtype=torch.int32, device=dev)
+    mx = max(seqlens)
+
+    def step(qq, kk, vv, dd):
+        out = F.flash_moba_varlen_func(qq, kk, vv, cu, cu, mx, mx, chunk, topk, causal=True)
+        if backward:
+            return (out,) + torch.autograd.grad(out, (qq, kk, vv), dd)
+        return (out,)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step(q, k, v, do)
+    barrier()
+    launches0 = _lib.lib.fmb_launch_count()
+    _lib.lib.fmb_profile_enable(1)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        barrier()
+        ev0.record()
+        for _ in range(args.steps):
+            step(q, k, v, do)
+        ev1.record()
+        barrier()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    launches = _lib.lib.fmb_launch_count() - launches0
+    import ctypes
+    kern_ms = {}
+    for kind, name in ((0, "fwd_main"), (1, "bwd_main"), (2, "gate"), (3, "pool")):
+        buf = (ctypes.c_float * 256)()
+        n = _lib.lib.fmb_profile_read(kind, ctypes.cast(buf, ctypes.c_void_p), 256)
+        kern_ms[name] = (sum(buf[:n]) / n) if n > 0 else None
+    _lib.lib.fmb_profile_enable(0)
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+
+    fwd_f, bwd_f, both_f = ACC.attention_flops(seqlens, H, d, chunk, topk)
+    job_flops = both_f if backward else fwd_f
+    value = job_flops / (ms * 1e-3) / 1e12
+
+    # ---- end to end: pinned host inputs in, results out, every step
+    e2e = None
+    if not args.no_e2e:
+        host_in = [t.detach().cpu().pin_memory() for t in (q, k, v, do)]
+        dev_in = [torch.empty_like(t, device=dev) for t in host_in]
+        n_out = 4 if backward else 1
+        host_out = [torch.empty((T, h_loc if i < 2 else hk_loc, d), dtype=torch.bfloat16).pin_memory() for i in range(n_out)]
+
+        def e2e_step():
+            for hsrc, ddst in zip(host_in, dev_in):
+                ddst.copy_(hsrc, non_blocking=True)
+            qq, kk, vv = [t.requires_grad_(True) for t in dev_in[:3]]
+            res = step(qq, kk, vv, dev_in[3])
+            for hdst, r in zip(host_out, res):
+                hdst.copy_(r.detach(), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            for t in dev_in[:3]:
+                t.requires_grad_(False)
+
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        n_e2e = max(2, min(args.steps, 5))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        barrier()
+        e_ms = e0.elapsed_time(e1) / n_e2e
+        if dist is not None:
+            t = torch.tensor([e_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e_ms = float(t.item())
+        e2e = {"value": job_flops / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e_ms,
+               "h2d_bytes_per_step": sum(t.numel() * 2 for t in host_in) * world,
+               "d2h_bytes_per_step": sum(t.numel() * 2 for t in host_out) * world}
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    peak_tf = peaks.get("bf16_tflops_sustained", 1400.0)
+    peak_src = "measured (MEASURED_PEAKS.json bf16_tflops_sustained: kernel timed inside a long step)" if peaks else \
+        "fallback 1.4 PFLOP/s sustained"
+    dom = "bwd_main" if backward else "fwd_main"
+    dom_flops = (bwd_f if backward else fwd_f) / world
+    roof = None
+    if kern_ms.get(dom):
+        ach = dom_flops / (kern_ms[dom] * 1e-3) / 1e12
+        roof = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s",
+                "frac": ach / peak_tf, "traffic": None, "peak_source": peak_src,
+                "launch_ms": kern_ms[dom], "flops_per_launch": dom_flops,
+                "other_kernels_ms": {k_: v_ for k_, v_ in kern_ms.items() if k_ != dom}}
+    line = {
+        "metric": "moba_fwd_bwd_selected_block_tflops" if backward else "moba_fwd_selected_block_tflops",
+        "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": wl, "seqlens": seqlens, "heads": H, "heads_k": Hk, "head_dim": d, "chunk": chunk,
+                   "topk": topk, "causal": True, "step": "pattern(pool+gate+csc) + fwd" + (" + bwd" if backward else ""),
+                   "sharding": f"heads/{world}", "l2": "inputs (q,k,v,dO > 500 MB each at N=1) exceed the 126 MB L2",
+                   "engine": "tcgen05" if args.engine == 1 else "cuda-core"},
+        "gpu_launches": int(launches), "clocks": clk.summary(), "e2e": e2e, "roofline": roof,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        dt, fl, rows, threads = cpu_sample(seqlens, d, chunk, topk, rows=8192)
+        line["cpu_baseline"] = {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                                "sample": f"pattern+fwd+bwd of the last {rows} query rows of 1 head vs all "
+                                          f"{seqlens[0]} keys, fp32 PyTorch oracle, {dt:.1f} s"}
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -3,7 +3,7 @@
     from flash_moba_b200 import (flash_moba_varlen_func, flash_topk_varlen_func,
                                  flash_moba_attn_varlen_func)
 
-Importing the package loads libflashmoba_b200.so (built by `python -m flash_moba_b200.build`)
+Importing the package loads libflashmoba_b200.so (built by `python flash_moba_b200/build.py`)
 and fails loudly if it is missing: there is no CPU or PyTorch fallback.
 """
 __version__ = "0.1.0"

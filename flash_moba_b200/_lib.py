@@ -19,7 +19,7 @@ FMB_BF16, FMB_FP16 = 0, 1
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
-        f"{LIB_PATH} is missing: build it with `python -m flash_moba_b200.build` "
+        f"{LIB_PATH} is missing: build it with `python flash_moba_b200/build.py` "
         "(needs nvcc with sm_100a support). flash_moba_b200 has no CPU or PyTorch fallback."
     )
 
@@ -29,6 +29,9 @@ _SIGS = {
     "fmb_version": (i32, []),
     "fmb_last_error": (ctypes.c_char_p, []),
     "fmb_set_engine": (i32, [i32]),
+    "fmb_launch_count": (ctypes.c_ulonglong, []),
+    "fmb_profile_enable": (i32, [i32]),
+    "fmb_profile_read": (i32, [i32, c_ptr, i32]),
     "fmb_chunk_offsets": (i32, [c_ptr, i32, i32, c_ptr, c_ptr]),
     "fmb_mean_pool": (i32, [c_ptr, i64, i64, c_ptr, c_ptr, c_ptr, i32, i32, i32, i32, i32, i32, c_ptr]),
     "fmb_gate_topk": (i32, [c_ptr, i64, i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, i64, i64,

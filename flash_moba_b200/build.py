@@ -1,6 +1,6 @@
 """In-tree build of libflashmoba_b200.so with nvcc for sm_100a (no torch headers involved).
 
-    python -m flash_moba_b200.build [--force]
+    python flash_moba_b200/build.py [--force]
 
 Objects go to flash_moba_b200/_build/, the library next to this file, so that the built
 library travels with a snapshot of the source tree.

@@ -18,6 +18,31 @@ int fail(int code, const char* fmt, ...) {
 
 static int g_engine = 1;
 
+static unsigned long long g_launches = 0;
+void note_launch() { __atomic_fetch_add(&g_launches, 1ull, __ATOMIC_RELAXED); }
+
+// ---- optional event timing of the dominant kernels ------------------------------------
+constexpr int kProfKinds = 4, kProfRing = 256;
+struct ProfState {
+  bool on = false;
+  cudaEvent_t ev[kProfKinds][kProfRing][2] = {};
+  int count[kProfKinds] = {};
+};
+static ProfState g_prof;
+void prof_begin(int kind, cudaStream_t s) {
+  if (!g_prof.on || g_prof.count[kind] >= kProfRing) return;
+  cudaEvent_t& e = g_prof.ev[kind][g_prof.count[kind]][0];
+  if (!e) cudaEventCreate(&e);
+  cudaEventRecord(e, s);
+}
+void prof_end(int kind, cudaStream_t s) {
+  if (!g_prof.on || g_prof.count[kind] >= kProfRing) return;
+  cudaEvent_t& e = g_prof.ev[kind][g_prof.count[kind]][1];
+  if (!e) cudaEventCreate(&e);
+  cudaEventRecord(e, s);
+  ++g_prof.count[kind];
+}
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static int check_tensor(const char* name, const void* p, int64_t rs, int64_t hs, int d) {
@@ -49,6 +74,26 @@ extern "C" {
 int fmb_version(void) { return 100; }
 
 const char* fmb_last_error(void) { return error_buffer(); }
+
+unsigned long long fmb_launch_count(void) { return __atomic_load_n(&g_launches, __ATOMIC_RELAXED); }
+
+int fmb_profile_enable(int on) {
+  g_prof.on = on != 0;
+  for (int k = 0; k < kProfKinds; ++k) g_prof.count[k] = 0;
+  return FMB_OK;
+}
+
+int fmb_profile_read(int kind, float* ms, int max_entries) {
+  if (kind < 0 || kind >= kProfKinds || (!ms && max_entries > 0)) return -1;
+  int n = g_prof.count[kind] < max_entries ? g_prof.count[kind] : max_entries;
+  for (int i = 0; i < n; ++i) {
+    if (cudaEventElapsedTime(&ms[i], g_prof.ev[kind][i][0], g_prof.ev[kind][i][1]) != cudaSuccess) {
+      cudaGetLastError();
+      return -1;
+    }
+  }
+  return n;
+}
 
 int fmb_set_engine(int engine) {
   if (engine == 0 || engine == 1) g_engine = engine;

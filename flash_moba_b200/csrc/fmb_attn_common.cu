@@ -361,8 +361,10 @@ int launch_attn_fwd(const AttnArgs& a, int engine, cudaStream_t s) {
     return fail(FMB_ERR_WORKSPACE, "attn_fwd: workspace too small (%zu < %zu)", a.ws_bytes, w.bytes);
   int rc = build_row_lists(a, w, s);
   if (rc) return rc;
+  prof_begin(0, s);
   if (engine == 1 && tc_supported(a, false)) rc = launch_fwd_main_tc(a, w, s);
   else rc = launch_fwd_main_simt(a, w, s);
+  prof_end(0, s);
   if (rc) return rc;
   return launch_fwd_combine(a, w, s);
 }
@@ -375,8 +377,10 @@ int launch_attn_bwd(const AttnArgs& a, int engine, cudaStream_t s) {
   if (rc) return rc;
   rc = launch_dot_do_o(a, s);
   if (rc) return rc;
+  prof_begin(1, s);
   if (engine == 1 && tc_supported(a, true)) rc = launch_bwd_main_tc(a, w, s);
   else rc = launch_bwd_main_simt(a, w, s);
+  prof_end(1, s);
   if (rc) return rc;
   return launch_bwd_combine(a, w, s);
 }

@@ -17,6 +17,11 @@ namespace fmb {
 // ---- error reporting (thread-local message behind fmb_last_error) -------------------
 char* error_buffer();          // defined in fmb_api.cu
 int fail(int code, const char* fmt, ...);
+void note_launch();            // counts kernel launches (fmb_launch_count)
+// optional CUDA-event timing of the dominant kernels (fmb_profile_*); kind 0 = forward
+// main kernel, 1 = backward main kernel, 2 = gating kernel, 3 = mean-pool kernel
+void prof_begin(int kind, cudaStream_t s);
+void prof_end(int kind, cudaStream_t s);
 
 #define FMB_CHECK_ARG(cond, ...)                                   \
   do {                                                             \
@@ -36,6 +41,7 @@ int fail(int code, const char* fmt, ...);
     if (e_ != cudaSuccess)                                                               \
       return ::fmb::fail(FMB_ERR_CUDA, "launch of %s failed: %s", name,                  \
                          cudaGetErrorString(e_));                                        \
+    ::fmb::note_launch();                                                                \
   } while (0)
 
 // ---- small device helpers -----------------------------------------------------------

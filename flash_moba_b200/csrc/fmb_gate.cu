@@ -244,8 +244,11 @@ int launch_gate_topk(const GateArgs& a, cudaStream_t s) {
   p.cu_q = a.cu_q; p.cu_k = a.cu_k; p.cu_km = a.cu_km;
   p.topk_idx = a.topk_idx; p.topk_val = a.topk_val; p.t_rs = a.t_rs; p.t_hs = a.t_hs;
   p.heads = a.heads; p.heads_k = a.heads_k; p.d = a.d; p.topk = a.topk; p.chunk = a.chunk; p.causal = a.causal;
-  if (a.dtype == FMB_BF16) return gate_dispatch<__nv_bfloat16>(p, a.batch, a.max_q, s);
-  return gate_dispatch<__half>(p, a.batch, a.max_q, s);
+  prof_begin(2, s);
+  const int rc = a.dtype == FMB_BF16 ? gate_dispatch<__nv_bfloat16>(p, a.batch, a.max_q, s)
+                                     : gate_dispatch<__half>(p, a.batch, a.max_q, s);
+  prof_end(2, s);
+  return rc;
 }
 
 }  // namespace fmb

@@ -132,9 +132,12 @@ static int pool_dispatch(const void* k, int64_t rs, int64_t hs, const int32_t* c
 int launch_mean_pool(const void* k, int64_t rs, int64_t hs, const int32_t* cu_k, const int32_t* cu_km,
                      void* km, int batch, int heads_k, int d, int max_seqlen_k, int chunk, int dtype,
                      cudaStream_t s) {
-  if (dtype == FMB_BF16)
-    return pool_dispatch<__nv_bfloat16>(k, rs, hs, cu_k, cu_km, km, batch, heads_k, d, max_seqlen_k, chunk, s);
-  return pool_dispatch<__half>(k, rs, hs, cu_k, cu_km, km, batch, heads_k, d, max_seqlen_k, chunk, s);
+  prof_begin(3, s);
+  const int rc = dtype == FMB_BF16
+      ? pool_dispatch<__nv_bfloat16>(k, rs, hs, cu_k, cu_km, km, batch, heads_k, d, max_seqlen_k, chunk, s)
+      : pool_dispatch<__half>(k, rs, hs, cu_k, cu_km, km, batch, heads_k, d, max_seqlen_k, chunk, s);
+  prof_end(3, s);
+  return rc;
 }
 
 }  // namespace fmb

@@ -158,6 +158,20 @@ int fmb_attn_bwd(const void* dout, int64_t do_row_stride, int64_t do_head_stride
  * engine now in use. */
 int fmb_set_engine(int engine);
 
+/* ------------------------------------------------------------------ measurement aids
+ * No counterpart in the reference (it is timed from Python with torch.utils.benchmark,
+ * flash_moba/utils/benchmark.py:120-156).
+ * Kernel launches made by this library in this process so far. */
+unsigned long long fmb_launch_count(void);
+
+/* CUDA-event timing of the dominant kernels on the launching stream.  While enabled, up to
+ * 256 launches per kind are bracketed by events (no synchronisation is added); enabling
+ * also clears the record.  kind: 0 forward main kernel, 1 backward main kernel, 2 gating
+ * kernel, 3 mean-pool kernel.  After the caller has synchronised, fmb_profile_read stores
+ * the elapsed milliseconds of each recorded launch and returns how many (or -1). */
+int fmb_profile_enable(int on);
+int fmb_profile_read(int kind, float* ms, int max_entries);
+
 #ifdef __cplusplus
 }
 #endif
