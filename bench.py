@@ -305,7 +305,8 @@ def main():
         "config": {"workload": wl, "seqlens": seqlens, "heads": H, "heads_k": Hk, "head_dim": d, "chunk": chunk,
                    "topk": topk, "causal": True, "step": "pattern(pool+gate+csc) + fwd" + (" + bwd" if backward else ""),
                    "sharding": f"heads/{world}", "l2": "inputs (q,k,v,dO > 500 MB each at N=1) exceed the 126 MB L2",
-                   "engine": "tcgen05" if args.engine == 1 else "cuda-core"},
+                   "engine": {"fwd": ["cuda-core", "tcgen05"][_lib.lib.fmb_attn_engine(chunk, d, 0)],
+                              "bwd": ["cuda-core", "tcgen05"][_lib.lib.fmb_attn_engine(chunk, d, 1)]}},
         "gpu_launches": int(launches), "clocks": clk.summary(), "e2e": e2e, "roofline": roof,
     }
     if world == 1 and not args.no_cpu_baseline:

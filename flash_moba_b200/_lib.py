@@ -29,6 +29,8 @@ _SIGS = {
     "fmb_version": (i32, []),
     "fmb_last_error": (ctypes.c_char_p, []),
     "fmb_set_engine": (i32, [i32]),
+    "fmb_attn_engine": (i32, [i32, i32, i32]),
+    "fmb_selftest_umma": (i32, [c_ptr, c_ptr, c_ptr, i32, i32, c_ptr, c_ptr]),
     "fmb_launch_count": (ctypes.c_ulonglong, []),
     "fmb_profile_enable": (i32, [i32]),
     "fmb_profile_read": (i32, [i32, c_ptr, i32]),

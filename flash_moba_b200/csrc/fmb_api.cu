@@ -95,6 +95,20 @@ int fmb_profile_read(int kind, float* ms, int max_entries) {
   return n;
 }
 
+int fmb_attn_engine(int chunk, int head_dim, int backward) {
+  AttnArgs a;
+  memset(&a, 0, sizeof(a));
+  a.chunk = chunk; a.d = head_dim;
+  return (g_engine == 1 && tc_supported(a, backward != 0)) ? 1 : 0;
+}
+
+int fmb_selftest_umma(const void* a, const void* b, float* d, int b_mn_major, int dtype, int* status,
+                      fmb_stream_t stream) {
+  FMB_CHECK_ARG(a && b && d && status, "selftest_umma: null pointer");
+  FMB_CHECK_ARG(dtype == FMB_BF16 || dtype == FMB_FP16, "selftest_umma: only fp16 and bf16");
+  return launch_selftest_umma(a, b, d, b_mn_major, dtype, status, (cudaStream_t)stream);
+}
+
 int fmb_set_engine(int engine) {
   if (engine == 0 || engine == 1) g_engine = engine;
   return g_engine;

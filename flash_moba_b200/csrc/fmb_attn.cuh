@@ -17,6 +17,7 @@
 namespace fmb {
 
 struct AttnWorkspace {
+  int* status;         // first word of the workspace: 0, or where a bounded device wait gave up
   void* part_o;        // fwd: n_indices * d elements of the I/O dtype;  bwd: n_indices * d floats
   float* part_lse;     // fwd only: n_indices
   uint32_t* row_ptr;   // heads*total_q + 1
@@ -48,5 +49,7 @@ int launch_bwd_main_simt(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t
 int launch_fwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s);
 int launch_bwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s);
 bool tc_supported(const AttnArgs& a, bool backward);
+int launch_selftest_umma(const void* a, const void* b, float* d, int b_mn_major, int dtype, int* status,
+                         cudaStream_t s);
 
 }  // namespace fmb

@@ -1,12 +1,323 @@
-// tcgen05 tensor-core engine of the block-sparse attention (placeholder until validated).
+// tcgen05 tensor-core engine of the block-sparse attention main kernels.
+//
+// Key-chunk-major, like the CUDA-core engine: a CTA owns key chunk c of one (sequence, head),
+// keeps the chunk's K and V in shared memory (128-byte-swizzled UMMA tiles) for its whole
+// life, and walks the chunk's CSC column in dense tiles of 128 gathered query rows:
+//     gather Q rows -> smem     S = Q.K^T   (tcgen05.mma, fp32 accumulator in TMEM)
+//     softmax of the tile, one thread per row (tcgen05.ld), P -> smem (bf16)
+//     O = P.V (tcgen05.mma, V consumed MN-major straight from its row-major tile)
+//     O / l -> workspace partial at the pair's CSC position, chunk-local log-sum-exp beside it
+// Two CTAs share an SM (256 TMEM columns each), so one CTA's softmax overlaps the other's MMAs.
+// Every mbarrier wait is bounded; a wait that expires records where in the status word of the
+// workspace and the CTA leaves through the normal exit (TMEM released).
 #include "fmb_attn.cuh"
+#include "fmb_tc.cuh"
 
 namespace fmb {
-bool tc_supported(const AttnArgs&, bool) { return false; }
-int launch_fwd_main_tc(const AttnArgs&, const AttnWorkspace&, cudaStream_t) {
-  return fail(FMB_ERR_UNSUPPORTED, "tensor-core engine not built");
+
+using namespace tc;
+
+constexpr int kTcM = 128;   // gathered rows per tile = TMEM lanes
+constexpr float kLog2eTc = 1.4426950408889634f;
+
+struct TcParams {
+  const void *q, *k, *v, *dout;
+  int64_t q_rs, q_hs, k_rs, k_hs, v_rs, v_hs, do_rs, do_hs;
+  void *dk, *dv; int64_t dk_rs, dk_hs, dv_rs, dv_hs;
+  const float *lse, *softmax_d;
+  const int64_t* col_offsets; const int32_t* col_nnz; const int32_t* indices; int64_t n_indices;
+  const int32_t *cu_q, *cu_k;
+  void* part_o; float* part_lse; int* status;
+  int heads, heads_k, ncol; int64_t total_q;
+  float scale; int causal;
+};
+
+// rows x (NCHUNK*8 elements) from global memory into a swizzled UMMA tile.
+// row_of(r) gives the source row (or -1 for zero fill).
+template <typename T, int NCHUNK, typename RowFn>
+__device__ __forceinline__ void stage_tile_sw128(unsigned char* tile, uint32_t block_stride, const T* base,
+                                                 int64_t row_stride, int nrows, RowFn row_of) {
+  for (int e = threadIdx.x; e < nrows * NCHUNK; e += blockDim.x) {
+    const int r = e / NCHUNK, j = e % NCHUNK;
+    const int64_t src = row_of(r);
+    uint4 u = make_uint4(0, 0, 0, 0);
+    if (src >= 0) u = ldg_nc_16(base + src * row_stride + j * 8);
+    *reinterpret_cast<uint4*>(tile + sw128_offset(r, j, block_stride)) = u;
+  }
 }
+
+template <typename T> struct FmtOf;
+template <> struct FmtOf<__nv_bfloat16> { static constexpr int v = 1; };
+template <> struct FmtOf<__half> { static constexpr int v = 0; };
+
+__host__ __device__ constexpr int next_pow2_cols(int x) { return x <= 32 ? 32 : x <= 64 ? 64 : x <= 128 ? 128 : x <= 256 ? 256 : 512; }
+
+// ======================================================================== forward
+template <typename T, int C, int D>
+__global__ void __launch_bounds__(kTcM) fwd_main_tc_kernel(TcParams p) {
+  constexpr int QP = (C > D ? C : D);
+  constexpr uint32_t kKBlock = C * 128;        // bytes between 64-element blocks of the K / V tiles
+  constexpr uint32_t kQBlock = kTcM * 128;     // same for the 128-row Q / P tiles
+  constexpr int NCOLS = next_pow2_cols(C + D);
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int sRow[kTcM];
+
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* sK = smem;
+  unsigned char* sV = sK + C * D * 2;
+  unsigned char* sQP = sV + C * D * 2;     // Q tile, later overwritten by P
+
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int64_t ci = ((int64_t)b * p.heads + h) * p.ncol + c;
+  const int nnz = p.col_nnz[ci];
+  if (nnz <= 0) return;
+  const int64_t off = p.col_offsets[ci];
+  if (off < 0 || off + nnz > p.n_indices) return;
+  const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
+  const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
+  const int key0 = c * C;
+  const int keys_valid = max(0, min(C, len_k - key0));
+  const int hk = h / (p.heads / p.heads_k);
+  const int shift = len_k - len_q;
+  const float scale_log2 = p.scale * kLog2eTc;
+  const int tid = threadIdx.x, warp = tid >> 5;
+
+  if (warp == 0) tmem_alloc(&tmem_base_s, NCOLS);
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  const T* kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + key0) * p.k_rs + (int64_t)hk * p.k_hs;
+  const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
+  const T* qbase = static_cast<const T*>(p.q) + (int64_t)q0 * p.q_rs + (int64_t)h * p.q_hs;
+  stage_tile_sw128<T, D / 8>(sK, kKBlock, kbase, p.k_rs, C, [&](int r) { return r < keys_valid ? (int64_t)r : -1; });
+  stage_tile_sw128<T, D / 8>(sV, kKBlock, vbase, p.v_rs, C, [&](int r) { return r < keys_valid ? (int64_t)r : -1; });
+  fence_async_smem();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+  const uint32_t tS = tmem_base, tO = tmem_base + C;
+  const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+  const uint32_t sK_a = smem_u32(sK), sV_a = smem_u32(sV), sQP_a = smem_u32(sQP);
+  constexpr uint32_t idesc_s = make_idesc(FmtOf<T>::v, kTcM, C, 0, 0);
+  constexpr uint32_t idesc_o = make_idesc(FmtOf<T>::v, kTcM, D, 0, 1);
+  T* part_o = static_cast<T*>(p.part_o);
+  uint32_t phase = 0;
+
+  for (int t0 = 0; t0 < nnz; t0 += kTcM) {
+    const int rows = min(kTcM, nnz - t0);
+    {
+      int r = -1;
+      if (tid < rows) {
+        r = p.indices[off + t0 + tid];
+        if (r < 0 || r >= len_q) r = -1;
+      }
+      sRow[tid] = r;
+    }
+    __syncthreads();   // row ids visible; the previous tile's MMAs and TMEM reads are complete
+    stage_tile_sw128<T, D / 8>(sQP, kQBlock, qbase, p.q_rs, kTcM, [&](int r) { return (int64_t)sRow[r]; });
+    fence_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after_sync();
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const uint64_t a = make_desc_sw128(sQP_a + (ks >> 2) * kQBlock + (ks & 3) * 32, 16, 1024);
+        const uint64_t bd = make_desc_sw128(sK_a + (ks >> 2) * kKBlock + (ks & 3) * 32, 16, 1024);
+        umma_ss(tS, a, bd, idesc_s, ks > 0);
+      }
+      umma_commit(&bar);
+    }
+    bool ok = mbar_wait(&bar, phase, p.status, 1);
+    phase ^= 1;
+    if (!__syncthreads_and(ok)) break;
+    tc_fence_after_sync();
+
+    // ---- chunk-local softmax of row `tid`
+    const int r = sRow[tid];
+    const int lim = r < 0 ? 0 : (p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid);
+    float s[C];
+#pragma unroll
+    for (int i = 0; i < C / 32; ++i) tmem_ld32(tS + lane_sel + i * 32, s + i * 32);
+    tmem_ld_wait();
+    float mx = -CUDART_INF_F;
+#pragma unroll
+    for (int j = 0; j < C; ++j) {
+      s[j] = j < lim ? s[j] : -CUDART_INF_F;
+      mx = fmaxf(mx, s[j]);
+    }
+    const float mref = lim > 0 ? mx * scale_log2 : 0.f;
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < C; ++j) {
+      s[j] = exp2f(s[j] * scale_log2 - mref);   // exp2(-inf) = 0 for masked keys
+      sum += s[j];
+    }
+#pragma unroll
+    for (int j = 0; j < C / 8; ++j)
+      *reinterpret_cast<uint4*>(sQP + sw128_offset(tid, j, kQBlock)) = pack8<T>(s + j * 8);
+    const float inv = sum > 0.f ? 1.f / sum : 0.f;
+    if (tid < rows) p.part_lse[off + t0 + tid] = sum > 0.f ? mx * p.scale + logf(sum) : -CUDART_INF_F;
+    tc_fence_before_sync();
+    fence_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after_sync();
+#pragma unroll
+      for (int ks = 0; ks < C / 16; ++ks) {
+        const uint64_t a = make_desc_sw128(sQP_a + (ks >> 2) * kQBlock + (ks & 3) * 32, 16, 1024);
+        const uint64_t bd = make_desc_sw128(sV_a + ks * 2048, kKBlock, 1024);
+        umma_ss(tO, a, bd, idesc_o, ks > 0);
+      }
+      umma_commit(&bar);
+    }
+    ok = mbar_wait(&bar, phase, p.status, 2);
+    phase ^= 1;
+    if (!__syncthreads_and(ok)) break;
+    tc_fence_after_sync();
+
+    // ---- epilogue: normalised partial O of row `tid`
+    T* dst = part_o + (off + t0 + tid) * D;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) {
+      float o[32];
+      tmem_ld32(tO + lane_sel + i * 32, o);
+      tmem_ld_wait();
+      if (tid < rows) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] *= inv;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(dst + i * 32 + j * 8) = pack8<T>(o + j * 8);
+      }
+    }
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, NCOLS);
+}
+
+// ------------------------------------------------------------------ self test of the MMA path
+// D[128][128] (fp32) = A[128][128] . B, with B given [N][K] (K contiguous) when b_mn_major == 0
+// or [K][N] (N contiguous) when 1.  Exercises exactly the descriptors the attention kernels use.
+template <typename T>
+__global__ void __launch_bounds__(128) selftest_umma_kernel(const T* a, const T* b, float* d, int b_mn_major,
+                                                            int* status) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_base_s;
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* sA = smem;
+  unsigned char* sB = smem + 128 * 128 * 2;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (warp == 0) tmem_alloc(&tmem_base_s, 128);
+  if (tid == 0) { mbar_init(&bar, 1); mbar_fence_init(); }
+  stage_tile_sw128<T, 16>(sA, 128 * 128, a, 128, 128, [](int r) { return (int64_t)r; });
+  stage_tile_sw128<T, 16>(sB, 128 * 128, b, 128, 128, [](int r) { return (int64_t)r; });
+  fence_async_smem();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tD = tmem_base_s;
+  if (tid == 0) {
+    const uint32_t idesc = make_idesc(FmtOf<T>::v, 128, 128, 0, b_mn_major);
+    for (int ks = 0; ks < 8; ++ks) {
+      const uint64_t ad = make_desc_sw128(smem_u32(sA) + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
+      const uint64_t bd = b_mn_major ? make_desc_sw128(smem_u32(sB) + ks * 2048, 16384, 1024)
+                                     : make_desc_sw128(smem_u32(sB) + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
+      umma_ss(tD, ad, bd, idesc, ks > 0);
+    }
+    umma_commit(&bar);
+  }
+  const bool ok = mbar_wait(&bar, 0, status, 9);
+  if (__syncthreads_and(ok)) {
+    tc_fence_after_sync();
+    for (int i = 0; i < 4; ++i) {
+      float o[32];
+      tmem_ld32(tD + ((uint32_t)(warp * 32) << 16) + i * 32, o);
+      tmem_ld_wait();
+      for (int j = 0; j < 32; ++j) d[tid * 128 + i * 32 + j] = o[j];
+    }
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tD, 128);
+}
+
+int launch_selftest_umma(const void* a, const void* b, float* d, int b_mn_major, int dtype, int* status,
+                         cudaStream_t s) {
+  const size_t smem = 2 * 128 * 128 * 2 + 1024;
+  if (dtype == FMB_BF16) {
+    auto kern = selftest_umma_kernel<__nv_bfloat16>;
+    FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<1, 128, smem, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, d, b_mn_major, status);
+  } else {
+    auto kern = selftest_umma_kernel<__half>;
+    FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<1, 128, smem, s>>>((const __half*)a, (const __half*)b, d, b_mn_major, status);
+  }
+  FMB_LAUNCH_CHECK("selftest_umma_kernel");
+  return FMB_OK;
+}
+
+// ------------------------------------------------------------------ launchers
+static TcParams make_tc_params(const AttnArgs& a, const AttnWorkspace& w) {
+  TcParams p;
+  p.q = a.q; p.k = a.k; p.v = a.v; p.dout = a.dout;
+  p.q_rs = a.q_rs; p.q_hs = a.q_hs; p.k_rs = a.k_rs; p.k_hs = a.k_hs; p.v_rs = a.v_rs; p.v_hs = a.v_hs;
+  p.do_rs = a.do_rs; p.do_hs = a.do_hs;
+  p.dk = a.dk; p.dv = a.dv; p.dk_rs = a.dk_rs; p.dk_hs = a.dk_hs; p.dv_rs = a.dv_rs; p.dv_hs = a.dv_hs;
+  p.lse = a.lse; p.softmax_d = a.softmax_d;
+  p.col_offsets = a.col_offsets; p.col_nnz = a.col_nnz; p.indices = a.indices; p.n_indices = a.n_indices;
+  p.cu_q = a.cu_q; p.cu_k = a.cu_k; p.part_o = w.part_o; p.part_lse = w.part_lse; p.status = w.status;
+  p.heads = a.heads; p.heads_k = a.heads_k; p.ncol = a.ncol; p.total_q = a.total_q;
+  p.scale = a.scale; p.causal = a.causal;
+  return p;
+}
+
+// Dynamic shared memory is padded so that the CTAs that fit an SM never need more than the
+// 512 TMEM columns between them (tcgen05.alloc would otherwise stall until a CTA retires).
+static size_t pad_smem_for_tmem(size_t smem, int ncols) {
+  const size_t sm_bytes = 227 * 1024;
+  const size_t max_ctas = 512 / ncols;
+  while (sm_bytes / smem > max_ctas) smem += 4096;
+  return smem;
+}
+
+template <typename T, int C, int D>
+static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+  TcParams p = make_tc_params(a, w);
+  constexpr int QP = (C > D ? C : D);
+  size_t smem = (size_t)2 * C * D * 2 + (size_t)kTcM * QP * 2 + 1024;
+  smem = pad_smem_for_tmem(smem, next_pow2_cols(C + D));
+  auto kern = fwd_main_tc_kernel<T, C, D>;
+  FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<dim3(a.ncol, a.heads, a.batch), kTcM, smem, s>>>(p);
+  FMB_LAUNCH_CHECK("fwd_main_tc_kernel");
+  return FMB_OK;
+}
+
+bool tc_supported(const AttnArgs& a, bool backward) {
+  if (backward) return false;
+  return (a.chunk == 64 || a.chunk == 128) && (a.d == 64 || a.d == 128);
+}
+
+int launch_fwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+  if (a.ncol == 0 || a.batch == 0 || a.heads == 0) return FMB_OK;
+#define FMB_TC_FWD(TT)                                                       \
+  if (a.chunk == 64 && a.d == 64) return fwd_tc_launch<TT, 64, 64>(a, w, s);   \
+  if (a.chunk == 64 && a.d == 128) return fwd_tc_launch<TT, 64, 128>(a, w, s); \
+  if (a.chunk == 128 && a.d == 64) return fwd_tc_launch<TT, 128, 64>(a, w, s); \
+  if (a.chunk == 128 && a.d == 128) return fwd_tc_launch<TT, 128, 128>(a, w, s);
+  if (a.dtype == FMB_BF16) { FMB_TC_FWD(__nv_bfloat16) } else { FMB_TC_FWD(__half) }
+#undef FMB_TC_FWD
+  return fail(FMB_ERR_UNSUPPORTED, "tensor-core forward: chunk %d / head_dim %d not built", a.chunk, a.d);
+}
+
 int launch_bwd_main_tc(const AttnArgs&, const AttnWorkspace&, cudaStream_t) {
-  return fail(FMB_ERR_UNSUPPORTED, "tensor-core engine not built");
+  return fail(FMB_ERR_UNSUPPORTED, "tensor-core backward not built");
 }
+
 }  // namespace fmb

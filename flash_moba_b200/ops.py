@@ -48,6 +48,29 @@ def ptr(t: Optional[torch.Tensor]) -> int:
     return 0 if t is None else t.data_ptr()
 
 
+def _check_status(ws: torch.Tensor, what: str) -> None:
+    """With FMB_CHECK_STATUS=1 every attention call synchronises and reads the device-side
+    status word (first 4 bytes of the workspace); a bounded wait that expired raises."""
+    import os
+    if os.environ.get("FMB_CHECK_STATUS", "0") == "1":
+        code = int(ws[:4].view(torch.int32).item())
+        if code != 0:
+            raise RuntimeError(f"flash_moba_b200: {what}: a bounded device-side wait expired (code {code})")
+
+
+def selftest_umma(a: torch.Tensor, b: torch.Tensor, b_mn_major: bool) -> torch.Tensor:
+    """128x128x128 product on the tcgen05 path (see fmb_selftest_umma)."""
+    _require_cuda(a, b)
+    a, b = a.contiguous(), b.contiguous()
+    with torch.cuda.device(a.device):
+        d = torch.empty((128, 128), dtype=torch.float32, device=a.device)
+        status = torch.zeros((1,), dtype=torch.int32, device=a.device)
+        check(lib.fmb_selftest_umma(ptr(a), ptr(b), ptr(d), int(b_mn_major), _dtype_code(a), ptr(status), _stream()))
+        if int(status.item()) != 0:
+            raise RuntimeError(f"selftest_umma: bounded wait expired (code {int(status.item())})")
+    return d
+
+
 def set_engine(engine: int) -> int:
     """0 = CUDA-core validation kernels, 1 = tcgen05 kernels.  Returns the engine in use."""
     return lib.fmb_set_engine(int(engine))
@@ -174,6 +197,7 @@ def attn_fwd(q, k, v, col_offsets, col_nnz, indices, cu_seqlens_q, cu_seqlens_k,
                                ptr(_i32c(cu_seqlens_q, "cu_seqlens_q")), ptr(_i32c(cu_seqlens_k, "cu_seqlens_k")),
                                ptr(ws), nbytes, batch, h, hk, d, total_q, int(max_seqlen_q), int(max_seqlen_k),
                                int(chunk), float(softmax_scale), int(bool(causal)), _dtype_code(q), _stream()))
+        _check_status(ws, "attn_fwd")
     return out, lse
 
 
@@ -205,4 +229,5 @@ def attn_bwd(dout, q, k, v, out, lse, dq, dk, dv, col_offsets, col_nnz, indices,
                                ptr(ws), nbytes, batch, h, hk, d, total_q, total_k, int(max_seqlen_q),
                                int(max_seqlen_k), int(chunk), float(softmax_scale), int(bool(causal)),
                                _dtype_code(q), _stream()))
+        _check_status(ws, "attn_bwd")
     return softmax_d

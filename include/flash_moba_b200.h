@@ -158,6 +158,23 @@ int fmb_attn_bwd(const void* dout, int64_t do_row_stride, int64_t do_head_stride
  * engine now in use. */
 int fmb_set_engine(int engine);
 
+/* Which engine fmb_attn_fwd (backward = 0) or fmb_attn_bwd (backward = 1) will use for this
+ * chunk size and head dimension under the current fmb_set_engine setting: 1 = tcgen05,
+ * 0 = CUDA cores. */
+int fmb_attn_engine(int chunk, int head_dim, int backward);
+
+/* Self test of the tcgen05 path, no counterpart in the reference: d[128][128] (float) =
+ * a[128][128] . b, where b is [n][k] (k contiguous) if b_mn_major == 0, or [k][n]
+ * (n contiguous) if 1; uses the same shared-memory descriptors as the attention kernels.
+ * *status (device int, zeroed by the caller) receives a non-zero code if a bounded wait on
+ * the device expired. */
+int fmb_selftest_umma(const void* a, const void* b, float* d, int b_mn_major, int dtype, int* status,
+                      fmb_stream_t stream);
+
+/* The first 4 bytes of the workspace given to fmb_attn_fwd / fmb_attn_bwd hold a device-side
+ * status word after the call: 0 = ok, non-zero = a bounded wait inside a kernel expired
+ * (FMB_ERR_TIMEOUT condition; results are then invalid). */
+
 /* ------------------------------------------------------------------ measurement aids
  * No counterpart in the reference (it is timed from Python with torch.utils.benchmark,
  * flash_moba/utils/benchmark.py:120-156).

@@ -10,6 +10,8 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 GOLDEN = os.path.join(ROOT, "tests", "golden")
+# every attention call in the tests reads back the device-side status word
+os.environ.setdefault("FMB_CHECK_STATUS", "1")
 
 
 def pytest_configure(config):
