@@ -199,6 +199,219 @@ __global__ void __launch_bounds__(kTcM) fwd_main_tc_kernel(TcParams p) {
   if (warp == 0) tmem_dealloc(tmem_base, NCOLS);
 }
 
+
+// ======================================================================== backward
+// CTA = key chunk c of (sequence b, kv head hk); it loops over the q heads of the kv head's
+// group and over 128-row tiles of each head's CSC column.  Per tile, five GEMMs:
+//     S  = Q.K^T          dP = dO.V^T                       (both K-major operands)
+//     dV += P^T.dO        dK += dS^T.Q   (A and B consumed MN-major from the row-major tiles)
+//     dQ_partial = dS.K   (K consumed MN-major)             -> workspace at the pair's position
+// dK and dV stay in TMEM (fp32) for the CTA's whole life: no atomics, no cross-head reduction
+// pass.  TMEM columns: [0,C) S then dQ, [C,2C) dP, [2C,2C+D) dV, [2C+D,2C+2D) dK.
+template <typename T, int C, int D>
+__global__ void __launch_bounds__(kTcM) bwd_main_tc_kernel(TcParams p) {
+  static_assert(C == 128, "tensor-core backward keeps one key per TMEM lane");
+  constexpr uint32_t kKBlock = C * 128;
+  constexpr uint32_t kQBlock = kTcM * 128;
+  constexpr int NCOLS = 512;
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int sRow[kTcM];
+
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* sK = smem;                       // [C][D]
+  unsigned char* sV = sK + C * D * 2;             // [C][D]
+  unsigned char* sQ = sV + C * D * 2;             // [128][D]
+  unsigned char* sdO = sQ + kTcM * D * 2;         // [128][D]
+  unsigned char* sP = sdO + kTcM * D * 2;         // [128][C]
+  unsigned char* sdS = sP + kTcM * C * 2;         // [128][C]
+
+  const int c = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
+  const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
+  const int key0 = c * C;
+  if (key0 >= len_k) return;
+  const int keys_valid = min(C, len_k - key0);
+  const int group = p.heads / p.heads_k;
+  const int shift = len_k - len_q;
+  const float scale_log2 = p.scale * kLog2eTc;
+  const int tid = threadIdx.x, warp = tid >> 5;
+
+  if (warp == 0) tmem_alloc(&tmem_base_s, NCOLS);
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  const T* kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + key0) * p.k_rs + (int64_t)hk * p.k_hs;
+  const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
+  stage_tile_sw128<T, D / 8>(sK, kKBlock, kbase, p.k_rs, C, [&](int r) { return r < keys_valid ? (int64_t)r : -1; });
+  stage_tile_sw128<T, D / 8>(sV, kKBlock, vbase, p.v_rs, C, [&](int r) { return r < keys_valid ? (int64_t)r : -1; });
+  fence_async_smem();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+  const uint32_t tS = tmem_base, tdP = tmem_base + C, tdV = tmem_base + 2 * C, tdK = tmem_base + 2 * C + D;
+  const uint32_t tdQ = tS;
+  const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+  const uint32_t sK_a = smem_u32(sK), sV_a = smem_u32(sV), sQ_a = smem_u32(sQ), sdO_a = smem_u32(sdO),
+                 sP_a = smem_u32(sP), sdS_a = smem_u32(sdS);
+  constexpr uint32_t idesc_s = make_idesc(FmtOf<T>::v, kTcM, C, 0, 0);     // rows x keys
+  constexpr uint32_t idesc_kv = make_idesc(FmtOf<T>::v, C, D, 1, 1);       // keys x d, both MN-major
+  constexpr uint32_t idesc_dq = make_idesc(FmtOf<T>::v, kTcM, D, 0, 1);    // rows x d
+  float* part_dq = static_cast<float*>(p.part_o);
+  uint32_t phase = 0;
+  bool any_tile = false, alive = true;
+
+  for (int hg = 0; hg < group && alive; ++hg) {
+    const int h = hk * group + hg;
+    if (c >= p.ncol) break;
+    const int64_t ci = ((int64_t)b * p.heads + h) * p.ncol + c;
+    const int nnz = p.col_nnz[ci];
+    const int64_t off = p.col_offsets[ci];
+    if (nnz <= 0 || off < 0 || off + nnz > p.n_indices) continue;
+    const T* qbase = static_cast<const T*>(p.q) + (int64_t)q0 * p.q_rs + (int64_t)h * p.q_hs;
+    const T* dobase = static_cast<const T*>(p.dout) + (int64_t)q0 * p.do_rs + (int64_t)h * p.do_hs;
+    const float* lse = p.lse + (int64_t)h * p.total_q + q0;
+    const float* dsum = p.softmax_d + (int64_t)h * p.total_q + q0;
+
+    for (int t0 = 0; t0 < nnz; t0 += kTcM) {
+      const int rows = min(kTcM, nnz - t0);
+      int r = -1;
+      if (tid < rows) {
+        r = p.indices[off + t0 + tid];
+        if (r < 0 || r >= len_q) r = -1;
+      }
+      sRow[tid] = r;
+      const float lse2 = r >= 0 ? lse[r] * kLog2eTc : CUDART_INF_F;
+      const float dd = r >= 0 ? dsum[r] : 0.f;
+      __syncthreads();   // row ids visible; every MMA of the previous tile has completed
+      stage_tile_sw128<T, D / 8>(sQ, kQBlock, qbase, p.q_rs, kTcM, [&](int rr) { return (int64_t)sRow[rr]; });
+      stage_tile_sw128<T, D / 8>(sdO, kQBlock, dobase, p.do_rs, kTcM, [&](int rr) { return (int64_t)sRow[rr]; });
+      fence_async_smem();
+      __syncthreads();
+      if (tid == 0) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t ko = (ks >> 2) * kQBlock + (ks & 3) * 32, kb = (ks >> 2) * kKBlock + (ks & 3) * 32;
+          umma_ss(tS, make_desc_sw128(sQ_a + ko, 16, 1024), make_desc_sw128(sK_a + kb, 16, 1024), idesc_s, ks > 0);
+        }
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t ko = (ks >> 2) * kQBlock + (ks & 3) * 32, kb = (ks >> 2) * kKBlock + (ks & 3) * 32;
+          umma_ss(tdP, make_desc_sw128(sdO_a + ko, 16, 1024), make_desc_sw128(sV_a + kb, 16, 1024), idesc_s, ks > 0);
+        }
+        umma_commit(&bar);
+      }
+      bool ok = mbar_wait(&bar, phase, p.status, 3);
+      phase ^= 1;
+      if (!__syncthreads_and(ok)) { alive = false; break; }
+      tc_fence_after_sync();
+
+      // ---- P and dS of row `tid`, 32 keys at a time
+      const int lim = r < 0 ? 0 : (p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid);
+#pragma unroll
+      for (int i = 0; i < C / 32; ++i) {
+        float s[32], dp[32];
+        tmem_ld32(tS + lane_sel + i * 32, s);
+        tmem_ld32(tdP + lane_sel + i * 32, dp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float pr = (i * 32 + j < lim) ? exp2f(s[j] * scale_log2 - lse2) : 0.f;
+          s[j] = pr;
+          dp[j] = pr * (dp[j] - dd);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          *reinterpret_cast<uint4*>(sP + sw128_offset(tid, i * 4 + j, kQBlock)) = pack8<T>(s + j * 8);
+          *reinterpret_cast<uint4*>(sdS + sw128_offset(tid, i * 4 + j, kQBlock)) = pack8<T>(dp + j * 8);
+        }
+      }
+      tc_fence_before_sync();
+      fence_async_smem();
+      __syncthreads();
+      if (tid == 0) {
+        tc_fence_after_sync();
+        const uint32_t acc = any_tile ? 1u : 0u;
+        // dV += P^T.dO, dK += dS^T.Q : M = keys, N = d, K = the 128 gathered rows
+#pragma unroll
+        for (int ks = 0; ks < kTcM / 16; ++ks) {
+          umma_ss(tdV, make_desc_sw128(sP_a + ks * 2048, kQBlock, 1024),
+                  make_desc_sw128(sdO_a + ks * 2048, kQBlock, 1024), idesc_kv, acc | (ks > 0));
+        }
+#pragma unroll
+        for (int ks = 0; ks < kTcM / 16; ++ks) {
+          umma_ss(tdK, make_desc_sw128(sdS_a + ks * 2048, kQBlock, 1024),
+                  make_desc_sw128(sQ_a + ks * 2048, kQBlock, 1024), idesc_kv, acc | (ks > 0));
+        }
+        // dQ partial = dS.K : M = rows, N = d, K = keys
+#pragma unroll
+        for (int ks = 0; ks < C / 16; ++ks) {
+          umma_ss(tdQ, make_desc_sw128(sdS_a + (ks >> 2) * kQBlock + (ks & 3) * 32, 16, 1024),
+                  make_desc_sw128(sK_a + ks * 2048, kKBlock, 1024), idesc_dq, ks > 0);
+        }
+        umma_commit(&bar);
+      }
+      any_tile = true;
+      ok = mbar_wait(&bar, phase, p.status, 4);
+      phase ^= 1;
+      if (!__syncthreads_and(ok)) { alive = false; break; }
+      tc_fence_after_sync();
+      float* dst = part_dq + (off + t0 + tid) * D;
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) {
+        float o[32];
+        tmem_ld32(tdQ + lane_sel + i * 32, o);
+        tmem_ld_wait();
+        if (tid < rows) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(dst + i * 32 + j * 4) = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+        }
+      }
+      tc_fence_before_sync();
+    }
+  }
+  __syncthreads();
+  // ---- dK (scaled) and dV of key `tid`
+  if (alive) {
+    tc_fence_after_sync();
+    T* dkp = static_cast<T*>(p.dk) + (int64_t)(k0 + key0 + tid) * p.dk_rs + (int64_t)hk * p.dk_hs;
+    T* dvp = static_cast<T*>(p.dv) + (int64_t)(k0 + key0 + tid) * p.dv_rs + (int64_t)hk * p.dv_hs;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) {
+      float o[32];
+      if (any_tile) {
+        tmem_ld32(tdK + lane_sel + i * 32, o);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] = 0.f;
+      }
+      if (tid < keys_valid) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] *= p.scale;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(dkp + i * 32 + j * 8) = pack8<T>(o + j * 8);
+      }
+      if (any_tile) {
+        tmem_ld32(tdV + lane_sel + i * 32, o);
+        tmem_ld_wait();
+      }
+      if (tid < keys_valid) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(dvp + i * 32 + j * 8) = pack8<T>(o + j * 8);
+      }
+    }
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, NCOLS);
+}
+
 // ------------------------------------------------------------------ self test of the MMA path
 // D[128][128] (fp32) = A[128][128] . B, with B given [N][K] (K contiguous) when b_mn_major == 0
 // or [K][N] (N contiguous) when 1.  Exercises exactly the descriptors the attention kernels use.
@@ -299,8 +512,20 @@ static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t
   return FMB_OK;
 }
 
+template <typename T, int C, int D>
+static int bwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+  TcParams p = make_tc_params(a, w);
+  const size_t smem = (size_t)2 * C * D * 2 + (size_t)2 * kTcM * D * 2 + (size_t)2 * kTcM * C * 2 + 1024;
+  auto kern = bwd_main_tc_kernel<T, C, D>;
+  FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int nchunk = max(a.ncol, ceil_div(a.max_k, C));
+  kern<<<dim3(nchunk, a.heads_k, a.batch), kTcM, smem, s>>>(p);
+  FMB_LAUNCH_CHECK("bwd_main_tc_kernel");
+  return FMB_OK;
+}
+
 bool tc_supported(const AttnArgs& a, bool backward) {
-  if (backward) return false;
+  if (backward) return a.chunk == 128 && (a.d == 64 || a.d == 128);
   return (a.chunk == 64 || a.chunk == 128) && (a.d == 64 || a.d == 128);
 }
 
@@ -316,8 +541,13 @@ int launch_fwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s
   return fail(FMB_ERR_UNSUPPORTED, "tensor-core forward: chunk %d / head_dim %d not built", a.chunk, a.d);
 }
 
-int launch_bwd_main_tc(const AttnArgs&, const AttnWorkspace&, cudaStream_t) {
-  return fail(FMB_ERR_UNSUPPORTED, "tensor-core backward not built");
+int launch_bwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+  if (a.batch == 0 || a.heads == 0) return FMB_OK;
+  if (a.chunk == 128 && a.d == 64)
+    return a.dtype == FMB_BF16 ? bwd_tc_launch<__nv_bfloat16, 128, 64>(a, w, s) : bwd_tc_launch<__half, 128, 64>(a, w, s);
+  if (a.chunk == 128 && a.d == 128)
+    return a.dtype == FMB_BF16 ? bwd_tc_launch<__nv_bfloat16, 128, 128>(a, w, s) : bwd_tc_launch<__half, 128, 128>(a, w, s);
+  return fail(FMB_ERR_UNSUPPORTED, "tensor-core backward: chunk %d / head_dim %d not built", a.chunk, a.d);
 }
 
 }  // namespace fmb
