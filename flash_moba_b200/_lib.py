@@ -30,6 +30,8 @@ _SIGS = {
     "fmb_last_error": (ctypes.c_char_p, []),
     "fmb_set_engine": (i32, [i32]),
     "fmb_attn_engine": (i32, [i32, i32, i32]),
+    "fmb_gate_engine": (i32, [i32, i32]),
+    "fmb_gate_status": (i32, [c_ptr]),
     "fmb_selftest_umma": (i32, [c_ptr, c_ptr, c_ptr, i32, i32, c_ptr, c_ptr]),
     "fmb_launch_count": (ctypes.c_ulonglong, []),
     "fmb_profile_enable": (i32, [i32]),

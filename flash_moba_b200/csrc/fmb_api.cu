@@ -110,8 +110,18 @@ int fmb_selftest_umma(const void* a, const void* b, float* d, int b_mn_major, in
 }
 
 int fmb_set_engine(int engine) {
-  if (engine == 0 || engine == 1) g_engine = engine;
+  if (engine == 0 || engine == 1) {
+    g_engine = engine;
+    set_gate_engine(engine);
+  }
   return g_engine;
+}
+
+int fmb_gate_engine(int head_dim, int topk) { return (g_engine == 1 && gate_tc_supported(head_dim, topk)) ? 1 : 0; }
+
+int fmb_gate_status(int* host_status) {
+  FMB_CHECK_ARG(host_status, "gate_status: null pointer");
+  return read_gate_status(host_status);
 }
 
 int fmb_chunk_offsets(const int32_t* cu_seqlens_k, int batch, int chunk, int32_t* cu_seqlens_km,

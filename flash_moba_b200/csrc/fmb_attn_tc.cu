@@ -32,24 +32,6 @@ struct TcParams {
   float scale; int causal;
 };
 
-// rows x (NCHUNK*8 elements) from global memory into a swizzled UMMA tile.
-// row_of(r) gives the source row (or -1 for zero fill).
-template <typename T, int NCHUNK, typename RowFn>
-__device__ __forceinline__ void stage_tile_sw128(unsigned char* tile, uint32_t block_stride, const T* base,
-                                                 int64_t row_stride, int nrows, RowFn row_of) {
-  for (int e = threadIdx.x; e < nrows * NCHUNK; e += blockDim.x) {
-    const int r = e / NCHUNK, j = e % NCHUNK;
-    const int64_t src = row_of(r);
-    uint4 u = make_uint4(0, 0, 0, 0);
-    if (src >= 0) u = ldg_nc_16(base + src * row_stride + j * 8);
-    *reinterpret_cast<uint4*>(tile + sw128_offset(r, j, block_stride)) = u;
-  }
-}
-
-template <typename T> struct FmtOf;
-template <> struct FmtOf<__nv_bfloat16> { static constexpr int v = 1; };
-template <> struct FmtOf<__half> { static constexpr int v = 0; };
-
 __host__ __device__ constexpr int next_pow2_cols(int x) { return x <= 32 ? 32 : x <= 64 ? 64 : x <= 128 ? 128 : x <= 256 ? 256 : 512; }
 
 // ======================================================================== forward

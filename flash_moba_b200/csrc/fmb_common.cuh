@@ -113,6 +113,9 @@ struct GateArgs {
   int batch, heads, heads_k, d, max_q, max_k, topk, chunk, causal, dtype;
 };
 int launch_gate_topk(const GateArgs& a, cudaStream_t s);
+void set_gate_engine(int e);
+bool gate_tc_supported(int d, int topk);
+int read_gate_status(int* out);
 
 size_t csc_workspace_bytes(int batch, int heads, int max_q, int ncol);
 int launch_build_csc(const int32_t* topk_idx, int64_t idx_rs, int64_t idx_hs, const int32_t* cu_q, int64_t* col_offsets, int32_t* col_nnz,

@@ -11,6 +11,7 @@
 // score, and on equal scores the higher chunk id first
 // (csrc/flash_topk/src/flash_topk_kernel.h:261-285).
 #include "fmb_common.cuh"
+#include "fmb_tc.cuh"
 
 namespace fmb {
 
@@ -82,6 +83,34 @@ __device__ __forceinline__ void list_offer(RowList& L, float v, int n, bool elig
     ti = __shfl_sync(full, (kTwoHalves && topk > 32) ? L.i1 : L.i0, kl);
     cand = cand && lane != src && ranks_ahead(v, n, tv, ti);
     m = __ballot_sync(full, cand);
+  }
+}
+
+// One score tile (rows x ncols in sS) offered to the rows' lists; warp w owns rows w*R..,
+// R = 128 / number of warps.
+template <bool kTwoHalves>
+__device__ __forceinline__ void select_tile(const float* sS, float* sTV, int* sTI, int r0, int rows, int n0,
+                                            int ncols, int shift, int topk, int chunk, int causal) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rows_per_warp = kGateM / (blockDim.x >> 5);
+  for (int rr = 0; rr < rows_per_warp; ++rr) {
+    const int r = warp * rows_per_warp + rr;
+    if (r >= rows) break;
+    const int pos = r0 + r + shift;
+    RowList L;
+    L.v0 = lane < topk ? sTV[r * topk + lane] : -CUDART_INF_F;
+    L.i0 = lane < topk ? sTI[r * topk + lane] : -1;
+    L.v1 = -CUDART_INF_F; L.i1 = -1;
+    if (kTwoHalves && lane + 32 < topk) { L.v1 = sTV[r * topk + lane + 32]; L.i1 = sTI[r * topk + lane + 32]; }
+    for (int g = 0; g < kGateN; g += 32) {
+      if (g >= ncols) break;
+      const int n = n0 + g + lane;
+      const float v = sS[r * kGateSStride + g + lane];
+      const bool ok = (g + lane < ncols) && (!causal || ((n + 1) * chunk - 1 < pos));
+      list_offer<kTwoHalves>(L, v, n, ok, topk, lane);
+    }
+    if (lane < topk) { sTV[r * topk + lane] = L.v0; sTI[r * topk + lane] = L.i0; }
+    if (kTwoHalves && lane + 32 < topk) { sTV[r * topk + lane + 32] = L.v1; sTI[r * topk + lane + 32] = L.i1; }
   }
 }
 
@@ -187,26 +216,7 @@ __global__ void __launch_bounds__(kGateThreads) gate_topk_kernel(GateParams p) {
       }
     }
     __syncthreads();
-    // selection: warp w owns rows w*16 .. w*16+15
-    for (int rr = 0; rr < 16; ++rr) {
-      const int r = warp * 16 + rr;
-      if (r >= rows) break;
-      const int pos = r0 + r + shift;
-      RowList L;
-      L.v0 = lane < topk ? sTV[r * topk + lane] : -CUDART_INF_F;
-      L.i0 = lane < topk ? sTI[r * topk + lane] : -1;
-      L.v1 = -CUDART_INF_F; L.i1 = -1;
-      if (kTwoHalves && lane + 32 < topk) { L.v1 = sTV[r * topk + lane + 32]; L.i1 = sTI[r * topk + lane + 32]; }
-      for (int g = 0; g < kGateN; g += 32) {
-        if (g >= ncols) break;
-        const int n = n0 + g + lane;
-        const float v = sS[r * kGateSStride + g + lane];
-        const bool ok = (g + lane < ncols) && (!p.causal || ((n + 1) * p.chunk - 1 < pos));
-        list_offer<kTwoHalves>(L, v, n, ok, topk, lane);
-      }
-      if (lane < topk) { sTV[r * topk + lane] = L.v0; sTI[r * topk + lane] = L.i0; }
-      if (kTwoHalves && lane + 32 < topk) { sTV[r * topk + lane + 32] = L.v1; sTI[r * topk + lane + 32] = L.i1; }
-    }
+    select_tile<kTwoHalves>(sS, sTV, sTI, r0, rows, n0, ncols, shift, topk, p.chunk, p.causal);
     __syncthreads();
   }
   __syncthreads();
@@ -219,11 +229,201 @@ __global__ void __launch_bounds__(kGateThreads) gate_topk_kernel(GateParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Tensor-core variant (head_dim 64 or 128, top-k <= 32).  The score tile is a tcgen05 MMA
+// with the accumulator in TMEM; TMEM lane = query row, so thread t reads row t's scores
+// straight from TMEM (no shared-memory staging of scores) and keeps that row's top-k list
+// in registers as 64-bit keys: (order-preserving image of the fp32 score) << 32 | chunk id.
+// One unsigned compare then implements the reference's order — descending score, higher
+// chunk id first on ties — and the empty slot (-inf, id 0xffffffff) can never be displaced
+// by a -inf or NaN score.  Q is staged once; centroid tiles and TMEM accumulators are
+// double-buffered so the MMA of tile n+1 runs under the selection of tile n; two CTAs share
+// an SM.  All waits are bounded (status word g_gate_status).
+// ---------------------------------------------------------------------------------------
+__device__ int g_gate_status = 0;
+
+__device__ __forceinline__ uint32_t score_to_ordered(float v) {
+  const uint32_t b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float ordered_to_score(uint32_t o) {
+  return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o);
+}
+
+constexpr int kGateTcThreads = 128;
+
+template <typename T, int D, int KMAX>
+__global__ void __launch_bounds__(kGateTcThreads) gate_topk_tc_kernel(GateParams p) {
+  using namespace tc;
+  constexpr uint32_t kBlock = 128 * 128;       // bytes between 64-element blocks of a 128-row tile
+  constexpr uint32_t kTile = 128 * D * 2;
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ uint64_t bar[2];
+  __shared__ uint32_t tmem_base_s;
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* sQ = smem;
+  unsigned char* sKM = sQ + kTile;             // two buffers
+
+  const int mt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
+  const int len_k = p.cu_k[b + 1] - p.cu_k[b];
+  const int km0 = p.cu_km[b], nchunks = p.cu_km[b + 1] - km0;
+  const int r0 = mt * kGateM;
+  if (r0 >= len_q) return;
+  const int rows = min(kGateM, len_q - r0);
+  const int hk = h / (p.heads / p.heads_k);
+  const int shift = len_k - len_q;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int topk = p.topk;
+
+  // this thread's row: list of KMAX keys, descending; the first KMAX-topk are sentinels
+  const int pos = r0 + tid + shift;
+  const bool row_ok = tid < rows;
+  int nlim = nchunks;                          // candidate chunks of the row: n < nlim
+  if (p.causal) nlim = pos < 0 ? 0 : min(nchunks, pos / p.chunk);
+  if (!row_ok) nlim = 0;
+  constexpr uint64_t kEmpty = ((uint64_t)0x007fffffu << 32) | 0xffffffffu;   // (-inf, id -1)
+  const bool own = p.causal && row_ok && pos >= 0 && nchunks > 0;
+  const uint64_t own_key = ((uint64_t)score_to_ordered(CUDART_INF_F) << 32) | (uint32_t)(own ? pos / p.chunk : 0);
+  uint64_t key[KMAX];
+#pragma unroll
+  for (int j = 0; j < KMAX; ++j)   // static indices only: the list must stay in registers
+    key[j] = (j < KMAX - topk) ? ~0ull : ((j == KMAX - topk && own) ? own_key : kEmpty);
+
+  int n_end = nchunks;
+  if (p.causal) {
+    const int pmax = r0 + rows - 1 + shift;
+    n_end = pmax < 0 ? 0 : min(nchunks, pmax / p.chunk);
+  }
+  const int ntiles = (n_end + kGateN - 1) / kGateN;
+  if (ntiles > 0) {   // CTA-uniform
+    if (warp == 0) tmem_alloc(&tmem_base_s, 256);
+    if (tid == 0) {
+      mbar_init(&bar[0], 1);
+      mbar_init(&bar[1], 1);
+      mbar_fence_init();
+    }
+    const T* qbase = static_cast<const T*>(p.q) + (int64_t)(q0 + r0) * p.q_rs + (int64_t)h * p.q_hs;
+    const T* kmbase = static_cast<const T*>(p.km) + ((int64_t)km0 * p.heads_k + hk) * p.d;
+    const int64_t km_rs = (int64_t)p.heads_k * p.d;
+    stage_tile_sw128<T, D / 8>(sQ, kBlock, qbase, p.q_rs, kGateM, [&](int r) { return r < rows ? (int64_t)r : -1; });
+    {
+      const int ncols = min(kGateN, n_end);
+      stage_tile_sw128<T, D / 8>(sKM, kBlock, kmbase, km_rs, kGateN, [&](int r) { return r < ncols ? (int64_t)r : -1; });
+    }
+    fence_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_s;
+    const uint32_t sQ_a = smem_u32(sQ), sKM_a = smem_u32(sKM);
+    constexpr uint32_t idesc = make_idesc(FmtOf<T>::v, 128, 128, 0, 0);
+    auto issue = [&](int buf) {
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const uint32_t o = (ks >> 2) * kBlock + (ks & 3) * 32;
+        umma_ss(tmem_base + buf * 128, make_desc_sw128(sQ_a + o, 16, 1024),
+                make_desc_sw128(sKM_a + buf * kTile + o, 16, 1024), idesc, ks > 0);
+      }
+      umma_commit(&bar[buf]);
+    };
+    if (tid == 0) issue(0);
+    uint32_t phases = 0;   // bit b = parity to wait for on bar[b]
+    for (int t = 0; t < ntiles; ++t) {
+      const int buf = t & 1;
+      const int n0 = t * kGateN;
+      if (t + 1 < ntiles) {   // stage the next centroid tile (its buffer was read by MMA t-1, long complete)
+        const int n1 = n0 + kGateN, nc1 = min(kGateN, n_end - n1);
+        stage_tile_sw128<T, D / 8>(sKM + (buf ^ 1) * kTile, kBlock, kmbase + (int64_t)n1 * km_rs, km_rs, kGateN,
+                                   [&](int r) { return r < nc1 ? (int64_t)r : -1; });
+        fence_async_smem();
+      }
+      tc_fence_before_sync();
+      __syncthreads();   // next tile staged; every thread has finished reading TMEM buffer buf^1
+      if (tid == 0 && t + 1 < ntiles) {
+        tc_fence_after_sync();
+        issue(buf ^ 1);
+      }
+      const bool ok = mbar_wait(&bar[buf], (phases >> buf) & 1u, &g_gate_status, 1);
+      phases ^= 1u << buf;
+      if (!__syncthreads_and(ok)) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + buf * 128 + ((uint32_t)(warp * 32) << 16);
+#pragma unroll 1
+      for (int i = 0; i < 4; ++i) {
+        float v[32];
+        tmem_ld32(taddr + i * 32, v);
+        tmem_ld_wait();
+        const int nb = n0 + i * 32;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int n = nb + j;
+          const uint64_t cand = ((uint64_t)score_to_ordered(v[j]) << 32) | (uint32_t)n;
+          if (n < nlim && v[j] > -CUDART_INF_F && cand > key[KMAX - 1]) {
+            key[KMAX - 1] = cand;
+#pragma unroll
+            for (int x = KMAX - 1; x > 0; --x) {
+              const uint64_t lo = key[x], hi = key[x - 1];
+              const bool sw = lo > hi;
+              key[x] = sw ? hi : lo;
+              key[x - 1] = sw ? lo : hi;
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, 256);
+  }
+  if (row_ok) {
+    const int64_t o = (int64_t)(q0 + r0 + tid) * p.t_rs + (int64_t)h * p.t_hs;
+#pragma unroll
+    for (int j = 0; j < KMAX; ++j) {
+      const int slot = j - (KMAX - topk);
+      if (slot >= 0) {
+        p.topk_idx[o + slot] = (int)(uint32_t)key[j];
+        if (p.topk_val) p.topk_val[o + slot] = ordered_to_score((uint32_t)(key[j] >> 32));
+      }
+    }
+  }
+}
+
+static int g_gate_engine = 1;
+void set_gate_engine(int e) { g_gate_engine = e; }
+bool gate_tc_supported(int d, int topk) { return (d == 64 || d == 128) && topk <= 32; }
+
+int read_gate_status(int* out) {
+  FMB_CUDA(cudaMemcpyFromSymbol(out, g_gate_status, sizeof(int)));
+  return FMB_OK;
+}
+
+template <typename T, int D, int KMAX>
+static int gate_tc_launch(const GateParams& p, int batch, int max_q, cudaStream_t s) {
+  // 2 CTAs per SM at most (256 TMEM columns each): keep dynamic shared memory above a third of the SM's
+  size_t smem = 1024 + (size_t)3 * 128 * D * 2;
+  if (smem < 80 * 1024) smem = 80 * 1024;
+  auto kern = gate_topk_tc_kernel<T, D, KMAX>;
+  FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<dim3(ceil_div(max_q, kGateM), p.heads, batch), kGateTcThreads, smem, s>>>(p);
+  FMB_LAUNCH_CHECK("gate_topk_tc_kernel");
+  return FMB_OK;
+}
+template <typename T, int D>
+static int gate_tc_pick(const GateParams& p, int batch, int max_q, cudaStream_t s) {
+  if (p.topk <= 8) return gate_tc_launch<T, D, 8>(p, batch, max_q, s);
+  if (p.topk <= 16) return gate_tc_launch<T, D, 16>(p, batch, max_q, s);
+  return gate_tc_launch<T, D, 32>(p, batch, max_q, s);
+}
+
 template <typename T>
 static int gate_dispatch(const GateParams& p, int batch, int max_q, cudaStream_t s) {
   const size_t smem = (size_t)kGateDSlab * (kGateM + kGateN) * sizeof(T) +
                       (size_t)kGateM * kGateSStride * sizeof(float) + (size_t)kGateM * p.topk * 8;
   dim3 grid(ceil_div(max_q, kGateM), p.heads, batch);
+  if (g_gate_engine == 1 && gate_tc_supported(p.d, p.topk)) {
+    return p.d == 64 ? gate_tc_pick<T, 64>(p, batch, max_q, s) : gate_tc_pick<T, 128>(p, batch, max_q, s);
+  }
   if (p.topk > 32) {
     auto kern = gate_topk_kernel<T, true>;
     FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

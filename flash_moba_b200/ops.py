@@ -117,6 +117,13 @@ def gate_topk(q, km, cu_seqlens_q, cu_seqlens_k, cu_seqlens_km, max_seqlen_q: in
                                 ptr(idx), ptr(val), topk, total_q * topk, batch, h, hk, d, int(max_seqlen_q),
                                 int(max_seqlen_k), int(topk), int(chunk), int(bool(causal)), _dtype_code(q),
                                 _stream()))
+        import os
+        if os.environ.get("FMB_CHECK_STATUS", "0") == "1":
+            import ctypes
+            code = ctypes.c_int(0)
+            check(lib.fmb_gate_status(ctypes.addressof(code)))
+            if code.value != 0:
+                raise RuntimeError(f"flash_moba_b200: gate_topk: a bounded device-side wait expired (code {code.value})")
     return idx.permute(1, 0, 2), (val.permute(1, 0, 2) if val is not None else None)
 
 

@@ -153,7 +153,7 @@ int fmb_attn_bwd(const void* dout, int64_t do_row_stride, int64_t do_head_stride
                  int max_seqlen_k, int chunk, float softmax_scale, int causal, int dtype,
                  fmb_stream_t stream);
 
-/* Selects the attention engine for this process: 0 = CUDA-core validation kernels,
+/* Selects the engine of the attention and gating kernels for this process: 0 = CUDA-core validation kernels,
  * 1 = tcgen05 tensor-core kernels (default when built).  Testing aid; returns the
  * engine now in use. */
 int fmb_set_engine(int engine);
@@ -162,6 +162,13 @@ int fmb_set_engine(int engine);
  * chunk size and head dimension under the current fmb_set_engine setting: 1 = tcgen05,
  * 0 = CUDA cores. */
 int fmb_attn_engine(int chunk, int head_dim, int backward);
+
+/* Same for fmb_gate_topk (tcgen05 for head_dim 64/128 and topk <= 32). */
+int fmb_gate_engine(int head_dim, int topk);
+
+/* Synchronising read of the gating kernel's device-side status word into *host_status
+ * (0 = ok, non-zero = a bounded wait expired at some point in this process). */
+int fmb_gate_status(int* host_status);
 
 /* Self test of the tcgen05 path, no counterpart in the reference: d[128][128] (float) =
  * a[128][128] . b, where b is [n][k] (k contiguous) if b_mn_major == 0, or [k][n]
