@@ -187,6 +187,20 @@ int fmb_build_csc(const int32_t* topk_idx, int64_t topk_row_stride, int64_t topk
                           (cudaStream_t)stream);
 }
 
+size_t fmb_build_csc_static_capacity(void) { return csc_static_scratch_bytes(); }
+
+int fmb_build_csc_static(const int32_t* topk_idx, int64_t topk_row_stride, int64_t topk_head_stride,
+                         const int32_t* cu_seqlens_q, int64_t* col_offsets, int32_t* col_nnz, int32_t* indices,
+                         int batch, int heads, int topk, int max_seqlen_q, int ncol, fmb_stream_t stream) {
+  FMB_CHECK_ARG(batch >= 0 && heads >= 0 && topk >= 1 && max_seqlen_q >= 0 && ncol >= 0,
+                "build_csc_static: bad sizes");
+  if (batch == 0 || heads == 0 || ncol == 0) return FMB_OK;
+  FMB_CHECK_ARG(topk_idx && cu_seqlens_q && col_offsets && col_nnz && indices, "build_csc_static: null pointer");
+  FMB_CHECK_ARG(max_seqlen_q / 512 < 65535, "build_csc_static: max_seqlen_q too large");
+  return launch_build_csc_static(topk_idx, topk_row_stride, topk_head_stride, cu_seqlens_q, col_offsets, col_nnz,
+                                 indices, batch, heads, topk, max_seqlen_q, ncol, (cudaStream_t)stream);
+}
+
 int fmb_varlen_sort(const int64_t* starts, const int64_t* ends, const int32_t* src, int32_t* dst,
                     int64_t num_segments, int64_t num_items, fmb_stream_t stream) {
   FMB_CHECK_ARG(num_segments >= 0 && num_items >= 0, "varlen_sort: bad sizes");

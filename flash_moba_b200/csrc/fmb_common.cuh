@@ -121,6 +121,10 @@ size_t csc_workspace_bytes(int batch, int heads, int max_q, int ncol);
 int launch_build_csc(const int32_t* topk_idx, int64_t idx_rs, int64_t idx_hs, const int32_t* cu_q, int64_t* col_offsets, int32_t* col_nnz,
                      int32_t* indices, void* ws, size_t ws_bytes, int batch, int heads, int topk, int max_q,
                      int ncol, cudaStream_t s);
+size_t csc_static_scratch_bytes();
+int launch_build_csc_static(const int32_t* topk_idx, int64_t idx_rs, int64_t idx_hs, const int32_t* cu_q,
+                            int64_t* col_offsets, int32_t* col_nnz, int32_t* indices, int batch, int heads,
+                            int topk, int max_q, int ncol, cudaStream_t s);
 int launch_varlen_sort(const int64_t* starts, const int64_t* ends, const int32_t* src, int32_t* dst,
                        int64_t nseg, int64_t nitems, cudaStream_t s);
 

@@ -15,6 +15,8 @@
 //                  order and writes them at col_offsets + cursor -> columns come out
 //                  ascending, bit-exact and run-to-run deterministic.
 // HBM bound.  Algorithmic bytes: 4*nnz read + 4*nnz written + 12*B*H*ncol.
+#include <mutex>
+
 #include "fmb_common.cuh"
 
 namespace fmb {
@@ -201,6 +203,67 @@ int launch_build_csc(const int32_t* topk_idx, int64_t idx_rs, int64_t idx_hs, co
   csc_scatter_kernel<<<grid, kCscThreads, smem, s>>>(p);
   FMB_LAUNCH_CHECK("csc_scatter_kernel");
   return FMB_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Pattern build for callers that cannot allocate device memory.
+//
+// Some hosts of this library have no way to hand over a workspace: a serving runtime that
+// claims all device memory at start-up and forbids cudaMalloc afterwards (the call
+// synchronises the whole device and can fail once the arena owns the memory), or a thin
+// FFI shim in another language that only forwards the pointers it was given.  For them the
+// tile-histogram scratch of the builder lives in this file-scope device array instead.
+//   * capacity: kStaticScratchBytes (8 MiB), i.e. batch*heads*ceil(max_seqlen_q/512)*ncol
+//     <= 2,097,152 counters (e.g. one 64K-token sequence x 32 heads x 512 chunks); larger
+//     problems are rejected with FMB_ERR_WORKSPACE and must use fmb_build_csc;
+//   * every GPU that loads the library holds the array until the process exits;
+//   * the array is shared by all calls and keeps the previous call's contents.  Nothing has
+//     to start at zero: the histogram kernel writes every counter the later kernels read;
+//   * two calls that overlap on the GPU (different streams, or different host threads)
+//     race on the array: issue them on one stream, or order them with events.
+// In host code the array's name is only a stand-in; the device address is obtained once per
+// device with cudaGetSymbolAddress, on the first call made with that device current.  That
+// first call should therefore be made outside any stream capture.
+// ---------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = 8u << 20;
+static __device__ __align__(256) int32_t g_csc_static_scratch[kStaticScratchBytes / sizeof(int32_t)];
+
+static int csc_static_scratch_ptr(int32_t** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static int32_t* ptrs[kMaxDevices] = {};
+  int dev = 0;
+  FMB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(FMB_ERR_CUDA, "build_csc_static: device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    int32_t* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_csc_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(FMB_ERR_CUDA, "build_csc_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return FMB_OK;
+}
+
+size_t csc_static_scratch_bytes() { return kStaticScratchBytes; }
+
+int launch_build_csc_static(const int32_t* topk_idx, int64_t idx_rs, int64_t idx_hs, const int32_t* cu_q,
+                            int64_t* col_offsets, int32_t* col_nnz, int32_t* indices, int batch, int heads,
+                            int topk, int max_q, int ncol, cudaStream_t s) {
+  if (batch == 0 || heads == 0 || ncol == 0) return FMB_OK;
+  const size_t need = csc_workspace_bytes(batch, heads, max_q, ncol);
+  if (need > kStaticScratchBytes)
+    return fail(FMB_ERR_WORKSPACE,
+                "build_csc_static: this problem needs %zu bytes of scratch, the built-in array holds %zu "
+                "(batch*heads*ceil(max_seqlen_q/512)*ncol must be <= %zu); use fmb_build_csc with a workspace",
+                need, kStaticScratchBytes, kStaticScratchBytes / sizeof(int32_t));
+  int32_t* scratch = nullptr;
+  const int rc = csc_static_scratch_ptr(&scratch);
+  if (rc) return rc;
+  return launch_build_csc(topk_idx, idx_rs, idx_hs, cu_q, col_offsets, col_nnz, indices, scratch,
+                          kStaticScratchBytes, batch, heads, topk, max_q, ncol, s);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -105,6 +105,27 @@ int fmb_build_csc(const int32_t* topk_idx, int64_t topk_row_stride, int64_t topk
                   int batch, int heads, int topk, int max_seqlen_q, int ncol,
                   fmb_stream_t stream);
 
+/* fmb_build_csc for callers that cannot allocate device memory.  This entry point has no
+ * counterpart in the reference (there the C++ side allocates with torch::empty).  It is for
+ * hosts that may not call cudaMalloc once they are running — a serving runtime that took
+ * all device memory at start-up, a thin foreign-language shim that can only forward the
+ * pointers it was handed — and so cannot supply the workspace fmb_build_csc wants.  The
+ * scratch is a device array built into the library instead: 8 MiB
+ * (fmb_build_csc_static_capacity()), held by every GPU that loads the library until the
+ * process ends.  Inputs and outputs are still the caller's.  Limits and rules:
+ *   - fmb_build_csc_workspace_bytes(batch, heads, max_seqlen_q, ncol) must not exceed the
+ *     capacity, otherwise FMB_ERR_WORKSPACE is returned and nothing is launched;
+ *   - all calls share the array; calls that overlap on the GPU (two streams, two host
+ *     threads) race — keep them on one stream or order them with events;
+ *   - the first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call outside any stream capture.
+ * It allocates nothing and gives bit-identical results to fmb_build_csc. */
+size_t fmb_build_csc_static_capacity(void);
+int fmb_build_csc_static(const int32_t* topk_idx, int64_t topk_row_stride, int64_t topk_head_stride,
+                         const int32_t* cu_seqlens_q, int64_t* col_offsets, int32_t* col_nnz,
+                         int32_t* indices, int batch, int heads, int topk, int max_seqlen_q, int ncol,
+                         fmb_stream_t stream);
+
 /* Ascending sort of int32 keys inside each segment [starts[i], ends[i]) of src into dst
  * (dst is first filled with 0).  Kept for callers of the reference's stand-alone
  * varlen_sort, csrc/flash_topk/src/varlen_sort.cu:127-162. */
