@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(kTcM) fwd_main_tc_kernel(TcParams p) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ uint64_t bar;
   __shared__ uint32_t tmem_base_s;
-  __shared__ int sRow[kTcM];
+  __shared__ int sRow[2][kTcM];
 
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* sK = smem;
@@ -89,20 +89,26 @@ __global__ void __launch_bounds__(kTcM) fwd_main_tc_kernel(TcParams p) {
   T* part_o = static_cast<T*>(p.part_o);
   uint32_t phase = 0;
 
-  for (int t0 = 0; t0 < nnz; t0 += kTcM) {
-    const int rows = min(kTcM, nnz - t0);
-    {
-      int r = -1;
-      if (tid < rows) {
-        r = p.indices[off + t0 + tid];
-        if (r < 0 || r >= len_q) r = -1;
-      }
-      sRow[tid] = r;
+  auto load_rows = [&](int t0, int buf) {
+    int r = -1;
+    if (t0 + tid < nnz) {
+      r = p.indices[off + t0 + tid];
+      if (r < 0 || r >= len_q) r = -1;
     }
-    __syncthreads();   // row ids visible; the previous tile's MMAs and TMEM reads are complete
-    stage_tile_sw128<T, D / 8>(sQP, kQBlock, qbase, p.q_rs, kTcM, [&](int r) { return (int64_t)sRow[r]; });
-    fence_async_smem();
-    __syncthreads();
+    sRow[buf][tid] = r;
+  };
+  uint4 pre[D / 8];   // the next tile's Q rows, in flight while this tile computes
+  load_rows(0, 0);
+  __syncthreads();
+  gather_load<T, D / 8>(pre, qbase, p.q_rs, sRow[0]);
+  gather_store<D / 8>(pre, sQP, kQBlock);
+  fence_async_smem();
+  __syncthreads();
+
+  int buf = 0;
+  for (int t0 = 0; t0 < nnz; t0 += kTcM, buf ^= 1) {
+    const int rows = min(kTcM, nnz - t0);
+    const bool more = t0 + kTcM < nnz;
     if (tid == 0) {
       tc_fence_after_sync();
 #pragma unroll
@@ -113,36 +119,40 @@ __global__ void __launch_bounds__(kTcM) fwd_main_tc_kernel(TcParams p) {
       }
       umma_commit(&bar);
     }
+    if (more) load_rows(t0 + kTcM, buf ^ 1);   // published by the barrier after the softmax
     bool ok = mbar_wait(&bar, phase, p.status, 1);
     phase ^= 1;
     if (!__syncthreads_and(ok)) break;
     tc_fence_after_sync();
 
     // ---- chunk-local softmax of row `tid`
-    const int r = sRow[tid];
+    const int r = sRow[buf][tid];
     const int lim = r < 0 ? 0 : (p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid);
-    float s[C];
+    float inv;
+    {
+      float s[C];
 #pragma unroll
-    for (int i = 0; i < C / 32; ++i) tmem_ld32(tS + lane_sel + i * 32, s + i * 32);
-    tmem_ld_wait();
-    float mx = -CUDART_INF_F;
+      for (int i = 0; i < C / 32; ++i) tmem_ld32(tS + lane_sel + i * 32, s + i * 32);
+      tmem_ld_wait();
+      float mx = -CUDART_INF_F;
 #pragma unroll
-    for (int j = 0; j < C; ++j) {
-      s[j] = j < lim ? s[j] : -CUDART_INF_F;
-      mx = fmaxf(mx, s[j]);
+      for (int jj = 0; jj < C; ++jj) {
+        s[jj] = jj < lim ? s[jj] : -CUDART_INF_F;
+        mx = fmaxf(mx, s[jj]);
+      }
+      const float mref = lim > 0 ? mx * scale_log2 : 0.f;
+      float sum = 0.f;
+#pragma unroll
+      for (int jj = 0; jj < C; ++jj) {
+        s[jj] = exp2f(s[jj] * scale_log2 - mref);   // exp2(-inf) = 0 for masked keys
+        sum += s[jj];
+      }
+#pragma unroll
+      for (int jj = 0; jj < C / 8; ++jj)
+        *reinterpret_cast<uint4*>(sQP + sw128_offset(tid, jj, kQBlock)) = pack8<T>(s + jj * 8);
+      inv = sum > 0.f ? 1.f / sum : 0.f;
+      if (tid < rows) p.part_lse[off + t0 + tid] = sum > 0.f ? mx * p.scale + logf(sum) : -CUDART_INF_F;
     }
-    const float mref = lim > 0 ? mx * scale_log2 : 0.f;
-    float sum = 0.f;
-#pragma unroll
-    for (int j = 0; j < C; ++j) {
-      s[j] = exp2f(s[j] * scale_log2 - mref);   // exp2(-inf) = 0 for masked keys
-      sum += s[j];
-    }
-#pragma unroll
-    for (int j = 0; j < C / 8; ++j)
-      *reinterpret_cast<uint4*>(sQP + sw128_offset(tid, j, kQBlock)) = pack8<T>(s + j * 8);
-    const float inv = sum > 0.f ? 1.f / sum : 0.f;
-    if (tid < rows) p.part_lse[off + t0 + tid] = sum > 0.f ? mx * p.scale + logf(sum) : -CUDART_INF_F;
     tc_fence_before_sync();
     fence_async_smem();
     __syncthreads();
@@ -156,6 +166,7 @@ __global__ void __launch_bounds__(kTcM) fwd_main_tc_kernel(TcParams p) {
       }
       umma_commit(&bar);
     }
+    if (more) gather_load<T, D / 8>(pre, qbase, p.q_rs, sRow[buf ^ 1]);   // flies under the P.V MMAs
     ok = mbar_wait(&bar, phase, p.status, 2);
     phase ^= 1;
     if (!__syncthreads_and(ok)) break;
@@ -170,12 +181,17 @@ __global__ void __launch_bounds__(kTcM) fwd_main_tc_kernel(TcParams p) {
       tmem_ld_wait();
       if (tid < rows) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) o[j] *= inv;
+        for (int jj = 0; jj < 32; ++jj) o[jj] *= inv;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(dst + i * 32 + j * 8) = pack8<T>(o + j * 8);
+        for (int jj = 0; jj < 4; ++jj) *reinterpret_cast<uint4*>(dst + i * 32 + jj * 8) = pack8<T>(o + jj * 8);
       }
     }
     tc_fence_before_sync();
+    if (more) {   // P has been consumed (the MMAs completed): the tile buffer takes the next Q
+      gather_store<D / 8>(pre, sQP, kQBlock);
+      fence_async_smem();
+    }
+    __syncthreads();
   }
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, NCOLS);
@@ -199,7 +215,8 @@ __global__ void __launch_bounds__(kTcM) bwd_main_tc_kernel(TcParams p) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ uint64_t bar;
   __shared__ uint32_t tmem_base_s;
-  __shared__ int sRow[kTcM];
+  __shared__ int sRow[2][kTcM];
+  __shared__ float sLse[2][kTcM], sDs[2][kTcM];
 
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* sK = smem;                       // [C][D]
@@ -258,21 +275,31 @@ __global__ void __launch_bounds__(kTcM) bwd_main_tc_kernel(TcParams p) {
     const float* lse = p.lse + (int64_t)h * p.total_q + q0;
     const float* dsum = p.softmax_d + (int64_t)h * p.total_q + q0;
 
-    for (int t0 = 0; t0 < nnz; t0 += kTcM) {
-      const int rows = min(kTcM, nnz - t0);
+    auto load_rows = [&](int t0, int buf) {
       int r = -1;
-      if (tid < rows) {
+      float l2 = CUDART_INF_F, dd = 0.f;
+      if (t0 + tid < nnz) {
         r = p.indices[off + t0 + tid];
         if (r < 0 || r >= len_q) r = -1;
+        else { l2 = lse[r] * kLog2eTc; dd = dsum[r]; }
       }
-      sRow[tid] = r;
-      const float lse2 = r >= 0 ? lse[r] * kLog2eTc : CUDART_INF_F;
-      const float dd = r >= 0 ? dsum[r] : 0.f;
-      __syncthreads();   // row ids visible; every MMA of the previous tile has completed
-      stage_tile_sw128<T, D / 8>(sQ, kQBlock, qbase, p.q_rs, kTcM, [&](int rr) { return (int64_t)sRow[rr]; });
-      stage_tile_sw128<T, D / 8>(sdO, kQBlock, dobase, p.do_rs, kTcM, [&](int rr) { return (int64_t)sRow[rr]; });
-      fence_async_smem();
-      __syncthreads();
+      sRow[buf][tid] = r; sLse[buf][tid] = l2; sDs[buf][tid] = dd;
+    };
+    uint4 pre[D / 8];   // half of the next tile's operands in flight at a time
+    __syncthreads();    // the previous head's last tile has been consumed
+    load_rows(0, 0);
+    __syncthreads();
+    gather_load<T, D / 8>(pre, qbase, p.q_rs, sRow[0]);
+    gather_store<D / 8>(pre, sQ, kQBlock);
+    gather_load<T, D / 8>(pre, dobase, p.do_rs, sRow[0]);
+    gather_store<D / 8>(pre, sdO, kQBlock);
+    fence_async_smem();
+    __syncthreads();
+
+    int buf = 0;
+    for (int t0 = 0; t0 < nnz; t0 += kTcM, buf ^= 1) {
+      const int rows = min(kTcM, nnz - t0);
+      const bool more = t0 + kTcM < nnz;
       if (tid == 0) {
         tc_fence_after_sync();
 #pragma unroll
@@ -287,12 +314,15 @@ __global__ void __launch_bounds__(kTcM) bwd_main_tc_kernel(TcParams p) {
         }
         umma_commit(&bar);
       }
+      if (more) load_rows(t0 + kTcM, buf ^ 1);   // published by the barrier after P/dS
       bool ok = mbar_wait(&bar, phase, p.status, 3);
       phase ^= 1;
       if (!__syncthreads_and(ok)) { alive = false; break; }
       tc_fence_after_sync();
 
       // ---- P and dS of row `tid`, 32 keys at a time
+      const int r = sRow[buf][tid];
+      const float lse2 = sLse[buf][tid], dd = sDs[buf][tid];
       const int lim = r < 0 ? 0 : (p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid);
 #pragma unroll
       for (int i = 0; i < C / 32; ++i) {
@@ -301,15 +331,15 @@ __global__ void __launch_bounds__(kTcM) bwd_main_tc_kernel(TcParams p) {
         tmem_ld32(tdP + lane_sel + i * 32, dp);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float pr = (i * 32 + j < lim) ? exp2f(s[j] * scale_log2 - lse2) : 0.f;
-          s[j] = pr;
-          dp[j] = pr * (dp[j] - dd);
+        for (int jj = 0; jj < 32; ++jj) {
+          const float pr = (i * 32 + jj < lim) ? exp2f(s[jj] * scale_log2 - lse2) : 0.f;
+          s[jj] = pr;
+          dp[jj] = pr * (dp[jj] - dd);
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          *reinterpret_cast<uint4*>(sP + sw128_offset(tid, i * 4 + j, kQBlock)) = pack8<T>(s + j * 8);
-          *reinterpret_cast<uint4*>(sdS + sw128_offset(tid, i * 4 + j, kQBlock)) = pack8<T>(dp + j * 8);
+        for (int jj = 0; jj < 4; ++jj) {
+          *reinterpret_cast<uint4*>(sP + sw128_offset(tid, i * 4 + jj, kQBlock)) = pack8<T>(s + jj * 8);
+          *reinterpret_cast<uint4*>(sdS + sw128_offset(tid, i * 4 + jj, kQBlock)) = pack8<T>(dp + jj * 8);
         }
       }
       tc_fence_before_sync();
@@ -338,10 +368,15 @@ __global__ void __launch_bounds__(kTcM) bwd_main_tc_kernel(TcParams p) {
         umma_commit(&bar);
       }
       any_tile = true;
+      if (more) gather_load<T, D / 8>(pre, qbase, p.q_rs, sRow[buf ^ 1]);   // flies under the three GEMMs
       ok = mbar_wait(&bar, phase, p.status, 4);
       phase ^= 1;
       if (!__syncthreads_and(ok)) { alive = false; break; }
       tc_fence_after_sync();
+      if (more) {   // Q and dO of this tile are consumed: refill, dO loads fly under the dQ epilogue
+        gather_store<D / 8>(pre, sQ, kQBlock);
+        gather_load<T, D / 8>(pre, dobase, p.do_rs, sRow[buf ^ 1]);
+      }
       float* dst = part_dq + (off + t0 + tid) * D;
 #pragma unroll
       for (int i = 0; i < D / 32; ++i) {
@@ -350,11 +385,17 @@ __global__ void __launch_bounds__(kTcM) bwd_main_tc_kernel(TcParams p) {
         tmem_ld_wait();
         if (tid < rows) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<float4*>(dst + i * 32 + j * 4) = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+          for (int jj = 0; jj < 8; ++jj)
+            *reinterpret_cast<float4*>(dst + i * 32 + jj * 4) =
+                make_float4(o[4 * jj], o[4 * jj + 1], o[4 * jj + 2], o[4 * jj + 3]);
         }
       }
       tc_fence_before_sync();
+      if (more) {
+        gather_store<D / 8>(pre, sdO, kQBlock);
+        fence_async_smem();
+      }
+      __syncthreads();
     }
   }
   __syncthreads();

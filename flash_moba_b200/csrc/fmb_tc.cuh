@@ -146,6 +146,29 @@ __device__ __forceinline__ void stage_tile_sw128(unsigned char* tile, uint32_t b
   }
 }
 
+// Gather of a 128-row tile by a 128-thread CTA, split in two so that the global loads can
+// be in flight while the CTA waits on something else: gather_load() issues NCHUNK
+// independent 16-byte loads per thread into registers (row ids from sRow, -1 = zero fill),
+// gather_store() writes them to the swizzled tile.
+template <typename T, int NCHUNK>
+__device__ __forceinline__ void gather_load(uint4 (&u)[NCHUNK], const T* base, int64_t row_stride,
+                                            const int* sRow) {
+  const int j = threadIdx.x % NCHUNK, rb = threadIdx.x / NCHUNK;
+#pragma unroll
+  for (int i = 0; i < NCHUNK; ++i) {
+    const int src = sRow[rb + (128 / NCHUNK) * i];
+    u[i] = make_uint4(0, 0, 0, 0);
+    if (src >= 0) u[i] = ldg_nc_16(base + (int64_t)src * row_stride + j * 8);
+  }
+}
+template <int NCHUNK>
+__device__ __forceinline__ void gather_store(const uint4 (&u)[NCHUNK], unsigned char* tile, uint32_t block_stride) {
+  const int j = threadIdx.x % NCHUNK, rb = threadIdx.x / NCHUNK;
+#pragma unroll
+  for (int i = 0; i < NCHUNK; ++i)
+    *reinterpret_cast<uint4*>(tile + sw128_offset(rb + (128 / NCHUNK) * i, j, block_stride)) = u[i];
+}
+
 
 template <typename T> struct FmtOf;
 template <> struct FmtOf<__nv_bfloat16> { static constexpr int v = 1; };
