@@ -36,6 +36,7 @@ WORKLOADS = {
     "c2": ([32768], 16, 16, 128, 128, 8, False, 0.5),
     "c3": ([8192] * 8, 32, 32, 128, 128, 8, True, 1.0),
     "small": ([4096], 8, 8, 128, 128, 8, True, 1.0),
+    "mid": ([16384], 16, 16, 128, 128, 8, True, 1.0),
 }
 
 

@@ -45,6 +45,7 @@ def _deps_mtime():
 
 def _compile(nvcc, src, obj, log):
     flags = [f for f in NVCC_FLAGS if not (f == "--use_fast_math" and os.path.basename(src) in PRECISE)]
+    flags = flags + os.environ.get("FMB_EXTRA_NVCC_FLAGS", "").split()
     cmd = [nvcc] + flags + ["-I", INCLUDE, "-c", src, "-o", obj]
     r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     with open(log, "w") as f:

@@ -16,6 +16,16 @@
 
 namespace fmb {
 
+// Partial rows are stored with their 16-byte chunks permuted: chunk c of the pair at position
+// `pos` sits at chunk (c ^ (pos & 7)).  The tensor-core kernels stage a tile of partial rows
+// in shared memory before one bulk copy per warp; with this permutation the 32 lanes of a
+// warp (consecutive positions) write their rows without bank conflicts, and the linear copy
+// preserves it.  Writers and the combine kernels use part_col() for the element index.
+__host__ __device__ __forceinline__ int part_col(int64_t pos, int col, int elems_per_chunk) {
+  const int chunk = col / elems_per_chunk;
+  return ((chunk ^ (int)(pos & 7)) * elems_per_chunk) + (col % elems_per_chunk);
+}
+
 struct AttnWorkspace {
   int* status;         // first word of the workspace: 0, or where a bounded device wait gave up
   void* part_o;        // fwd: n_indices * d elements of the I/O dtype;  bwd: n_indices * d floats

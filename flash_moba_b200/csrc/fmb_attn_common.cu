@@ -226,7 +226,7 @@ __global__ void __launch_bounds__(256) fwd_combine_kernel(const T* __restrict__ 
       for (int i = 0; i < 4; ++i) {
         const int c = lane * 2 + i * 64;
         if (c < d) {
-          const float2 x = Elem<T>::to_f2(*reinterpret_cast<const T2*>(src + c));
+          const float2 x = Elem<T>::to_f2(*reinterpret_cast<const T2*>(src + part_col(pos, c, 8)));
           acc[i].x = fmaf(wgt, x.x, acc[i].x);
           acc[i].y = fmaf(wgt, x.y, acc[i].y);
         }
@@ -271,7 +271,7 @@ __global__ void __launch_bounds__(256) bwd_combine_kernel(const float* __restric
     for (int i = 0; i < 4; ++i) {
       const int c = lane * 2 + i * 64;
       if (c < d) {
-        const float2 x = *reinterpret_cast<const float2*>(src + c);
+        const float2 x = *reinterpret_cast<const float2*>(src + part_col(pos, c, 4));
         acc[i].x += x.x;
         acc[i].y += x.y;
       }

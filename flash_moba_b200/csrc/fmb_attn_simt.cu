@@ -195,9 +195,10 @@ __global__ void __launch_bounds__(kSimtThreads) fwd_main_simt_kernel(SimtParams 
       const int m = ty * 4 + i;
       if (m < rows) {
         const float inv = sInv[m];
-        T* dst = part_o + (off + t0 + m) * D + tx * TD;
+        const int64_t pos = off + t0 + m;
+        T* dst = part_o + pos * D;
 #pragma unroll
-        for (int x = 0; x < TD; ++x) dst[x] = Elem<T>::from_f(o[i][x] * inv);
+        for (int x = 0; x < TD; ++x) dst[part_col(pos, tx * TD + x, 8)] = Elem<T>::from_f(o[i][x] * inv);
       }
     }
   }
@@ -341,9 +342,10 @@ __global__ void __launch_bounds__(kSimtThreads) bwd_main_simt_kernel(SimtParams 
         for (int i = 0; i < 4; ++i) {
           const int m = ty * 4 + i;
           if (m < rows) {
-            float* dst = part_dq + (off + t0 + m) * D + tx * TD;
+            const int64_t pos = off + t0 + m;
+            float* dst = part_dq + pos * D;
 #pragma unroll
-            for (int j = 0; j < TD; ++j) dst[j] = dq[i][j];
+            for (int j = 0; j < TD; ++j) dst[part_col(pos, tx * TD + j, 4)] = dq[i][j];
           }
         }
       }

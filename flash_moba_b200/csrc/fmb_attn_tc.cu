@@ -18,6 +18,24 @@ namespace fmb {
 using namespace tc;
 
 constexpr int kTcM = 128;   // gathered rows per tile = TMEM lanes
+
+// Optional phase timing (build with -DFMB_TC_TIMING): thread 0 of every CTA accumulates clock64
+// deltas per phase into 64-bit counters that start 64 bytes into the workspace status block.
+#ifdef FMB_TC_TIMING
+#define FMB_T0() long long t_prev_ = clock64()
+#define FMB_TICK(slot)                                                                          \
+  do {                                                                                          \
+    if (threadIdx.x == 0) {                                                                     \
+      const long long t_now_ = clock64();                                                       \
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (slot),                   \
+                (unsigned long long)(t_now_ - t_prev_));                                        \
+      t_prev_ = t_now_;                                                                         \
+    }                                                                                           \
+  } while (0)
+#else
+#define FMB_T0() do {} while (0)
+#define FMB_TICK(slot) do {} while (0)
+#endif
 constexpr float kLog2eTc = 1.4426950408889634f;
 
 struct TcParams {
@@ -66,6 +84,7 @@ __global__ void __launch_bounds__(kTcM) fwd_main_tc_kernel(TcParams p) {
   const float scale_log2 = p.scale * kLog2eTc;
   const int tid = threadIdx.x, warp = tid >> 5;
 
+  FMB_T0();
   if (warp == 0) tmem_alloc(&tmem_base_s, NCOLS);
   if (tid == 0) {
     mbar_init(&bar, 1);
@@ -74,8 +93,8 @@ __global__ void __launch_bounds__(kTcM) fwd_main_tc_kernel(TcParams p) {
   const T* kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + key0) * p.k_rs + (int64_t)hk * p.k_hs;
   const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
   const T* qbase = static_cast<const T*>(p.q) + (int64_t)q0 * p.q_rs + (int64_t)h * p.q_hs;
-  stage_tile_sw128<T, D / 8>(sK, kKBlock, kbase, p.k_rs, C, [&](int r) { return r < keys_valid ? (int64_t)r : -1; });
-  stage_tile_sw128<T, D / 8>(sV, kKBlock, vbase, p.v_rs, C, [&](int r) { return r < keys_valid ? (int64_t)r : -1; });
+  stage_dense_sw128<T, D / 8, C>(sK, kKBlock, kbase, p.k_rs, keys_valid);
+  stage_dense_sw128<T, D / 8, C>(sV, kKBlock, vbase, p.v_rs, keys_valid);
   fence_async_smem();
   tc_fence_before_sync();
   __syncthreads();
@@ -97,6 +116,7 @@ __global__ void __launch_bounds__(kTcM) fwd_main_tc_kernel(TcParams p) {
     }
     sRow[buf][tid] = r;
   };
+  FMB_TICK(0);   // prologue: TMEM alloc + K/V staging
   uint4 pre[D / 8];   // the next tile's Q rows, in flight while this tile computes
   load_rows(0, 0);
   __syncthreads();
@@ -105,6 +125,7 @@ __global__ void __launch_bounds__(kTcM) fwd_main_tc_kernel(TcParams p) {
   fence_async_smem();
   __syncthreads();
 
+  FMB_TICK(1);   // first Q gather
   int buf = 0;
   for (int t0 = 0; t0 < nnz; t0 += kTcM, buf ^= 1) {
     const int rows = min(kTcM, nnz - t0);
@@ -124,6 +145,7 @@ __global__ void __launch_bounds__(kTcM) fwd_main_tc_kernel(TcParams p) {
     phase ^= 1;
     if (!__syncthreads_and(ok)) break;
     tc_fence_after_sync();
+    FMB_TICK(2);   // S = Q.K^T issue -> complete
 
     // ---- chunk-local softmax of row `tid`
     const int r = sRow[buf][tid];
@@ -155,7 +177,9 @@ __global__ void __launch_bounds__(kTcM) fwd_main_tc_kernel(TcParams p) {
     }
     tc_fence_before_sync();
     fence_async_smem();
+    FMB_TICK(3);   // softmax of thread 0's row
     __syncthreads();
+    FMB_TICK(4);   // barrier after softmax
     if (tid == 0) {
       tc_fence_after_sync();
 #pragma unroll
@@ -171,28 +195,45 @@ __global__ void __launch_bounds__(kTcM) fwd_main_tc_kernel(TcParams p) {
     phase ^= 1;
     if (!__syncthreads_and(ok)) break;
     tc_fence_after_sync();
+    FMB_TICK(5);   // O = P.V issue -> complete (next gather issued)
 
-    // ---- epilogue: normalised partial O of row `tid`
-    T* dst = part_o + (off + t0 + tid) * D;
+    // ---- epilogue: normalised partial O of row `tid`, staged in shared memory (the tile
+    // buffer is free: the P.V MMAs have completed) and written with one bulk copy per row
+    {
+      const int64_t pos = off + t0 + tid;
+      const int key = (int)(pos & 7);
+      unsigned char* srow = sQP + tid * (D * 2);
+      float o[D];
 #pragma unroll
-    for (int i = 0; i < D / 32; ++i) {
-      float o[32];
-      tmem_ld32(tO + lane_sel + i * 32, o);
+      for (int i = 0; i < D / 32; ++i) tmem_ld32(tO + lane_sel + i * 32, o + i * 32);   // one exposed latency
       tmem_ld_wait();
-      if (tid < rows) {
+      FMB_TICK(8);
 #pragma unroll
-        for (int jj = 0; jj < 32; ++jj) o[jj] *= inv;
+      for (int jj = 0; jj < D; ++jj) o[jj] *= inv;
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) *reinterpret_cast<uint4*>(dst + i * 32 + jj * 8) = pack8<T>(o + jj * 8);
+      for (int jj = 0; jj < D / 8; ++jj) *reinterpret_cast<uint4*>(srow + ((jj ^ key) << 4)) = pack8<T>(o + jj * 8);
+      FMB_TICK(9);
+      tc_fence_before_sync();
+      fence_async_smem();
+      __syncwarp();
+      FMB_TICK(10);
+      const int wrows = min(32, rows - warp * 32);   // this warp's rows are contiguous in the workspace
+      if ((tid & 31) == 0 && wrows > 0) {
+        bulk_store(part_o + (off + t0 + warp * 32) * D, sQP + warp * 32 * (D * 2), (uint32_t)wrows * D * 2);
+        bulk_commit();
       }
     }
-    tc_fence_before_sync();
-    if (more) {   // P has been consumed (the MMAs completed): the tile buffer takes the next Q
+    FMB_TICK(6);   // epilogue
+    bulk_wait_read();
+    __syncthreads();   // every row's copy has read its staging row
+    if (more) {        // the tile buffer takes the next Q
       gather_store<D / 8>(pre, sQP, kQBlock);
       fence_async_smem();
     }
     __syncthreads();
+    FMB_TICK(7);   // next Q into shared memory + barrier
   }
+  bulk_wait_read();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, NCOLS);
 }
@@ -244,8 +285,8 @@ __global__ void __launch_bounds__(kTcM) bwd_main_tc_kernel(TcParams p) {
   }
   const T* kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + key0) * p.k_rs + (int64_t)hk * p.k_hs;
   const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
-  stage_tile_sw128<T, D / 8>(sK, kKBlock, kbase, p.k_rs, C, [&](int r) { return r < keys_valid ? (int64_t)r : -1; });
-  stage_tile_sw128<T, D / 8>(sV, kKBlock, vbase, p.v_rs, C, [&](int r) { return r < keys_valid ? (int64_t)r : -1; });
+  stage_dense_sw128<T, D / 8, C>(sK, kKBlock, kbase, p.k_rs, keys_valid);
+  stage_dense_sw128<T, D / 8, C>(sV, kKBlock, vbase, p.v_rs, keys_valid);
   fence_async_smem();
   tc_fence_before_sync();
   __syncthreads();
@@ -320,26 +361,31 @@ __global__ void __launch_bounds__(kTcM) bwd_main_tc_kernel(TcParams p) {
       if (!__syncthreads_and(ok)) { alive = false; break; }
       tc_fence_after_sync();
 
-      // ---- P and dS of row `tid`, 32 keys at a time
+      // ---- P and dS of row `tid`, 32 keys at a time (the previous tile's dQ staging, which
+      // shares this memory, must have been read out first)
+      bulk_wait_read();
+      __syncthreads();
       const int r = sRow[buf][tid];
       const float lse2 = sLse[buf][tid], dd = sDs[buf][tid];
       const int lim = r < 0 ? 0 : (p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid);
 #pragma unroll
-      for (int i = 0; i < C / 32; ++i) {
-        float s[32], dp[32];
-        tmem_ld32(tS + lane_sel + i * 32, s);
-        tmem_ld32(tdP + lane_sel + i * 32, dp);
+      for (int i = 0; i < C / 64; ++i) {   // 64 keys per exposed TMEM latency
+        float s[64], dp[64];
+        tmem_ld32(tS + lane_sel + i * 64, s);
+        tmem_ld32(tS + lane_sel + i * 64 + 32, s + 32);
+        tmem_ld32(tdP + lane_sel + i * 64, dp);
+        tmem_ld32(tdP + lane_sel + i * 64 + 32, dp + 32);
         tmem_ld_wait();
 #pragma unroll
-        for (int jj = 0; jj < 32; ++jj) {
-          const float pr = (i * 32 + jj < lim) ? exp2f(s[jj] * scale_log2 - lse2) : 0.f;
+        for (int jj = 0; jj < 64; ++jj) {
+          const float pr = (i * 64 + jj < lim) ? exp2f(s[jj] * scale_log2 - lse2) : 0.f;
           s[jj] = pr;
           dp[jj] = pr * (dp[jj] - dd);
         }
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          *reinterpret_cast<uint4*>(sP + sw128_offset(tid, i * 4 + jj, kQBlock)) = pack8<T>(s + jj * 8);
-          *reinterpret_cast<uint4*>(sdS + sw128_offset(tid, i * 4 + jj, kQBlock)) = pack8<T>(dp + jj * 8);
+        for (int jj = 0; jj < 8; ++jj) {
+          *reinterpret_cast<uint4*>(sP + sw128_offset(tid, i * 8 + jj, kQBlock)) = pack8<T>(s + jj * 8);
+          *reinterpret_cast<uint4*>(sdS + sw128_offset(tid, i * 8 + jj, kQBlock)) = pack8<T>(dp + jj * 8);
         }
       }
       tc_fence_before_sync();
@@ -377,17 +423,25 @@ __global__ void __launch_bounds__(kTcM) bwd_main_tc_kernel(TcParams p) {
         gather_store<D / 8>(pre, sQ, kQBlock);
         gather_load<T, D / 8>(pre, dobase, p.do_rs, sRow[buf ^ 1]);
       }
-      float* dst = part_dq + (off + t0 + tid) * D;
+      // dQ partial of row `tid`: staged (fp32) over the P/dS tiles, which the three GEMMs have
+      // finished reading, and written with one bulk copy per row
+      {
+        const int64_t pos = off + t0 + tid;
+        const int key = (int)(pos & 7);
+        unsigned char* srow = sP + tid * (D * 4);
+        float o[D];
 #pragma unroll
-      for (int i = 0; i < D / 32; ++i) {
-        float o[32];
-        tmem_ld32(tdQ + lane_sel + i * 32, o);
+        for (int i = 0; i < D / 32; ++i) tmem_ld32(tdQ + lane_sel + i * 32, o + i * 32);
         tmem_ld_wait();
-        if (tid < rows) {
 #pragma unroll
-          for (int jj = 0; jj < 8; ++jj)
-            *reinterpret_cast<float4*>(dst + i * 32 + jj * 4) =
-                make_float4(o[4 * jj], o[4 * jj + 1], o[4 * jj + 2], o[4 * jj + 3]);
+        for (int jj = 0; jj < D / 4; ++jj)
+          *reinterpret_cast<float4*>(srow + ((jj ^ key) << 4)) = make_float4(o[4 * jj], o[4 * jj + 1], o[4 * jj + 2], o[4 * jj + 3]);
+        fence_async_smem();
+        __syncwarp();
+        const int wrows = min(32, rows - warp * 32);
+        if ((tid & 31) == 0 && wrows > 0) {
+          bulk_store(part_dq + (off + t0 + warp * 32) * D, sP + warp * 32 * (D * 4), (uint32_t)wrows * D * 4);
+          bulk_commit();
         }
       }
       tc_fence_before_sync();
@@ -398,6 +452,7 @@ __global__ void __launch_bounds__(kTcM) bwd_main_tc_kernel(TcParams p) {
       __syncthreads();
     }
   }
+  bulk_wait_read();
   __syncthreads();
   // ---- dK (scaled) and dV of key `tid`
   if (alive) {

@@ -350,13 +350,14 @@ __global__ void __launch_bounds__(kGateTcThreads) gate_topk_tc_kernel(GateParams
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + buf * 128 + ((uint32_t)(warp * 32) << 16);
 #pragma unroll 1
-      for (int i = 0; i < 4; ++i) {
-        float v[32];
-        tmem_ld32(taddr + i * 32, v);
+      for (int i = 0; i < 2; ++i) {   // 64 scores per exposed TMEM latency
+        float v[64];
+        tmem_ld32(taddr + i * 64, v);
+        tmem_ld32(taddr + i * 64 + 32, v + 32);
         tmem_ld_wait();
-        const int nb = n0 + i * 32;
+        const int nb = n0 + i * 64;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < 64; ++j) {
           const int n = nb + j;
           const uint64_t cand = ((uint64_t)score_to_ordered(v[j]) << 32) | (uint32_t)n;
           if (n < nlim && v[j] > -CUDART_INF_F && cand > key[KMAX - 1]) {

@@ -169,6 +169,37 @@ __device__ __forceinline__ void gather_store(const uint4 (&u)[NCHUNK], unsigned 
     *reinterpret_cast<uint4*>(tile + sw128_offset(rb + (128 / NCHUNK) * i, j, block_stride)) = u[i];
 }
 
+// ---- bulk (TMA, non-tensor) shared -> global stores -----------------------------------
+// 16-byte aligned addresses, size a multiple of 16.  The issuing thread commits its copies
+// as a group and must wait for the group's READS before the shared-memory source is reused
+// (or the CTA exits).
+__device__ __forceinline__ void bulk_store(void* gdst, const void* ssrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(ssrc)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
+// rows x NCHUNK 16-byte chunks of a dense (row_stride) matrix into a swizzled tile, with all
+// of a thread's loads in flight at once.  nrows * NCHUNK must be a multiple of 128 * PER.
+template <typename T, int NCHUNK, int NROWS>
+__device__ __forceinline__ void stage_dense_sw128(unsigned char* tile, uint32_t block_stride, const T* base,
+                                                  int64_t row_stride, int rows_valid) {
+  constexpr int PER = NROWS * NCHUNK / 128;
+  const int j = threadIdx.x % NCHUNK, rb = threadIdx.x / NCHUNK;
+  uint4 u[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int r = rb + (128 / NCHUNK) * i;
+    u[i] = make_uint4(0, 0, 0, 0);
+    if (r < rows_valid) u[i] = ldg_nc_16(base + (int64_t)r * row_stride + j * 8);
+  }
+#pragma unroll
+  for (int i = 0; i < PER; ++i)
+    *reinterpret_cast<uint4*>(tile + sw128_offset(rb + (128 / NCHUNK) * i, j, block_stride)) = u[i];
+}
+
 
 template <typename T> struct FmtOf;
 template <> struct FmtOf<__nv_bfloat16> { static constexpr int v = 1; };
