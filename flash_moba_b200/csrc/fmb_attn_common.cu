@@ -194,8 +194,10 @@ __global__ void __launch_bounds__(256) fwd_combine_kernel(const T* __restrict__ 
                                                           const uint32_t* __restrict__ row_ptr,
                                                           const uint32_t* __restrict__ row_pos, T* out,
                                                           int64_t o_rs, int64_t o_hs, float* lse,
-                                                          int64_t total_q, int heads, int d) {
+                                                          int64_t total_q, int heads, int d,
+                                                          const int* only_if, int min_n) {
   using T2 = typename Elem<T>::T2;
+  if (only_if && *only_if == 0) return;   // the earlier stages met no row they had to leave
   const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (wid >= total_q * heads) return;
@@ -204,6 +206,7 @@ __global__ void __launch_bounds__(256) fwd_combine_kernel(const T* __restrict__ 
   const int64_t rid = (int64_t)h * total_q + t;
   const uint32_t p0 = row_ptr[rid];
   const int n = (int)(row_ptr[rid + 1] - p0);
+  if (n < min_n) return;
   const uint32_t* rp = row_pos + p0;
   // pass 1: maximum of the partial log-sum-exps
   float m = -CUDART_INF_F;
@@ -248,8 +251,9 @@ __global__ void __launch_bounds__(256) bwd_combine_kernel(const float* __restric
                                                           const uint32_t* __restrict__ row_ptr,
                                                           const uint32_t* __restrict__ row_pos, T* dq,
                                                           int64_t rs, int64_t hs, int64_t total_q, int heads,
-                                                          int d, float scale) {
+                                                          int d, float scale, const int* only_if, int min_n) {
   using T2 = typename Elem<T>::T2;
+  if (only_if && *only_if == 0) return;
   const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (wid >= total_q * heads) return;
@@ -258,6 +262,7 @@ __global__ void __launch_bounds__(256) bwd_combine_kernel(const float* __restric
   const int64_t rid = (int64_t)h * total_q + t;
   const uint32_t p0 = row_ptr[rid];
   const int n = (int)(row_ptr[rid + 1] - p0);
+  if (n < min_n) return;
   const uint32_t* rp = row_pos + p0;
   float2 acc[4];
 #pragma unroll
@@ -282,6 +287,185 @@ __global__ void __launch_bounds__(256) bwd_combine_kernel(const float* __restric
   for (int i = 0; i < 4; ++i) {
     const int c = lane * 2 + i * 64;
     if (c < d) *reinterpret_cast<T2*>(dst + c) = Elem<T>::from_f2(acc[i].x * scale, acc[i].y * scale);
+  }
+}
+
+// ------------------------------------------------------------------ fast combine (rows of <= G partials)
+// G lanes per (token, head) row, 32/G rows per warp.  Lane j of a group first fetches the
+// position and log-sum-exp of the row's j-th partial; the group ranks the positions (merge
+// order = ascending position, whatever order the atomics of the row-list build produced);
+// then every lane fetches its d/G elements of ALL the row's partial rows before the ordered
+// accumulation.  Several rows per warp and all loads of a row in flight at once hide the
+// chain of dependent, scattered reads.  Rows with more than G partials set *overflow and are
+// left to the next kernel (larger G, finally the generic one).
+template <int G>
+__device__ __forceinline__ unsigned group_mask(int lane) {
+  return G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (lane & ~(G - 1)));
+}
+
+template <typename T, int G, int EPL>
+__global__ void __launch_bounds__(256) fwd_combine_group_kernel(const T* __restrict__ part_o,
+                                                                const float* __restrict__ part_lse,
+                                                                const uint32_t* __restrict__ row_ptr,
+                                                                const uint32_t* __restrict__ row_pos, T* out,
+                                                                int64_t o_rs, int64_t o_hs, float* lse,
+                                                                int64_t total_q, int heads, int min_n,
+                                                                const int* only_if, int* overflow) {
+  constexpr int d = G * EPL;
+  constexpr int NV = EPL / 8;                 // 16-byte loads per partial row per lane
+  static_assert(EPL % 8 == 0, "a lane owns whole 16-byte chunks");
+  if (only_if && *only_if == 0) return;
+  const int lane = threadIdx.x & 31, gl = lane & (G - 1);
+  const int64_t gid = (((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * (32 / G) + (lane / G);
+  const bool row_ok = gid < total_q * heads;
+  const unsigned gm = group_mask<G>(lane);
+  const int64_t t = row_ok ? gid / heads : 0;
+  const int h = row_ok ? (int)(gid - t * heads) : 0;
+  const int64_t rid = (int64_t)h * total_q + t;
+  uint32_t p0 = 0;
+  int n = 0;
+  if (row_ok) {
+    p0 = row_ptr[rid];
+    n = (int)(row_ptr[rid + 1] - p0);
+  }
+  bool mine = row_ok && n >= min_n;           // rows below min_n were done by the previous kernel
+  if (n > G) {
+    if (gl == 0) *overflow = 1;
+    mine = false;
+  }
+  if (!mine) n = 0;
+  const bool valid = gl < n;
+  const uint32_t pos = valid ? row_pos[p0 + gl] : 0xffffffffu;
+  const float l = valid ? part_lse[pos] : -CUDART_INF_F;
+  float m = l;
+#pragma unroll
+  for (int o = G / 2; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(gm, m, o, G));
+  const float w = (valid && m > -CUDART_INF_F) ? __expf(l - m) : 0.f;
+  int rank = 0;
+#pragma unroll
+  for (int i = 0; i < G; ++i) rank += (__shfl_sync(gm, pos, i, G) < pos) ? 1 : 0;
+  float acc[EPL];
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) acc[i] = 0.f;
+  float ssum = 0.f;
+  constexpr int B = G < 8 ? G : 8;            // partial rows in flight per step
+#pragma unroll
+  for (int r0 = 0; r0 < G; r0 += B) {
+    uint4 x[B][NV];
+    float wk[B];
+#pragma unroll
+    for (int k = 0; k < B; ++k) {
+      // the lane of this group whose partial has rank r0+k (none if the row is shorter)
+      const unsigned hit = __ballot_sync(0xffffffffu, valid && rank == r0 + k) & gm;
+      const int src = hit ? (__ffs(hit) - 1) : lane;
+      const uint32_t pk = __shfl_sync(0xffffffffu, pos, src);
+      wk[k] = hit ? __shfl_sync(0xffffffffu, w, src) : 0.f;
+      if (hit && wk[k] > 0.f) {
+        const T* row = part_o + (int64_t)pk * d;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) x[k][v] = *reinterpret_cast<const uint4*>(row + part_col(pk, gl * EPL + 8 * v, 8));
+      } else {
+#pragma unroll
+        for (int v = 0; v < NV; ++v) x[k][v] = make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < B; ++k) {
+      ssum += wk[k];
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        float f[8];
+        unpack8<T>(x[k][v], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[8 * v + e] = fmaf(wk[k], f[e], acc[8 * v + e]);
+      }
+    }
+  }
+  if (mine) {
+    const float inv = ssum > 0.f ? 1.f / ssum : 0.f;
+    T* dst = out + t * o_rs + (int64_t)h * o_hs + gl * EPL;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[8 * v + e] *= inv;
+      *reinterpret_cast<uint4*>(dst + 8 * v) = pack8<T>(acc + 8 * v);
+    }
+    if (gl == 0) lse[rid] = ssum > 0.f ? m + logf(ssum) : CUDART_INF_F;
+  }
+}
+
+template <typename T, int G, int EPL>
+__global__ void __launch_bounds__(256) bwd_combine_group_kernel(const float* __restrict__ part_dq,
+                                                                const uint32_t* __restrict__ row_ptr,
+                                                                const uint32_t* __restrict__ row_pos, T* dq,
+                                                                int64_t rs, int64_t hs, int64_t total_q,
+                                                                int heads, float scale, int min_n,
+                                                                const int* only_if, int* overflow) {
+  constexpr int d = G * EPL;
+  constexpr int NV = EPL / 4;                 // 16-byte (4 float) loads per partial row per lane
+  static_assert(EPL % 8 == 0, "a lane owns whole 16-byte chunks of the output");
+  if (only_if && *only_if == 0) return;
+  const int lane = threadIdx.x & 31, gl = lane & (G - 1);
+  const int64_t gid = (((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * (32 / G) + (lane / G);
+  const bool row_ok = gid < total_q * heads;
+  const unsigned gm = group_mask<G>(lane);
+  const int64_t t = row_ok ? gid / heads : 0;
+  const int h = row_ok ? (int)(gid - t * heads) : 0;
+  const int64_t rid = (int64_t)h * total_q + t;
+  uint32_t p0 = 0;
+  int n = 0;
+  if (row_ok) {
+    p0 = row_ptr[rid];
+    n = (int)(row_ptr[rid + 1] - p0);
+  }
+  bool mine = row_ok && n >= min_n;
+  if (n > G) {
+    if (gl == 0) *overflow = 1;
+    mine = false;
+  }
+  if (!mine) n = 0;
+  const bool valid = gl < n;
+  const uint32_t pos = valid ? row_pos[p0 + gl] : 0xffffffffu;
+  int rank = 0;
+#pragma unroll
+  for (int i = 0; i < G; ++i) rank += (__shfl_sync(gm, pos, i, G) < pos) ? 1 : 0;
+  float acc[EPL];
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) acc[i] = 0.f;
+  constexpr int B = 4;
+#pragma unroll
+  for (int r0 = 0; r0 < G; r0 += B) {
+    float4 x[B][NV];
+#pragma unroll
+    for (int k = 0; k < B; ++k) {
+      const unsigned hit = __ballot_sync(0xffffffffu, valid && rank == r0 + k) & gm;
+      const int src = hit ? (__ffs(hit) - 1) : lane;
+      const uint32_t pk = __shfl_sync(0xffffffffu, pos, src);
+      if (hit) {
+        const float* row = part_dq + (int64_t)pk * d;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) x[k][v] = *reinterpret_cast<const float4*>(row + part_col(pk, gl * EPL + 4 * v, 4));
+      } else {
+#pragma unroll
+        for (int v = 0; v < NV; ++v) x[k][v] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < B; ++k) {
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        acc[4 * v] += x[k][v].x; acc[4 * v + 1] += x[k][v].y; acc[4 * v + 2] += x[k][v].z; acc[4 * v + 3] += x[k][v].w;
+      }
+    }
+  }
+  if (mine) {
+    T* dst = dq + t * rs + (int64_t)h * hs + gl * EPL;
+#pragma unroll
+    for (int v = 0; v < EPL / 8; ++v) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[8 * v + e] *= scale;
+      *reinterpret_cast<uint4*>(dst + 8 * v) = pack8<T>(acc + 8 * v);
+    }
   }
 }
 
@@ -311,34 +495,77 @@ __global__ void __launch_bounds__(256) dot_do_o_kernel(const T* __restrict__ dou
 
 static unsigned warp_grid(int64_t warps) { return (unsigned)ceil_div64(warps, 8); }
 
-int launch_fwd_combine(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+// Cascade: G = 8 (rows of <= 8 partials), 16, 32, then the generic kernel; each later stage
+// runs only the rows the earlier ones left and exits at once if there were none.
+static unsigned group_grid(int64_t rows, int G) { return (unsigned)ceil_div64(ceil_div64(rows, 32 / G), 8); }
+
+template <typename T, int D>
+static int fwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
   const int64_t rows = a.total_q * a.heads;
-  if (rows == 0) return FMB_OK;
-  if (a.dtype == FMB_BF16)
-    fwd_combine_kernel<__nv_bfloat16><<<warp_grid(rows), 256, 0, s>>>(
-        (const __nv_bfloat16*)w.part_o, w.part_lse, w.row_ptr, w.row_pos, (__nv_bfloat16*)a.o, a.o_rs, a.o_hs,
-        a.lse, a.total_q, a.heads, a.d);
-  else
-    fwd_combine_kernel<__half><<<warp_grid(rows), 256, 0, s>>>((const __half*)w.part_o, w.part_lse, w.row_ptr,
-                                                              w.row_pos, (__half*)a.o, a.o_rs, a.o_hs, a.lse,
-                                                              a.total_q, a.heads, a.d);
+  int* ovf = w.status + 1;   // words 1..3 of the status block, zeroed with it
+  const T* po = (const T*)w.part_o;
+  T* out = (T*)a.o;
+  fwd_combine_group_kernel<T, 8, D / 8><<<group_grid(rows, 8), 256, 0, s>>>(
+      po, w.part_lse, w.row_ptr, w.row_pos, out, a.o_rs, a.o_hs, a.lse, a.total_q, a.heads, 0, nullptr, ovf);
+  FMB_LAUNCH_CHECK("fwd_combine_group_kernel<8>");
+  fwd_combine_group_kernel<T, 16, D / 16><<<group_grid(rows, 16), 256, 0, s>>>(
+      po, w.part_lse, w.row_ptr, w.row_pos, out, a.o_rs, a.o_hs, a.lse, a.total_q, a.heads, 9, ovf, ovf + 1);
+  FMB_LAUNCH_CHECK("fwd_combine_group_kernel<16>");
+  fwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>(po, w.part_lse, w.row_ptr, w.row_pos, out, a.o_rs, a.o_hs,
+                                                        a.lse, a.total_q, a.heads, a.d, ovf + 1, 17);
   FMB_LAUNCH_CHECK("fwd_combine_kernel");
   return FMB_OK;
 }
 
-int launch_bwd_combine(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+template <typename T>
+static int fwd_combine_any(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+  if (a.d == 128) return fwd_combine_dispatch<T, 128>(a, w, s);
+  if (a.d == 256) return fwd_combine_dispatch<T, 256>(a, w, s);
   const int64_t rows = a.total_q * a.heads;
-  if (rows == 0) return FMB_OK;
-  if (a.dtype == FMB_BF16)
-    bwd_combine_kernel<__nv_bfloat16><<<warp_grid(rows), 256, 0, s>>>(
-        (const float*)w.part_o, w.row_ptr, w.row_pos, (__nv_bfloat16*)a.dq, a.dq_rs, a.dq_hs, a.total_q,
-        a.heads, a.d, a.scale);
-  else
-    bwd_combine_kernel<__half><<<warp_grid(rows), 256, 0, s>>>((const float*)w.part_o, w.row_ptr, w.row_pos,
-                                                              (__half*)a.dq, a.dq_rs, a.dq_hs, a.total_q,
-                                                              a.heads, a.d, a.scale);
+  fwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>((const T*)w.part_o, w.part_lse, w.row_ptr, w.row_pos,
+                                                        (T*)a.o, a.o_rs, a.o_hs, a.lse, a.total_q, a.heads, a.d,
+                                                        nullptr, 0);
+  FMB_LAUNCH_CHECK("fwd_combine_kernel");
+  return FMB_OK;
+}
+
+int launch_fwd_combine(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+  if (a.total_q * a.heads == 0) return FMB_OK;
+  return a.dtype == FMB_BF16 ? fwd_combine_any<__nv_bfloat16>(a, w, s) : fwd_combine_any<__half>(a, w, s);
+}
+
+template <typename T, int D>
+static int bwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+  const int64_t rows = a.total_q * a.heads;
+  int* ovf = w.status + 1;
+  const float* pd = (const float*)w.part_o;
+  T* dq = (T*)a.dq;
+  bwd_combine_group_kernel<T, 8, D / 8><<<group_grid(rows, 8), 256, 0, s>>>(
+      pd, w.row_ptr, w.row_pos, dq, a.dq_rs, a.dq_hs, a.total_q, a.heads, a.scale, 0, nullptr, ovf);
+  FMB_LAUNCH_CHECK("bwd_combine_group_kernel<8>");
+  bwd_combine_group_kernel<T, 16, D / 16><<<group_grid(rows, 16), 256, 0, s>>>(
+      pd, w.row_ptr, w.row_pos, dq, a.dq_rs, a.dq_hs, a.total_q, a.heads, a.scale, 9, ovf, ovf + 1);
+  FMB_LAUNCH_CHECK("bwd_combine_group_kernel<16>");
+  bwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>(pd, w.row_ptr, w.row_pos, dq, a.dq_rs, a.dq_hs, a.total_q,
+                                                        a.heads, a.d, a.scale, ovf + 1, 17);
   FMB_LAUNCH_CHECK("bwd_combine_kernel");
   return FMB_OK;
+}
+
+template <typename T>
+static int bwd_combine_any(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+  if (a.d == 128) return bwd_combine_dispatch<T, 128>(a, w, s);
+  if (a.d == 256) return bwd_combine_dispatch<T, 256>(a, w, s);
+  const int64_t rows = a.total_q * a.heads;
+  bwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>((const float*)w.part_o, w.row_ptr, w.row_pos, (T*)a.dq,
+                                                        a.dq_rs, a.dq_hs, a.total_q, a.heads, a.d, a.scale, nullptr, 0);
+  FMB_LAUNCH_CHECK("bwd_combine_kernel");
+  return FMB_OK;
+}
+
+int launch_bwd_combine(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+  if (a.total_q * a.heads == 0) return FMB_OK;
+  return a.dtype == FMB_BF16 ? bwd_combine_any<__nv_bfloat16>(a, w, s) : bwd_combine_any<__half>(a, w, s);
 }
 
 int launch_dot_do_o(const AttnArgs& a, cudaStream_t s) {

@@ -349,25 +349,31 @@ __global__ void __launch_bounds__(kGateTcThreads) gate_topk_tc_kernel(GateParams
       if (!__syncthreads_and(ok)) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + buf * 128 + ((uint32_t)(warp * 32) << 16);
+      // 16 scores per step keeps the unrolled insertion network small enough for the
+      // instruction cache; the next 16 are fetched while these are examined
+      float v[2][16];
+      tmem_ld16(taddr, v[0]);
 #pragma unroll 1
-      for (int i = 0; i < 2; ++i) {   // 64 scores per exposed TMEM latency
-        float v[64];
-        tmem_ld32(taddr + i * 64, v);
-        tmem_ld32(taddr + i * 64 + 32, v + 32);
-        tmem_ld_wait();
-        const int nb = n0 + i * 64;
+      for (int i = 0; i < 8; i += 2) {
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          const int n = nb + j;
-          const uint64_t cand = ((uint64_t)score_to_ordered(v[j]) << 32) | (uint32_t)n;
-          if (n < nlim && v[j] > -CUDART_INF_F && cand > key[KMAX - 1]) {
-            key[KMAX - 1] = cand;
+        for (int half = 0; half < 2; ++half) {
+          tmem_ld_wait();
+          if (i + half + 1 < 8) tmem_ld16(taddr + (i + half + 1) * 16, v[half ^ 1]);
+          const int nb = n0 + (i + half) * 16;
 #pragma unroll
-            for (int x = KMAX - 1; x > 0; --x) {
-              const uint64_t lo = key[x], hi = key[x - 1];
-              const bool sw = lo > hi;
-              key[x] = sw ? hi : lo;
-              key[x - 1] = sw ? lo : hi;
+          for (int j = 0; j < 16; ++j) {
+            const int n = nb + j;
+            const float x = v[half][j];
+            const uint64_t cand = ((uint64_t)score_to_ordered(x) << 32) | (uint32_t)n;
+            if (n < nlim && x > -CUDART_INF_F && cand > key[KMAX - 1]) {
+              key[KMAX - 1] = cand;
+#pragma unroll
+              for (int y = KMAX - 1; y > 0; --y) {
+                const uint64_t lo = key[y], hi = key[y - 1];
+                const bool sw = lo > hi;
+                key[y] = sw ? hi : lo;
+                key[y - 1] = sw ? lo : hi;
+              }
             }
           }
         }

@@ -297,6 +297,23 @@ def test_attention_random_patterns(lens_q, lens_k, d, chunk, causal, mha, engine
 
 
 @pytest.mark.parametrize("engine", [0, 1])
+def test_attention_rows_with_more_than_32_partials(engine):
+    """A dense pattern (every row attends every one of 40 chunks) takes the generic merge path
+    next to the fast one (rows with <= 32 partials)."""
+    torch.manual_seed(0)
+    lens_q, lens_k, H, Hk, d, chunk = [70, 33], [2560, 1000], 2, 1, 64, 64
+    q = torch.randn(sum(lens_q), H, d).bfloat16()
+    k = torch.randn(sum(lens_k), Hk, d).bfloat16()
+    v = torch.randn(sum(lens_k), Hk, d).bfloat16()
+    do = torch.randn(sum(lens_q), H, d).bfloat16()
+    ncol = (max(lens_k) + chunk - 1) // chunk
+    mask = torch.zeros(2, H, max(lens_q), ncol, dtype=torch.bool)
+    mask[0, :, :70, :40] = True
+    mask[1, :, :33, :16] = True
+    _attn_check(q, k, v, do, cu_of(lens_q), cu_of(lens_k), mask, chunk, False, engine)
+
+
+@pytest.mark.parametrize("engine", [0, 1])
 def test_attention_fp16(engine):
     torch.manual_seed(0)
     lens = [200, 130]
