@@ -98,7 +98,8 @@ int fmb_profile_read(int kind, float* ms, int max_entries) {
 int fmb_attn_engine(int chunk, int head_dim, int backward) {
   AttnArgs a;
   memset(&a, 0, sizeof(a));
-  a.chunk = chunk; a.d = head_dim;
+  a.chunk = chunk; a.d = head_dim; a.heads = 1;
+  a.q_rs = a.do_rs = head_dim; a.q_hs = a.do_hs = head_dim;   // a packed layout
   return (g_engine == 1 && tc_supported(a, backward != 0)) ? 1 : 0;
 }
 
@@ -107,6 +108,13 @@ int fmb_selftest_umma(const void* a, const void* b, float* d, int b_mn_major, in
   FMB_CHECK_ARG(a && b && d && status, "selftest_umma: null pointer");
   FMB_CHECK_ARG(dtype == FMB_BF16 || dtype == FMB_FP16, "selftest_umma: only fp16 and bf16");
   return launch_selftest_umma(a, b, d, b_mn_major, dtype, status, (cudaStream_t)stream);
+}
+
+int fmb_selftest_gather(const void* a, int a_rows, const int* idx, const void* b, float* d, int dtype,
+                        int* status, fmb_stream_t stream) {
+  FMB_CHECK_ARG(a && idx && b && d && status && a_rows > 0, "selftest_gather: bad arguments");
+  FMB_CHECK_ARG(dtype == FMB_BF16 || dtype == FMB_FP16, "selftest_gather: only fp16 and bf16");
+  return launch_selftest_gather(a, a_rows, idx, b, d, dtype, status, (cudaStream_t)stream);
 }
 
 int fmb_set_engine(int engine) {

@@ -17,7 +17,7 @@ AttnWorkspace carve_attn_workspace(void* base, int64_t total_q, int heads, int d
     return p;
   };
   const int64_t rows = total_q * heads;
-  w.status = static_cast<int*>(take(256));
+  w.status = static_cast<int*>(take(512));
   w.part_o = take((size_t)n_indices * d * part_elem_bytes);
   w.part_lse = static_cast<float*>(take(with_lse ? (size_t)n_indices * sizeof(float) : 0));
   w.row_ptr = static_cast<uint32_t*>(take((size_t)(rows + 1) * sizeof(uint32_t)));
@@ -145,7 +145,7 @@ __global__ void __launch_bounds__(1024) scan_add_kernel(uint32_t* data, int64_t 
 
 int build_row_lists(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
   const int64_t rows = a.total_q * a.heads;
-  FMB_CUDA(cudaMemsetAsync(w.status, 0, 256, s));
+  FMB_CUDA(cudaMemsetAsync(w.status, 0, 512, s));
   FMB_CUDA(cudaMemsetAsync(w.row_ptr, 0, (size_t)(rows + 1) * sizeof(uint32_t), s));
   FMB_CUDA(cudaMemsetAsync(w.row_fill, 0, (size_t)rows * sizeof(uint32_t), s));
   if (a.ncol == 0 || a.batch == 0) return FMB_OK;

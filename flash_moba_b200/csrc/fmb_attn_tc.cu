@@ -11,7 +11,7 @@
 // Every mbarrier wait is bounded; a wait that expires records where in the status word of the
 // workspace and the CTA leaves through the normal exit (TMEM released).
 #include "fmb_attn.cuh"
-#include "fmb_tc.cuh"
+#include "fmb_tma.cuh"
 
 namespace fmb {
 
@@ -32,9 +32,19 @@ constexpr int kTcM = 128;   // gathered rows per tile = TMEM lanes
       t_prev_ = t_now_;                                                                         \
     }                                                                                           \
   } while (0)
+#define FMB_TICK_AT(slot, who)                                                                  \
+  do {                                                                                          \
+    if (threadIdx.x == (who)) {                                                                 \
+      const long long t_now_ = clock64();                                                       \
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (slot),                   \
+                (unsigned long long)(t_now_ - t_prev_));                                        \
+      t_prev_ = t_now_;                                                                         \
+    }                                                                                           \
+  } while (0)
 #else
 #define FMB_T0() do {} while (0)
 #define FMB_TICK(slot) do {} while (0)
+#define FMB_TICK_AT(slot, who) do {} while (0)
 #endif
 constexpr float kLog2eTc = 1.4426950408889634f;
 
@@ -240,21 +250,42 @@ __global__ void __launch_bounds__(kTcM) fwd_main_tc_kernel(TcParams p) {
 
 
 // ======================================================================== backward
-// CTA = key chunk c of (sequence b, kv head hk); it loops over the q heads of the kv head's
-// group and over 128-row tiles of each head's CSC column.  Per tile, five GEMMs:
+// CTA = key chunk c of (sequence b, kv head hk); 288 threads:
+//   warps 0-7  compute.  TMEM lane = gathered query row (at the end: key); warps w and w+4 share
+//              a lane quarter and split the columns in halves.  Thread 0 issues the MMAs.
+//   warps 8-11 loaders.  For every tile they read the tile's row ids, LSE and D, and gather the
+//              Q and dO rows with 16-byte cp.async copies straight into the swizzled UMMA tiles
+//              (no registers; measured ~4x the throughput of loads into registers, and ~3.5x that
+//              of TMA tile::gather4 row gathers for these isolated 256-byte rows).  They run one
+//              tile ahead: the next tile's rows are requested as soon as the GEMMs that read Q and
+//              dO have completed, and land under the dQ GEMM and epilogue.
+// The CTA walks the q heads of the kv head's group and the 128-row tiles of each head's CSC
+// column as one sequence of tiles.  Per tile, five GEMMs:
 //     S  = Q.K^T          dP = dO.V^T                       (both K-major operands)
 //     dV += P^T.dO        dK += dS^T.Q   (A and B consumed MN-major from the row-major tiles)
 //     dQ_partial = dS.K   (K consumed MN-major)             -> workspace at the pair's position
 // dK and dV stay in TMEM (fp32) for the CTA's whole life: no atomics, no cross-head reduction
 // pass.  TMEM columns: [0,C) S then dQ, [C,2C) dP, [2C,2C+D) dV, [2C+D,2C+2D) dK.
+constexpr int kBwdCompute = 256;
+constexpr int kBwdLoaders = 128;
+constexpr int kBwdThreads = kBwdCompute + kBwdLoaders;
+
+struct BwdTile {
+  int hg;        // head within the group
+  int t0;        // first entry of the tile inside the head's column
+  int nnz;       // entries of the head's column
+  int64_t off;   // position of the column's first entry
+};
+
 template <typename T, int C, int D>
-__global__ void __launch_bounds__(kTcM) bwd_main_tc_kernel(TcParams p) {
+__global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   static_assert(C == 128, "tensor-core backward keeps one key per TMEM lane");
   constexpr uint32_t kKBlock = C * 128;
   constexpr uint32_t kQBlock = kTcM * 128;
   constexpr int NCOLS = 512;
+  constexpr int DH = D / 2;                       // head-dim columns per thread in the epilogues
   extern __shared__ unsigned char smem_raw[];
-  __shared__ uint64_t bar;
+  __shared__ uint64_t bar, bar_c, bar_full;
   __shared__ uint32_t tmem_base_s;
   __shared__ int sRow[2][kTcM];
   __shared__ float sLse[2][kTcM], sDs[2][kTcM];
@@ -264,7 +295,7 @@ __global__ void __launch_bounds__(kTcM) bwd_main_tc_kernel(TcParams p) {
   unsigned char* sV = sK + C * D * 2;             // [C][D]
   unsigned char* sQ = sV + C * D * 2;             // [128][D]
   unsigned char* sdO = sQ + kTcM * D * 2;         // [128][D]
-  unsigned char* sP = sdO + kTcM * D * 2;         // [128][C]
+  unsigned char* sP = sdO + kTcM * D * 2;         // [128][C]   (fp32 dQ staging spans sP|sdS)
   unsigned char* sdS = sP + kTcM * C * 2;         // [128][C]
 
   const int c = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
@@ -276,121 +307,172 @@ __global__ void __launch_bounds__(kTcM) bwd_main_tc_kernel(TcParams p) {
   const int group = p.heads / p.heads_k;
   const int shift = len_k - len_q;
   const float scale_log2 = p.scale * kLog2eTc;
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool loader = warp >= 8;
+  const int lt = tid & (kTcM - 1);                // row (TMEM lane) of a compute thread
+  const int hf = (tid >> 7) & 1;                  // column half of a compute thread
 
+  // ---- the CTA's tile sequence
+  auto seek_head = [&](BwdTile& it) {             // first head >= it.hg with a non-empty column
+    for (; it.hg < group; ++it.hg) {
+      if (c >= p.ncol) break;
+      const int h = hk * group + it.hg;
+      const int64_t ci = ((int64_t)b * p.heads + h) * p.ncol + c;
+      const int nnz = p.col_nnz[ci];
+      const int64_t off = p.col_offsets[ci];
+      if (nnz > 0 && off >= 0 && off + nnz <= p.n_indices) {
+        it.nnz = nnz; it.off = off; it.t0 = 0;
+        return true;
+      }
+    }
+    it.hg = group;
+    return false;
+  };
+  auto next_tile = [&](BwdTile& it) {
+    it.t0 += kTcM;
+    if (it.t0 < it.nnz) return true;
+    ++it.hg;
+    return seek_head(it);
+  };
+
+  FMB_T0();
   if (warp == 0) tmem_alloc(&tmem_base_s, NCOLS);
   if (tid == 0) {
     mbar_init(&bar, 1);
+    mbar_init(&bar_c, 1);
+    mbar_init(&bar_full, kBwdLoaders);
     mbar_fence_init();
   }
-  const T* kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + key0) * p.k_rs + (int64_t)hk * p.k_hs;
-  const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
-  stage_dense_sw128<T, D / 8, C>(sK, kKBlock, kbase, p.k_rs, keys_valid);
-  stage_dense_sw128<T, D / 8, C>(sV, kKBlock, vbase, p.v_rs, keys_valid);
-  fence_async_smem();
+  if (!loader) {
+    const T* kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + key0) * p.k_rs + (int64_t)hk * p.k_hs;
+    const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
+    if (hf == 0) stage_dense_sw128_t<T, D / 8, C>(lt, sK, kKBlock, kbase, p.k_rs, keys_valid);
+    else stage_dense_sw128_t<T, D / 8, C>(lt, sV, kKBlock, vbase, p.v_rs, keys_valid);
+    fence_async_smem();
+  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  FMB_TICK(16);   // prologue
   const uint32_t tmem_base = tmem_base_s;
-  const uint32_t tS = tmem_base, tdP = tmem_base + C, tdV = tmem_base + 2 * C, tdK = tmem_base + 2 * C + D;
-  const uint32_t tdQ = tS;
-  const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
-  const uint32_t sK_a = smem_u32(sK), sV_a = smem_u32(sV), sQ_a = smem_u32(sQ), sdO_a = smem_u32(sdO),
-                 sP_a = smem_u32(sP), sdS_a = smem_u32(sdS);
-  constexpr uint32_t idesc_s = make_idesc(FmtOf<T>::v, kTcM, C, 0, 0);     // rows x keys
-  constexpr uint32_t idesc_kv = make_idesc(FmtOf<T>::v, C, D, 1, 1);       // keys x d, both MN-major
-  constexpr uint32_t idesc_dq = make_idesc(FmtOf<T>::v, kTcM, D, 0, 1);    // rows x d
-  float* part_dq = static_cast<float*>(p.part_o);
-  uint32_t phase = 0;
-  bool any_tile = false, alive = true;
 
-  for (int hg = 0; hg < group && alive; ++hg) {
-    const int h = hk * group + hg;
-    if (c >= p.ncol) break;
-    const int64_t ci = ((int64_t)b * p.heads + h) * p.ncol + c;
-    const int nnz = p.col_nnz[ci];
-    const int64_t off = p.col_offsets[ci];
-    if (nnz <= 0 || off < 0 || off + nnz > p.n_indices) continue;
-    const T* qbase = static_cast<const T*>(p.q) + (int64_t)q0 * p.q_rs + (int64_t)h * p.q_hs;
-    const T* dobase = static_cast<const T*>(p.dout) + (int64_t)q0 * p.do_rs + (int64_t)h * p.do_hs;
-    const float* lse = p.lse + (int64_t)h * p.total_q + q0;
-    const float* dsum = p.softmax_d + (int64_t)h * p.total_q + q0;
+  BwdTile it{0, 0, 0, 0};
+  bool have = seek_head(it);
 
-    auto load_rows = [&](int t0, int buf) {
-      int r = -1;
-      float l2 = CUDART_INF_F, dd = 0.f;
-      if (t0 + tid < nnz) {
-        r = p.indices[off + t0 + tid];
-        if (r < 0 || r >= len_q) r = -1;
-        else { l2 = lse[r] * kLog2eTc; dd = dsum[r]; }
+  if (loader) {
+    // =============================================================== loader warps
+    uint32_t phase_c = 0;
+    for (int i = 0; have; ++i) {
+      const int buf = i & 1;
+      FMB_TICK_AT(26, 256);   // loader: tile bookkeeping
+      // row data of the tile (independent of the operand buffers)
+      const int h = hk * group + it.hg;
+      {
+        int r = -1;
+        if (it.t0 + lt < it.nnz) {
+          r = p.indices[it.off + it.t0 + lt];
+          if (r < 0 || r >= len_q) r = -1;
+        }
+        float l2 = CUDART_INF_F, dd = 0.f;
+        if (r >= 0) {
+          l2 = p.lse[(int64_t)h * p.total_q + q0 + r] * kLog2eTc;
+          dd = p.softmax_d[(int64_t)h * p.total_q + q0 + r];
+        }
+        sRow[buf][lt] = r; sLse[buf][lt] = l2; sDs[buf][lt] = dd;
       }
-      sRow[buf][tid] = r; sLse[buf][tid] = l2; sDs[buf][tid] = dd;
-    };
-    uint4 pre[D / 8];   // half of the next tile's operands in flight at a time
-    __syncthreads();    // the previous head's last tile has been consumed
-    load_rows(0, 0);
-    __syncthreads();
-    gather_load<T, D / 8>(pre, qbase, p.q_rs, sRow[0]);
-    gather_store<D / 8>(pre, sQ, kQBlock);
-    gather_load<T, D / 8>(pre, dobase, p.do_rs, sRow[0]);
-    gather_store<D / 8>(pre, sdO, kQBlock);
-    fence_async_smem();
-    __syncthreads();
+      FMB_TICK_AT(28, 256);   // loader: row ids, LSE, D
+      bool ok = true;
+      if (i > 0) {   // the GEMMs that read Q / dO of the previous tile must have completed
+        ok = mbar_wait(&bar_c, phase_c, p.status, 5);
+        phase_c ^= 1;
+      }
+      ok = bar_and(1, kBwdLoaders, ok);   // also makes every loader's row ids visible to the others
+      FMB_TICK_AT(27, 256);   // loader: waiting for the buffers
+      if (!ok) break;
+      const T* qbase = static_cast<const T*>(p.q) + (int64_t)q0 * p.q_rs + (int64_t)h * p.q_hs;
+      const T* dobase = static_cast<const T*>(p.dout) + (int64_t)q0 * p.do_rs + (int64_t)h * p.do_hs;
+      gather_cp_async<T, D / 8>(lt, sQ, kQBlock, qbase, p.q_rs, sRow[buf]);
+      gather_cp_async<T, D / 8>(lt, sdO, kQBlock, dobase, p.do_rs, sRow[buf]);
+      cp_async_wait_all();
+      fence_async_smem();        // the copies are generic-proxy writes; the MMAs read through the async proxy
+      mbar_arrive(&bar_full);
+      FMB_TICK_AT(29, 256);   // loader: gather
+      have = next_tile(it);
+    }
+  } else {
+    // =============================================================== compute warps
+    const uint32_t tS = tmem_base, tdP = tmem_base + C, tdV = tmem_base + 2 * C, tdK = tmem_base + 2 * C + D;
+    const uint32_t tdQ = tS;
+    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t sK_a = smem_u32(sK), sV_a = smem_u32(sV), sQ_a = smem_u32(sQ), sdO_a = smem_u32(sdO),
+                   sP_a = smem_u32(sP), sdS_a = smem_u32(sdS);
+    constexpr uint32_t idesc_s = make_idesc(FmtOf<T>::v, kTcM, C, 0, 0);     // rows x keys
+    constexpr uint32_t idesc_kv = make_idesc(FmtOf<T>::v, C, D, 1, 1);       // keys x d, both MN-major
+    constexpr uint32_t idesc_dq = make_idesc(FmtOf<T>::v, kTcM, D, 0, 1);    // rows x d
+    float* part_dq = static_cast<float*>(p.part_o);
+    uint32_t phase = 0, phase_full = 0;
+    bool any_tile = false, good = true;
 
-    int buf = 0;
-    for (int t0 = 0; t0 < nnz; t0 += kTcM, buf ^= 1) {
-      const int rows = min(kTcM, nnz - t0);
-      const bool more = t0 + kTcM < nnz;
+    for (int i = 0; have && good; ++i) {
+      const int buf = i & 1;
+      const int rows = min(kTcM, it.nnz - it.t0);
       if (tid == 0) {
-        tc_fence_after_sync();
+        // the tile's Q / dO rows (and its row data) have landed
+        if (mbar_wait(&bar_full, phase_full, p.status, 6)) {
+          FMB_TICK(17);   // waiting for the tile's operands
+          tc_fence_after_sync();
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t ko = (ks >> 2) * kQBlock + (ks & 3) * 32, kb = (ks >> 2) * kKBlock + (ks & 3) * 32;
-          umma_ss(tS, make_desc_sw128(sQ_a + ko, 16, 1024), make_desc_sw128(sK_a + kb, 16, 1024), idesc_s, ks > 0);
-        }
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t ko = (ks >> 2) * kQBlock + (ks & 3) * 32, kb = (ks >> 2) * kKBlock + (ks & 3) * 32;
+            umma_ss(tS, make_desc_sw128(sQ_a + ko, 16, 1024), make_desc_sw128(sK_a + kb, 16, 1024), idesc_s, ks > 0);
+          }
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t ko = (ks >> 2) * kQBlock + (ks & 3) * 32, kb = (ks >> 2) * kKBlock + (ks & 3) * 32;
-          umma_ss(tdP, make_desc_sw128(sdO_a + ko, 16, 1024), make_desc_sw128(sV_a + kb, 16, 1024), idesc_s, ks > 0);
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t ko = (ks >> 2) * kQBlock + (ks & 3) * 32, kb = (ks >> 2) * kKBlock + (ks & 3) * 32;
+            umma_ss(tdP, make_desc_sw128(sdO_a + ko, 16, 1024), make_desc_sw128(sV_a + kb, 16, 1024), idesc_s, ks > 0);
+          }
+          umma_commit(&bar);
         }
-        umma_commit(&bar);
       }
-      if (more) load_rows(t0 + kTcM, buf ^ 1);   // published by the barrier after P/dS
-      bool ok = mbar_wait(&bar, phase, p.status, 3);
+      phase_full ^= 1;
+      if (warp < 4 && lane == 0) bulk_wait_read();   // the previous tile's dQ staging has been read out
+      good = bar_and(2, kBwdCompute, mbar_wait(&bar, phase, p.status, 3));
       phase ^= 1;
-      if (!__syncthreads_and(ok)) { alive = false; break; }
       tc_fence_after_sync();
+      FMB_TICK(18);   // operands landed + S, dP GEMMs
+      if (!good) break;
 
-      // ---- P and dS of row `tid`, 32 keys at a time (the previous tile's dQ staging, which
-      // shares this memory, must have been read out first)
-      bulk_wait_read();
-      __syncthreads();
-      const int r = sRow[buf][tid];
-      const float lse2 = sLse[buf][tid], dd = sDs[buf][tid];
-      const int lim = r < 0 ? 0 : (p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid);
+      // ---- P and dS of row `lt`, this thread's 64 keys.  The previous tile's dQ staging shares
+      // the P/dS memory; its bulk copies were waited for before the barrier above.
+      {
+        const int r = sRow[buf][lt];
+        const float lse2 = sLse[buf][lt], dd = sDs[buf][lt];
+        const int lim = r < 0 ? 0 : (p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid);
 #pragma unroll
-      for (int i = 0; i < C / 64; ++i) {   // 64 keys per exposed TMEM latency
-        float s[64], dp[64];
-        tmem_ld32(tS + lane_sel + i * 64, s);
-        tmem_ld32(tS + lane_sel + i * 64 + 32, s + 32);
-        tmem_ld32(tdP + lane_sel + i * 64, dp);
-        tmem_ld32(tdP + lane_sel + i * 64 + 32, dp + 32);
-        tmem_ld_wait();
+        for (int i2 = 0; i2 < 2; ++i2) {
+          const int col0 = hf * 64 + i2 * 32;
+          float s[32], dp[32];
+          tmem_ld32(tS + lane_sel + col0, s);
+          tmem_ld32(tdP + lane_sel + col0, dp);
+          tmem_ld_wait();
 #pragma unroll
-        for (int jj = 0; jj < 64; ++jj) {
-          const float pr = (i * 64 + jj < lim) ? exp2f(s[jj] * scale_log2 - lse2) : 0.f;
-          s[jj] = pr;
-          dp[jj] = pr * (dp[jj] - dd);
+          for (int jj = 0; jj < 32; ++jj) {
+            const float pr = (col0 + jj < lim) ? exp2f(s[jj] * scale_log2 - lse2) : 0.f;
+            s[jj] = pr;
+            dp[jj] = pr * (dp[jj] - dd);
+          }
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            *reinterpret_cast<uint4*>(sP + sw128_offset(lt, col0 / 8 + jj, kQBlock)) = pack8<T>(s + jj * 8);
+            *reinterpret_cast<uint4*>(sdS + sw128_offset(lt, col0 / 8 + jj, kQBlock)) = pack8<T>(dp + jj * 8);
+          }
         }
-#pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-          *reinterpret_cast<uint4*>(sP + sw128_offset(tid, i * 8 + jj, kQBlock)) = pack8<T>(s + jj * 8);
-          *reinterpret_cast<uint4*>(sdS + sw128_offset(tid, i * 8 + jj, kQBlock)) = pack8<T>(dp + jj * 8);
-        }
+        tc_fence_before_sync();
+        fence_async_smem();
       }
-      tc_fence_before_sync();
-      fence_async_smem();
-      __syncthreads();
+      FMB_TICK(20);   // P, dS
+      bar_sync(2, kBwdCompute);
+      FMB_TICK(21);
       if (tid == 0) {
         tc_fence_after_sync();
         const uint32_t acc = any_tile ? 1u : 0u;
@@ -405,6 +487,7 @@ __global__ void __launch_bounds__(kTcM) bwd_main_tc_kernel(TcParams p) {
           umma_ss(tdK, make_desc_sw128(sdS_a + ks * 2048, kQBlock, 1024),
                   make_desc_sw128(sQ_a + ks * 2048, kQBlock, 1024), idesc_kv, acc | (ks > 0));
         }
+        umma_commit(&bar_c);   // Q and dO are free once these complete: the loader's signal
         // dQ partial = dS.K : M = rows, N = d, K = keys
 #pragma unroll
         for (int ks = 0; ks < C / 16; ++ks) {
@@ -414,77 +497,75 @@ __global__ void __launch_bounds__(kTcM) bwd_main_tc_kernel(TcParams p) {
         umma_commit(&bar);
       }
       any_tile = true;
-      if (more) gather_load<T, D / 8>(pre, qbase, p.q_rs, sRow[buf ^ 1]);   // flies under the three GEMMs
-      ok = mbar_wait(&bar, phase, p.status, 4);
+      good = bar_and(2, kBwdCompute, mbar_wait(&bar, phase, p.status, 4));
       phase ^= 1;
-      if (!__syncthreads_and(ok)) { alive = false; break; }
       tc_fence_after_sync();
-      if (more) {   // Q and dO of this tile are consumed: refill, dO loads fly under the dQ epilogue
-        gather_store<D / 8>(pre, sQ, kQBlock);
-        gather_load<T, D / 8>(pre, dobase, p.do_rs, sRow[buf ^ 1]);
-      }
-      // dQ partial of row `tid`: staged (fp32) over the P/dS tiles, which the three GEMMs have
-      // finished reading, and written with one bulk copy per row
+      FMB_TICK(22);   // dV, dK, dQ GEMMs
+      if (!good) break;
+
+      // dQ partial of row `lt`, this thread's half of the head dim: staged (fp32) over the P/dS
+      // tiles, which the GEMMs have finished reading; one bulk copy per 32 rows
       {
-        const int64_t pos = off + t0 + tid;
+        const int64_t pos = it.off + it.t0 + lt;
         const int key = (int)(pos & 7);
-        unsigned char* srow = sP + tid * (D * 4);
-        float o[D];
+        unsigned char* srow = sP + lt * (D * 4);
+        float o[DH];
 #pragma unroll
-        for (int i = 0; i < D / 32; ++i) tmem_ld32(tdQ + lane_sel + i * 32, o + i * 32);
+        for (int i2 = 0; i2 < DH / 32; ++i2) tmem_ld32(tdQ + lane_sel + hf * DH + i2 * 32, o + i2 * 32);
         tmem_ld_wait();
 #pragma unroll
-        for (int jj = 0; jj < D / 4; ++jj)
-          *reinterpret_cast<float4*>(srow + ((jj ^ key) << 4)) = make_float4(o[4 * jj], o[4 * jj + 1], o[4 * jj + 2], o[4 * jj + 3]);
+        for (int jj = 0; jj < DH / 4; ++jj)
+          *reinterpret_cast<float4*>(srow + (((hf * (DH / 4) + jj) ^ key) << 4)) =
+              make_float4(o[4 * jj], o[4 * jj + 1], o[4 * jj + 2], o[4 * jj + 3]);
+        tc_fence_before_sync();
         fence_async_smem();
-        __syncwarp();
+      }
+      bar_sync(2, kBwdCompute);   // both halves of every row staged; all reads of dQ done
+      if (warp < 4) {
         const int wrows = min(32, rows - warp * 32);
-        if ((tid & 31) == 0 && wrows > 0) {
-          bulk_store(part_dq + (off + t0 + warp * 32) * D, sP + warp * 32 * (D * 4), (uint32_t)wrows * D * 4);
-          bulk_commit();
+        if (lane == 0 && wrows > 0) {
+          bulk_store(part_dq + (it.off + it.t0 + warp * 32) * D, sP + warp * 32 * (D * 4), (uint32_t)wrows * D * 4);
+          bulk_commit();      // its reads are waited for under the next tile's first GEMMs
+        }
+      }
+      FMB_TICK(23);   // dQ epilogue
+      have = next_tile(it);
+    }
+
+    if (warp < 4 && lane == 0) bulk_wait_read();
+    bar_sync(2, kBwdCompute);
+    // ---- dK (scaled) and dV of key `lt`, this thread's half of the head dim
+    if (good) {
+      tc_fence_after_sync();
+      T* dkp = static_cast<T*>(p.dk) + (int64_t)(k0 + key0 + lt) * p.dk_rs + (int64_t)hk * p.dk_hs + hf * DH;
+      T* dvp = static_cast<T*>(p.dv) + (int64_t)(k0 + key0 + lt) * p.dv_rs + (int64_t)hk * p.dv_hs + hf * DH;
+#pragma unroll
+      for (int i2 = 0; i2 < DH / 32; ++i2) {
+        float o[32];
+        if (any_tile) {
+          tmem_ld32(tdK + lane_sel + hf * DH + i2 * 32, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = 0.f;
+        }
+        if (lt < keys_valid) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] *= p.scale;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(dkp + i2 * 32 + j * 8) = pack8<T>(o + j * 8);
+        }
+        if (any_tile) {
+          tmem_ld32(tdV + lane_sel + hf * DH + i2 * 32, o);
+          tmem_ld_wait();
+        }
+        if (lt < keys_valid) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(dvp + i2 * 32 + j * 8) = pack8<T>(o + j * 8);
         }
       }
       tc_fence_before_sync();
-      if (more) {
-        gather_store<D / 8>(pre, sdO, kQBlock);
-        fence_async_smem();
-      }
-      __syncthreads();
     }
-  }
-  bulk_wait_read();
-  __syncthreads();
-  // ---- dK (scaled) and dV of key `tid`
-  if (alive) {
-    tc_fence_after_sync();
-    T* dkp = static_cast<T*>(p.dk) + (int64_t)(k0 + key0 + tid) * p.dk_rs + (int64_t)hk * p.dk_hs;
-    T* dvp = static_cast<T*>(p.dv) + (int64_t)(k0 + key0 + tid) * p.dv_rs + (int64_t)hk * p.dv_hs;
-#pragma unroll
-    for (int i = 0; i < D / 32; ++i) {
-      float o[32];
-      if (any_tile) {
-        tmem_ld32(tdK + lane_sel + i * 32, o);
-        tmem_ld_wait();
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) o[j] = 0.f;
-      }
-      if (tid < keys_valid) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) o[j] *= p.scale;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(dkp + i * 32 + j * 8) = pack8<T>(o + j * 8);
-      }
-      if (any_tile) {
-        tmem_ld32(tdV + lane_sel + i * 32, o);
-        tmem_ld_wait();
-      }
-      if (tid < keys_valid) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(dvp + i * 32 + j * 8) = pack8<T>(o + j * 8);
-      }
-    }
-    tc_fence_before_sync();
   }
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, NCOLS);
@@ -553,6 +634,92 @@ int launch_selftest_umma(const void* a, const void* b, float* d, int b_mn_major,
   return FMB_OK;
 }
 
+// Self test of the TMA row gather: A' = rows `idx` of a (T x 128) matrix a (idx -1 or >= T reads
+// zeros), fetched with tile::gather4 into the swizzled UMMA tile; then d = A' . b^T as above.
+template <typename T>
+__global__ void __launch_bounds__(128) selftest_gather_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                              const int* idx, int nrows_total, const T* b,
+                                                              float* d, int* status) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ uint64_t bar, bar_full;
+  __shared__ uint32_t tmem_base_s;
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* sA = smem;
+  unsigned char* sB = smem + 128 * 128 * 2;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (warp == 0) tmem_alloc(&tmem_base_s, 128);
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    mbar_init(&bar_full, 1);
+    mbar_fence_init();
+  }
+  stage_tile_sw128<T, 16>(sB, 128 * 128, b, 128, 128, [](int r) { return (int64_t)r; });
+  fence_async_smem();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) {   // one warp issues the gathers: lane l fetches rows 4l..4l+3, both 64-column halves
+    const int lane = tid & 31;
+    if (lane == 0) mbar_expect_tx(&bar_full, 128 * 128 * 2);
+    __syncwarp();
+    int y[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = idx[lane * 4 + i];
+      y[i] = (r < 0 || r >= nrows_total) ? nrows_total : r;   // out of range -> zero fill
+    }
+    tma_gather4(sA + lane * 512, &map_a, 0, y[0], y[1], y[2], y[3], &bar_full);
+    tma_gather4(sA + 16384 + lane * 512, &map_a, 64, y[0], y[1], y[2], y[3], &bar_full);
+  }
+  bool ok = mbar_wait(&bar_full, 0, status, 8);
+  ok = __syncthreads_and(ok);
+  const uint32_t tD = tmem_base_s;
+  if (ok) {
+    if (tid == 0) {
+      tc_fence_after_sync();
+      const uint32_t idesc = make_idesc(FmtOf<T>::v, 128, 128, 0, 0);
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t o = (ks >> 2) * 16384 + (ks & 3) * 32;
+        umma_ss(tD, make_desc_sw128(smem_u32(sA) + o, 16, 1024), make_desc_sw128(smem_u32(sB) + o, 16, 1024), idesc,
+                ks > 0);
+      }
+      umma_commit(&bar);
+    }
+    ok = mbar_wait(&bar, 0, status, 9);
+    if (__syncthreads_and(ok)) {
+      tc_fence_after_sync();
+      for (int i = 0; i < 4; ++i) {
+        float o[32];
+        tmem_ld32(tD + ((uint32_t)(warp * 32) << 16) + i * 32, o);
+        tmem_ld_wait();
+        for (int j = 0; j < 32; ++j) d[tid * 128 + i * 32 + j] = o[j];
+      }
+      tc_fence_before_sync();
+    }
+  }
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tD, 128);
+}
+
+int launch_selftest_gather(const void* a, int a_rows, const int* idx, const void* b, float* d, int dtype,
+                           int* status, cudaStream_t s) {
+  CUtensorMap map;
+  int rc = make_tmap_2d(&map, a, dtype, 128, (uint64_t)a_rows, 256, 64, 1);
+  if (rc) return rc;
+  const size_t smem = 2 * 128 * 128 * 2 + 1024;
+  if (dtype == FMB_BF16) {
+    auto kern = selftest_gather_kernel<__nv_bfloat16>;
+    FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<1, 128, smem, s>>>(map, idx, a_rows, (const __nv_bfloat16*)b, d, status);
+  } else {
+    auto kern = selftest_gather_kernel<__half>;
+    FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<1, 128, smem, s>>>(map, idx, a_rows, (const __half*)b, d, status);
+  }
+  FMB_LAUNCH_CHECK("selftest_gather_kernel");
+  return FMB_OK;
+}
+
 // ------------------------------------------------------------------ launchers
 static TcParams make_tc_params(const AttnArgs& a, const AttnWorkspace& w) {
   TcParams p;
@@ -597,13 +764,14 @@ static int bwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t
   auto kern = bwd_main_tc_kernel<T, C, D>;
   FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int nchunk = max(a.ncol, ceil_div(a.max_k, C));
-  kern<<<dim3(nchunk, a.heads_k, a.batch), kTcM, smem, s>>>(p);
+  kern<<<dim3(nchunk, a.heads_k, a.batch), kBwdThreads, smem, s>>>(p);
   FMB_LAUNCH_CHECK("bwd_main_tc_kernel");
   return FMB_OK;
 }
 
 bool tc_supported(const AttnArgs& a, bool backward) {
-  if (backward) return a.chunk == 128 && (a.d == 64 || a.d == 128);
+  if (backward)
+    return a.chunk == 128 && (a.d == 64 || a.d == 128);
   return (a.chunk == 64 || a.chunk == 128) && (a.d == 64 || a.d == 128);
 }
 

@@ -199,6 +199,12 @@ int fmb_gate_status(int* host_status);
 int fmb_selftest_umma(const void* a, const void* b, float* d, int b_mn_major, int dtype, int* status,
                       fmb_stream_t stream);
 
+/* Self test of the TMA row gather (tile::gather4), no counterpart in the reference:
+ * d[128][128] (float) = A' . b^T where A'[i] = a[idx[i]] (a is a_rows x 128, contiguous; an
+ * index < 0 or >= a_rows gives a zero row) and b is [128][128]; idx is a device int[128]. */
+int fmb_selftest_gather(const void* a, int a_rows, const int* idx, const void* b, float* d, int dtype,
+                        int* status, fmb_stream_t stream);
+
 /* The first 4 bytes of the workspace given to fmb_attn_fwd / fmb_attn_bwd hold a device-side
  * status word after the call: 0 = ok, non-zero = a bounded wait inside a kernel expired
  * (FMB_ERR_TIMEOUT condition; results are then invalid). */
