@@ -63,21 +63,43 @@ struct TcParams {
 __host__ __device__ constexpr int next_pow2_cols(int x) { return x <= 32 ? 32 : x <= 64 ? 64 : x <= 128 ? 128 : x <= 256 ? 256 : 512; }
 
 // ======================================================================== forward
+// CTA = key chunk c of one (sequence, head); K and V are staged once and shared by two compute
+// warpgroups that take alternate 128-row tiles of the chunk's CSC column; a third group of four
+// warps gathers the query rows one tile ahead with 16-byte cp.async copies (straight into the
+// swizzled UMMA tile, no registers).  384 threads, one CTA per SM:
+//   warps 0-3 / 4-7  compute group 0 / 1: own Q tile, own P/O-staging tile, own 256 TMEM
+//                    columns (S | O), own mbarriers; thread 0 of the group issues its MMAs.
+//                    Per tile:  S = Q.K^T  ->  chunk-local softmax, one thread per row (two
+//                    passes over TMEM: row maximum, then exponentials)  ->  P (bf16) to shared
+//                    memory  ->  O = P.V (V consumed MN-major)  ->  O / l staged and written
+//                    with one bulk copy per warp, log-sum-exp beside it.
+//   warps 8-11       loaders: row ids of the next tile, then its Q rows as soon as the group's
+//                    previous S GEMM has released the Q tile.
+// While one group is in its softmax the other group's MMAs and the loaders' copies proceed.
+constexpr int kFwdGroups = 2;
+constexpr int kFwdGroupThreads = 256;          // two threads per row: each owns half of the columns
+constexpr int kFwdLoaders = 128;
+constexpr int kFwdLoaderSet = kFwdLoaders / kFwdGroups;   // loader threads per compute group
+constexpr int kFwdThreads = kFwdGroups * kFwdGroupThreads + kFwdLoaders;
+
 template <typename T, int C, int D>
-__global__ void __launch_bounds__(kTcM) fwd_main_tc_kernel(TcParams p) {
+__global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
   constexpr int QP = (C > D ? C : D);
   constexpr uint32_t kKBlock = C * 128;        // bytes between 64-element blocks of the K / V tiles
   constexpr uint32_t kQBlock = kTcM * 128;     // same for the 128-row Q / P tiles
-  constexpr int NCOLS = next_pow2_cols(C + D);
+  constexpr int NCOLS = 512;
+  constexpr int CH = C / 2, DH = D / 2;        // columns per thread in the softmax / epilogue
   extern __shared__ unsigned char smem_raw[];
-  __shared__ uint64_t bar;
+  __shared__ uint64_t bar_s[kFwdGroups], bar_o[kFwdGroups], bar_full[kFwdGroups], bar_qfree[kFwdGroups];
   __shared__ uint32_t tmem_base_s;
-  __shared__ int sRow[2][kTcM];
+  __shared__ int sRow[kFwdGroups][2][kTcM];
+  __shared__ float sMax[kFwdGroups][2][kTcM], sSum[kFwdGroups][2][kTcM];
 
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* sK = smem;
   unsigned char* sV = sK + C * D * 2;
-  unsigned char* sQP = sV + C * D * 2;     // Q tile, later overwritten by P
+  unsigned char* sQg = sV + C * D * 2;                         // [group][128][D]
+  unsigned char* sPOg = sQg + kFwdGroups * kTcM * D * 2;       // [group][128][max(C,D)]
 
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int64_t ci = ((int64_t)b * p.heads + h) * p.ncol + c;
@@ -92,158 +114,205 @@ __global__ void __launch_bounds__(kTcM) fwd_main_tc_kernel(TcParams p) {
   const int hk = h / (p.heads / p.heads_k);
   const int shift = len_k - len_q;
   const float scale_log2 = p.scale * kLog2eTc;
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool loader = tid >= kFwdGroups * kFwdGroupThreads;
+  const int g = loader ? 0 : tid / kFwdGroupThreads;   // compute group
+  const int gt = tid % kFwdGroupThreads;               // thread inside the group
+  const int lt = tid & (kTcM - 1);                     // row (TMEM lane); for loaders: index in the role
+  const int hf = (gt >> 7) & 1;                        // column half of a compute thread
+  const int ntiles = (nnz + kTcM - 1) / kTcM;
 
   FMB_T0();
   if (warp == 0) tmem_alloc(&tmem_base_s, NCOLS);
   if (tid == 0) {
-    mbar_init(&bar, 1);
+    for (int i = 0; i < kFwdGroups; ++i) {
+      mbar_init(&bar_s[i], 1);
+      mbar_init(&bar_o[i], 1);
+      mbar_init(&bar_full[i], kFwdLoaderSet);
+      mbar_init(&bar_qfree[i], 1);
+    }
     mbar_fence_init();
   }
-  const T* kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + key0) * p.k_rs + (int64_t)hk * p.k_hs;
-  const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
-  const T* qbase = static_cast<const T*>(p.q) + (int64_t)q0 * p.q_rs + (int64_t)h * p.q_hs;
-  stage_dense_sw128<T, D / 8, C>(sK, kKBlock, kbase, p.k_rs, keys_valid);
-  stage_dense_sw128<T, D / 8, C>(sV, kKBlock, vbase, p.v_rs, keys_valid);
-  fence_async_smem();
+  if (!loader && hf == 0) {   // 2 x 128 threads stage K and V
+    const T* kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + key0) * p.k_rs + (int64_t)hk * p.k_hs;
+    const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
+    if (g == 0) stage_dense_sw128_t<T, D / 8, C>(lt, sK, kKBlock, kbase, p.k_rs, keys_valid);
+    else stage_dense_sw128_t<T, D / 8, C>(lt, sV, kKBlock, vbase, p.v_rs, keys_valid);
+    fence_async_smem();
+  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = tmem_base_s;
-  const uint32_t tS = tmem_base, tO = tmem_base + C;
-  const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
-  const uint32_t sK_a = smem_u32(sK), sV_a = smem_u32(sV), sQP_a = smem_u32(sQP);
-  constexpr uint32_t idesc_s = make_idesc(FmtOf<T>::v, kTcM, C, 0, 0);
-  constexpr uint32_t idesc_o = make_idesc(FmtOf<T>::v, kTcM, D, 0, 1);
-  T* part_o = static_cast<T*>(p.part_o);
-  uint32_t phase = 0;
-
-  auto load_rows = [&](int t0, int buf) {
-    int r = -1;
-    if (t0 + tid < nnz) {
-      r = p.indices[off + t0 + tid];
-      if (r < 0 || r >= len_q) r = -1;
-    }
-    sRow[buf][tid] = r;
-  };
   FMB_TICK(0);   // prologue: TMEM alloc + K/V staging
-  uint4 pre[D / 8];   // the next tile's Q rows, in flight while this tile computes
-  load_rows(0, 0);
-  __syncthreads();
-  gather_load<T, D / 8>(pre, qbase, p.q_rs, sRow[0]);
-  gather_store<D / 8>(pre, sQP, kQBlock);
-  fence_async_smem();
-  __syncthreads();
+  const uint32_t tmem_base = tmem_base_s;
 
-  FMB_TICK(1);   // first Q gather
-  int buf = 0;
-  for (int t0 = 0; t0 < nnz; t0 += kTcM, buf ^= 1) {
-    const int rows = min(kTcM, nnz - t0);
-    const bool more = t0 + kTcM < nnz;
-    if (tid == 0) {
-      tc_fence_after_sync();
-#pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) {
-        const uint64_t a = make_desc_sw128(sQP_a + (ks >> 2) * kQBlock + (ks & 3) * 32, 16, 1024);
-        const uint64_t bd = make_desc_sw128(sK_a + (ks >> 2) * kKBlock + (ks & 3) * 32, 16, 1024);
-        umma_ss(tS, a, bd, idesc_s, ks > 0);
+  if (loader) {
+    // =============================================================== loader warps
+    // two independent sets of 64 threads, one per compute group
+    const T* qbase = static_cast<const T*>(p.q) + (int64_t)q0 * p.q_rs + (int64_t)h * p.q_hs;
+    const int gi = (tid - kFwdGroups * kFwdGroupThreads) / kFwdLoaderSet;   // the group this set serves
+    const int st = tid % kFwdLoaderSet;
+    uint32_t ph_free = 0;
+    auto row_of = [&](int tile, int e) {
+      int r = -1;
+      if (tile < ntiles && tile * kTcM + e < nnz) {
+        r = p.indices[off + tile * kTcM + e];
+        if (r < 0 || r >= len_q) r = -1;
       }
-      umma_commit(&bar);
+      return r;
+    };
+    int r_a = row_of(gi, st), r_b = row_of(gi, st + kFwdLoaderSet);   // the set's first tile
+    for (int i = gi, n = 0; i < ntiles; i += kFwdGroups, ++n) {
+      int* rows = sRow[gi][n & 1];
+      bool ok = true;
+      if (n > 0) {   // the group's previous S GEMM must have finished reading its Q tile; it is
+                     // issued after the softmax of the tile before, the last reader of rows[]
+        ok = mbar_wait(&bar_qfree[gi], ph_free, p.status, 5);
+        ph_free ^= 1;
+      }
+      rows[st] = r_a;
+      rows[st + kFwdLoaderSet] = r_b;
+      r_a = row_of(i + kFwdGroups, st);                   // next tile's row ids, in flight meanwhile
+      r_b = row_of(i + kFwdGroups, st + kFwdLoaderSet);
+      ok = bar_and(4 + gi, kFwdLoaderSet, ok);   // also publishes the row ids inside the set
+      if (!ok) break;
+      gather_cp_async<T, D / 8, kFwdLoaderSet>(st, sQg + gi * (kTcM * D * 2), kQBlock, qbase, p.q_rs, rows);
+      cp_async_wait_all();
+      fence_async_smem();   // the copies are generic-proxy writes; the MMAs read through the async proxy
+      mbar_arrive(&bar_full[gi]);
     }
-    if (more) load_rows(t0 + kTcM, buf ^ 1);   // published by the barrier after the softmax
-    bool ok = mbar_wait(&bar, phase, p.status, 1);
-    phase ^= 1;
-    if (!__syncthreads_and(ok)) break;
-    tc_fence_after_sync();
-    FMB_TICK(2);   // S = Q.K^T issue -> complete
+  } else {
+    // =============================================================== compute groups
+    unsigned char* sQ = sQg + g * (kTcM * D * 2);
+    unsigned char* sPO = sPOg + g * (kTcM * QP * 2);
+    const uint32_t tS = tmem_base + g * 256, tO = tS + 128;
+    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t sK_a = smem_u32(sK), sV_a = smem_u32(sV), sQ_a = smem_u32(sQ), sPO_a = smem_u32(sPO);
+    constexpr uint32_t idesc_s = make_idesc(FmtOf<T>::v, kTcM, C, 0, 0);
+    constexpr uint32_t idesc_o = make_idesc(FmtOf<T>::v, kTcM, D, 0, 1);
+    T* part_o = static_cast<T*>(p.part_o);
+    const int bar_id = 2 + g;
+    const int gw = gt >> 5;                    // warp inside the group (0..7)
+    // S and O completions use separate mbarriers: the next S GEMM is issued behind this tile's
+    // P.V GEMM, and a single barrier must never run two phases ahead of its waiters
+    uint32_t phase_s = 0, phase_o = 0, phase_full = 0;
+    bool good = true;
 
-    // ---- chunk-local softmax of row `tid`
-    const int r = sRow[buf][tid];
-    const int lim = r < 0 ? 0 : (p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid);
-    float inv;
-    {
-      float s[C];
+    // S = Q.K^T of a tile: waits for its Q rows, then issues (thread 0 of the group)
+    auto issue_s = [&]() {
+      if (mbar_wait(&bar_full[g], phase_full, p.status, 6)) {   // the tile's Q rows have landed
+        tc_fence_after_sync();
 #pragma unroll
-      for (int i = 0; i < C / 32; ++i) tmem_ld32(tS + lane_sel + i * 32, s + i * 32);
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint64_t a = make_desc_sw128(sQ_a + (ks >> 2) * kQBlock + (ks & 3) * 32, 16, 1024);
+          const uint64_t bd = make_desc_sw128(sK_a + (ks >> 2) * kKBlock + (ks & 3) * 32, 16, 1024);
+          umma_ss(tS, a, bd, idesc_s, ks > 0);
+        }
+        umma_commit(&bar_qfree[g]);   // the loaders may refill the Q tile
+        umma_commit(&bar_s[g]);
+      }
+      phase_full ^= 1;
+    };
+    if (gt == 0 && g < ntiles) issue_s();   // first tile; later ones are issued one tile ahead
+
+    for (int i = g, n = 0; i < ntiles && good; i += kFwdGroups, ++n) {
+      const int t0 = i * kTcM;
+      const int rows = min(kTcM, nnz - t0);
+      if (gw < 4 && lane == 0) bulk_wait_read();   // the previous tile's O staging has been read out
+      good = bar_and(bar_id, kFwdGroupThreads, mbar_wait(&bar_s[g], phase_s, p.status, 1));
+      phase_s ^= 1;
+      tc_fence_after_sync();
+      if (!good) break;
+      if (tid == 0) FMB_TICK(2);   // operands + S = Q.K^T
+
+      // ---- chunk-local softmax of row `lt`, this thread's half of the keys
+      const int r = sRow[g][n & 1][lt];
+      const int lim = r < 0 ? 0 : (p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid);
+      float s[CH];
+#pragma unroll
+      for (int q4 = 0; q4 < CH / 32; ++q4) tmem_ld32(tS + lane_sel + hf * CH + q4 * 32, s + q4 * 32);
       tmem_ld_wait();
       float mx = -CUDART_INF_F;
+      if (lim >= C) {   // nothing masked: the common case away from the causal diagonal
 #pragma unroll
-      for (int jj = 0; jj < C; ++jj) {
-        s[jj] = jj < lim ? s[jj] : -CUDART_INF_F;
-        mx = fmaxf(mx, s[jj]);
+        for (int jj = 0; jj < CH; ++jj) mx = fmaxf(mx, s[jj]);
+      } else {
+#pragma unroll
+        for (int jj = 0; jj < CH; ++jj) {
+          s[jj] = hf * CH + jj < lim ? s[jj] : -CUDART_INF_F;
+          mx = fmaxf(mx, s[jj]);
+        }
       }
+      sMax[g][hf][lt] = mx;
+      tc_fence_before_sync();
+      bar_sync(bar_id, kFwdGroupThreads);
+      mx = fmaxf(mx, sMax[g][hf ^ 1][lt]);
       const float mref = lim > 0 ? mx * scale_log2 : 0.f;
       float sum = 0.f;
 #pragma unroll
-      for (int jj = 0; jj < C; ++jj) {
+      for (int jj = 0; jj < CH; ++jj) {
         s[jj] = exp2f(s[jj] * scale_log2 - mref);   // exp2(-inf) = 0 for masked keys
         sum += s[jj];
       }
 #pragma unroll
-      for (int jj = 0; jj < C / 8; ++jj)
-        *reinterpret_cast<uint4*>(sQP + sw128_offset(tid, jj, kQBlock)) = pack8<T>(s + jj * 8);
-      inv = sum > 0.f ? 1.f / sum : 0.f;
-      if (tid < rows) p.part_lse[off + t0 + tid] = sum > 0.f ? mx * p.scale + logf(sum) : -CUDART_INF_F;
-    }
-    tc_fence_before_sync();
-    fence_async_smem();
-    FMB_TICK(3);   // softmax of thread 0's row
-    __syncthreads();
-    FMB_TICK(4);   // barrier after softmax
-    if (tid == 0) {
+      for (int jj = 0; jj < CH / 8; ++jj)
+        *reinterpret_cast<uint4*>(sPO + sw128_offset(lt, hf * (CH / 8) + jj, kQBlock)) = pack8<T>(s + jj * 8);
+      sSum[g][hf][lt] = sum;
+      fence_async_smem();
+      if (tid == 0) FMB_TICK(3);   // softmax
+      bar_sync(bar_id, kFwdGroupThreads);
+      if (gt == 0) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < C / 16; ++ks) {
+          const uint64_t a = make_desc_sw128(sPO_a + (ks >> 2) * kQBlock + (ks & 3) * 32, 16, 1024);
+          const uint64_t bd = make_desc_sw128(sV_a + ks * 2048, kKBlock, 1024);
+          umma_ss(tO, a, bd, idesc_o, ks > 0);
+        }
+        umma_commit(&bar_o[g]);
+        // the group's next S GEMM goes out right behind: S has been consumed, and the result
+        // is ready by the time this tile's epilogue is done
+        if (i + kFwdGroups < ntiles) issue_s();
+      }
+      sum += sSum[g][hf ^ 1][lt];
+      const float inv = sum > 0.f ? 1.f / sum : 0.f;
+      if (hf == 0 && lt < rows) p.part_lse[off + t0 + lt] = sum > 0.f ? mx * p.scale + logf(sum) : -CUDART_INF_F;
+      good = bar_and(bar_id, kFwdGroupThreads, mbar_wait(&bar_o[g], phase_o, p.status, 2));
+      phase_o ^= 1;
       tc_fence_after_sync();
-#pragma unroll
-      for (int ks = 0; ks < C / 16; ++ks) {
-        const uint64_t a = make_desc_sw128(sQP_a + (ks >> 2) * kQBlock + (ks & 3) * 32, 16, 1024);
-        const uint64_t bd = make_desc_sw128(sV_a + ks * 2048, kKBlock, 1024);
-        umma_ss(tO, a, bd, idesc_o, ks > 0);
-      }
-      umma_commit(&bar);
-    }
-    if (more) gather_load<T, D / 8>(pre, qbase, p.q_rs, sRow[buf ^ 1]);   // flies under the P.V MMAs
-    ok = mbar_wait(&bar, phase, p.status, 2);
-    phase ^= 1;
-    if (!__syncthreads_and(ok)) break;
-    tc_fence_after_sync();
-    FMB_TICK(5);   // O = P.V issue -> complete (next gather issued)
+      if (!good) break;
+      if (tid == 0) FMB_TICK(5);   // O = P.V
 
-    // ---- epilogue: normalised partial O of row `tid`, staged in shared memory (the tile
-    // buffer is free: the P.V MMAs have completed) and written with one bulk copy per row
-    {
-      const int64_t pos = off + t0 + tid;
-      const int key = (int)(pos & 7);
-      unsigned char* srow = sQP + tid * (D * 2);
-      float o[D];
+      // ---- epilogue: normalised partial O of row `lt`, this thread's half of the head dim,
+      // staged in the P tile (its MMAs have completed); one bulk copy per 32 rows
+      {
+        const int64_t pos = off + t0 + lt;
+        const int key = (int)(pos & 7);
+        unsigned char* srow = sPO + lt * (D * 2);
+        float o[DH];
 #pragma unroll
-      for (int i = 0; i < D / 32; ++i) tmem_ld32(tO + lane_sel + i * 32, o + i * 32);   // one exposed latency
-      tmem_ld_wait();
-      FMB_TICK(8);
+        for (int q4 = 0; q4 < DH / 32; ++q4) tmem_ld32(tO + lane_sel + hf * DH + q4 * 32, o + q4 * 32);
+        tmem_ld_wait();
 #pragma unroll
-      for (int jj = 0; jj < D; ++jj) o[jj] *= inv;
+        for (int jj = 0; jj < DH; ++jj) o[jj] *= inv;
 #pragma unroll
-      for (int jj = 0; jj < D / 8; ++jj) *reinterpret_cast<uint4*>(srow + ((jj ^ key) << 4)) = pack8<T>(o + jj * 8);
-      FMB_TICK(9);
-      tc_fence_before_sync();
-      fence_async_smem();
-      __syncwarp();
-      FMB_TICK(10);
-      const int wrows = min(32, rows - warp * 32);   // this warp's rows are contiguous in the workspace
-      if ((tid & 31) == 0 && wrows > 0) {
-        bulk_store(part_o + (off + t0 + warp * 32) * D, sQP + warp * 32 * (D * 2), (uint32_t)wrows * D * 2);
-        bulk_commit();
+        for (int jj = 0; jj < DH / 8; ++jj)
+          *reinterpret_cast<uint4*>(srow + (((hf * (DH / 8) + jj) ^ key) << 4)) = pack8<T>(o + jj * 8);
+        tc_fence_before_sync();
+        fence_async_smem();
       }
+      bar_sync(bar_id, kFwdGroupThreads);   // both halves of every row staged
+      if (gw < 4) {
+        const int wrows = min(32, rows - gw * 32);   // a warp's rows are contiguous in the workspace
+        if (lane == 0 && wrows > 0) {
+          bulk_store(part_o + (off + t0 + gw * 32) * D, sPO + gw * 32 * (D * 2), (uint32_t)wrows * D * 2);
+          bulk_commit();   // its reads are waited for under the next tile's S GEMM
+        }
+      }
+      if (tid == 0) FMB_TICK(6);   // epilogue
     }
-    FMB_TICK(6);   // epilogue
-    bulk_wait_read();
-    __syncthreads();   // every row's copy has read its staging row
-    if (more) {        // the tile buffer takes the next Q
-      gather_store<D / 8>(pre, sQP, kQBlock);
-      fence_async_smem();
-    }
-    __syncthreads();
-    FMB_TICK(7);   // next Q into shared memory + barrier
+    if (gw < 4 && lane == 0) bulk_wait_read();
   }
-  bulk_wait_read();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, NCOLS);
 }
@@ -735,24 +804,17 @@ static TcParams make_tc_params(const AttnArgs& a, const AttnWorkspace& w) {
   return p;
 }
 
-// Dynamic shared memory is padded so that the CTAs that fit an SM never need more than the
-// 512 TMEM columns between them (tcgen05.alloc would otherwise stall until a CTA retires).
-static size_t pad_smem_for_tmem(size_t smem, int ncols) {
-  const size_t sm_bytes = 227 * 1024;
-  const size_t max_ctas = 512 / ncols;
-  while (sm_bytes / smem > max_ctas) smem += 4096;
-  return smem;
-}
-
 template <typename T, int C, int D>
 static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
   TcParams p = make_tc_params(a, w);
   constexpr int QP = (C > D ? C : D);
-  size_t smem = (size_t)2 * C * D * 2 + (size_t)kTcM * QP * 2 + 1024;
-  smem = pad_smem_for_tmem(smem, next_pow2_cols(C + D));
+  // K, V, and per compute group a Q tile and a P / O-staging tile; one CTA per SM by size
+  // (all 512 TMEM columns are allocated)
+  size_t smem = (size_t)2 * C * D * 2 + (size_t)kFwdGroups * kTcM * (D + QP) * 2 + 1024;
+  if (smem < 120 * 1024) smem = 120 * 1024;
   auto kern = fwd_main_tc_kernel<T, C, D>;
   FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<dim3(a.ncol, a.heads, a.batch), kTcM, smem, s>>>(p);
+  kern<<<dim3(a.ncol, a.heads, a.batch), kFwdThreads, smem, s>>>(p);
   FMB_LAUNCH_CHECK("fwd_main_tc_kernel");
   return FMB_OK;
 }

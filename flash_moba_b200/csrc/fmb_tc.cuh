@@ -35,7 +35,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait: gives up after kSpinLimit polls (each poll may itself block for a short,
 // hardware-defined time), records `where` in *status and returns false.  The caller then
 // leaves the kernel through its normal exit path (TMEM is still released).
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint32_t kSpinLimit = 1u << 17;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int where) {
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -210,15 +210,16 @@ __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;" ::: "memory");
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
-// one 128-row x NCHUNK*16-byte tile gathered by a 128-thread group (t = index in the group);
+// one 128-row x NCHUNK*16-byte tile gathered by a group of NT threads (t = index in the group);
 // rows[] holds the source row of each tile row, -1 = zero fill
-template <typename T, int NCHUNK>
+template <typename T, int NCHUNK, int NT = 128>
 __device__ __forceinline__ void gather_cp_async(int t, unsigned char* tile, uint32_t block_stride, const T* base,
                                                 int64_t row_stride, const int* rows) {
+  constexpr int RPP = NT / NCHUNK;           // rows per pass
   const int j = t % NCHUNK, rb = t / NCHUNK;
 #pragma unroll
-  for (int i = 0; i < NCHUNK; ++i) {
-    const int r = rb + (128 / NCHUNK) * i;
+  for (int i = 0; i < 128 / RPP; ++i) {
+    const int r = rb + RPP * i;
     const int src = rows[r];
     cp_async_16(tile + sw128_offset(r, j, block_stride), base + (int64_t)(src < 0 ? 0 : src) * row_stride + j * 8,
                 src >= 0);
