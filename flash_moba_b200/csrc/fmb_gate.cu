@@ -250,10 +250,11 @@ __device__ __forceinline__ float ordered_to_score(uint32_t o) {
   return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o);
 }
 
-constexpr int kGateTcThreads = 128;
-
-template <typename T, int D, int KMAX>
-__global__ void __launch_bounds__(kGateTcThreads) gate_topk_tc_kernel(GateParams p) {
+// NQ threads share a row (TMEM lane): warps w, w+4, w+8, ... may all read lane quarter w%4, so
+// each of them scans 128/NQ of a tile's columns into a private list; the NQ lists of a row are
+// merged once at the end.  More warps per row hide the latency of the (divergent) insertions.
+template <typename T, int D, int KMAX, int NQ>
+__global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
   using namespace tc;
   constexpr uint32_t kBlock = 128 * 128;       // bytes between 64-element blocks of a 128-row tile
   constexpr uint32_t kTile = 128 * D * 2;
@@ -274,16 +275,17 @@ __global__ void __launch_bounds__(kGateTcThreads) gate_topk_tc_kernel(GateParams
   const int hk = h / (p.heads / p.heads_k);
   const int shift = len_k - len_q;
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int lt = tid & 127, qd = tid >> 7;     // row, and which share of the columns
   const int topk = p.topk;
 
   // this thread's row: list of KMAX keys, descending; the first KMAX-topk are sentinels
-  const int pos = r0 + tid + shift;
-  const bool row_ok = tid < rows;
+  const int pos = r0 + lt + shift;
+  const bool row_ok = lt < rows;
   int nlim = nchunks;                          // candidate chunks of the row: n < nlim
   if (p.causal) nlim = pos < 0 ? 0 : min(nchunks, pos / p.chunk);
   if (!row_ok) nlim = 0;
   constexpr uint64_t kEmpty = ((uint64_t)0x007fffffu << 32) | 0xffffffffu;   // (-inf, id -1)
-  const bool own = p.causal && row_ok && pos >= 0 && nchunks > 0;
+  const bool own = p.causal && row_ok && pos >= 0 && nchunks > 0 && qd == 0;
   const uint64_t own_key = ((uint64_t)score_to_ordered(CUDART_INF_F) << 32) | (uint32_t)(own ? pos / p.chunk : 0);
   uint64_t key[KMAX];
 #pragma unroll
@@ -348,32 +350,34 @@ __global__ void __launch_bounds__(kGateTcThreads) gate_topk_tc_kernel(GateParams
       phases ^= 1u << buf;
       if (!__syncthreads_and(ok)) break;
       tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + buf * 128 + ((uint32_t)(warp * 32) << 16);
-      // 16 scores per step keeps the unrolled insertion network small enough for the
-      // instruction cache; the next 16 are fetched while these are examined
+      constexpr int kCols = kGateN / NQ;        // columns of a tile examined by this thread
+      const uint32_t taddr = tmem_base + buf * 128 + qd * kCols + ((uint32_t)((warp & 3) * 32) << 16);
+      // 16 scores per step keeps the unrolled insertion code small enough for the instruction
+      // cache; the next 16 are fetched while these are examined
       float v[2][16];
       tmem_ld16(taddr, v[0]);
 #pragma unroll 1
-      for (int i = 0; i < 8; i += 2) {
+      for (int i = 0; i < kCols / 16; i += 2) {
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           tmem_ld_wait();
-          if (i + half + 1 < 8) tmem_ld16(taddr + (i + half + 1) * 16, v[half ^ 1]);
-          const int nb = n0 + (i + half) * 16;
+          if (i + half + 1 < kCols / 16) tmem_ld16(taddr + (i + half + 1) * 16, v[half ^ 1]);
+          const int nb = n0 + qd * kCols + (i + half) * 16;
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int n = nb + j;
             const float x = v[half][j];
             const uint64_t cand = ((uint64_t)score_to_ordered(x) << 32) | (uint32_t)n;
             if (n < nlim && x > -CUDART_INF_F && cand > key[KMAX - 1]) {
-              key[KMAX - 1] = cand;
+              // insertion with independent compares and selects (no dependent swap chain):
+              // slot y takes its upper neighbour if the candidate outranks that one, else the
+              // candidate if it outranks the slot, else keeps its key
+              bool gt[KMAX];
 #pragma unroll
-              for (int y = KMAX - 1; y > 0; --y) {
-                const uint64_t lo = key[y], hi = key[y - 1];
-                const bool sw = lo > hi;
-                key[y] = sw ? hi : lo;
-                key[y - 1] = sw ? lo : hi;
-              }
+              for (int y = 0; y < KMAX; ++y) gt[y] = cand > key[y];
+#pragma unroll
+              for (int y = KMAX - 1; y > 0; --y) key[y] = gt[y - 1] ? key[y - 1] : (gt[y] ? cand : key[y]);
+              key[0] = gt[0] ? cand : key[0];
             }
           }
         }
@@ -382,9 +386,31 @@ __global__ void __launch_bounds__(kGateTcThreads) gate_topk_tc_kernel(GateParams
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_base, 256);
+    if (NQ > 1) {   // merge the row's NQ lists (the centroid buffers are free: every MMA has completed)
+      uint64_t* sMerge = reinterpret_cast<uint64_t*>(sKM);
+      if (qd > 0) {
+#pragma unroll
+        for (int j = 0; j < KMAX; ++j) sMerge[((qd - 1) * KMAX + j) * 128 + lt] = key[j];
+      }
+      __syncthreads();
+      if (qd == 0) {
+        for (int e = 0; e < (NQ - 1) * KMAX; ++e) {
+          const uint64_t cand = sMerge[e * 128 + lt];
+          // sentinels of the other lists (~0) are skipped; empty slots never outrank anything
+          if (cand != ~0ull && cand > key[KMAX - 1]) {
+            bool gt[KMAX];
+#pragma unroll
+            for (int y = 0; y < KMAX; ++y) gt[y] = cand > key[y];
+#pragma unroll
+            for (int y = KMAX - 1; y > 0; --y) key[y] = gt[y - 1] ? key[y - 1] : (gt[y] ? cand : key[y]);
+            key[0] = gt[0] ? cand : key[0];
+          }
+        }
+      }
+    }
   }
-  if (row_ok) {
-    const int64_t o = (int64_t)(q0 + r0 + tid) * p.t_rs + (int64_t)h * p.t_hs;
+  if (row_ok && qd == 0) {
+    const int64_t o = (int64_t)(q0 + r0 + lt) * p.t_rs + (int64_t)h * p.t_hs;
 #pragma unroll
     for (int j = 0; j < KMAX; ++j) {
       const int slot = j - (KMAX - topk);
@@ -405,22 +431,25 @@ int read_gate_status(int* out) {
   return FMB_OK;
 }
 
-template <typename T, int D, int KMAX>
+template <typename T, int D, int KMAX, int NQ>
 static int gate_tc_launch(const GateParams& p, int batch, int max_q, cudaStream_t s) {
   // 2 CTAs per SM at most (256 TMEM columns each): keep dynamic shared memory above a third of the SM's
   size_t smem = 1024 + (size_t)3 * 128 * D * 2;
   if (smem < 80 * 1024) smem = 80 * 1024;
-  auto kern = gate_topk_tc_kernel<T, D, KMAX>;
+  static_assert(NQ == 1 || (size_t)(NQ - 1) * KMAX * 128 * 8 <= (size_t)2 * 128 * D * 2, "merge buffer fits the centroid tiles");
+  auto kern = gate_topk_tc_kernel<T, D, KMAX, NQ>;
   FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<dim3(ceil_div(max_q, kGateM), p.heads, batch), kGateTcThreads, smem, s>>>(p);
+  kern<<<dim3(ceil_div(max_q, kGateM), p.heads, batch), 128 * NQ, smem, s>>>(p);
   FMB_LAUNCH_CHECK("gate_topk_tc_kernel");
   return FMB_OK;
 }
 template <typename T, int D>
 static int gate_tc_pick(const GateParams& p, int batch, int max_q, cudaStream_t s) {
-  if (p.topk <= 8) return gate_tc_launch<T, D, 8>(p, batch, max_q, s);
-  if (p.topk <= 16) return gate_tc_launch<T, D, 16>(p, batch, max_q, s);
-  return gate_tc_launch<T, D, 32>(p, batch, max_q, s);
+  // one thread per row measured fastest at 64K tokens (2.8 ms against 3.0 ms with four): the cost is
+  // instruction issue under divergence, not latency
+  if (p.topk <= 8) return gate_tc_launch<T, D, 8, 1>(p, batch, max_q, s);
+  if (p.topk <= 16) return gate_tc_launch<T, D, 16, 1>(p, batch, max_q, s);
+  return gate_tc_launch<T, D, 32, 1>(p, batch, max_q, s);
 }
 
 template <typename T>
