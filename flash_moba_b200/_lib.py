@@ -46,8 +46,8 @@ _SIGS = {
     "fmb_build_csc_static_capacity": (sz, []),
     "fmb_build_csc_static": (i32, [c_ptr, i64, i64, c_ptr, c_ptr, c_ptr, c_ptr, i32, i32, i32, i32, i32, c_ptr]),
     "fmb_varlen_sort": (i32, [c_ptr, c_ptr, c_ptr, c_ptr, i64, i64, c_ptr]),
-    "fmb_attn_fwd_workspace_bytes": (sz, [i64, i32, i32, i64]),
-    "fmb_attn_bwd_workspace_bytes": (sz, [i64, i32, i32, i64]),
+    "fmb_attn_fwd_workspace_bytes": (sz, [i64, i32, i32, i32, i64, i32, i32, i32, i32]),
+    "fmb_attn_bwd_workspace_bytes": (sz, [i64, i32, i32, i32, i64, i32, i32, i32, i32]),
     "fmb_attn_fwd": (i32, [c_ptr, i64, i64, c_ptr, i64, i64, c_ptr, i64, i64, c_ptr, i64, i64, c_ptr,
                            c_ptr, c_ptr, c_ptr, i64, c_ptr, c_ptr, c_ptr, sz,
                            i32, i32, i32, i32, i64, i32, i32, i32, f32, i32, i32, c_ptr]),

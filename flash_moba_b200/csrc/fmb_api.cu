@@ -217,11 +217,15 @@ int fmb_varlen_sort(const int64_t* starts, const int64_t* ends, const int32_t* s
   return launch_varlen_sort(starts, ends, src, dst, num_segments, num_items, (cudaStream_t)stream);
 }
 
-size_t fmb_attn_fwd_workspace_bytes(int64_t total_q, int heads, int head_dim, int64_t n_indices) {
-  return attn_fwd_workspace_bytes(total_q, heads, head_dim, n_indices);
+size_t fmb_attn_fwd_workspace_bytes(int64_t total_q, int heads, int heads_k, int head_dim, int64_t n_indices,
+                                    int batch, int max_seqlen_k, int chunk, int heads_per_pass) {
+  return attn_workspace_bytes(total_q, heads, heads_k, head_dim, n_indices, batch, max_seqlen_k, chunk,
+                              heads_per_pass, false);
 }
-size_t fmb_attn_bwd_workspace_bytes(int64_t total_q, int heads, int head_dim, int64_t n_indices) {
-  return attn_bwd_workspace_bytes(total_q, heads, head_dim, n_indices);
+size_t fmb_attn_bwd_workspace_bytes(int64_t total_q, int heads, int heads_k, int head_dim, int64_t n_indices,
+                                    int batch, int max_seqlen_k, int chunk, int heads_per_pass) {
+  return attn_workspace_bytes(total_q, heads, heads_k, head_dim, n_indices, batch, max_seqlen_k, chunk,
+                              heads_per_pass, true);
 }
 
 static int check_attn(const char* op, const AttnArgs& a) {

@@ -26,38 +26,89 @@ __host__ __device__ __forceinline__ int part_col(int64_t pos, int col, int elems
   return ((chunk ^ (int)(pos & 7)) * elems_per_chunk) + (col % elems_per_chunk);
 }
 
+// A call is processed in one or more PASSES over ranges of query heads [h0, h0+nh), so that the
+// per-pair partials need memory for one pass only.  Inside a pass, column (b, h, c) owns the
+// slots [slot_base, slot_base + nnz) of every partial array ("slot" = running count of pattern
+// entries over the pass's columns in (b, h, c) order), and a key chunk wider than the kernels'
+// key block KB is handled as nsub = chunk / KB sub-blocks, each with its own plane of `cap`
+// slots: the partial of (entry j of the column, sub-block sb) lives at sb*cap + slot_base + j.
 struct AttnWorkspace {
-  int* status;         // first word of the workspace: 0, or where a bounded device wait gave up
-  void* part_o;        // fwd: n_indices * d elements of the I/O dtype;  bwd: n_indices * d floats
-  float* part_lse;     // fwd only: n_indices
-  uint32_t* row_ptr;   // heads*total_q + 1
-  uint32_t* row_fill;  // heads*total_q
-  uint32_t* row_pos;   // n_indices
-  uint32_t* scan_tmp;  // block sums of the scan
+  int* status;          // first word: 0, or where a bounded device wait gave up / 7 = slot overflow
+  void* part_o;         // fwd: nsub*cap*d elements of the I/O dtype;  bwd: nsub*cap*d floats
+  float* part_lse;      // fwd only: nsub*cap
+  uint32_t* slot_base;  // batch*nh*ncol + 1
+  uint32_t* row_ptr;    // nh*total_q + 1
+  uint32_t* row_fill;   // nh*total_q
+  uint32_t* row_pos;    // cap: slots of a row's entries
+  uint32_t* scan_tmp;   // block sums of the scans
+  int nh;               // heads per pass
+  int nsub, kb;         // sub-blocks per chunk, keys per sub-block
+  int64_t cap;          // slots per plane
   size_t bytes;
 };
 
-AttnWorkspace carve_attn_workspace(void* base, int64_t total_q, int heads, int d, int64_t n_indices,
-                                   size_t part_elem_bytes, bool with_lse);
+// Pass geometry + pattern access shared by every attention kernel
+struct PassParams {
+  const int64_t* col_offsets; const int32_t* col_nnz; const int32_t* indices; int64_t n_indices;
+  const uint32_t* slot_base;
+  int heads, ncol, h0, nh, nsub, kb, chunk;
+  int64_t cap;
+  int* status;
+};
+struct ColRef {
+  int nnz;          // 0 if the column is empty, malformed or does not fit the pass's slots
+  int64_t off;      // first entry in `indices`
+  int64_t slot;     // first slot of the column in the pass
+};
+__device__ __forceinline__ ColRef column_of(const PassParams& r, int b, int h, int c) {
+  ColRef o{0, 0, 0};
+  if (c >= r.ncol) return o;
+  const int64_t ci = ((int64_t)b * r.heads + h) * r.ncol + c;
+  const int nnz = r.col_nnz[ci];
+  const int64_t off = r.col_offsets[ci];
+  if (nnz <= 0 || off < 0 || off + nnz > r.n_indices) return o;   // malformed: ignored, never read
+  const int64_t slot = r.slot_base[((int64_t)b * r.nh + (h - r.h0)) * r.ncol + c];
+  if (slot + nnz > r.cap) {          // cannot happen for a pattern whose columns do not overlap
+    atomicCAS(r.status, 0, 7);
+    return o;
+  }
+  o.nnz = nnz; o.off = off; o.slot = slot;
+  return o;
+}
 
-// Builds row_ptr / row_pos (CSR transpose of the CSC pattern).  Row id = h*total_q + token.
-int build_row_lists(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s);
+// A key block that starts beyond the sequence's keys contributes nothing: its dQ partials are
+// zero (the combine still reads them).  Called by a whole CTA of the backward kernels.
+__device__ __forceinline__ void zero_dq_partials(const PassParams& r, float* part_dq, int64_t plane, int b, int hk,
+                                                 int group, int c, int d) {
+  for (int hg = 0; hg < group; ++hg) {
+    const ColRef col = column_of(r, b, hk * group + hg, c);
+    if (col.nnz <= 0) continue;
+    float4* dst = reinterpret_cast<float4*>(part_dq + (plane + col.slot) * d);
+    const int64_t n4 = (int64_t)col.nnz * d / 4;
+    for (int64_t i = threadIdx.x; i < n4; i += blockDim.x) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+AttnWorkspace carve_attn_workspace(void* base, size_t bytes_available, const AttnArgs& a, size_t part_elem_bytes,
+                                   bool with_lse, int heads_per_pass);
+PassParams make_pass(const AttnArgs& a, const AttnWorkspace& w, int h0, int nh);
+
+// Builds slot_base and row_ptr / row_pos (CSR transpose of the pass's part of the pattern).
+// Row id = (h - h0)*total_q + token.
+int build_row_lists(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s);
 
 // out/lse from the forward partials
-int launch_fwd_combine(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s);
+int launch_fwd_combine(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s);
 // dq from the backward partials (multiplies by softmax_scale)
-int launch_bwd_combine(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s);
+int launch_bwd_combine(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s);
 // softmax_d[h, t] = sum_d dout*out
 int launch_dot_do_o(const AttnArgs& a, cudaStream_t s);
 
-// forward partials of pattern entries whose chunk starts beyond the sequence's keys
-int launch_fwd_dead_columns(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s);
-
 // engines: main kernels that produce the partials (and dk/dv in backward)
-int launch_fwd_main_simt(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s);
-int launch_bwd_main_simt(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s);
-int launch_fwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s);
-int launch_bwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s);
+int launch_fwd_main_simt(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s);
+int launch_bwd_main_simt(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s);
+int launch_fwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s);
+int launch_bwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s);
 bool tc_supported(const AttnArgs& a, bool backward);
 int launch_selftest_gather(const void* a, int a_rows, const int* idx, const void* b, float* d, int dtype,
                            int* status, cudaStream_t s);

@@ -1,67 +1,114 @@
-// Row lists (CSR transpose of the pattern), the row-major combine kernels and the
-// forward / backward drivers shared by both attention engines.
+// Pass planning, slot and row lists (CSR transpose of the pattern), the row-major combine
+// kernels and the forward / backward drivers shared by both attention engines.
 #include "fmb_attn.cuh"
 
 namespace fmb {
 
-// ------------------------------------------------------------------ workspace layout
+// ------------------------------------------------------------------ workspace layout / passes
 static size_t scan_tmp_elems(int64_t n) { return (size_t)ceil_div64(n, 4096) + 1; }
 
-AttnWorkspace carve_attn_workspace(void* base, int64_t total_q, int heads, int d, int64_t n_indices,
-                                   size_t part_elem_bytes, bool with_lse) {
-  AttnWorkspace w;
+static size_t layout(AttnWorkspace& w, void* base, const AttnArgs& a, size_t part_elem_bytes, bool with_lse, int nh) {
   size_t off = 0;
   auto take = [&](size_t bytes) {
     void* p = base ? static_cast<char*>(base) + off : nullptr;
     off += align_up(bytes, 256);
     return p;
   };
-  const int64_t rows = total_q * heads;
+  w.nh = nh;
+  w.kb = (a.chunk % 128 == 0) ? 128 : 64;
+  w.nsub = a.chunk / w.kb;
+  // one pass over all heads can never need more slots than the pattern has entries; a pass over a
+  // share of the heads is given that share (exact for the top-k packing), rounded up
+  w.cap = nh >= a.heads ? a.n_indices : ceil_div64(a.n_indices * nh, a.heads) + 128;
+  w.cap = ceil_div64(w.cap, 8) * 8;
+  const int64_t rows = a.total_q * nh;
+  const int64_t ncols = (int64_t)a.batch * nh * a.ncol;
   w.status = static_cast<int*>(take(512));
-  w.part_o = take((size_t)n_indices * d * part_elem_bytes);
-  w.part_lse = static_cast<float*>(take(with_lse ? (size_t)n_indices * sizeof(float) : 0));
+  w.part_o = take((size_t)w.nsub * w.cap * a.d * part_elem_bytes);
+  w.part_lse = static_cast<float*>(take(with_lse ? (size_t)w.nsub * w.cap * sizeof(float) : 0));
+  w.slot_base = static_cast<uint32_t*>(take((size_t)(ncols + 1) * sizeof(uint32_t)));
   w.row_ptr = static_cast<uint32_t*>(take((size_t)(rows + 1) * sizeof(uint32_t)));
   w.row_fill = static_cast<uint32_t*>(take((size_t)rows * sizeof(uint32_t)));
-  w.row_pos = static_cast<uint32_t*>(take((size_t)n_indices * sizeof(uint32_t)));
-  w.scan_tmp = static_cast<uint32_t*>(take(scan_tmp_elems(rows + 1) * sizeof(uint32_t)));
+  w.row_pos = static_cast<uint32_t*>(take((size_t)w.cap * sizeof(uint32_t)));
+  const int64_t longest = rows + 1 > ncols + 1 ? rows + 1 : ncols + 1;
+  w.scan_tmp = static_cast<uint32_t*>(take(scan_tmp_elems(longest) * sizeof(uint32_t)));
   w.bytes = off;
+  return off;
+}
+
+AttnWorkspace carve_attn_workspace(void* base, size_t bytes_available, const AttnArgs& a, size_t part_elem_bytes,
+                                   bool with_lse, int heads_per_pass) {
+  AttnWorkspace w;
+  const int group = a.heads / a.heads_k;
+  int nh = a.heads;
+  if (heads_per_pass > 0) {
+    nh = min(a.heads, max(group, heads_per_pass / group * group));
+  } else if (base != nullptr) {   // the largest pass (whole kv-head groups) that fits what the caller gave
+    while (nh > group && layout(w, nullptr, a, part_elem_bytes, with_lse, nh) > bytes_available) nh -= group;
+  }
+  layout(w, base, a, part_elem_bytes, with_lse, nh);
   return w;
 }
 
-size_t attn_fwd_workspace_bytes(int64_t total_q, int heads, int d, int64_t n_indices) {
-  return carve_attn_workspace(nullptr, total_q, heads, d, n_indices, 2, true).bytes;
-}
-size_t attn_bwd_workspace_bytes(int64_t total_q, int heads, int d, int64_t n_indices) {
-  return carve_attn_workspace(nullptr, total_q, heads, d, n_indices, 4, false).bytes;
+size_t attn_workspace_bytes(int64_t total_q, int heads, int heads_k, int d, int64_t n_indices, int batch, int max_k,
+                            int chunk, int heads_per_pass, bool backward) {
+  AttnArgs a;
+  memset(&a, 0, sizeof(a));
+  a.total_q = total_q; a.heads = heads; a.heads_k = heads_k > 0 ? heads_k : heads; a.d = d; a.n_indices = n_indices;
+  a.batch = batch; a.chunk = chunk > 0 ? chunk : 128; a.ncol = ceil_div(max_k, a.chunk);
+  return carve_attn_workspace(nullptr, 0, a, backward ? 4 : 2, !backward, heads_per_pass > 0 ? heads_per_pass : heads)
+      .bytes;
 }
 
-// ------------------------------------------------------------------ row lists
+PassParams make_pass(const AttnArgs& a, const AttnWorkspace& w, int h0, int nh) {
+  PassParams r;
+  r.col_offsets = a.col_offsets; r.col_nnz = a.col_nnz; r.indices = a.indices; r.n_indices = a.n_indices;
+  r.slot_base = w.slot_base;
+  r.heads = a.heads; r.ncol = a.ncol; r.h0 = h0; r.nh = nh; r.nsub = w.nsub; r.kb = w.kb; r.chunk = a.chunk;
+  r.cap = w.cap; r.status = w.status;
+  return r;
+}
+
+// ------------------------------------------------------------------ slot and row lists
+// slot_base[i + 1] = entries of the i-th column of the pass (0 if the column is malformed);
+// an inclusive scan then turns the array into first slots
+__global__ void __launch_bounds__(256) slot_count_kernel(PassParams r, uint32_t* slot_base, int batch) {
+  const int64_t n = (int64_t)batch * r.nh * r.ncol;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i == 0) slot_base[0] = 0;
+  if (i >= n) return;
+  const int c = (int)(i % r.ncol);
+  const int hr = (int)((i / r.ncol) % r.nh);
+  const int b = (int)(i / ((int64_t)r.ncol * r.nh));
+  const int64_t ci = ((int64_t)b * r.heads + r.h0 + hr) * r.ncol + c;
+  const int nnz = r.col_nnz[ci];
+  const int64_t off = r.col_offsets[ci];
+  slot_base[i + 1] = (nnz > 0 && off >= 0 && off + nnz <= r.n_indices) ? (uint32_t)nnz : 0u;
+}
+
 struct RowListParams {
-  const int64_t* col_offsets; const int32_t* col_nnz; const int32_t* indices; int64_t n_indices;
+  PassParams r;
   const int32_t* cu_q;
   uint32_t *row_ptr, *row_fill, *row_pos;
-  int heads, ncol; int64_t total_q;
+  int64_t total_q;
 };
 
-// grid (ncol, heads, batch): one CTA per column
+// grid (ncol, nh, batch): one CTA per column of the pass
 template <bool kFill>
 __global__ void __launch_bounds__(256) row_list_kernel(RowListParams p) {
-  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int64_t ci = ((int64_t)b * p.heads + h) * p.ncol + c;
-  const int nnz = p.col_nnz[ci];
-  if (nnz <= 0) return;
-  const int64_t off = p.col_offsets[ci];
-  if (off < 0 || off + nnz > p.n_indices) return;   // malformed pattern: ignored, never read out of bounds
+  const int c = blockIdx.x, hr = blockIdx.y, b = blockIdx.z;
+  const ColRef col = column_of(p.r, b, p.r.h0 + hr, c);
+  if (col.nnz <= 0) return;
   const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
-  const int64_t rbase = (int64_t)h * p.total_q + q0;
-  for (int j = threadIdx.x; j < nnz; j += blockDim.x) {
-    const int r = p.indices[off + j];
+  const int64_t rbase = (int64_t)hr * p.total_q + q0;
+  for (int j = threadIdx.x; j < col.nnz; j += blockDim.x) {
+    const int r = p.r.indices[col.off + j];
     if (r < 0 || r >= len_q) continue;
     if (!kFill) {
       atomicAdd(&p.row_ptr[rbase + r + 1], 1u);     // counts, shifted by one for the scan
     } else {
-      const uint32_t slot = atomicAdd(&p.row_fill[rbase + r], 1u);
-      p.row_pos[p.row_ptr[rbase + r] + slot] = (uint32_t)(off + j);
+      const uint32_t k = atomicAdd(&p.row_fill[rbase + r], 1u);
+      p.row_pos[p.row_ptr[rbase + r] + k] = (uint32_t)(col.slot + j);
     }
   }
 }
@@ -143,38 +190,55 @@ __global__ void __launch_bounds__(1024) scan_add_kernel(uint32_t* data, int64_t 
     if (base + i < n) data[base + i] += add;
 }
 
-int build_row_lists(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
-  const int64_t rows = a.total_q * a.heads;
-  FMB_CUDA(cudaMemsetAsync(w.status, 0, 512, s));
-  FMB_CUDA(cudaMemsetAsync(w.row_ptr, 0, (size_t)(rows + 1) * sizeof(uint32_t), s));
-  FMB_CUDA(cudaMemsetAsync(w.row_fill, 0, (size_t)rows * sizeof(uint32_t), s));
-  if (a.ncol == 0 || a.batch == 0) return FMB_OK;
-  RowListParams p;
-  p.col_offsets = a.col_offsets; p.col_nnz = a.col_nnz; p.indices = a.indices; p.n_indices = a.n_indices;
-  p.cu_q = a.cu_q; p.row_ptr = w.row_ptr; p.row_fill = w.row_fill; p.row_pos = w.row_pos;
-  p.heads = a.heads; p.ncol = a.ncol; p.total_q = a.total_q;
-  dim3 grid(a.ncol, a.heads, a.batch);
-  row_list_kernel<false><<<grid, 256, 0, s>>>(p);
-  FMB_LAUNCH_CHECK("row_list_kernel<count>");
-  const int64_t n = rows + 1;
+static int inclusive_scan(uint32_t* data, int64_t n, uint32_t* tmp, cudaStream_t s) {
   const int nblocks = (int)ceil_div64(n, kScanItems);
-  scan_block_kernel<<<nblocks, 1024, 0, s>>>(w.row_ptr, n, w.scan_tmp);
+  scan_block_kernel<<<nblocks, 1024, 0, s>>>(data, n, tmp);
   FMB_LAUNCH_CHECK("scan_block_kernel");
   if (nblocks > 1) {
-    scan_sums_kernel<<<1, 1024, 0, s>>>(w.scan_tmp, nblocks);
+    scan_sums_kernel<<<1, 1024, 0, s>>>(tmp, nblocks);
     FMB_LAUNCH_CHECK("scan_sums_kernel");
-    scan_add_kernel<<<nblocks, 1024, 0, s>>>(w.row_ptr, n, w.scan_tmp);
+    scan_add_kernel<<<nblocks, 1024, 0, s>>>(data, n, tmp);
     FMB_LAUNCH_CHECK("scan_add_kernel");
   }
+  return FMB_OK;
+}
+
+int build_row_lists(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
+  const int64_t rows = a.total_q * ps.nh;
+  const int64_t ncols = (int64_t)a.batch * ps.nh * a.ncol;
+  FMB_CUDA(cudaMemsetAsync(w.row_ptr, 0, (size_t)(rows + 1) * sizeof(uint32_t), s));
+  FMB_CUDA(cudaMemsetAsync(w.row_fill, 0, (size_t)rows * sizeof(uint32_t), s));
+  if (ncols == 0) return FMB_OK;
+  slot_count_kernel<<<(unsigned)ceil_div64(ncols + 1, 256), 256, 0, s>>>(ps, w.slot_base, a.batch);
+  FMB_LAUNCH_CHECK("slot_count_kernel");
+  int rc = inclusive_scan(w.slot_base, ncols + 1, w.scan_tmp, s);
+  if (rc) return rc;
+  RowListParams p;
+  p.r = ps; p.cu_q = a.cu_q; p.row_ptr = w.row_ptr; p.row_fill = w.row_fill; p.row_pos = w.row_pos;
+  p.total_q = a.total_q;
+  dim3 grid(a.ncol, ps.nh, a.batch);
+  row_list_kernel<false><<<grid, 256, 0, s>>>(p);
+  FMB_LAUNCH_CHECK("row_list_kernel<count>");
+  rc = inclusive_scan(w.row_ptr, rows + 1, w.scan_tmp, s);
+  if (rc) return rc;
   row_list_kernel<true><<<grid, 256, 0, s>>>(p);
   FMB_LAUNCH_CHECK("row_list_kernel<fill>");
   return FMB_OK;
 }
 
 // ------------------------------------------------------------------ combine kernels
-// A warp per (token, head).  The row's partials are visited in ascending `pos`.
-// next_pos(): smallest position of the row that is greater than `last` (-1 first).
-__device__ __forceinline__ int64_t next_pos(const uint32_t* rp, int n, int64_t last, int lane) {
+// What a combine kernel needs to know about the pass
+struct CombineParams {
+  const uint32_t* row_ptr; const uint32_t* row_pos;
+  int64_t total_q, cap;
+  int heads_out;   // heads of the output tensor's row (for nothing but documentation)
+  int h0, nh, nsub, d;
+};
+
+// Generic kernel: a warp per (token, head of the pass).  The row's partials are visited plane by
+// plane, inside a plane in ascending slot order = ascending (sb*cap + slot).
+// next_slot(): smallest slot of the row that is greater than `last` (-1 first).
+__device__ __forceinline__ int64_t next_slot(const uint32_t* rp, int n, int64_t last, int lane) {
   int64_t best = INT64_MAX;
   for (int j = lane; j < n; j += 32) {
     const int64_t x = rp[j];
@@ -190,27 +254,24 @@ __device__ __forceinline__ int64_t next_pos(const uint32_t* rp, int n, int64_t l
 
 template <typename T>
 __global__ void __launch_bounds__(256) fwd_combine_kernel(const T* __restrict__ part_o,
-                                                          const float* __restrict__ part_lse,
-                                                          const uint32_t* __restrict__ row_ptr,
-                                                          const uint32_t* __restrict__ row_pos, T* out,
-                                                          int64_t o_rs, int64_t o_hs, float* lse,
-                                                          int64_t total_q, int heads, int d,
+                                                          const float* __restrict__ part_lse, CombineParams c,
+                                                          T* out, int64_t o_rs, int64_t o_hs, float* lse,
                                                           const int* only_if, int min_n) {
   using T2 = typename Elem<T>::T2;
   if (only_if && *only_if == 0) return;   // the earlier stages met no row they had to leave
   const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (wid >= total_q * heads) return;
-  const int64_t t = wid / heads;
-  const int h = (int)(wid - t * heads);
-  const int64_t rid = (int64_t)h * total_q + t;
-  const uint32_t p0 = row_ptr[rid];
-  const int n = (int)(row_ptr[rid + 1] - p0);
-  if (n < min_n) return;
-  const uint32_t* rp = row_pos + p0;
-  // pass 1: maximum of the partial log-sum-exps
+  if (wid >= c.total_q * c.nh) return;
+  const int64_t t = wid / c.nh;
+  const int hr = (int)(wid - t * c.nh);
+  const int64_t rid = (int64_t)hr * c.total_q + t;
+  const uint32_t p0 = c.row_ptr[rid];
+  const int n = (int)(c.row_ptr[rid + 1] - p0);
+  if (n * c.nsub < min_n) return;
+  const uint32_t* rp = c.row_pos + p0;
   float m = -CUDART_INF_F;
-  for (int j = lane; j < n; j += 32) m = fmaxf(m, part_lse[rp[j]]);
+  for (int sb = 0; sb < c.nsub; ++sb)
+    for (int j = lane; j < n; j += 32) m = fmaxf(m, part_lse[(int64_t)sb * c.cap + rp[j]]);
 #pragma unroll
   for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   float2 acc[4];
@@ -218,132 +279,148 @@ __global__ void __launch_bounds__(256) fwd_combine_kernel(const T* __restrict__ 
   for (int i = 0; i < 4; ++i) acc[i] = make_float2(0.f, 0.f);
   float ssum = 0.f;
   if (m > -CUDART_INF_F) {
-    int64_t last = -1;
-    for (int r = 0; r < n; ++r) {
-      const int64_t pos = next_pos(rp, n, last, lane);
-      last = pos;
-      const float wgt = __expf(part_lse[pos] - m);
-      ssum += wgt;
-      const T* src = part_o + pos * d;
+    for (int sb = 0; sb < c.nsub; ++sb) {
+      int64_t last = -1;
+      for (int r = 0; r < n; ++r) {
+        const int64_t slot = next_slot(rp, n, last, lane);
+        last = slot;
+        const int64_t pp = (int64_t)sb * c.cap + slot;
+        const float wgt = __expf(part_lse[pp] - m);
+        ssum += wgt;
+        const T* src = part_o + pp * c.d;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int c = lane * 2 + i * 64;
-        if (c < d) {
-          const float2 x = Elem<T>::to_f2(*reinterpret_cast<const T2*>(src + part_col(pos, c, 8)));
-          acc[i].x = fmaf(wgt, x.x, acc[i].x);
-          acc[i].y = fmaf(wgt, x.y, acc[i].y);
+        for (int i = 0; i < 4; ++i) {
+          const int col = lane * 2 + i * 64;
+          if (col < c.d) {
+            const float2 x = Elem<T>::to_f2(*reinterpret_cast<const T2*>(src + part_col(slot, col, 8)));
+            acc[i].x = fmaf(wgt, x.x, acc[i].x);
+            acc[i].y = fmaf(wgt, x.y, acc[i].y);
+          }
         }
       }
     }
   }
   const float inv = ssum > 0.f ? 1.f / ssum : 0.f;
+  const int h = c.h0 + hr;
   T* dst = out + t * o_rs + (int64_t)h * o_hs;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int c = lane * 2 + i * 64;
-    if (c < d) *reinterpret_cast<T2*>(dst + c) = Elem<T>::from_f2(acc[i].x * inv, acc[i].y * inv);
+    const int col = lane * 2 + i * 64;
+    if (col < c.d) *reinterpret_cast<T2*>(dst + col) = Elem<T>::from_f2(acc[i].x * inv, acc[i].y * inv);
   }
-  if (lane == 0) lse[rid] = ssum > 0.f ? m + logf(ssum) : CUDART_INF_F;
+  if (lane == 0) lse[(int64_t)h * c.total_q + t] = ssum > 0.f ? m + logf(ssum) : CUDART_INF_F;
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) bwd_combine_kernel(const float* __restrict__ part_dq,
-                                                          const uint32_t* __restrict__ row_ptr,
-                                                          const uint32_t* __restrict__ row_pos, T* dq,
-                                                          int64_t rs, int64_t hs, int64_t total_q, int heads,
-                                                          int d, float scale, const int* only_if, int min_n) {
+__global__ void __launch_bounds__(256) bwd_combine_kernel(const float* __restrict__ part_dq, CombineParams c, T* dq,
+                                                          int64_t rs, int64_t hs, float scale, const int* only_if,
+                                                          int min_n) {
   using T2 = typename Elem<T>::T2;
   if (only_if && *only_if == 0) return;
   const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (wid >= total_q * heads) return;
-  const int64_t t = wid / heads;
-  const int h = (int)(wid - t * heads);
-  const int64_t rid = (int64_t)h * total_q + t;
-  const uint32_t p0 = row_ptr[rid];
-  const int n = (int)(row_ptr[rid + 1] - p0);
-  if (n < min_n) return;
-  const uint32_t* rp = row_pos + p0;
+  if (wid >= c.total_q * c.nh) return;
+  const int64_t t = wid / c.nh;
+  const int hr = (int)(wid - t * c.nh);
+  const int64_t rid = (int64_t)hr * c.total_q + t;
+  const uint32_t p0 = c.row_ptr[rid];
+  const int n = (int)(c.row_ptr[rid + 1] - p0);
+  if (n * c.nsub < min_n) return;
+  const uint32_t* rp = c.row_pos + p0;
   float2 acc[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) acc[i] = make_float2(0.f, 0.f);
-  int64_t last = -1;
-  for (int r = 0; r < n; ++r) {
-    const int64_t pos = next_pos(rp, n, last, lane);
-    last = pos;
-    const float* src = part_dq + pos * d;
+  for (int sb = 0; sb < c.nsub; ++sb) {
+    int64_t last = -1;
+    for (int r = 0; r < n; ++r) {
+      const int64_t slot = next_slot(rp, n, last, lane);
+      last = slot;
+      const float* src = part_dq + ((int64_t)sb * c.cap + slot) * c.d;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int c = lane * 2 + i * 64;
-      if (c < d) {
-        const float2 x = *reinterpret_cast<const float2*>(src + part_col(pos, c, 4));
-        acc[i].x += x.x;
-        acc[i].y += x.y;
+      for (int i = 0; i < 4; ++i) {
+        const int col = lane * 2 + i * 64;
+        if (col < c.d) {
+          const float2 x = *reinterpret_cast<const float2*>(src + part_col(slot, col, 4));
+          acc[i].x += x.x;
+          acc[i].y += x.y;
+        }
       }
     }
   }
-  T* dst = dq + t * rs + (int64_t)h * hs;
+  T* dst = dq + t * rs + (int64_t)(c.h0 + hr) * hs;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int c = lane * 2 + i * 64;
-    if (c < d) *reinterpret_cast<T2*>(dst + c) = Elem<T>::from_f2(acc[i].x * scale, acc[i].y * scale);
+    const int col = lane * 2 + i * 64;
+    if (col < c.d) *reinterpret_cast<T2*>(dst + col) = Elem<T>::from_f2(acc[i].x * scale, acc[i].y * scale);
   }
 }
 
 // ------------------------------------------------------------------ fast combine (rows of <= G partials)
-// G lanes per (token, head) row, 32/G rows per warp.  Lane j of a group first fetches the
-// position and log-sum-exp of the row's j-th partial; the group ranks the positions (merge
-// order = ascending position, whatever order the atomics of the row-list build produced);
+// G lanes per (token, head) row, 32/G rows per warp.  Lane j of a group first fetches the plane
+// position (sb*cap + slot) and log-sum-exp of the row's j-th partial; the group ranks the positions
+// (merge order = ascending position, whatever order the atomics of the row-list build produced);
 // then every lane fetches its d/G elements of ALL the row's partial rows before the ordered
-// accumulation.  Several rows per warp and all loads of a row in flight at once hide the
-// chain of dependent, scattered reads.  Rows with more than G partials set *overflow and are
-// left to the next kernel (larger G, finally the generic one).
+// accumulation.  Several rows per warp and all loads of a row in flight at once hide the chain of
+// dependent, scattered reads.  Rows with more than G partials set *overflow and are left to the
+// next kernel (larger G, finally the generic one).
 template <int G>
 __device__ __forceinline__ unsigned group_mask(int lane) {
   return G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (lane & ~(G - 1)));
 }
 
+// common prologue: the row of this lane group and the plane position held by this lane
+struct GroupRow {
+  int64_t t; int hr; int64_t rid; int n; bool mine; bool valid; uint32_t pos; uint32_t slot;
+};
+template <int G>
+__device__ __forceinline__ GroupRow group_row(const CombineParams& c, int min_n, int* overflow) {
+  GroupRow g;
+  const int lane = threadIdx.x & 31, gl = lane & (G - 1);
+  const int64_t gid = (((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * (32 / G) + (lane / G);
+  const bool row_ok = gid < c.total_q * c.nh;
+  g.t = row_ok ? gid / c.nh : 0;
+  g.hr = row_ok ? (int)(gid - g.t * c.nh) : 0;
+  g.rid = (int64_t)g.hr * c.total_q + g.t;
+  uint32_t p0 = 0;
+  int n_e = 0;
+  if (row_ok) {
+    p0 = c.row_ptr[g.rid];
+    n_e = (int)(c.row_ptr[g.rid + 1] - p0);
+  }
+  g.n = n_e * c.nsub;                       // partials of the row
+  g.mine = row_ok && g.n >= min_n;          // rows below min_n were done by the previous kernel
+  if (g.n > G) {
+    if (gl == 0) *overflow = 1;
+    g.mine = false;
+  }
+  if (!g.mine) g.n = 0;
+  g.valid = gl < g.n;
+  g.slot = g.valid ? c.row_pos[p0 + gl / c.nsub] : 0u;
+  g.pos = g.valid ? (uint32_t)((gl % c.nsub) * c.cap) + g.slot : 0xffffffffu;
+  return g;
+}
+
 template <typename T, int G, int EPL>
 __global__ void __launch_bounds__(256) fwd_combine_group_kernel(const T* __restrict__ part_o,
                                                                 const float* __restrict__ part_lse,
-                                                                const uint32_t* __restrict__ row_ptr,
-                                                                const uint32_t* __restrict__ row_pos, T* out,
-                                                                int64_t o_rs, int64_t o_hs, float* lse,
-                                                                int64_t total_q, int heads, int min_n,
-                                                                const int* only_if, int* overflow) {
+                                                                CombineParams c, T* out, int64_t o_rs, int64_t o_hs,
+                                                                float* lse, int min_n, const int* only_if,
+                                                                int* overflow) {
   constexpr int d = G * EPL;
   constexpr int NV = EPL / 8;                 // 16-byte loads per partial row per lane
   static_assert(EPL % 8 == 0, "a lane owns whole 16-byte chunks");
   if (only_if && *only_if == 0) return;
   const int lane = threadIdx.x & 31, gl = lane & (G - 1);
-  const int64_t gid = (((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * (32 / G) + (lane / G);
-  const bool row_ok = gid < total_q * heads;
   const unsigned gm = group_mask<G>(lane);
-  const int64_t t = row_ok ? gid / heads : 0;
-  const int h = row_ok ? (int)(gid - t * heads) : 0;
-  const int64_t rid = (int64_t)h * total_q + t;
-  uint32_t p0 = 0;
-  int n = 0;
-  if (row_ok) {
-    p0 = row_ptr[rid];
-    n = (int)(row_ptr[rid + 1] - p0);
-  }
-  bool mine = row_ok && n >= min_n;           // rows below min_n were done by the previous kernel
-  if (n > G) {
-    if (gl == 0) *overflow = 1;
-    mine = false;
-  }
-  if (!mine) n = 0;
-  const bool valid = gl < n;
-  const uint32_t pos = valid ? row_pos[p0 + gl] : 0xffffffffu;
-  const float l = valid ? part_lse[pos] : -CUDART_INF_F;
+  const GroupRow g = group_row<G>(c, min_n, overflow);
+  const float l = g.valid ? part_lse[g.pos] : -CUDART_INF_F;
   float m = l;
 #pragma unroll
   for (int o = G / 2; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(gm, m, o, G));
-  const float w = (valid && m > -CUDART_INF_F) ? __expf(l - m) : 0.f;
+  const float w = (g.valid && m > -CUDART_INF_F) ? __expf(l - m) : 0.f;
   int rank = 0;
 #pragma unroll
-  for (int i = 0; i < G; ++i) rank += (__shfl_sync(gm, pos, i, G) < pos) ? 1 : 0;
+  for (int i = 0; i < G; ++i) rank += (__shfl_sync(gm, g.pos, i, G) < g.pos) ? 1 : 0;
   float acc[EPL];
 #pragma unroll
   for (int i = 0; i < EPL; ++i) acc[i] = 0.f;
@@ -356,14 +433,15 @@ __global__ void __launch_bounds__(256) fwd_combine_group_kernel(const T* __restr
 #pragma unroll
     for (int k = 0; k < B; ++k) {
       // the lane of this group whose partial has rank r0+k (none if the row is shorter)
-      const unsigned hit = __ballot_sync(0xffffffffu, valid && rank == r0 + k) & gm;
+      const unsigned hit = __ballot_sync(0xffffffffu, g.valid && rank == r0 + k) & gm;
       const int src = hit ? (__ffs(hit) - 1) : lane;
-      const uint32_t pk = __shfl_sync(0xffffffffu, pos, src);
+      const uint32_t pk = __shfl_sync(0xffffffffu, g.pos, src);
+      const uint32_t sk = __shfl_sync(0xffffffffu, g.slot, src);
       wk[k] = hit ? __shfl_sync(0xffffffffu, w, src) : 0.f;
       if (hit && wk[k] > 0.f) {
         const T* row = part_o + (int64_t)pk * d;
 #pragma unroll
-        for (int v = 0; v < NV; ++v) x[k][v] = *reinterpret_cast<const uint4*>(row + part_col(pk, gl * EPL + 8 * v, 8));
+        for (int v = 0; v < NV; ++v) x[k][v] = *reinterpret_cast<const uint4*>(row + part_col(sk, gl * EPL + 8 * v, 8));
       } else {
 #pragma unroll
         for (int v = 0; v < NV; ++v) x[k][v] = make_uint4(0, 0, 0, 0);
@@ -381,54 +459,34 @@ __global__ void __launch_bounds__(256) fwd_combine_group_kernel(const T* __restr
       }
     }
   }
-  if (mine) {
+  if (g.mine) {
     const float inv = ssum > 0.f ? 1.f / ssum : 0.f;
-    T* dst = out + t * o_rs + (int64_t)h * o_hs + gl * EPL;
+    const int h = c.h0 + g.hr;
+    T* dst = out + g.t * o_rs + (int64_t)h * o_hs + gl * EPL;
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[8 * v + e] *= inv;
       *reinterpret_cast<uint4*>(dst + 8 * v) = pack8<T>(acc + 8 * v);
     }
-    if (gl == 0) lse[rid] = ssum > 0.f ? m + logf(ssum) : CUDART_INF_F;
+    if (gl == 0) lse[(int64_t)h * c.total_q + g.t] = ssum > 0.f ? m + logf(ssum) : CUDART_INF_F;
   }
 }
 
 template <typename T, int G, int EPL>
-__global__ void __launch_bounds__(256) bwd_combine_group_kernel(const float* __restrict__ part_dq,
-                                                                const uint32_t* __restrict__ row_ptr,
-                                                                const uint32_t* __restrict__ row_pos, T* dq,
-                                                                int64_t rs, int64_t hs, int64_t total_q,
-                                                                int heads, float scale, int min_n,
+__global__ void __launch_bounds__(256) bwd_combine_group_kernel(const float* __restrict__ part_dq, CombineParams c,
+                                                                T* dq, int64_t rs, int64_t hs, float scale, int min_n,
                                                                 const int* only_if, int* overflow) {
   constexpr int d = G * EPL;
   constexpr int NV = EPL / 4;                 // 16-byte (4 float) loads per partial row per lane
   static_assert(EPL % 8 == 0, "a lane owns whole 16-byte chunks of the output");
   if (only_if && *only_if == 0) return;
   const int lane = threadIdx.x & 31, gl = lane & (G - 1);
-  const int64_t gid = (((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * (32 / G) + (lane / G);
-  const bool row_ok = gid < total_q * heads;
   const unsigned gm = group_mask<G>(lane);
-  const int64_t t = row_ok ? gid / heads : 0;
-  const int h = row_ok ? (int)(gid - t * heads) : 0;
-  const int64_t rid = (int64_t)h * total_q + t;
-  uint32_t p0 = 0;
-  int n = 0;
-  if (row_ok) {
-    p0 = row_ptr[rid];
-    n = (int)(row_ptr[rid + 1] - p0);
-  }
-  bool mine = row_ok && n >= min_n;
-  if (n > G) {
-    if (gl == 0) *overflow = 1;
-    mine = false;
-  }
-  if (!mine) n = 0;
-  const bool valid = gl < n;
-  const uint32_t pos = valid ? row_pos[p0 + gl] : 0xffffffffu;
+  const GroupRow g = group_row<G>(c, min_n, overflow);
   int rank = 0;
 #pragma unroll
-  for (int i = 0; i < G; ++i) rank += (__shfl_sync(gm, pos, i, G) < pos) ? 1 : 0;
+  for (int i = 0; i < G; ++i) rank += (__shfl_sync(gm, g.pos, i, G) < g.pos) ? 1 : 0;
   float acc[EPL];
 #pragma unroll
   for (int i = 0; i < EPL; ++i) acc[i] = 0.f;
@@ -438,13 +496,14 @@ __global__ void __launch_bounds__(256) bwd_combine_group_kernel(const float* __r
     float4 x[B][NV];
 #pragma unroll
     for (int k = 0; k < B; ++k) {
-      const unsigned hit = __ballot_sync(0xffffffffu, valid && rank == r0 + k) & gm;
+      const unsigned hit = __ballot_sync(0xffffffffu, g.valid && rank == r0 + k) & gm;
       const int src = hit ? (__ffs(hit) - 1) : lane;
-      const uint32_t pk = __shfl_sync(0xffffffffu, pos, src);
+      const uint32_t pk = __shfl_sync(0xffffffffu, g.pos, src);
+      const uint32_t sk = __shfl_sync(0xffffffffu, g.slot, src);
       if (hit) {
         const float* row = part_dq + (int64_t)pk * d;
 #pragma unroll
-        for (int v = 0; v < NV; ++v) x[k][v] = *reinterpret_cast<const float4*>(row + part_col(pk, gl * EPL + 4 * v, 4));
+        for (int v = 0; v < NV; ++v) x[k][v] = *reinterpret_cast<const float4*>(row + part_col(sk, gl * EPL + 4 * v, 4));
       } else {
 #pragma unroll
         for (int v = 0; v < NV; ++v) x[k][v] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -458,8 +517,8 @@ __global__ void __launch_bounds__(256) bwd_combine_group_kernel(const float* __r
       }
     }
   }
-  if (mine) {
-    T* dst = dq + t * rs + (int64_t)h * hs + gl * EPL;
+  if (g.mine) {
+    T* dst = dq + g.t * rs + (int64_t)(c.h0 + g.hr) * hs + gl * EPL;
 #pragma unroll
     for (int v = 0; v < EPL / 8; ++v) {
 #pragma unroll
@@ -495,77 +554,83 @@ __global__ void __launch_bounds__(256) dot_do_o_kernel(const T* __restrict__ dou
 
 static unsigned warp_grid(int64_t warps) { return (unsigned)ceil_div64(warps, 8); }
 
-// Cascade: G = 8 (rows of <= 8 partials), 16, 32, then the generic kernel; each later stage
-// runs only the rows the earlier ones left and exits at once if there were none.
+// Cascade: G = 8 (rows of <= 8 partials), 16, then the generic kernel; each later stage runs only
+// the rows the earlier ones left and exits at once if there were none.
 static unsigned group_grid(int64_t rows, int G) { return (unsigned)ceil_div64(ceil_div64(rows, 32 / G), 8); }
 
+static CombineParams make_combine(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps) {
+  CombineParams c;
+  c.row_ptr = w.row_ptr; c.row_pos = w.row_pos; c.total_q = a.total_q; c.cap = w.cap; c.heads_out = a.heads;
+  c.h0 = ps.h0; c.nh = ps.nh; c.nsub = w.nsub; c.d = a.d;
+  return c;
+}
+
 template <typename T, int D>
-static int fwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
-  const int64_t rows = a.total_q * a.heads;
+static int fwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
+  const int64_t rows = a.total_q * ps.nh;
+  const CombineParams c = make_combine(a, w, ps);
   int* ovf = w.status + 1;   // words 1..3 of the status block, zeroed with it
   const T* po = (const T*)w.part_o;
   T* out = (T*)a.o;
-  fwd_combine_group_kernel<T, 8, D / 8><<<group_grid(rows, 8), 256, 0, s>>>(
-      po, w.part_lse, w.row_ptr, w.row_pos, out, a.o_rs, a.o_hs, a.lse, a.total_q, a.heads, 0, nullptr, ovf);
+  fwd_combine_group_kernel<T, 8, D / 8><<<group_grid(rows, 8), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs,
+                                                                            a.lse, 0, nullptr, ovf);
   FMB_LAUNCH_CHECK("fwd_combine_group_kernel<8>");
-  fwd_combine_group_kernel<T, 16, D / 16><<<group_grid(rows, 16), 256, 0, s>>>(
-      po, w.part_lse, w.row_ptr, w.row_pos, out, a.o_rs, a.o_hs, a.lse, a.total_q, a.heads, 9, ovf, ovf + 1);
+  fwd_combine_group_kernel<T, 16, D / 16><<<group_grid(rows, 16), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs,
+                                                                              a.o_hs, a.lse, 9, ovf, ovf + 1);
   FMB_LAUNCH_CHECK("fwd_combine_group_kernel<16>");
-  fwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>(po, w.part_lse, w.row_ptr, w.row_pos, out, a.o_rs, a.o_hs,
-                                                        a.lse, a.total_q, a.heads, a.d, ovf + 1, 17);
+  fwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, ovf + 1, 17);
   FMB_LAUNCH_CHECK("fwd_combine_kernel");
   return FMB_OK;
 }
 
 template <typename T>
-static int fwd_combine_any(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
-  if (a.d == 128) return fwd_combine_dispatch<T, 128>(a, w, s);
-  if (a.d == 256) return fwd_combine_dispatch<T, 256>(a, w, s);
-  const int64_t rows = a.total_q * a.heads;
-  fwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>((const T*)w.part_o, w.part_lse, w.row_ptr, w.row_pos,
-                                                        (T*)a.o, a.o_rs, a.o_hs, a.lse, a.total_q, a.heads, a.d,
-                                                        nullptr, 0);
+static int fwd_combine_any(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
+  if (a.d == 128) return fwd_combine_dispatch<T, 128>(a, w, ps, s);
+  if (a.d == 256) return fwd_combine_dispatch<T, 256>(a, w, ps, s);
+  const int64_t rows = a.total_q * ps.nh;
+  fwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>((const T*)w.part_o, w.part_lse, make_combine(a, w, ps),
+                                                        (T*)a.o, a.o_rs, a.o_hs, a.lse, nullptr, 0);
   FMB_LAUNCH_CHECK("fwd_combine_kernel");
   return FMB_OK;
 }
 
-int launch_fwd_combine(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
-  if (a.total_q * a.heads == 0) return FMB_OK;
-  return a.dtype == FMB_BF16 ? fwd_combine_any<__nv_bfloat16>(a, w, s) : fwd_combine_any<__half>(a, w, s);
+int launch_fwd_combine(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
+  if (a.total_q * ps.nh == 0) return FMB_OK;
+  return a.dtype == FMB_BF16 ? fwd_combine_any<__nv_bfloat16>(a, w, ps, s) : fwd_combine_any<__half>(a, w, ps, s);
 }
 
 template <typename T, int D>
-static int bwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
-  const int64_t rows = a.total_q * a.heads;
+static int bwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
+  const int64_t rows = a.total_q * ps.nh;
+  const CombineParams c = make_combine(a, w, ps);
   int* ovf = w.status + 1;
   const float* pd = (const float*)w.part_o;
   T* dq = (T*)a.dq;
-  bwd_combine_group_kernel<T, 8, D / 8><<<group_grid(rows, 8), 256, 0, s>>>(
-      pd, w.row_ptr, w.row_pos, dq, a.dq_rs, a.dq_hs, a.total_q, a.heads, a.scale, 0, nullptr, ovf);
+  bwd_combine_group_kernel<T, 8, D / 8><<<group_grid(rows, 8), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, a.scale, 0,
+                                                                            nullptr, ovf);
   FMB_LAUNCH_CHECK("bwd_combine_group_kernel<8>");
-  bwd_combine_group_kernel<T, 16, D / 16><<<group_grid(rows, 16), 256, 0, s>>>(
-      pd, w.row_ptr, w.row_pos, dq, a.dq_rs, a.dq_hs, a.total_q, a.heads, a.scale, 9, ovf, ovf + 1);
+  bwd_combine_group_kernel<T, 16, D / 16><<<group_grid(rows, 16), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, a.scale,
+                                                                              9, ovf, ovf + 1);
   FMB_LAUNCH_CHECK("bwd_combine_group_kernel<16>");
-  bwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>(pd, w.row_ptr, w.row_pos, dq, a.dq_rs, a.dq_hs, a.total_q,
-                                                        a.heads, a.d, a.scale, ovf + 1, 17);
+  bwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, a.scale, ovf + 1, 17);
   FMB_LAUNCH_CHECK("bwd_combine_kernel");
   return FMB_OK;
 }
 
 template <typename T>
-static int bwd_combine_any(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
-  if (a.d == 128) return bwd_combine_dispatch<T, 128>(a, w, s);
-  if (a.d == 256) return bwd_combine_dispatch<T, 256>(a, w, s);
-  const int64_t rows = a.total_q * a.heads;
-  bwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>((const float*)w.part_o, w.row_ptr, w.row_pos, (T*)a.dq,
-                                                        a.dq_rs, a.dq_hs, a.total_q, a.heads, a.d, a.scale, nullptr, 0);
+static int bwd_combine_any(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
+  if (a.d == 128) return bwd_combine_dispatch<T, 128>(a, w, ps, s);
+  if (a.d == 256) return bwd_combine_dispatch<T, 256>(a, w, ps, s);
+  const int64_t rows = a.total_q * ps.nh;
+  bwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>((const float*)w.part_o, make_combine(a, w, ps), (T*)a.dq,
+                                                        a.dq_rs, a.dq_hs, a.scale, nullptr, 0);
   FMB_LAUNCH_CHECK("bwd_combine_kernel");
   return FMB_OK;
 }
 
-int launch_bwd_combine(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
-  if (a.total_q * a.heads == 0) return FMB_OK;
-  return a.dtype == FMB_BF16 ? bwd_combine_any<__nv_bfloat16>(a, w, s) : bwd_combine_any<__half>(a, w, s);
+int launch_bwd_combine(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
+  if (a.total_q * ps.nh == 0) return FMB_OK;
+  return a.dtype == FMB_BF16 ? bwd_combine_any<__nv_bfloat16>(a, w, ps, s) : bwd_combine_any<__half>(a, w, ps, s);
 }
 
 int launch_dot_do_o(const AttnArgs& a, cudaStream_t s) {
@@ -584,34 +649,52 @@ int launch_dot_do_o(const AttnArgs& a, cudaStream_t s) {
 }
 
 // ------------------------------------------------------------------ drivers
-int launch_attn_fwd(const AttnArgs& a, int engine, cudaStream_t s) {
-  AttnWorkspace w = carve_attn_workspace(a.ws, a.total_q, a.heads, a.d, a.n_indices, 2, true);
+// Each pass: slot and row lists of its heads, main kernel (partials), combine.  The status block
+// is cleared once per call, so a failure in any pass stays visible.
+static int check_pass_sizes(const char* op, const AttnArgs& a, const AttnWorkspace& w, size_t need_one_group) {
   if (a.ws == nullptr || a.ws_bytes < w.bytes)
-    return fail(FMB_ERR_WORKSPACE, "attn_fwd: workspace too small (%zu < %zu)", a.ws_bytes, w.bytes);
-  int rc = build_row_lists(a, w, s);
+    return fail(FMB_ERR_WORKSPACE, "%s: workspace too small (%zu bytes given; a pass over one kv-head group needs %zu)",
+                op, a.ws_bytes, need_one_group);
+  if ((int64_t)w.nsub * w.cap >= (int64_t)0xffffffffll)
+    return fail(FMB_ERR_BAD_ARG, "%s: too many partial slots in one pass; give a smaller workspace", op);
+  return FMB_OK;
+}
+
+int launch_attn_fwd(const AttnArgs& a, int engine, cudaStream_t s) {
+  AttnWorkspace w = carve_attn_workspace(a.ws, a.ws_bytes, a, 2, true, 0);
+  int rc = check_pass_sizes("attn_fwd", a, w, w.bytes);
   if (rc) return rc;
-  prof_begin(0, s);
-  if (engine == 1 && tc_supported(a, false)) rc = launch_fwd_main_tc(a, w, s);
-  else rc = launch_fwd_main_simt(a, w, s);
-  prof_end(0, s);
-  if (rc) return rc;
-  return launch_fwd_combine(a, w, s);
+  FMB_CUDA(cudaMemsetAsync(w.status, 0, 512, s));
+  for (int h0 = 0; h0 < a.heads; h0 += w.nh) {
+    const PassParams ps = make_pass(a, w, h0, min(w.nh, a.heads - h0));
+    if ((rc = build_row_lists(a, w, ps, s))) return rc;
+    prof_begin(0, s);
+    if (engine == 1 && tc_supported(a, false)) rc = launch_fwd_main_tc(a, w, ps, s);
+    else rc = launch_fwd_main_simt(a, w, ps, s);
+    prof_end(0, s);
+    if (rc) return rc;
+    if ((rc = launch_fwd_combine(a, w, ps, s))) return rc;
+  }
+  return FMB_OK;
 }
 
 int launch_attn_bwd(const AttnArgs& a, int engine, cudaStream_t s) {
-  AttnWorkspace w = carve_attn_workspace(a.ws, a.total_q, a.heads, a.d, a.n_indices, 4, false);
-  if (a.ws == nullptr || a.ws_bytes < w.bytes)
-    return fail(FMB_ERR_WORKSPACE, "attn_bwd: workspace too small (%zu < %zu)", a.ws_bytes, w.bytes);
-  int rc = build_row_lists(a, w, s);
+  AttnWorkspace w = carve_attn_workspace(a.ws, a.ws_bytes, a, 4, false, 0);
+  int rc = check_pass_sizes("attn_bwd", a, w, w.bytes);
   if (rc) return rc;
-  rc = launch_dot_do_o(a, s);
-  if (rc) return rc;
-  prof_begin(1, s);
-  if (engine == 1 && tc_supported(a, true)) rc = launch_bwd_main_tc(a, w, s);
-  else rc = launch_bwd_main_simt(a, w, s);
-  prof_end(1, s);
-  if (rc) return rc;
-  return launch_bwd_combine(a, w, s);
+  FMB_CUDA(cudaMemsetAsync(w.status, 0, 512, s));
+  if ((rc = launch_dot_do_o(a, s))) return rc;
+  for (int h0 = 0; h0 < a.heads; h0 += w.nh) {
+    const PassParams ps = make_pass(a, w, h0, min(w.nh, a.heads - h0));
+    if ((rc = build_row_lists(a, w, ps, s))) return rc;
+    prof_begin(1, s);
+    if (engine == 1 && tc_supported(a, true)) rc = launch_bwd_main_tc(a, w, ps, s);
+    else rc = launch_bwd_main_simt(a, w, ps, s);
+    prof_end(1, s);
+    if (rc) return rc;
+    if ((rc = launch_bwd_combine(a, w, ps, s))) return rc;
+  }
+  return FMB_OK;
 }
 
 }  // namespace fmb

@@ -17,10 +17,10 @@ struct SimtParams {
   int64_t q_rs, q_hs, k_rs, k_hs, v_rs, v_hs, do_rs, do_hs;
   void *dk, *dv; int64_t dk_rs, dk_hs, dv_rs, dv_hs;
   const float *lse, *softmax_d;
-  const int64_t* col_offsets; const int32_t* col_nnz; const int32_t* indices; int64_t n_indices;
+  PassParams ps;
   const int32_t *cu_q, *cu_k;
   void* part_o; float* part_lse;
-  int heads, heads_k, ncol; int64_t total_q;
+  int heads, heads_k; int64_t total_q;
   float scale; int causal;
 };
 
@@ -98,15 +98,16 @@ __global__ void __launch_bounds__(kSimtThreads) fwd_main_simt_kernel(SimtParams 
   int* sRow = reinterpret_cast<int*>(sS + kSimtM * SS);     // [64]
   float* sInv = reinterpret_cast<float*>(sRow + kSimtM);    // [64]
 
-  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int64_t ci = ((int64_t)b * p.heads + h) * p.ncol + c;
-  const int nnz = p.col_nnz[ci];
+  // C is the key block: chunk c of the pattern is covered by nsub blocks of C keys
+  const int c = blockIdx.x / p.ps.nsub, sb = blockIdx.x % p.ps.nsub, h = p.ps.h0 + blockIdx.y, b = blockIdx.z;
+  const ColRef col = column_of(p.ps, b, h, c);
+  const int nnz = col.nnz;
   if (nnz <= 0) return;
-  const int64_t off = p.col_offsets[ci];
-  if (off < 0 || off + nnz > p.n_indices) return;
+  const int64_t off = col.off;
+  const int64_t slot0 = col.slot, plane = (int64_t)sb * p.ps.cap;
   const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
   const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
-  const int key0 = c * C;
+  const int key0 = c * p.ps.chunk + sb * C;
   const int keys_valid = max(0, min(C, len_k - key0));
   const int hk = h / (p.heads / p.heads_k);
   const int shift = len_k - len_q;
@@ -127,7 +128,7 @@ __global__ void __launch_bounds__(kSimtThreads) fwd_main_simt_kernel(SimtParams 
     if (threadIdx.x < kSimtM) {
       int r = -1;
       if (threadIdx.x < rows) {
-        r = p.indices[off + t0 + threadIdx.x];
+        r = p.ps.indices[off + t0 + threadIdx.x];
         if (r < 0 || r >= len_q) r = -1;
       }
       sRow[threadIdx.x] = r;
@@ -169,7 +170,7 @@ __global__ void __launch_bounds__(kSimtThreads) fwd_main_simt_kernel(SimtParams 
       for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
       if (lane == 0) {
         sInv[m] = sum > 0.f ? 1.f / sum : 0.f;
-        if (m < rows) p.part_lse[off + t0 + m] = sum > 0.f ? mx * p.scale + logf(sum) : -CUDART_INF_F;
+        if (m < rows) p.part_lse[plane + slot0 + t0 + m] = sum > 0.f ? mx * p.scale + logf(sum) : -CUDART_INF_F;
       }
     }
     __syncthreads();
@@ -195,10 +196,10 @@ __global__ void __launch_bounds__(kSimtThreads) fwd_main_simt_kernel(SimtParams 
       const int m = ty * 4 + i;
       if (m < rows) {
         const float inv = sInv[m];
-        const int64_t pos = off + t0 + m;
-        T* dst = part_o + pos * D;
+        const int64_t slot = slot0 + t0 + m;
+        T* dst = part_o + (plane + slot) * D;
 #pragma unroll
-        for (int x = 0; x < TD; ++x) dst[part_col(pos, tx * TD + x, 8)] = Elem<T>::from_f(o[i][x] * inv);
+        for (int x = 0; x < TD; ++x) dst[part_col(slot, tx * TD + x, 8)] = Elem<T>::from_f(o[i][x] * inv);
       }
     }
   }
@@ -222,13 +223,17 @@ __global__ void __launch_bounds__(kSimtThreads) bwd_main_simt_kernel(SimtParams 
   float* sLse = reinterpret_cast<float*>(sRow + kSimtM);    // [64]
   float* sD = sLse + kSimtM;                                // [64]
 
-  const int c = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int group = p.heads / p.heads_k;
+  const int c = blockIdx.x / p.ps.nsub, sb = blockIdx.x % p.ps.nsub, hk = p.ps.h0 / group + blockIdx.y, b = blockIdx.z;
+  const int64_t plane = (int64_t)sb * p.ps.cap;
   const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
   const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
-  const int key0 = c * C;
-  if (key0 >= len_k) return;
+  const int key0 = c * p.ps.chunk + sb * C;
+  if (key0 >= len_k) {
+    zero_dq_partials(p.ps, static_cast<float*>(p.part_o), plane, b, hk, group, c, D);
+    return;
+  }
   const int keys_valid = min(C, len_k - key0);
-  const int group = p.heads / p.heads_k;
   const int shift = len_k - len_q;
   const float scale_log2 = p.scale * kLog2e;
   const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
@@ -248,11 +253,10 @@ __global__ void __launch_bounds__(kSimtThreads) bwd_main_simt_kernel(SimtParams 
 
   for (int hg = 0; hg < group; ++hg) {
     const int h = hk * group + hg;
-    if (c >= p.ncol) break;
-    const int64_t ci = ((int64_t)b * p.heads + h) * p.ncol + c;
-    const int nnz = p.col_nnz[ci];
-    const int64_t off = p.col_offsets[ci];
-    if (nnz <= 0 || off < 0 || off + nnz > p.n_indices) continue;
+    const ColRef col = column_of(p.ps, b, h, c);
+    const int nnz = col.nnz;
+    const int64_t off = col.off, slot0 = col.slot;
+    if (nnz <= 0) continue;
     const T* qbase = static_cast<const T*>(p.q) + (int64_t)q0 * p.q_rs + (int64_t)h * p.q_hs;
     const T* dobase = static_cast<const T*>(p.dout) + (int64_t)q0 * p.do_rs + (int64_t)h * p.do_hs;
     const float* lse = p.lse + (int64_t)h * p.total_q + q0;
@@ -265,7 +269,7 @@ __global__ void __launch_bounds__(kSimtThreads) bwd_main_simt_kernel(SimtParams 
         int r = -1;
         float l = CUDART_INF_F, dd = 0.f;
         if (threadIdx.x < rows) {
-          r = p.indices[off + t0 + threadIdx.x];
+          r = p.ps.indices[off + t0 + threadIdx.x];
           if (r < 0 || r >= len_q) r = -1;
           else { l = lse[r]; dd = dsum[r]; }
         }
@@ -342,10 +346,10 @@ __global__ void __launch_bounds__(kSimtThreads) bwd_main_simt_kernel(SimtParams 
         for (int i = 0; i < 4; ++i) {
           const int m = ty * 4 + i;
           if (m < rows) {
-            const int64_t pos = off + t0 + m;
-            float* dst = part_dq + pos * D;
+            const int64_t slot = slot0 + t0 + m;
+            float* dst = part_dq + (plane + slot) * D;
 #pragma unroll
-            for (int j = 0; j < TD; ++j) dst[part_col(pos, tx * TD + j, 4)] = dq[i][j];
+            for (int j = 0; j < TD; ++j) dst[part_col(slot, tx * TD + j, 4)] = dq[i][j];
           }
         }
       }
@@ -367,86 +371,63 @@ __global__ void __launch_bounds__(kSimtThreads) bwd_main_simt_kernel(SimtParams 
   }
 }
 
-// pairs whose chunk lies beyond the keys of the sequence: empty partials
-__global__ void __launch_bounds__(256) fwd_dead_columns_kernel(SimtParams p, int chunk, int d, int elem_bytes) {
-  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int len_k = p.cu_k[b + 1] - p.cu_k[b];
-  if (c * chunk < len_k) return;
-  const int64_t ci = ((int64_t)b * p.heads + h) * p.ncol + c;
-  const int nnz = p.col_nnz[ci];
-  const int64_t off = p.col_offsets[ci];
-  if (nnz <= 0 || off < 0 || off + nnz > p.n_indices) return;
-  for (int j = threadIdx.x; j < nnz; j += blockDim.x) p.part_lse[off + j] = -CUDART_INF_F;
-  const int64_t words = (int64_t)nnz * d * elem_bytes / 4;
-  uint32_t* dst = reinterpret_cast<uint32_t*>(static_cast<char*>(p.part_o) + off * d * elem_bytes);
-  for (int64_t i = threadIdx.x; i < words; i += blockDim.x) dst[i] = 0u;
-}
-
-static SimtParams make_params(const AttnArgs& a, const AttnWorkspace& w) {
+static SimtParams make_params(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps) {
   SimtParams p;
   p.q = a.q; p.k = a.k; p.v = a.v; p.dout = a.dout;
   p.q_rs = a.q_rs; p.q_hs = a.q_hs; p.k_rs = a.k_rs; p.k_hs = a.k_hs; p.v_rs = a.v_rs; p.v_hs = a.v_hs;
   p.do_rs = a.do_rs; p.do_hs = a.do_hs;
   p.dk = a.dk; p.dv = a.dv; p.dk_rs = a.dk_rs; p.dk_hs = a.dk_hs; p.dv_rs = a.dv_rs; p.dv_hs = a.dv_hs;
   p.lse = a.lse; p.softmax_d = a.softmax_d;
-  p.col_offsets = a.col_offsets; p.col_nnz = a.col_nnz; p.indices = a.indices; p.n_indices = a.n_indices;
+  p.ps = ps;
   p.cu_q = a.cu_q; p.cu_k = a.cu_k; p.part_o = w.part_o; p.part_lse = w.part_lse;
-  p.heads = a.heads; p.heads_k = a.heads_k; p.ncol = a.ncol; p.total_q = a.total_q;
+  p.heads = a.heads; p.heads_k = a.heads_k; p.total_q = a.total_q;
   p.scale = a.scale; p.causal = a.causal;
   return p;
 }
 
-int launch_fwd_dead_columns(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
-  if (a.ncol == 0 || a.batch == 0) return FMB_OK;
-  SimtParams p = make_params(a, w);
-  fwd_dead_columns_kernel<<<dim3(a.ncol, a.heads, a.batch), 256, 0, s>>>(p, a.chunk, a.d, 2);
-  FMB_LAUNCH_CHECK("fwd_dead_columns_kernel");
-  return FMB_OK;
-}
-
 template <typename T, int C, int D>
-static int fwd_launch(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
-  SimtParams p = make_params(a, w);
+static int fwd_launch(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
+  SimtParams p = make_params(a, w, ps);
   const size_t smem = (size_t)(2 * C * D + D * kSimtM) * sizeof(T) + (size_t)kSimtM * (C + 4) * 4 + kSimtM * 8;
   auto kern = fwd_main_simt_kernel<T, C, D>;
   FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<dim3(a.ncol, a.heads, a.batch), kSimtThreads, smem, s>>>(p);
+  kern<<<dim3(a.ncol * ps.nsub, ps.nh, a.batch), kSimtThreads, smem, s>>>(p);
   FMB_LAUNCH_CHECK("fwd_main_simt_kernel");
   return FMB_OK;
 }
 template <typename T, int C, int D>
-static int bwd_launch(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
-  SimtParams p = make_params(a, w);
+static int bwd_launch(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
+  SimtParams p = make_params(a, w, ps);
   const size_t smem = (size_t)(3 * C * D + 4 * D * kSimtM) * sizeof(T) + (size_t)2 * kSimtM * (C + 4) * 4 +
                       kSimtM * 12;
   auto kern = bwd_main_simt_kernel<T, C, D>;
   FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  const int nchunk = max(a.ncol, ceil_div(a.max_k, C));
-  kern<<<dim3(nchunk, a.heads_k, a.batch), kSimtThreads, smem, s>>>(p);
+  const int nchunk = max(a.ncol, ceil_div(a.max_k, a.chunk));
+  kern<<<dim3(nchunk * ps.nsub, ps.nh / (a.heads / a.heads_k), a.batch), kSimtThreads, smem, s>>>(p);
   FMB_LAUNCH_CHECK("bwd_main_simt_kernel");
   return FMB_OK;
 }
 
 #define FMB_SIMT_DISPATCH(FN)                                                               \
   if (a.dtype == FMB_BF16) {                                                                \
-    if (a.chunk == 64 && a.d == 64) return FN<__nv_bfloat16, 64, 64>(a, w, s);              \
-    if (a.chunk == 64 && a.d == 128) return FN<__nv_bfloat16, 64, 128>(a, w, s);            \
-    if (a.chunk == 128 && a.d == 64) return FN<__nv_bfloat16, 128, 64>(a, w, s);            \
-    if (a.chunk == 128 && a.d == 128) return FN<__nv_bfloat16, 128, 128>(a, w, s);          \
+    if (w.kb == 64 && a.d == 64) return FN<__nv_bfloat16, 64, 64>(a, w, ps, s);             \
+    if (w.kb == 64 && a.d == 128) return FN<__nv_bfloat16, 64, 128>(a, w, ps, s);           \
+    if (w.kb == 128 && a.d == 64) return FN<__nv_bfloat16, 128, 64>(a, w, ps, s);           \
+    if (w.kb == 128 && a.d == 128) return FN<__nv_bfloat16, 128, 128>(a, w, ps, s);         \
   } else {                                                                                  \
-    if (a.chunk == 64 && a.d == 64) return FN<__half, 64, 64>(a, w, s);                     \
-    if (a.chunk == 64 && a.d == 128) return FN<__half, 64, 128>(a, w, s);                   \
-    if (a.chunk == 128 && a.d == 64) return FN<__half, 128, 64>(a, w, s);                   \
-    if (a.chunk == 128 && a.d == 128) return FN<__half, 128, 128>(a, w, s);                 \
+    if (w.kb == 64 && a.d == 64) return FN<__half, 64, 64>(a, w, ps, s);                    \
+    if (w.kb == 64 && a.d == 128) return FN<__half, 64, 128>(a, w, ps, s);                  \
+    if (w.kb == 128 && a.d == 64) return FN<__half, 128, 64>(a, w, ps, s);                  \
+    if (w.kb == 128 && a.d == 128) return FN<__half, 128, 128>(a, w, ps, s);                \
   }                                                                                         \
-  return fail(FMB_ERR_UNSUPPORTED, "attention (CUDA-core engine): chunk %d / head_dim %d not built "  \
-              "(chunk in {64,128}, head_dim in {64,128})", a.chunk, a.d);
+  return fail(FMB_ERR_UNSUPPORTED, "attention (CUDA-core engine): head_dim %d not built "  \
+              "(head_dim in {64,128})", a.d);
 
-int launch_fwd_main_simt(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+int launch_fwd_main_simt(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   if (a.ncol == 0 || a.batch == 0 || a.heads == 0) return FMB_OK;
   FMB_SIMT_DISPATCH(fwd_launch)
 }
-int launch_bwd_main_simt(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+int launch_bwd_main_simt(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   if (a.batch == 0 || a.heads == 0) return FMB_OK;
   FMB_SIMT_DISPATCH(bwd_launch)
 }

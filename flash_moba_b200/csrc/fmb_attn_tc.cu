@@ -53,10 +53,10 @@ struct TcParams {
   int64_t q_rs, q_hs, k_rs, k_hs, v_rs, v_hs, do_rs, do_hs;
   void *dk, *dv; int64_t dk_rs, dk_hs, dv_rs, dv_hs;
   const float *lse, *softmax_d;
-  const int64_t* col_offsets; const int32_t* col_nnz; const int32_t* indices; int64_t n_indices;
+  PassParams ps;
   const int32_t *cu_q, *cu_k;
   void* part_o; float* part_lse; int* status;
-  int heads, heads_k, ncol; int64_t total_q;
+  int heads, heads_k; int64_t total_q;
   float scale; int causal;
 };
 
@@ -101,15 +101,17 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
   unsigned char* sQg = sV + C * D * 2;                         // [group][128][D]
   unsigned char* sPOg = sQg + kFwdGroups * kTcM * D * 2;       // [group][128][max(C,D)]
 
-  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int64_t ci = ((int64_t)b * p.heads + h) * p.ncol + c;
-  const int nnz = p.col_nnz[ci];
+  // C is the key block: chunk c of the pattern is covered by nsub blocks of C keys
+  const int c = blockIdx.x / p.ps.nsub, sb = blockIdx.x % p.ps.nsub, h = p.ps.h0 + blockIdx.y, b = blockIdx.z;
+  const ColRef col = column_of(p.ps, b, h, c);
+  const int nnz = col.nnz;
   if (nnz <= 0) return;
-  const int64_t off = p.col_offsets[ci];
-  if (off < 0 || off + nnz > p.n_indices) return;
+  const int64_t off = col.off;                                   // first entry in `indices`
+  const int64_t slot0 = col.slot;                                // first slot of the column in the pass
+  const int64_t plane = (int64_t)sb * p.ps.cap;                  // this key block's plane of slots
   const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
   const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
-  const int key0 = c * C;
+  const int key0 = c * p.ps.chunk + sb * C;
   const int keys_valid = max(0, min(C, len_k - key0));
   const int hk = h / (p.heads / p.heads_k);
   const int shift = len_k - len_q;
@@ -156,7 +158,7 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
     auto row_of = [&](int tile, int e) {
       int r = -1;
       if (tile < ntiles && tile * kTcM + e < nnz) {
-        r = p.indices[off + tile * kTcM + e];
+        r = p.ps.indices[off + tile * kTcM + e];
         if (r < 0 || r >= len_q) r = -1;
       }
       return r;
@@ -276,7 +278,7 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
       }
       sum += sSum[g][hf ^ 1][lt];
       const float inv = sum > 0.f ? 1.f / sum : 0.f;
-      if (hf == 0 && lt < rows) p.part_lse[off + t0 + lt] = sum > 0.f ? mx * p.scale + logf(sum) : -CUDART_INF_F;
+      if (hf == 0 && lt < rows) p.part_lse[plane + slot0 + t0 + lt] = sum > 0.f ? mx * p.scale + logf(sum) : -CUDART_INF_F;
       good = bar_and(bar_id, kFwdGroupThreads, mbar_wait(&bar_o[g], phase_o, p.status, 2));
       phase_o ^= 1;
       tc_fence_after_sync();
@@ -286,8 +288,7 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
       // ---- epilogue: normalised partial O of row `lt`, this thread's half of the head dim,
       // staged in the P tile (its MMAs have completed); one bulk copy per 32 rows
       {
-        const int64_t pos = off + t0 + lt;
-        const int key = (int)(pos & 7);
+        const int key = (int)((slot0 + t0 + lt) & 7);
         unsigned char* srow = sPO + lt * (D * 2);
         float o[DH];
 #pragma unroll
@@ -305,7 +306,7 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
       if (gw < 4) {
         const int wrows = min(32, rows - gw * 32);   // a warp's rows are contiguous in the workspace
         if (lane == 0 && wrows > 0) {
-          bulk_store(part_o + (off + t0 + gw * 32) * D, sPO + gw * 32 * (D * 2), (uint32_t)wrows * D * 2);
+          bulk_store(part_o + (plane + slot0 + t0 + gw * 32) * D, sPO + gw * 32 * (D * 2), (uint32_t)wrows * D * 2);
           bulk_commit();   // its reads are waited for under the next tile's S GEMM
         }
       }
@@ -343,7 +344,8 @@ struct BwdTile {
   int hg;        // head within the group
   int t0;        // first entry of the tile inside the head's column
   int nnz;       // entries of the head's column
-  int64_t off;   // position of the column's first entry
+  int64_t off;   // the column's first entry in `indices`
+  int64_t slot;  // the column's first slot in the pass
 };
 
 template <typename T, int C, int D>
@@ -367,13 +369,17 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   unsigned char* sP = sdO + kTcM * D * 2;         // [128][C]   (fp32 dQ staging spans sP|sdS)
   unsigned char* sdS = sP + kTcM * C * 2;         // [128][C]
 
-  const int c = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int group = p.heads / p.heads_k;
+  const int c = blockIdx.x / p.ps.nsub, sb = blockIdx.x % p.ps.nsub, hk = p.ps.h0 / group + blockIdx.y, b = blockIdx.z;
+  const int64_t plane = (int64_t)sb * p.ps.cap;
   const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
   const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
-  const int key0 = c * C;
-  if (key0 >= len_k) return;
+  const int key0 = c * p.ps.chunk + sb * C;
+  if (key0 >= len_k) {
+    zero_dq_partials(p.ps, static_cast<float*>(p.part_o), plane, b, hk, group, c, D);
+    return;
+  }
   const int keys_valid = min(C, len_k - key0);
-  const int group = p.heads / p.heads_k;
   const int shift = len_k - len_q;
   const float scale_log2 = p.scale * kLog2eTc;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -384,13 +390,9 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   // ---- the CTA's tile sequence
   auto seek_head = [&](BwdTile& it) {             // first head >= it.hg with a non-empty column
     for (; it.hg < group; ++it.hg) {
-      if (c >= p.ncol) break;
-      const int h = hk * group + it.hg;
-      const int64_t ci = ((int64_t)b * p.heads + h) * p.ncol + c;
-      const int nnz = p.col_nnz[ci];
-      const int64_t off = p.col_offsets[ci];
-      if (nnz > 0 && off >= 0 && off + nnz <= p.n_indices) {
-        it.nnz = nnz; it.off = off; it.t0 = 0;
+      const ColRef col = column_of(p.ps, b, hk * group + it.hg, c);
+      if (col.nnz > 0) {
+        it.nnz = col.nnz; it.off = col.off; it.slot = col.slot; it.t0 = 0;
         return true;
       }
     }
@@ -425,7 +427,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   FMB_TICK(16);   // prologue
   const uint32_t tmem_base = tmem_base_s;
 
-  BwdTile it{0, 0, 0, 0};
+  BwdTile it{0, 0, 0, 0, 0};
   bool have = seek_head(it);
 
   if (loader) {
@@ -439,7 +441,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
       {
         int r = -1;
         if (it.t0 + lt < it.nnz) {
-          r = p.indices[it.off + it.t0 + lt];
+          r = p.ps.indices[it.off + it.t0 + lt];
           if (r < 0 || r >= len_q) r = -1;
         }
         float l2 = CUDART_INF_F, dd = 0.f;
@@ -575,8 +577,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
       // dQ partial of row `lt`, this thread's half of the head dim: staged (fp32) over the P/dS
       // tiles, which the GEMMs have finished reading; one bulk copy per 32 rows
       {
-        const int64_t pos = it.off + it.t0 + lt;
-        const int key = (int)(pos & 7);
+        const int key = (int)((it.slot + it.t0 + lt) & 7);
         unsigned char* srow = sP + lt * (D * 4);
         float o[DH];
 #pragma unroll
@@ -593,7 +594,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
       if (warp < 4) {
         const int wrows = min(32, rows - warp * 32);
         if (lane == 0 && wrows > 0) {
-          bulk_store(part_dq + (it.off + it.t0 + warp * 32) * D, sP + warp * 32 * (D * 4), (uint32_t)wrows * D * 4);
+          bulk_store(part_dq + (plane + it.slot + it.t0 + warp * 32) * D, sP + warp * 32 * (D * 4), (uint32_t)wrows * D * 4);
           bulk_commit();      // its reads are waited for under the next tile's first GEMMs
         }
       }
@@ -790,23 +791,23 @@ int launch_selftest_gather(const void* a, int a_rows, const int* idx, const void
 }
 
 // ------------------------------------------------------------------ launchers
-static TcParams make_tc_params(const AttnArgs& a, const AttnWorkspace& w) {
+static TcParams make_tc_params(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps) {
   TcParams p;
   p.q = a.q; p.k = a.k; p.v = a.v; p.dout = a.dout;
   p.q_rs = a.q_rs; p.q_hs = a.q_hs; p.k_rs = a.k_rs; p.k_hs = a.k_hs; p.v_rs = a.v_rs; p.v_hs = a.v_hs;
   p.do_rs = a.do_rs; p.do_hs = a.do_hs;
   p.dk = a.dk; p.dv = a.dv; p.dk_rs = a.dk_rs; p.dk_hs = a.dk_hs; p.dv_rs = a.dv_rs; p.dv_hs = a.dv_hs;
   p.lse = a.lse; p.softmax_d = a.softmax_d;
-  p.col_offsets = a.col_offsets; p.col_nnz = a.col_nnz; p.indices = a.indices; p.n_indices = a.n_indices;
+  p.ps = ps;
   p.cu_q = a.cu_q; p.cu_k = a.cu_k; p.part_o = w.part_o; p.part_lse = w.part_lse; p.status = w.status;
-  p.heads = a.heads; p.heads_k = a.heads_k; p.ncol = a.ncol; p.total_q = a.total_q;
+  p.heads = a.heads; p.heads_k = a.heads_k; p.total_q = a.total_q;
   p.scale = a.scale; p.causal = a.causal;
   return p;
 }
 
 template <typename T, int C, int D>
-static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
-  TcParams p = make_tc_params(a, w);
+static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
+  TcParams p = make_tc_params(a, w, ps);
   constexpr int QP = (C > D ? C : D);
   // K, V, and per compute group a Q tile and a P / O-staging tile; one CTA per SM by size
   // (all 512 TMEM columns are allocated)
@@ -814,48 +815,50 @@ static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t
   if (smem < 120 * 1024) smem = 120 * 1024;
   auto kern = fwd_main_tc_kernel<T, C, D>;
   FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<dim3(a.ncol, a.heads, a.batch), kFwdThreads, smem, s>>>(p);
+  kern<<<dim3(a.ncol * ps.nsub, ps.nh, a.batch), kFwdThreads, smem, s>>>(p);
   FMB_LAUNCH_CHECK("fwd_main_tc_kernel");
   return FMB_OK;
 }
 
 template <typename T, int C, int D>
-static int bwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
-  TcParams p = make_tc_params(a, w);
+static int bwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
+  TcParams p = make_tc_params(a, w, ps);
   const size_t smem = (size_t)2 * C * D * 2 + (size_t)2 * kTcM * D * 2 + (size_t)2 * kTcM * C * 2 + 1024;
   auto kern = bwd_main_tc_kernel<T, C, D>;
   FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  const int nchunk = max(a.ncol, ceil_div(a.max_k, C));
-  kern<<<dim3(nchunk, a.heads_k, a.batch), kBwdThreads, smem, s>>>(p);
+  const int nchunk = max(a.ncol, ceil_div(a.max_k, a.chunk));
+  kern<<<dim3(nchunk * ps.nsub, ps.nh / (a.heads / a.heads_k), a.batch), kBwdThreads, smem, s>>>(p);
   FMB_LAUNCH_CHECK("bwd_main_tc_kernel");
   return FMB_OK;
 }
 
 bool tc_supported(const AttnArgs& a, bool backward) {
-  if (backward)
-    return a.chunk == 128 && (a.d == 64 || a.d == 128);
-  return (a.chunk == 64 || a.chunk == 128) && (a.d == 64 || a.d == 128);
+  // key block = 128 keys when the chunk is a multiple of 128, else 64
+  if (backward) return a.chunk % 128 == 0 && (a.d == 64 || a.d == 128);
+  return a.chunk % 64 == 0 && (a.d == 64 || a.d == 128);
 }
 
-int launch_fwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+int launch_fwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   if (a.ncol == 0 || a.batch == 0 || a.heads == 0) return FMB_OK;
-#define FMB_TC_FWD(TT)                                                       \
-  if (a.chunk == 64 && a.d == 64) return fwd_tc_launch<TT, 64, 64>(a, w, s);   \
-  if (a.chunk == 64 && a.d == 128) return fwd_tc_launch<TT, 64, 128>(a, w, s); \
-  if (a.chunk == 128 && a.d == 64) return fwd_tc_launch<TT, 128, 64>(a, w, s); \
-  if (a.chunk == 128 && a.d == 128) return fwd_tc_launch<TT, 128, 128>(a, w, s);
+#define FMB_TC_FWD(TT)                                                          \
+  if (w.kb == 64 && a.d == 64) return fwd_tc_launch<TT, 64, 64>(a, w, ps, s);     \
+  if (w.kb == 64 && a.d == 128) return fwd_tc_launch<TT, 64, 128>(a, w, ps, s);   \
+  if (w.kb == 128 && a.d == 64) return fwd_tc_launch<TT, 128, 64>(a, w, ps, s);   \
+  if (w.kb == 128 && a.d == 128) return fwd_tc_launch<TT, 128, 128>(a, w, ps, s);
   if (a.dtype == FMB_BF16) { FMB_TC_FWD(__nv_bfloat16) } else { FMB_TC_FWD(__half) }
 #undef FMB_TC_FWD
-  return fail(FMB_ERR_UNSUPPORTED, "tensor-core forward: chunk %d / head_dim %d not built", a.chunk, a.d);
+  return fail(FMB_ERR_UNSUPPORTED, "tensor-core forward: head_dim %d not built", a.d);
 }
 
-int launch_bwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, cudaStream_t s) {
+int launch_bwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   if (a.batch == 0 || a.heads == 0) return FMB_OK;
-  if (a.chunk == 128 && a.d == 64)
-    return a.dtype == FMB_BF16 ? bwd_tc_launch<__nv_bfloat16, 128, 64>(a, w, s) : bwd_tc_launch<__half, 128, 64>(a, w, s);
-  if (a.chunk == 128 && a.d == 128)
-    return a.dtype == FMB_BF16 ? bwd_tc_launch<__nv_bfloat16, 128, 128>(a, w, s) : bwd_tc_launch<__half, 128, 128>(a, w, s);
-  return fail(FMB_ERR_UNSUPPORTED, "tensor-core backward: chunk %d / head_dim %d not built", a.chunk, a.d);
+  if (w.kb == 128 && a.d == 64)
+    return a.dtype == FMB_BF16 ? bwd_tc_launch<__nv_bfloat16, 128, 64>(a, w, ps, s)
+                               : bwd_tc_launch<__half, 128, 64>(a, w, ps, s);
+  if (w.kb == 128 && a.d == 128)
+    return a.dtype == FMB_BF16 ? bwd_tc_launch<__nv_bfloat16, 128, 128>(a, w, ps, s)
+                               : bwd_tc_launch<__half, 128, 128>(a, w, ps, s);
+  return fail(FMB_ERR_UNSUPPORTED, "tensor-core backward: key block %d / head_dim %d not built", w.kb, a.d);
 }
 
 }  // namespace fmb

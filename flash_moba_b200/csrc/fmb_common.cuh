@@ -141,8 +141,8 @@ struct AttnArgs {
   int batch, heads, heads_k, d; int64_t total_q, total_k; int max_q, max_k, chunk, ncol;
   float scale; int causal, dtype;
 };
-size_t attn_fwd_workspace_bytes(int64_t total_q, int heads, int d, int64_t n_indices);
-size_t attn_bwd_workspace_bytes(int64_t total_q, int heads, int d, int64_t n_indices);
+size_t attn_workspace_bytes(int64_t total_q, int heads, int heads_k, int d, int64_t n_indices, int batch, int max_k,
+                            int chunk, int heads_per_pass, bool backward);
 int launch_attn_fwd(const AttnArgs& a, int engine, cudaStream_t s);
 int launch_attn_bwd(const AttnArgs& a, int engine, cudaStream_t s);
 

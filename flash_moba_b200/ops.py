@@ -48,12 +48,30 @@ def ptr(t: Optional[torch.Tensor]) -> int:
     return 0 if t is None else t.data_ptr()
 
 
+def _workspace(query, total_q, h, hk, d, n_indices, batch, max_seqlen_k, chunk, device):
+    """Workspace for one attention call: the single-pass size if it fits the cap
+    (FMB_WORKSPACE_GB, default 24 GiB), otherwise the largest pass of whole kv-head groups that
+    does; the library then walks the heads in passes of that size."""
+    import os
+    cap = int(float(os.environ.get("FMB_WORKSPACE_GB", "24")) * (1 << 30))
+    group = h // hk
+    nh = h
+    nbytes = query(total_q, h, hk, d, n_indices, batch, int(max_seqlen_k), int(chunk), nh)
+    while nbytes > cap and nh > group:
+        nh = max(group, (nh // 2) // group * group)
+        nbytes = query(total_q, h, hk, d, n_indices, batch, int(max_seqlen_k), int(chunk), nh)
+    return torch.empty((max(nbytes, 1),), dtype=torch.uint8, device=device), nbytes
+
+
 def _check_status(ws: torch.Tensor, what: str) -> None:
     """With FMB_CHECK_STATUS=1 every attention call synchronises and reads the device-side
     status word (first 4 bytes of the workspace); a bounded wait that expired raises."""
     import os
     if os.environ.get("FMB_CHECK_STATUS", "0") == "1":
         code = int(ws[:4].view(torch.int32).item())
+        if code == 7:
+            raise RuntimeError(f"flash_moba_b200: {what}: the pattern does not fit the slots of a pass "
+                               "(overlapping columns, or raise FMB_WORKSPACE_GB)")
         if code != 0:
             raise RuntimeError(f"flash_moba_b200: {what}: a bounded device-side wait expired (code {code})")
 
@@ -209,8 +227,8 @@ def attn_fwd(q, k, v, col_offsets, col_nnz, indices, cu_seqlens_q, cu_seqlens_k,
         if out is None:
             out = torch.empty_like(q)
         lse = torch.empty((h, total_q), dtype=torch.float32, device=dev)
-        nbytes = lib.fmb_attn_fwd_workspace_bytes(total_q, h, d, indices.numel())
-        ws = torch.empty((max(nbytes, 1),), dtype=torch.uint8, device=dev)
+        ws, nbytes = _workspace(lib.fmb_attn_fwd_workspace_bytes, total_q, h, hk, d, indices.numel(), batch,
+                                max_seqlen_k, chunk, dev)
         check(lib.fmb_attn_fwd(ptr(q), q.stride(0), q.stride(1), ptr(k), k.stride(0), k.stride(1),
                                ptr(v), v.stride(0), v.stride(1), ptr(out), out.stride(0), out.stride(1), ptr(lse),
                                ptr(col_offsets), ptr(col_nnz), ptr(indices), indices.numel(),
@@ -237,8 +255,8 @@ def attn_bwd(dout, q, k, v, out, lse, dq, dk, dv, col_offsets, col_nnz, indices,
         raise RuntimeError("softmax_lse must be a contiguous float32 (heads, total_q) tensor")
     with torch.cuda.device(dev):
         softmax_d = torch.empty((h, total_q), dtype=torch.float32, device=dev)
-        nbytes = lib.fmb_attn_bwd_workspace_bytes(total_q, h, d, indices.numel())
-        ws = torch.empty((max(nbytes, 1),), dtype=torch.uint8, device=dev)
+        ws, nbytes = _workspace(lib.fmb_attn_bwd_workspace_bytes, total_q, h, hk, d, indices.numel(), batch,
+                                max_seqlen_k, chunk, dev)
         check(lib.fmb_attn_bwd(ptr(dout), dout.stride(0), dout.stride(1), ptr(q), q.stride(0), q.stride(1),
                                ptr(k), k.stride(0), k.stride(1), ptr(v), v.stride(0), v.stride(1),
                                ptr(out), out.stride(0), out.stride(1), ptr(lse),

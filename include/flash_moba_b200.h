@@ -133,9 +133,20 @@ int fmb_varlen_sort(const int64_t* starts, const int64_t* ends, const int32_t* s
                     int64_t num_segments, int64_t num_items, fmb_stream_t stream);
 
 /* ------------------------------------------------------------------ stage F: forward
- * Bytes of scratch for fmb_attn_fwd / fmb_attn_bwd (n_indices = entries of `indices`). */
-size_t fmb_attn_fwd_workspace_bytes(int64_t total_q, int heads, int head_dim, int64_t n_indices);
-size_t fmb_attn_bwd_workspace_bytes(int64_t total_q, int heads, int head_dim, int64_t n_indices);
+ * Scratch for fmb_attn_fwd / fmb_attn_bwd.  The kernels keep one partial result per
+ * (pattern entry, 128-key block of its chunk) in the workspace and work through the query
+ * heads in passes, so the workspace only has to hold one pass:
+ *   heads_per_pass <= 0 : bytes for a single pass over all heads (fastest);
+ *   heads_per_pass  > 0 : bytes for passes of that many query heads (rounded down to whole
+ *                         kv-head groups, at least one group).
+ * fmb_attn_fwd / fmb_attn_bwd accept any workspace of at least the one-group size and use the
+ * largest pass that fits.  n_indices = entries of `indices`; chunk = lg_block_n of the call. */
+size_t fmb_attn_fwd_workspace_bytes(int64_t total_q, int heads, int heads_k, int head_dim,
+                                    int64_t n_indices, int batch, int max_seqlen_k, int chunk,
+                                    int heads_per_pass);
+size_t fmb_attn_bwd_workspace_bytes(int64_t total_q, int heads, int heads_k, int head_dim,
+                                    int64_t n_indices, int batch, int max_seqlen_k, int chunk,
+                                    int heads_per_pass);
 
 /* out[row,h] = softmax over the visible keys (scale * q.k) . v, where key col of the row's
  * sequence is visible iff chunk col/chunk is in the row's pattern, col < len_k and, if
@@ -206,8 +217,9 @@ int fmb_selftest_gather(const void* a, int a_rows, const int* idx, const void* b
                         int* status, fmb_stream_t stream);
 
 /* The first 4 bytes of the workspace given to fmb_attn_fwd / fmb_attn_bwd hold a device-side
- * status word after the call: 0 = ok, non-zero = a bounded wait inside a kernel expired
- * (FMB_ERR_TIMEOUT condition; results are then invalid). */
+ * status word after the call: 0 = ok; 1..6 = a bounded wait inside a kernel expired
+ * (FMB_ERR_TIMEOUT condition); 7 = the pattern's columns overlap or exceed the slots of a pass
+ * (give a larger workspace).  Results are invalid when it is non-zero. */
 
 /* ------------------------------------------------------------------ measurement aids
  * No counterpart in the reference (it is timed from Python with torch.utils.benchmark,

@@ -27,11 +27,18 @@ def test_library_exports_every_declared_symbol():
 
 def test_workspace_size_queries_need_no_gpu():
     from flash_moba_b200 import _lib
-    small = _lib.lib.fmb_attn_fwd_workspace_bytes(1024, 4, 64, 1024 * 4 * 4)
-    big = _lib.lib.fmb_attn_fwd_workspace_bytes(2048, 4, 64, 2048 * 4 * 4)
+    f = _lib.lib.fmb_attn_fwd_workspace_bytes
+    small = f(1024, 4, 4, 64, 1024 * 4 * 4, 1, 1024, 64, 0)
+    big = f(2048, 4, 4, 64, 2048 * 4 * 4, 1, 2048, 64, 0)
     assert 0 < small < big
+    # passes over half of the heads need about half of the partial storage
+    assert f(2048, 4, 4, 64, 2048 * 4 * 4, 1, 2048, 64, 2) < 0.6 * big
+    # whole kv-head groups only: asking for 1 head of a group of 2 gives the 2-head size
+    assert f(2048, 4, 2, 64, 2048 * 4 * 4, 1, 2048, 64, 1) == f(2048, 4, 2, 64, 2048 * 4 * 4, 1, 2048, 64, 2)
+    # a 256-key chunk is two 128-key blocks: twice the partial storage
+    assert f(2048, 4, 4, 64, 2048 * 4 * 4, 1, 2048, 256, 0) > 1.8 * f(2048, 4, 4, 64, 2048 * 4 * 4, 1, 2048, 128, 0)
     assert _lib.lib.fmb_build_csc_workspace_bytes(2, 4, 1000, 8) >= 2 * 4 * 2 * 8 * 4
-    assert _lib.lib.fmb_attn_bwd_workspace_bytes(1024, 4, 64, 4096) > 4096 * 64 * 4
+    assert _lib.lib.fmb_attn_bwd_workspace_bytes(1024, 4, 4, 64, 4096, 1, 1024, 64, 0) > 4096 * 64 * 4
 
 
 def test_bad_arguments_are_rejected_before_any_launch():

@@ -313,6 +313,59 @@ def test_attention_rows_with_more_than_32_partials(engine):
     _attn_check(q, k, v, do, cu_of(lens_q), cu_of(lens_k), mask, chunk, False, engine)
 
 
+def _random_mask(lens_q, lens_k, H, chunk, causal, picks, seed=1):
+    B, Sq, ncol = len(lens_q), max(lens_q), (max(lens_k) + chunk - 1) // chunk
+    mask = torch.zeros(B, H, Sq, ncol, dtype=torch.bool)
+    g = torch.Generator().manual_seed(seed)
+    for b in range(B):
+        for h in range(H):
+            for r in range(lens_q[b]):
+                end = lens_k[b] - (lens_q[b] - r - 1) if causal else lens_k[b]
+                nb = max(0, math.ceil(end / chunk))
+                if nb > 0:
+                    sel = torch.randperm(nb - 1, generator=g)[:picks] if nb > 1 else torch.zeros(0, dtype=torch.long)
+                    mask[b, h, r, sel] = True
+                    mask[b, h, r, nb - 1] = True
+    return mask
+
+
+@pytest.mark.parametrize("engine", [0, 1])
+@pytest.mark.parametrize("chunk,d", [(256, 128), (192, 128), (256, 64), (320, 64)])
+def test_attention_chunks_wider_than_a_key_block(chunk, d, engine):
+    """Chunks of 192..320 keys are processed as several 64- or 128-key blocks per column
+    (BASELINE configuration 5 uses chunk 256)."""
+    torch.manual_seed(0)
+    lens, H, Hk = [700, 301], 4, 2
+    T = sum(lens)
+    q = torch.randn(T, H, d).bfloat16()
+    k = torch.randn(T, Hk, d).bfloat16()
+    v = torch.randn(T, Hk, d).bfloat16()
+    do = torch.randn(T, H, d).bfloat16()
+    mask = _random_mask(lens, lens, H, chunk, True, 2)
+    _attn_check(q, k, v, do, cu_of(lens), cu_of(lens), mask, chunk, True, engine)
+
+
+def test_attention_in_passes_is_bit_identical(monkeypatch):
+    """A workspace too small for all heads makes the library walk the heads in passes (whole
+    kv-head groups); results must not change by a bit."""
+    import flash_moba_b200 as F
+    torch.manual_seed(0)
+    lens, H, Hk, d, c, kk = [600, 424], 8, 4, 128, 128, 3
+    T = sum(lens)
+    q = torch.randn(T, H, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(T, Hk, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(T, Hk, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    cs = cu_of(lens).to(DEV)
+    res = []
+    for gb in ("24", "0.004"):
+        monkeypatch.setenv("FMB_WORKSPACE_GB", gb)
+        out = F.flash_moba_varlen_func(q, k, v, cs, cs, max(lens), max(lens), c, kk, causal=True)
+        grads = torch.autograd.grad(out, (q, k, v), torch.ones_like(out))
+        res.append((out.detach().clone(), *[x.clone() for x in grads]))
+    for a, b in zip(*res):
+        assert torch.equal(a, b)
+
+
 @pytest.mark.parametrize("engine", [0, 1])
 def test_attention_fp16(engine):
     torch.manual_seed(0)
