@@ -37,6 +37,7 @@ WORKLOADS = {
     "c3": ([8192] * 8, 32, 32, 128, 128, 8, True, 1.0),
     "small": ([4096], 8, 8, 128, 128, 8, True, 1.0),
     "mid": ([16384], 16, 16, 128, 128, 8, True, 1.0),
+    "64k_h4": ([65536], 4, 4, 128, 128, 8, True, 1.0),      # one rank's share of "64k" at 8 GPUs
 }
 
 
@@ -187,8 +188,10 @@ def main():
     ops.set_engine(args.engine)
 
     # shard: q heads (and their kv heads) split across ranks; no data-path collective
-    assert H % world == 0 and Hk % world == 0, "heads must divide across ranks"
-    h_loc, hk_loc = H // world, Hk // world
+    from flash_moba_b200.sharding import plan_head_shards
+    assert Hk >= world, "fewer kv heads than ranks: split the sequence by query range instead"
+    h0, h1 = plan_head_shards(H, Hk, world)[rank]
+    h_loc, hk_loc = h1 - h0, (h1 - h0) // (H // Hk)
     T = sum(seqlens)
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     mk = lambda h: (torch.randn(T, h, d, generator=g, device=dev, dtype=torch.float32) * scale).to(torch.bfloat16)
@@ -290,12 +293,19 @@ def main():
     peak_src = "measured (MEASURED_PEAKS.json bf16_tflops_sustained: kernel timed inside a long step)" if peaks else \
         "fallback 1.4 PFLOP/s sustained"
     dom = "bwd_main" if backward else "fwd_main"
-    dom_flops = (bwd_f if backward else fwd_f) / world
+    dom_flops = (bwd_f if backward else fwd_f) * h_loc / H      # rank 0's launch
     roof = None
+    # DRAM bytes per (row, chunk) entry of the dominant kernel, from one ncu capture of a 16K-token,
+    # 16-head case (dram__bytes_read.sum + dram__bytes_write.sum over its 2,039,808 entries); the
+    # traffic is per-entry work (gathered rows in, partial rows out), so it scales with the entries.
+    entry_bytes = {"bwd_main": 729.5}.get(dom) if (d == 128 and chunk == 128) else None
+    entries = ACC.selected_entries(seqlens, chunk, topk) * h_loc
     if kern_ms.get(dom):
         ach = dom_flops / (kern_ms[dom] * 1e-3) / 1e12
         roof = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s",
-                "frac": ach / peak_tf, "traffic": None, "peak_source": peak_src,
+                "frac": ach / peak_tf, "traffic": (entry_bytes * entries if entry_bytes else None),
+                "traffic_source": "ncu dram bytes of a 16K-token case, scaled by (row, chunk) entries" if entry_bytes else None,
+                "peak_source": peak_src,
                 "launch_ms": kern_ms[dom], "flops_per_launch": dom_flops,
                 "other_kernels_ms": {k_: v_ for k_, v_ in kern_ms.items() if k_ != dom}}
     line = {
@@ -305,7 +315,8 @@ def main():
         "data": "synthetic",
         "config": {"workload": wl, "seqlens": seqlens, "heads": H, "heads_k": Hk, "head_dim": d, "chunk": chunk,
                    "topk": topk, "causal": True, "step": "pattern(pool+gate+csc) + fwd" + (" + bwd" if backward else ""),
-                   "sharding": f"heads/{world}", "l2": "inputs (q,k,v,dO > 500 MB each at N=1) exceed the 126 MB L2",
+                   "sharding": f"query heads {h0}..{h1 - 1} of {H} on rank 0, whole kv-head groups per rank, no collective",
+                   "l2": f"inputs q,k,v,dO ({4 * T * h_loc * d * 2 >> 20} MB per rank) plus the per-pair partials exceed the 126 MB L2",
                    "engine": {"fwd": ["cuda-core", "tcgen05"][_lib.lib.fmb_attn_engine(chunk, d, 0)],
                               "bwd": ["cuda-core", "tcgen05"][_lib.lib.fmb_attn_engine(chunk, d, 1)]}},
         "gpu_launches": int(launches), "clocks": clk.summary(), "e2e": e2e, "roofline": roof,

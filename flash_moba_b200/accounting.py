@@ -22,6 +22,15 @@ def selected_pairs(seqlens: Sequence[int], chunk: int, topk: int) -> int:
     return total
 
 
+def selected_entries(seqlens: Sequence[int], chunk: int, topk: int) -> int:
+    """(query row, key chunk) entries of the pattern, per query head (causal, len_q == len_k)."""
+    total = 0
+    for s in seqlens:
+        for j in range((s + chunk - 1) // chunk):
+            total += min(chunk, s - j * chunk) * min(topk, j + 1)
+    return total
+
+
 def attention_flops(seqlens, heads: int, d: int, chunk: int, topk: int):
     """(forward, backward, forward+backward) FLOPs over selected blocks."""
     fwd = 4 * d * selected_pairs(seqlens, chunk, topk) * heads
