@@ -6,7 +6,7 @@
 // position is also where the pair's partial result lives in the workspace:
 //   forward : part_o[pos][d]  (chunk-local softmax(QK^T)V, normalised, in the I/O dtype)
 //             part_lse[pos]   (chunk-local log-sum-exp, natural log, of the scaled scores)
-//   backward: part_dq[pos][d] (fp32, unscaled dS.K of that chunk)
+//   backward: part_dq[pos][d] (softmax_scale * dS.K of that chunk, in the I/O dtype)
 // A row-major "combine" kernel then merges the partials of each row in ascending `pos`
 // order, found through a CSR transpose of the pattern (row_ptr / row_pos) that is rebuilt
 // per call with integer atomics; the merge order is fixed by sorting, so results are
@@ -34,7 +34,7 @@ __host__ __device__ __forceinline__ int part_col(int64_t pos, int col, int elems
 // slots: the partial of (entry j of the column, sub-block sb) lives at sb*cap + slot_base + j.
 struct AttnWorkspace {
   int* status;          // first word: 0, or where a bounded device wait gave up / 7 = slot overflow
-  void* part_o;         // fwd: nsub*cap*d elements of the I/O dtype;  bwd: nsub*cap*d floats
+  void* part_o;         // nsub*cap*d elements of the I/O dtype (fwd: O partials, bwd: dQ partials)
   float* part_lse;      // fwd only: nsub*cap
   uint32_t* slot_base;  // batch*nh*ncol + 1
   uint32_t* row_ptr;    // nh*total_q + 1
@@ -78,14 +78,15 @@ __device__ __forceinline__ ColRef column_of(const PassParams& r, int b, int h, i
 
 // A key block that starts beyond the sequence's keys contributes nothing: its dQ partials are
 // zero (the combine still reads them).  Called by a whole CTA of the backward kernels.
-__device__ __forceinline__ void zero_dq_partials(const PassParams& r, float* part_dq, int64_t plane, int b, int hk,
+template <typename T>
+__device__ __forceinline__ void zero_dq_partials(const PassParams& r, T* part_dq, int64_t plane, int b, int hk,
                                                  int group, int c, int d) {
   for (int hg = 0; hg < group; ++hg) {
     const ColRef col = column_of(r, b, hk * group + hg, c);
     if (col.nnz <= 0) continue;
-    float4* dst = reinterpret_cast<float4*>(part_dq + (plane + col.slot) * d);
-    const int64_t n4 = (int64_t)col.nnz * d / 4;
-    for (int64_t i = threadIdx.x; i < n4; i += blockDim.x) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    uint4* dst = reinterpret_cast<uint4*>(part_dq + (plane + col.slot) * d);
+    const int64_t n16 = (int64_t)col.nnz * d * (int64_t)sizeof(T) / 16;
+    for (int64_t i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
   }
 }
 
@@ -99,7 +100,7 @@ int build_row_lists(const AttnArgs& a, const AttnWorkspace& w, const PassParams&
 
 // out/lse from the forward partials
 int launch_fwd_combine(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s);
-// dq from the backward partials (multiplies by softmax_scale)
+// dq = sum of the row's backward partials (already scaled)
 int launch_bwd_combine(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s);
 // softmax_d[h, t] = sum_d dout*out
 int launch_dot_do_o(const AttnArgs& a, cudaStream_t s);

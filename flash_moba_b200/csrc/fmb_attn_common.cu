@@ -56,7 +56,7 @@ size_t attn_workspace_bytes(int64_t total_q, int heads, int heads_k, int d, int6
   memset(&a, 0, sizeof(a));
   a.total_q = total_q; a.heads = heads; a.heads_k = heads_k > 0 ? heads_k : heads; a.d = d; a.n_indices = n_indices;
   a.batch = batch; a.chunk = chunk > 0 ? chunk : 128; a.ncol = ceil_div(max_k, a.chunk);
-  return carve_attn_workspace(nullptr, 0, a, backward ? 4 : 2, !backward, heads_per_pass > 0 ? heads_per_pass : heads)
+  return carve_attn_workspace(nullptr, 0, a, 2, !backward, heads_per_pass > 0 ? heads_per_pass : heads)
       .bytes;
 }
 
@@ -312,9 +312,8 @@ __global__ void __launch_bounds__(256) fwd_combine_kernel(const T* __restrict__ 
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) bwd_combine_kernel(const float* __restrict__ part_dq, CombineParams c, T* dq,
-                                                          int64_t rs, int64_t hs, float scale, const int* only_if,
-                                                          int min_n) {
+__global__ void __launch_bounds__(256) bwd_combine_kernel(const T* __restrict__ part_dq, CombineParams c, T* dq,
+                                                          int64_t rs, int64_t hs, const int* only_if, int min_n) {
   using T2 = typename Elem<T>::T2;
   if (only_if && *only_if == 0) return;
   const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -335,12 +334,12 @@ __global__ void __launch_bounds__(256) bwd_combine_kernel(const float* __restric
     for (int r = 0; r < n; ++r) {
       const int64_t slot = next_slot(rp, n, last, lane);
       last = slot;
-      const float* src = part_dq + ((int64_t)sb * c.cap + slot) * c.d;
+      const T* src = part_dq + ((int64_t)sb * c.cap + slot) * c.d;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int col = lane * 2 + i * 64;
         if (col < c.d) {
-          const float2 x = *reinterpret_cast<const float2*>(src + part_col(slot, col, 4));
+          const float2 x = Elem<T>::to_f2(*reinterpret_cast<const T2*>(src + part_col(slot, col, 8)));
           acc[i].x += x.x;
           acc[i].y += x.y;
         }
@@ -351,7 +350,7 @@ __global__ void __launch_bounds__(256) bwd_combine_kernel(const float* __restric
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int col = lane * 2 + i * 64;
-    if (col < c.d) *reinterpret_cast<T2*>(dst + col) = Elem<T>::from_f2(acc[i].x * scale, acc[i].y * scale);
+    if (col < c.d) *reinterpret_cast<T2*>(dst + col) = Elem<T>::from_f2(acc[i].x, acc[i].y);
   }
 }
 
@@ -474,12 +473,12 @@ __global__ void __launch_bounds__(256) fwd_combine_group_kernel(const T* __restr
 }
 
 template <typename T, int G, int EPL>
-__global__ void __launch_bounds__(256) bwd_combine_group_kernel(const float* __restrict__ part_dq, CombineParams c,
-                                                                T* dq, int64_t rs, int64_t hs, float scale, int min_n,
+__global__ void __launch_bounds__(256) bwd_combine_group_kernel(const T* __restrict__ part_dq, CombineParams c,
+                                                                T* dq, int64_t rs, int64_t hs, int min_n,
                                                                 const int* only_if, int* overflow) {
   constexpr int d = G * EPL;
-  constexpr int NV = EPL / 4;                 // 16-byte (4 float) loads per partial row per lane
-  static_assert(EPL % 8 == 0, "a lane owns whole 16-byte chunks of the output");
+  constexpr int NV = EPL / 8;                 // 16-byte loads per partial row per lane
+  static_assert(EPL % 8 == 0, "a lane owns whole 16-byte chunks");
   if (only_if && *only_if == 0) return;
   const int lane = threadIdx.x & 31, gl = lane & (G - 1);
   const unsigned gm = group_mask<G>(lane);
@@ -490,10 +489,10 @@ __global__ void __launch_bounds__(256) bwd_combine_group_kernel(const float* __r
   float acc[EPL];
 #pragma unroll
   for (int i = 0; i < EPL; ++i) acc[i] = 0.f;
-  constexpr int B = 4;
+  constexpr int B = G < 8 ? G : 8;            // partial rows in flight per step
 #pragma unroll
   for (int r0 = 0; r0 < G; r0 += B) {
-    float4 x[B][NV];
+    uint4 x[B][NV];
 #pragma unroll
     for (int k = 0; k < B; ++k) {
       const unsigned hit = __ballot_sync(0xffffffffu, g.valid && rank == r0 + k) & gm;
@@ -501,30 +500,29 @@ __global__ void __launch_bounds__(256) bwd_combine_group_kernel(const float* __r
       const uint32_t pk = __shfl_sync(0xffffffffu, g.pos, src);
       const uint32_t sk = __shfl_sync(0xffffffffu, g.slot, src);
       if (hit) {
-        const float* row = part_dq + (int64_t)pk * d;
+        const T* row = part_dq + (int64_t)pk * d;
 #pragma unroll
-        for (int v = 0; v < NV; ++v) x[k][v] = *reinterpret_cast<const float4*>(row + part_col(sk, gl * EPL + 4 * v, 4));
+        for (int v = 0; v < NV; ++v) x[k][v] = *reinterpret_cast<const uint4*>(row + part_col(sk, gl * EPL + 8 * v, 8));
       } else {
 #pragma unroll
-        for (int v = 0; v < NV; ++v) x[k][v] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int v = 0; v < NV; ++v) x[k][v] = make_uint4(0, 0, 0, 0);
       }
     }
 #pragma unroll
     for (int k = 0; k < B; ++k) {
 #pragma unroll
       for (int v = 0; v < NV; ++v) {
-        acc[4 * v] += x[k][v].x; acc[4 * v + 1] += x[k][v].y; acc[4 * v + 2] += x[k][v].z; acc[4 * v + 3] += x[k][v].w;
+        float f[8];
+        unpack8<T>(x[k][v], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[8 * v + e] += f[e];
       }
     }
   }
   if (g.mine) {
     T* dst = dq + g.t * rs + (int64_t)(c.h0 + g.hr) * hs + gl * EPL;
 #pragma unroll
-    for (int v = 0; v < EPL / 8; ++v) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[8 * v + e] *= scale;
-      *reinterpret_cast<uint4*>(dst + 8 * v) = pack8<T>(acc + 8 * v);
-    }
+    for (int v = 0; v < NV; ++v) *reinterpret_cast<uint4*>(dst + 8 * v) = pack8<T>(acc + 8 * v);
   }
 }
 
@@ -604,15 +602,15 @@ static int bwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const
   const int64_t rows = a.total_q * ps.nh;
   const CombineParams c = make_combine(a, w, ps);
   int* ovf = w.status + 1;
-  const float* pd = (const float*)w.part_o;
+  const T* pd = (const T*)w.part_o;
   T* dq = (T*)a.dq;
-  bwd_combine_group_kernel<T, 8, D / 8><<<group_grid(rows, 8), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, a.scale, 0,
-                                                                            nullptr, ovf);
+  bwd_combine_group_kernel<T, 8, D / 8><<<group_grid(rows, 8), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 0, nullptr,
+                                                                            ovf);
   FMB_LAUNCH_CHECK("bwd_combine_group_kernel<8>");
-  bwd_combine_group_kernel<T, 16, D / 16><<<group_grid(rows, 16), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, a.scale,
-                                                                              9, ovf, ovf + 1);
+  bwd_combine_group_kernel<T, 16, D / 16><<<group_grid(rows, 16), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 9, ovf,
+                                                                              ovf + 1);
   FMB_LAUNCH_CHECK("bwd_combine_group_kernel<16>");
-  bwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, a.scale, ovf + 1, 17);
+  bwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, ovf + 1, 17);
   FMB_LAUNCH_CHECK("bwd_combine_kernel");
   return FMB_OK;
 }
@@ -622,8 +620,8 @@ static int bwd_combine_any(const AttnArgs& a, const AttnWorkspace& w, const Pass
   if (a.d == 128) return bwd_combine_dispatch<T, 128>(a, w, ps, s);
   if (a.d == 256) return bwd_combine_dispatch<T, 256>(a, w, ps, s);
   const int64_t rows = a.total_q * ps.nh;
-  bwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>((const float*)w.part_o, make_combine(a, w, ps), (T*)a.dq,
-                                                        a.dq_rs, a.dq_hs, a.scale, nullptr, 0);
+  bwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>((const T*)w.part_o, make_combine(a, w, ps), (T*)a.dq,
+                                                        a.dq_rs, a.dq_hs, nullptr, 0);
   FMB_LAUNCH_CHECK("bwd_combine_kernel");
   return FMB_OK;
 }
@@ -679,7 +677,7 @@ int launch_attn_fwd(const AttnArgs& a, int engine, cudaStream_t s) {
 }
 
 int launch_attn_bwd(const AttnArgs& a, int engine, cudaStream_t s) {
-  AttnWorkspace w = carve_attn_workspace(a.ws, a.ws_bytes, a, 4, false, 0);
+  AttnWorkspace w = carve_attn_workspace(a.ws, a.ws_bytes, a, 2, false, 0);
   int rc = check_pass_sizes("attn_bwd", a, w, w.bytes);
   if (rc) return rc;
   FMB_CUDA(cudaMemsetAsync(w.status, 0, 512, s));

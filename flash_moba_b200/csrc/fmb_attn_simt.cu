@@ -230,7 +230,7 @@ __global__ void __launch_bounds__(kSimtThreads) bwd_main_simt_kernel(SimtParams 
   const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
   const int key0 = c * p.ps.chunk + sb * C;
   if (key0 >= len_k) {
-    zero_dq_partials(p.ps, static_cast<float*>(p.part_o), plane, b, hk, group, c, D);
+    zero_dq_partials<T>(p.ps, static_cast<T*>(p.part_o), plane, b, hk, group, c, D);
     return;
   }
   const int keys_valid = min(C, len_k - key0);
@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(kSimtThreads) bwd_main_simt_kernel(SimtParams 
   const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
   stage_keys<T, C, D>(sK, sKt, kbase, p.k_rs, keys_valid);
   stage_keys<T, C, D>(nullptr, sVt, vbase, p.v_rs, keys_valid);
-  float* part_dq = static_cast<float*>(p.part_o);
+  T* part_dq = static_cast<T*>(p.part_o);
 
   // dK/dV accumulators: keys ty*TN.., dims tx*TD..
   float dk[TN][TD], dv[TN][TD];
@@ -347,9 +347,9 @@ __global__ void __launch_bounds__(kSimtThreads) bwd_main_simt_kernel(SimtParams 
           const int m = ty * 4 + i;
           if (m < rows) {
             const int64_t slot = slot0 + t0 + m;
-            float* dst = part_dq + (plane + slot) * D;
+            T* dst = part_dq + (plane + slot) * D;
 #pragma unroll
-            for (int j = 0; j < TD; ++j) dst[part_col(slot, tx * TD + j, 4)] = dq[i][j];
+            for (int j = 0; j < TD; ++j) dst[part_col(slot, tx * TD + j, 8)] = Elem<T>::from_f(dq[i][j] * p.scale);
           }
         }
       }

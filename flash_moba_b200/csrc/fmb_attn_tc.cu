@@ -320,25 +320,35 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
 
 
 // ======================================================================== backward
-// CTA = key chunk c of (sequence b, kv head hk); 288 threads:
-//   warps 0-7  compute.  TMEM lane = gathered query row (at the end: key); warps w and w+4 share
-//              a lane quarter and split the columns in halves.  Thread 0 issues the MMAs.
-//   warps 8-11 loaders.  For every tile they read the tile's row ids, LSE and D, and gather the
-//              Q and dO rows with 16-byte cp.async copies straight into the swizzled UMMA tiles
-//              (no registers; measured ~4x the throughput of loads into registers, and ~3.5x that
-//              of TMA tile::gather4 row gathers for these isolated 256-byte rows).  They run one
-//              tile ahead: the next tile's rows are requested as soon as the GEMMs that read Q and
-//              dO have completed, and land under the dQ GEMM and epilogue.
+// CTA = key block c of (sequence b, kv head hk); 384 threads, warp-specialised:
+//   warps 0-7   compute.  TMEM lane = gathered query row (at the end: key); warps w and w+4 share
+//               a lane quarter and split the columns in halves.
+//   warp 8      one thread issues every MMA; it alone waits for operand tiles, so a late gather
+//               never stalls a compute warp that still has work.
+//   warp 9      Q loader, warps 10-11 dO loader: 16-byte cp.async copies of the tile's rows
+//               straight into the swizzled UMMA tiles (no registers; measured ~4x the throughput
+//               of loads into registers, and ~3.5x that of TMA tile::gather4 row gathers for these
+//               isolated 256-byte rows).  Q is double buffered (its loader has two tiles of slack);
+//               dO is refilled as soon as the dV GEMM of the previous tile has completed.
 // The CTA walks the q heads of the kv head's group and the 128-row tiles of each head's CSC
 // column as one sequence of tiles.  Per tile, five GEMMs:
 //     S  = Q.K^T          dP = dO.V^T                       (both K-major operands)
 //     dV += P^T.dO        dK += dS^T.Q   (A and B consumed MN-major from the row-major tiles)
-//     dQ_partial = dS.K   (K consumed MN-major)             -> workspace at the pair's position
+//     dQ_partial = dS.K   (K consumed MN-major)             -> workspace at the entry's slot
 // dK and dV stay in TMEM (fp32) for the CTA's whole life: no atomics, no cross-head reduction
-// pass.  TMEM columns: [0,C) S then dQ, [C,2C) dP, [2C,2C+D) dV, [2C+D,2C+2D) dK.
+// pass.  TMEM columns: [0,C) S, [C,2C) dP then dQ, [2C,2C+D) dV, [2C+D,2C+2D) dK.
+//
+// All hand-offs are mbarriers.  Per tile i (the tensor pipe executes the GEMMs in issue order):
+//   compute:  wait S(i)  -> P = exp2(S.scale.log2e - LSE.log2e) -> shared (bf16) + registers (fp32) -> P_ready
+//             wait dP(i) -> dS = P.(dP - D) -> shared (bf16)                                        -> dS_ready
+//             wait dQ(i) -> dQ partial: TMEM -> registers -> global (scaled, I/O dtype)             -> dQ_free
+//   issuer:   P_ready(i)  -> dV(i)          [its completion frees dO and P]
+//             dS_ready(i) -> dQ(i) over dP's columns, dK(i) [its completion frees this Q buffer]
+//             Q(i+1) landed -> S(i+1);  dO(i+1) landed and dQ_free(i) -> dP(i+1)
 constexpr int kBwdCompute = 256;
-constexpr int kBwdLoaders = 128;
-constexpr int kBwdThreads = kBwdCompute + kBwdLoaders;
+constexpr int kBwdQLoaders = 32;
+constexpr int kBwdOLoaders = 64;
+constexpr int kBwdThreads = kBwdCompute + 32 + kBwdQLoaders + kBwdOLoaders;
 
 struct BwdTile {
   int hg;        // head within the group
@@ -348,25 +358,45 @@ struct BwdTile {
   int64_t slot;  // the column's first slot in the pass
 };
 
+// first head >= it.hg of the kv head's group whose column of key block c is not empty
+__device__ __forceinline__ bool bwd_seek_head(const PassParams& ps, int b, int hk, int group, int c, BwdTile& it) {
+  for (; it.hg < group; ++it.hg) {
+    const ColRef col = column_of(ps, b, hk * group + it.hg, c);
+    if (col.nnz > 0) {
+      it.nnz = col.nnz; it.off = col.off; it.slot = col.slot; it.t0 = 0;
+      return true;
+    }
+  }
+  it.hg = group;
+  return false;
+}
+__device__ __forceinline__ bool bwd_next_tile(const PassParams& ps, int b, int hk, int group, int c, BwdTile& it) {
+  it.t0 += kTcM;
+  if (it.t0 < it.nnz) return true;
+  ++it.hg;
+  return bwd_seek_head(ps, b, hk, group, c, it);
+}
+
 template <typename T, int C, int D>
 __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   static_assert(C == 128, "tensor-core backward keeps one key per TMEM lane");
   constexpr uint32_t kKBlock = C * 128;
   constexpr uint32_t kQBlock = kTcM * 128;
+  constexpr uint32_t kQTile = kTcM * D * 2;
   constexpr int NCOLS = 512;
   constexpr int DH = D / 2;                       // head-dim columns per thread in the epilogues
   extern __shared__ unsigned char smem_raw[];
-  __shared__ uint64_t bar, bar_c, bar_full;
+  __shared__ uint64_t bar_s, bar_p, bar_dq, bar_dv, bar_fin, bar_fulldo, bar_dk[2], bar_fullq[2];
+  __shared__ uint64_t bar_pready, bar_dsready, bar_dqfree;
   __shared__ uint32_t tmem_base_s;
-  __shared__ int sRow[2][kTcM];
-  __shared__ float sLse[2][kTcM], sDs[2][kTcM];
+  __shared__ int sRowQ[kTcM], sRowO[kTcM];        // row ids of the tile a loader group is fetching
 
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* sK = smem;                       // [C][D]
   unsigned char* sV = sK + C * D * 2;             // [C][D]
-  unsigned char* sQ = sV + C * D * 2;             // [128][D]
-  unsigned char* sdO = sQ + kTcM * D * 2;         // [128][D]
-  unsigned char* sP = sdO + kTcM * D * 2;         // [128][C]   (fp32 dQ staging spans sP|sdS)
+  unsigned char* sQ = sV + C * D * 2;             // 2 x [128][D]
+  unsigned char* sdO = sQ + 2 * kQTile;           // [128][D]
+  unsigned char* sP = sdO + kQTile;               // [128][C]
   unsigned char* sdS = sP + kTcM * C * 2;         // [128][C]
 
   const int group = p.heads / p.heads_k;
@@ -376,45 +406,38 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
   const int key0 = c * p.ps.chunk + sb * C;
   if (key0 >= len_k) {
-    zero_dq_partials(p.ps, static_cast<float*>(p.part_o), plane, b, hk, group, c, D);
+    zero_dq_partials<T>(p.ps, static_cast<T*>(p.part_o), plane, b, hk, group, c, D);
     return;
   }
   const int keys_valid = min(C, len_k - key0);
   const int shift = len_k - len_q;
   const float scale_log2 = p.scale * kLog2eTc;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool loader = warp >= 8;
   const int lt = tid & (kTcM - 1);                // row (TMEM lane) of a compute thread
   const int hf = (tid >> 7) & 1;                  // column half of a compute thread
 
   // ---- the CTA's tile sequence
-  auto seek_head = [&](BwdTile& it) {             // first head >= it.hg with a non-empty column
-    for (; it.hg < group; ++it.hg) {
-      const ColRef col = column_of(p.ps, b, hk * group + it.hg, c);
-      if (col.nnz > 0) {
-        it.nnz = col.nnz; it.off = col.off; it.slot = col.slot; it.t0 = 0;
-        return true;
-      }
-    }
-    it.hg = group;
-    return false;
+  auto seek_head = [&](BwdTile& it) { return bwd_seek_head(p.ps, b, hk, group, c, it); };
+  auto next_tile = [&](BwdTile& it) { return bwd_next_tile(p.ps, b, hk, group, c, it); };
+  // sequence-local query row of entry i of the tile (-1 = none).  row_raw() only issues the load;
+  // row_checked() is applied where the value is used, so that a prefetch does not wait for it.
+  auto row_raw = [&](const BwdTile& it, int i) {
+    return (it.t0 + i < it.nnz) ? p.ps.indices[it.off + it.t0 + i] : -1;
   };
-  auto next_tile = [&](BwdTile& it) {
-    it.t0 += kTcM;
-    if (it.t0 < it.nnz) return true;
-    ++it.hg;
-    return seek_head(it);
-  };
+  auto row_checked = [&](int r) { return (r < 0 || r >= len_q) ? -1 : r; };
 
   FMB_T0();
   if (warp == 0) tmem_alloc(&tmem_base_s, NCOLS);
   if (tid == 0) {
-    mbar_init(&bar, 1);
-    mbar_init(&bar_c, 1);
-    mbar_init(&bar_full, kBwdLoaders);
+    mbar_init(&bar_s, 1); mbar_init(&bar_p, 1); mbar_init(&bar_dq, 1); mbar_init(&bar_dv, 1); mbar_init(&bar_fin, 1);
+    mbar_init(&bar_dk[0], 1); mbar_init(&bar_dk[1], 1);
+    mbar_init(&bar_fullq[0], kBwdQLoaders / 32); mbar_init(&bar_fullq[1], kBwdQLoaders / 32);
+    mbar_init(&bar_fulldo, kBwdOLoaders / 32);   // one arrival per loader warp
+    mbar_init(&bar_pready, kBwdCompute / 32); mbar_init(&bar_dsready, kBwdCompute / 32);
+    mbar_init(&bar_dqfree, kBwdCompute / 32);   // one arrival per compute warp
     mbar_fence_init();
   }
-  if (!loader) {
+  if (warp < 8) {
     const T* kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + key0) * p.k_rs + (int64_t)hk * p.k_hs;
     const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
     if (hf == 0) stage_dense_sw128_t<T, D / 8, C>(lt, sK, kKBlock, kbase, p.k_rs, keys_valid);
@@ -426,185 +449,275 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   tc_fence_after_sync();
   FMB_TICK(16);   // prologue
   const uint32_t tmem_base = tmem_base_s;
+  const uint32_t tS = tmem_base, tdP = tmem_base + C, tdV = tmem_base + 2 * C, tdK = tmem_base + 2 * C + D;
+  const uint32_t tdQ = tdP;
 
   BwdTile it{0, 0, 0, 0, 0};
   bool have = seek_head(it);
 
-  if (loader) {
-    // =============================================================== loader warps
-    uint32_t phase_c = 0;
-    for (int i = 0; have; ++i) {
-      const int buf = i & 1;
-      FMB_TICK_AT(26, 256);   // loader: tile bookkeeping
-      // row data of the tile (independent of the operand buffers)
-      const int h = hk * group + it.hg;
-      {
-        int r = -1;
-        if (it.t0 + lt < it.nnz) {
-          r = p.ps.indices[it.off + it.t0 + lt];
-          if (r < 0 || r >= len_q) r = -1;
+  if (warp == 8) {
+    // =============================================================== MMA issuer
+    if (lane == 0) {
+      const uint32_t sK_a = smem_u32(sK), sV_a = smem_u32(sV), sQ_a = smem_u32(sQ), sdO_a = smem_u32(sdO),
+                     sP_a = smem_u32(sP), sdS_a = smem_u32(sdS);
+      constexpr uint32_t idesc_s = make_idesc(FmtOf<T>::v, kTcM, C, 0, 0);     // rows x keys
+      constexpr uint32_t idesc_kv = make_idesc(FmtOf<T>::v, C, D, 1, 1);       // keys x d, both MN-major
+      constexpr uint32_t idesc_dq = make_idesc(FmtOf<T>::v, kTcM, D, 0, 1);    // rows x d
+      auto issue_s = [&](int i) {      // S(i) = Q(i).K^T
+        const uint32_t q_a = sQ_a + (i & 1) * kQTile;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t ko = (ks >> 2) * kQBlock + (ks & 3) * 32, kb = (ks >> 2) * kKBlock + (ks & 3) * 32;
+          umma_ss(tS, make_desc_sw128(q_a + ko, 16, 1024), make_desc_sw128(sK_a + kb, 16, 1024), idesc_s, ks > 0);
         }
-        float l2 = CUDART_INF_F, dd = 0.f;
-        if (r >= 0) {
-          l2 = p.lse[(int64_t)h * p.total_q + q0 + r] * kLog2eTc;
-          dd = p.softmax_d[(int64_t)h * p.total_q + q0 + r];
+        umma_commit(&bar_s);
+      };
+      auto issue_dp = [&]() {          // dP = dO.V^T
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t ko = (ks >> 2) * kQBlock + (ks & 3) * 32, kb = (ks >> 2) * kKBlock + (ks & 3) * 32;
+          umma_ss(tdP, make_desc_sw128(sdO_a + ko, 16, 1024), make_desc_sw128(sV_a + kb, 16, 1024), idesc_s, ks > 0);
         }
-        sRow[buf][lt] = r; sLse[buf][lt] = l2; sDs[buf][lt] = dd;
-      }
-      FMB_TICK_AT(28, 256);   // loader: row ids, LSE, D
-      bool ok = true;
-      if (i > 0) {   // the GEMMs that read Q / dO of the previous tile must have completed
-        ok = mbar_wait(&bar_c, phase_c, p.status, 5);
-        phase_c ^= 1;
-      }
-      ok = bar_and(1, kBwdLoaders, ok);   // also makes every loader's row ids visible to the others
-      FMB_TICK_AT(27, 256);   // loader: waiting for the buffers
-      if (!ok) break;
-      const T* qbase = static_cast<const T*>(p.q) + (int64_t)q0 * p.q_rs + (int64_t)h * p.q_hs;
-      const T* dobase = static_cast<const T*>(p.dout) + (int64_t)q0 * p.do_rs + (int64_t)h * p.do_hs;
-      gather_cp_async<T, D / 8>(lt, sQ, kQBlock, qbase, p.q_rs, sRow[buf]);
-      gather_cp_async<T, D / 8>(lt, sdO, kQBlock, dobase, p.do_rs, sRow[buf]);
-      cp_async_wait_all();
-      fence_async_smem();        // the copies are generic-proxy writes; the MMAs read through the async proxy
-      mbar_arrive(&bar_full);
-      FMB_TICK_AT(29, 256);   // loader: gather
-      have = next_tile(it);
-    }
-  } else {
-    // =============================================================== compute warps
-    const uint32_t tS = tmem_base, tdP = tmem_base + C, tdV = tmem_base + 2 * C, tdK = tmem_base + 2 * C + D;
-    const uint32_t tdQ = tS;
-    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t sK_a = smem_u32(sK), sV_a = smem_u32(sV), sQ_a = smem_u32(sQ), sdO_a = smem_u32(sdO),
-                   sP_a = smem_u32(sP), sdS_a = smem_u32(sdS);
-    constexpr uint32_t idesc_s = make_idesc(FmtOf<T>::v, kTcM, C, 0, 0);     // rows x keys
-    constexpr uint32_t idesc_kv = make_idesc(FmtOf<T>::v, C, D, 1, 1);       // keys x d, both MN-major
-    constexpr uint32_t idesc_dq = make_idesc(FmtOf<T>::v, kTcM, D, 0, 1);    // rows x d
-    float* part_dq = static_cast<float*>(p.part_o);
-    uint32_t phase = 0, phase_full = 0;
-    bool any_tile = false, good = true;
-
-    for (int i = 0; have && good; ++i) {
-      const int buf = i & 1;
-      const int rows = min(kTcM, it.nnz - it.t0);
-      if (tid == 0) {
-        // the tile's Q / dO rows (and its row data) have landed
-        if (mbar_wait(&bar_full, phase_full, p.status, 6)) {
-          FMB_TICK(17);   // waiting for the tile's operands
-          tc_fence_after_sync();
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t ko = (ks >> 2) * kQBlock + (ks & 3) * 32, kb = (ks >> 2) * kKBlock + (ks & 3) * 32;
-            umma_ss(tS, make_desc_sw128(sQ_a + ko, 16, 1024), make_desc_sw128(sK_a + kb, 16, 1024), idesc_s, ks > 0);
-          }
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t ko = (ks >> 2) * kQBlock + (ks & 3) * 32, kb = (ks >> 2) * kKBlock + (ks & 3) * 32;
-            umma_ss(tdP, make_desc_sw128(sdO_a + ko, 16, 1024), make_desc_sw128(sV_a + kb, 16, 1024), idesc_s, ks > 0);
-          }
-          umma_commit(&bar);
-        }
-      }
-      phase_full ^= 1;
-      if (warp < 4 && lane == 0) bulk_wait_read();   // the previous tile's dQ staging has been read out
-      good = bar_and(2, kBwdCompute, mbar_wait(&bar, phase, p.status, 3));
-      phase ^= 1;
-      tc_fence_after_sync();
-      FMB_TICK(18);   // operands landed + S, dP GEMMs
-      if (!good) break;
-
-      // ---- P and dS of row `lt`, this thread's 64 keys.  The previous tile's dQ staging shares
-      // the P/dS memory; its bulk copies were waited for before the barrier above.
-      {
-        const int r = sRow[buf][lt];
-        const float lse2 = sLse[buf][lt], dd = sDs[buf][lt];
-        const int lim = r < 0 ? 0 : (p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid);
-#pragma unroll
-        for (int i2 = 0; i2 < 2; ++i2) {
-          const int col0 = hf * 64 + i2 * 32;
-          float s[32], dp[32];
-          tmem_ld32(tS + lane_sel + col0, s);
-          tmem_ld32(tdP + lane_sel + col0, dp);
-          tmem_ld_wait();
-#pragma unroll
-          for (int jj = 0; jj < 32; ++jj) {
-            const float pr = (col0 + jj < lim) ? exp2f(s[jj] * scale_log2 - lse2) : 0.f;
-            s[jj] = pr;
-            dp[jj] = pr * (dp[jj] - dd);
-          }
-#pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            *reinterpret_cast<uint4*>(sP + sw128_offset(lt, col0 / 8 + jj, kQBlock)) = pack8<T>(s + jj * 8);
-            *reinterpret_cast<uint4*>(sdS + sw128_offset(lt, col0 / 8 + jj, kQBlock)) = pack8<T>(dp + jj * 8);
-          }
-        }
-        tc_fence_before_sync();
-        fence_async_smem();
-      }
-      FMB_TICK(20);   // P, dS
-      bar_sync(2, kBwdCompute);
-      FMB_TICK(21);
-      if (tid == 0) {
+        umma_commit(&bar_p);
+      };
+      bool ok = have;
+      if (ok) ok = mbar_wait(&bar_fullq[0], 0, p.status, 6);
+      if (ok) { tc_fence_after_sync(); issue_s(0); ok = mbar_wait(&bar_fulldo, 0, p.status, 6); }
+      if (ok) { tc_fence_after_sync(); issue_dp(); }
+      int i = 0;
+#pragma unroll 1
+      for (; ok; ++i) {
+        const bool more = next_tile(it);
+        const uint32_t acc = i > 0 ? 1u : 0u;
+        const uint32_t q_a = sQ_a + (i & 1) * kQTile;
+        // dV += P^T.dO : M = keys, N = d, K = the 128 gathered rows
+        if (!(ok = mbar_wait(&bar_pready, i & 1, p.status, 1))) break;
         tc_fence_after_sync();
-        const uint32_t acc = any_tile ? 1u : 0u;
-        // dV += P^T.dO, dK += dS^T.Q : M = keys, N = d, K = the 128 gathered rows
 #pragma unroll
         for (int ks = 0; ks < kTcM / 16; ++ks) {
           umma_ss(tdV, make_desc_sw128(sP_a + ks * 2048, kQBlock, 1024),
                   make_desc_sw128(sdO_a + ks * 2048, kQBlock, 1024), idesc_kv, acc | (ks > 0));
         }
-#pragma unroll
-        for (int ks = 0; ks < kTcM / 16; ++ks) {
-          umma_ss(tdK, make_desc_sw128(sdS_a + ks * 2048, kQBlock, 1024),
-                  make_desc_sw128(sQ_a + ks * 2048, kQBlock, 1024), idesc_kv, acc | (ks > 0));
-        }
-        umma_commit(&bar_c);   // Q and dO are free once these complete: the loader's signal
+        umma_commit(&bar_dv);        // dO is free once this completes: the dO loader's signal
+        if (!(ok = mbar_wait(&bar_dsready, i & 1, p.status, 2))) break;
+        tc_fence_after_sync();
         // dQ partial = dS.K : M = rows, N = d, K = keys
 #pragma unroll
         for (int ks = 0; ks < C / 16; ++ks) {
           umma_ss(tdQ, make_desc_sw128(sdS_a + (ks >> 2) * kQBlock + (ks & 3) * 32, 16, 1024),
                   make_desc_sw128(sK_a + ks * 2048, kKBlock, 1024), idesc_dq, ks > 0);
         }
-        umma_commit(&bar);
+        umma_commit(&bar_dq);
+        // dK += dS^T.Q
+#pragma unroll
+        for (int ks = 0; ks < kTcM / 16; ++ks) {
+          umma_ss(tdK, make_desc_sw128(sdS_a + ks * 2048, kQBlock, 1024),
+                  make_desc_sw128(q_a + ks * 2048, kQBlock, 1024), idesc_kv, acc | (ks > 0));
+        }
+        umma_commit(&bar_dk[i & 1]); // this Q buffer is free once it completes: the Q loader's signal
+        if (!more) { ++i; break; }
+        if (!(ok = mbar_wait(&bar_fullq[(i + 1) & 1], ((i + 1) >> 1) & 1, p.status, 6))) break;
+        tc_fence_after_sync();
+        issue_s(i + 1);              // S's columns are free since P_ready(i)
+        if (!(ok = mbar_wait(&bar_fulldo, (i + 1) & 1, p.status, 6))) break;
+        if (!(ok = mbar_wait(&bar_dqfree, i & 1, p.status, 6))) break;
+        tc_fence_after_sync();
+        issue_dp();
       }
-      any_tile = true;
-      good = bar_and(2, kBwdCompute, mbar_wait(&bar, phase, p.status, 4));
-      phase ^= 1;
-      tc_fence_after_sync();
-      FMB_TICK(22);   // dV, dK, dQ GEMMs
-      if (!good) break;
+      if (ok && i > 0) umma_commit(&bar_fin);
+    }
+  } else if (warp >= 9) {
+    // =============================================================== loader warps
+    const bool q_side = warp == 9;
+    const int nt = q_side ? kBwdQLoaders : kBwdOLoaders;
+    const int t = q_side ? lane : tid - (kBwdCompute + 32 + kBwdQLoaders);
+    int* sRow = q_side ? sRowQ : sRowO;
+    const int bar_id = q_side ? 3 : 4;
+#pragma unroll 1
+    for (int m = 0; have; ++m) {
+      // the tile's row ids, fetched before the wait for the buffer
+      int rid[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) rid[k] = (t + k * nt < kTcM) ? row_checked(row_raw(it, t + k * nt)) : -1;
+      const int h = hk * group + it.hg;
+      bool ok = true;
+      if (q_side) {
+        if (m >= 2) ok = mbar_wait(&bar_dk[m & 1], ((m >> 1) - 1) & 1, p.status, 5);   // dK(m-2) has read Q
+      } else {
+        if (m >= 1) ok = mbar_wait(&bar_dv, (m - 1) & 1, p.status, 5);                 // dV(m-1) has read dO
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (t + k * nt < kTcM) sRow[t + k * nt] = rid[k];
+      ok = bar_and(bar_id, nt, ok);                // also publishes the row ids to the group
+      FMB_TICK_AT(24, 288); FMB_TICK_AT(26, 320);  // loaders: row ids + waiting for the buffer
+      if (!ok) break;
+      if (q_side) {
+        const T* qbase = static_cast<const T*>(p.q) + (int64_t)q0 * p.q_rs + (int64_t)h * p.q_hs;
+        gather_cp_async<T, D / 8, kBwdQLoaders>(t, sQ + (m & 1) * kQTile, kQBlock, qbase, p.q_rs, sRow);
+      } else {
+        const T* dobase = static_cast<const T*>(p.dout) + (int64_t)q0 * p.do_rs + (int64_t)h * p.do_hs;
+        gather_cp_async<T, D / 8, kBwdOLoaders>(t, sdO, kQBlock, dobase, p.do_rs, sRow);
+      }
+      cp_async_wait_all();
+      fence_async_smem();        // the copies are generic-proxy writes; the MMAs read through the async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(q_side ? &bar_fullq[m & 1] : &bar_fulldo);
+      FMB_TICK_AT(25, 288); FMB_TICK_AT(27, 320);  // loaders: gather
+      bar_sync(bar_id, nt);                        // every thread has read the row ids
+      have = next_tile(it);
+    }
+  } else {
+    // =============================================================== compute warps
+    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    T* part_dq = static_cast<T*>(p.part_o);
+    bool any_tile = false, good = true;
 
-      // dQ partial of row `lt`, this thread's half of the head dim: staged (fp32) over the P/dS
-      // tiles, which the GEMMs have finished reading; one bulk copy per 32 rows
+    // row data (query row, LSE, D) of the tiles are fetched into registers ahead of their use: the
+    // row id two tiles ahead, LSE and D (which need the row id) one tile ahead
+    BwdTile n1 = it, n2;
+    bool have1 = have && next_tile(n1);
+    n2 = n1;
+    bool have2 = have1 && next_tile(n2);
+    int r_cur = -1, r_n1 = -1, r_n2 = -1;
+    float lse_cur = CUDART_INF_F, dd_cur = 0.f, lse_n1 = CUDART_INF_F, dd_n1 = 0.f;
+    auto row_stats = [&](const BwdTile& tl, int r, float& l2, float& dd) {
+      l2 = CUDART_INF_F; dd = 0.f;
+      if (r >= 0) {
+        const int64_t at = (int64_t)(hk * group + tl.hg) * p.total_q + q0 + r;
+        l2 = p.lse[at] * kLog2eTc;
+        dd = p.softmax_d[at];
+      }
+    };
+    if (have) {
+      r_cur = row_checked(row_raw(it, lt));
+      if (have1) r_n1 = row_raw(n1, lt);
+      row_stats(it, r_cur, lse_cur, dd_cur);
+    }
+
+#pragma unroll 1
+    for (int i = 0; have && good; ++i) {
+      const int rows = min(kTcM, it.nnz - it.t0);
+      if (have2) r_n2 = row_raw(n2, lt);
+      if (have1) {
+        r_n1 = row_checked(r_n1);
+        row_stats(n1, r_n1, lse_n1, dd_n1);
+      }
+
+      // ---- P of row `lt`, this thread's 64 keys
+      if (!(good = mbar_wait(&bar_s, i & 1, p.status, 3))) break;
+      tc_fence_after_sync();
+      FMB_TICK(17);   // waiting for S
+      const int lim = r_cur < 0 ? 0 : (p.causal ? min(keys_valid, r_cur + shift - key0 + 1) : keys_valid);
+      float pr[64];
+#pragma unroll
+      for (int i2 = 0; i2 < 2; ++i2) {
+        const int col0 = hf * 64 + i2 * 32;
+        tmem_ld32(tS + lane_sel + col0, pr + i2 * 32);
+        tmem_ld_wait();
+        FMB_TICK(31);
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj)
+          pr[i2 * 32 + jj] = (col0 + jj < lim) ? exp2f(pr[i2 * 32 + jj] * scale_log2 - lse_cur) : 0.f;
+        FMB_TICK(32);
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+          *reinterpret_cast<uint4*>(sP + sw128_offset(lt, col0 / 8 + jj, kQBlock)) = pack8<T>(pr + i2 * 32 + jj * 8);
+        FMB_TICK(33);
+      }
+      tc_fence_before_sync();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_pready);      // S has been read, P is in shared memory
+      FMB_TICK(18);   // P
+
+      // ---- dS
+      if (!(good = mbar_wait(&bar_p, i & 1, p.status, 3))) break;
+      tc_fence_after_sync();
+      FMB_TICK(19);   // waiting for dP
+#pragma unroll
+      for (int i2 = 0; i2 < 2; ++i2) {
+        const int col0 = hf * 64 + i2 * 32;
+        float dp[32];
+        tmem_ld32(tdP + lane_sel + col0, dp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) dp[jj] = pr[i2 * 32 + jj] * (dp[jj] - dd_cur);
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+          *reinterpret_cast<uint4*>(sdS + sw128_offset(lt, col0 / 8 + jj, kQBlock)) = pack8<T>(dp + jj * 8);
+      }
+      tc_fence_before_sync();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_dsready);     // dP has been read, dS is in shared memory
+      FMB_TICK(20);   // dS
+      any_tile = true;
+
+      // ---- dQ partial of row `lt`, this thread's half of the head dim: scaled, rounded to the I/O
+      // dtype, stored at the entry's slot (16-byte chunks permuted like the forward partials)
+      if (!(good = mbar_wait(&bar_dq, i & 1, p.status, 4))) break;
+      tc_fence_after_sync();
+      FMB_TICK(21);   // waiting for dQ
       {
-        const int key = (int)((it.slot + it.t0 + lt) & 7);
-        unsigned char* srow = sP + lt * (D * 4);
         float o[DH];
 #pragma unroll
         for (int i2 = 0; i2 < DH / 32; ++i2) tmem_ld32(tdQ + lane_sel + hf * DH + i2 * 32, o + i2 * 32);
         tmem_ld_wait();
-#pragma unroll
-        for (int jj = 0; jj < DH / 4; ++jj)
-          *reinterpret_cast<float4*>(srow + (((hf * (DH / 4) + jj) ^ key) << 4)) =
-              make_float4(o[4 * jj], o[4 * jj + 1], o[4 * jj + 2], o[4 * jj + 3]);
         tc_fence_before_sync();
-        fence_async_smem();
-      }
-      bar_sync(2, kBwdCompute);   // both halves of every row staged; all reads of dQ done
-      if (warp < 4) {
-        const int wrows = min(32, rows - warp * 32);
-        if (lane == 0 && wrows > 0) {
-          bulk_store(part_dq + (plane + it.slot + it.t0 + warp * 32) * D, sP + warp * 32 * (D * 4), (uint32_t)wrows * D * 4);
-          bulk_commit();      // its reads are waited for under the next tile's first GEMMs
+        FMB_TICK(29);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_dqfree);    // dQ has been read out of dP's columns
+        constexpr int NCH = DH / 8;               // 16-byte chunks of this thread's half row
+        uint4 ch[NCH];
+#pragma unroll
+        for (int jj = 0; jj < NCH; ++jj) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[jj * 8 + e] *= p.scale;
+          ch[jj] = pack8<T>(o + jj * 8);
+        }
+        // transpose inside groups of NCH lanes: afterwards lane j of a group holds chunk j of each of
+        // the group's NCH rows, so one store instruction writes whole half rows (full memory lines)
+#pragma unroll
+        for (int m = 1; m < NCH; m <<= 1) {
+          const bool up = (lane & m) != 0;
+#pragma unroll
+          for (int a = 0; a < NCH; ++a) {
+            if (a & m) continue;
+            uint4 snd = up ? ch[a] : ch[a | m];
+            uint4 rcv;
+            rcv.x = __shfl_xor_sync(0xffffffffu, snd.x, m);
+            rcv.y = __shfl_xor_sync(0xffffffffu, snd.y, m);
+            rcv.z = __shfl_xor_sync(0xffffffffu, snd.z, m);
+            rcv.w = __shfl_xor_sync(0xffffffffu, snd.w, m);
+            if (up) ch[a] = rcv; else ch[a | m] = rcv;
+          }
+        }
+        FMB_TICK(30);
+        const int gl = lane & (NCH - 1);          // this lane's chunk
+        const int row_g = lt - gl;                // first row of the lane group
+#pragma unroll
+        for (int k = 0; k < NCH; ++k) {
+          const int row = row_g + k;
+          if (row < rows) {
+            const int64_t slot = it.slot + it.t0 + row;
+            T* dst = part_dq + (plane + slot) * D;
+            *reinterpret_cast<uint4*>(dst + (((hf * NCH + gl) ^ (int)(slot & 7)) << 3)) = ch[k];
+          }
         }
       }
-      FMB_TICK(23);   // dQ epilogue
-      have = next_tile(it);
+      FMB_TICK(22);   // dQ epilogue
+
+      it = n1; have = have1;
+      n1 = n2; have1 = have2;
+      if (have2) have2 = next_tile(n2);
+      r_cur = r_n1; lse_cur = lse_n1; dd_cur = dd_n1;
+      r_n1 = r_n2;
     }
 
-    if (warp < 4 && lane == 0) bulk_wait_read();
-    bar_sync(2, kBwdCompute);
-    // ---- dK (scaled) and dV of key `lt`, this thread's half of the head dim
+    // ---- all GEMMs done -> dK and dV of key `lt`, this thread's half of the head dim
+    if (any_tile && good) good = mbar_wait(&bar_fin, 0, p.status, 4);
+    good = bar_and(2, kBwdCompute, good);
     if (good) {
       tc_fence_after_sync();
       T* dkp = static_cast<T*>(p.dk) + (int64_t)(k0 + key0 + lt) * p.dk_rs + (int64_t)hk * p.dk_hs + hf * DH;
@@ -823,7 +936,8 @@ static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassPa
 template <typename T, int C, int D>
 static int bwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   TcParams p = make_tc_params(a, w, ps);
-  const size_t smem = (size_t)2 * C * D * 2 + (size_t)2 * kTcM * D * 2 + (size_t)2 * kTcM * C * 2 + 1024;
+  // K, V, two Q tiles, one dO tile, P and dS
+  const size_t smem = (size_t)2 * C * D * 2 + (size_t)3 * kTcM * D * 2 + (size_t)2 * kTcM * C * 2 + 1024;
   auto kern = bwd_main_tc_kernel<T, C, D>;
   FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int nchunk = max(a.ncol, ceil_div(a.max_k, a.chunk));

@@ -37,6 +37,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // leaves the kernel through its normal exit path (TMEM is still released).
 constexpr uint32_t kSpinLimit = 1u << 17;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int where) {
+#pragma unroll 1   // the compiler otherwise unrolls the poll 32 times at every call site
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
   }
@@ -217,7 +218,9 @@ __device__ __forceinline__ void gather_cp_async(int t, unsigned char* tile, uint
                                                 int64_t row_stride, const int* rows) {
   constexpr int RPP = NT / NCHUNK;           // rows per pass
   const int j = t % NCHUNK, rb = t / NCHUNK;
-#pragma unroll
+  // partly unrolled on purpose: the loader warps run beside other roles and the kernel's code has
+  // to stay small enough for the instruction cache
+#pragma unroll 4
   for (int i = 0; i < 128 / RPP; ++i) {
     const int r = rb + RPP * i;
     const int src = rows[r];

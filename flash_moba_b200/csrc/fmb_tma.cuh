@@ -1,6 +1,6 @@
 // TMA (tensor-map) support: host-side descriptor builder and device-side issue wrappers.
 // Only plain per-CTA loads are used: tiled loads and tile::gather4 row gathers, completion
-// through an mbarrier's transaction count.  No cluster multicast anywhere.
+// through an mbarrier's transaction count.
 #pragma once
 #include <cuda.h>
 
