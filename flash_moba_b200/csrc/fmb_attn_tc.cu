@@ -320,12 +320,12 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
 
 
 // ======================================================================== backward
-// CTA = key block c of (sequence b, kv head hk); 384 threads, warp-specialised:
+// CTA = key block c of (sequence b, kv head hk); 480 threads, warp-specialised:
 //   warps 0-7   compute.  TMEM lane = gathered query row (at the end: key); warps w and w+4 share
 //               a lane quarter and split the columns in halves.
 //   warp 8      one thread issues every MMA; it alone waits for operand tiles, so a late gather
 //               never stalls a compute warp that still has work.
-//   warp 9      Q loader, warps 10-11 dO loader: 16-byte cp.async copies of the tile's rows
+//   warps 9-10  Q loader, warps 11-14 dO loader: 16-byte cp.async copies of the tile's rows
 //               straight into the swizzled UMMA tiles (no registers; measured ~4x the throughput
 //               of loads into registers, and ~3.5x that of TMA tile::gather4 row gathers for these
 //               isolated 256-byte rows).  Q is double buffered (its loader has two tiles of slack);
@@ -342,12 +342,21 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
 //   compute:  wait S(i)  -> P = exp2(S.scale.log2e - LSE.log2e) -> shared (bf16) + registers (fp32) -> P_ready
 //             wait dP(i) -> dS = P.(dP - D) -> shared (bf16)                                        -> dS_ready
 //             wait dQ(i) -> dQ partial: TMEM -> registers -> global (scaled, I/O dtype)             -> dQ_free
-//   issuer:   P_ready(i)  -> dV(i)          [its completion frees dO and P]
+//   issuer:   P_ready(i)  -> dV(i) [its completion frees dO and P], S(i+1) once Q(i+1) has landed
 //             dS_ready(i) -> dQ(i) over dP's columns, dK(i) [its completion frees this Q buffer]
-//             Q(i+1) landed -> S(i+1);  dO(i+1) landed and dQ_free(i) -> dP(i+1)
+//             dO(i+1) landed and dQ_free(i) -> dP(i+1)
 constexpr int kBwdCompute = 256;
-constexpr int kBwdQLoaders = 32;
-constexpr int kBwdOLoaders = 64;
+#ifndef FMB_BWD_QW
+#define FMB_BWD_QW 1          // warps gathering Q rows
+#endif
+#ifndef FMB_BWD_OW
+#define FMB_BWD_OW 2          // warps gathering dO rows
+#endif
+#ifndef FMB_BWD_S_EARLY
+#define FMB_BWD_S_EARLY 0     // 1: S(i+1) is issued before dQ(i), dK(i) instead of after them
+#endif
+constexpr int kBwdQLoaders = 32 * FMB_BWD_QW;
+constexpr int kBwdOLoaders = 32 * FMB_BWD_OW;
 constexpr int kBwdThreads = kBwdCompute + 32 + kBwdQLoaders + kBwdOLoaders;
 
 struct BwdTile {
@@ -387,7 +396,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   constexpr int DH = D / 2;                       // head-dim columns per thread in the epilogues
   extern __shared__ unsigned char smem_raw[];
   __shared__ uint64_t bar_s, bar_p, bar_dq, bar_dv, bar_fin, bar_fulldo, bar_dk[2], bar_fullq[2];
-  __shared__ uint64_t bar_pready, bar_dsready, bar_dqfree;
+  __shared__ uint64_t bar_pready, bar_dsready, bar_dqfree, bar_kv;
   __shared__ uint32_t tmem_base_s;
   __shared__ int sRowQ[kTcM], sRowO[kTcM];        // row ids of the tile a loader group is fetching
 
@@ -435,18 +444,21 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
     mbar_init(&bar_fulldo, kBwdOLoaders / 32);   // one arrival per loader warp
     mbar_init(&bar_pready, kBwdCompute / 32); mbar_init(&bar_dsready, kBwdCompute / 32);
     mbar_init(&bar_dqfree, kBwdCompute / 32);   // one arrival per compute warp
+    mbar_init(&bar_kv, kBwdCompute / 32);
     mbar_fence_init();
   }
-  if (warp < 8) {
+  tc_fence_before_sync();
+  __syncthreads();                 // barriers initialised, TMEM allocated
+  tc_fence_after_sync();
+  if (warp < 8) {                  // K and V tiles; the loaders fetch the first row tiles meanwhile
     const T* kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + key0) * p.k_rs + (int64_t)hk * p.k_hs;
     const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
     if (hf == 0) stage_dense_sw128_t<T, D / 8, C>(lt, sK, kKBlock, kbase, p.k_rs, keys_valid);
     else stage_dense_sw128_t<T, D / 8, C>(lt, sV, kKBlock, vbase, p.v_rs, keys_valid);
     fence_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&bar_kv);
   }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
   FMB_TICK(16);   // prologue
   const uint32_t tmem_base = tmem_base_s;
   const uint32_t tS = tmem_base, tdP = tmem_base + C, tdV = tmem_base + 2 * C, tdK = tmem_base + 2 * C + D;
@@ -458,29 +470,29 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   if (warp == 8) {
     // =============================================================== MMA issuer
     if (lane == 0) {
-      const uint32_t sK_a = smem_u32(sK), sV_a = smem_u32(sV), sQ_a = smem_u32(sQ), sdO_a = smem_u32(sdO),
-                     sP_a = smem_u32(sP), sdS_a = smem_u32(sdS);
       constexpr uint32_t idesc_s = make_idesc(FmtOf<T>::v, kTcM, C, 0, 0);     // rows x keys
       constexpr uint32_t idesc_kv = make_idesc(FmtOf<T>::v, C, D, 1, 1);       // keys x d, both MN-major
       constexpr uint32_t idesc_dq = make_idesc(FmtOf<T>::v, kTcM, D, 0, 1);    // rows x d
+      // descriptor halves of every operand view, built once
+      const uint32_t hi = desc_hi_sw128(1024);
+      const uint32_t k_km = desc_lo_sw128(smem_u32(sK), 16), v_km = desc_lo_sw128(smem_u32(sV), 16);
+      const uint32_t k_mn = desc_lo_sw128(smem_u32(sK), kKBlock);
+      const uint32_t q_km = desc_lo_sw128(smem_u32(sQ), 16), q_mn = desc_lo_sw128(smem_u32(sQ), kQBlock);
+      const uint32_t do_km = desc_lo_sw128(smem_u32(sdO), 16), do_mn = desc_lo_sw128(smem_u32(sdO), kQBlock);
+      const uint32_t p_mn = desc_lo_sw128(smem_u32(sP), kQBlock);
+      const uint32_t ds_km = desc_lo_sw128(smem_u32(sdS), 16), ds_mn = desc_lo_sw128(smem_u32(sdS), kQBlock);
+      constexpr uint32_t kQBuf = kQTile >> 4;        // second Q buffer, in descriptor address units
+      constexpr uint32_t kQB = kQBlock >> 4, kKB = kKBlock >> 4;
       auto issue_s = [&](int i) {      // S(i) = Q(i).K^T
-        const uint32_t q_a = sQ_a + (i & 1) * kQTile;
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t ko = (ks >> 2) * kQBlock + (ks & 3) * 32, kb = (ks >> 2) * kKBlock + (ks & 3) * 32;
-          umma_ss(tS, make_desc_sw128(q_a + ko, 16, 1024), make_desc_sw128(sK_a + kb, 16, 1024), idesc_s, ks > 0);
-        }
+        umma_gemm<D / 16>(tS, q_km + (i & 1) * kQBuf, hi, 2, kQB, k_km, hi, 2, kKB, idesc_s, 0);
         umma_commit(&bar_s);
       };
       auto issue_dp = [&]() {          // dP = dO.V^T
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t ko = (ks >> 2) * kQBlock + (ks & 3) * 32, kb = (ks >> 2) * kKBlock + (ks & 3) * 32;
-          umma_ss(tdP, make_desc_sw128(sdO_a + ko, 16, 1024), make_desc_sw128(sV_a + kb, 16, 1024), idesc_s, ks > 0);
-        }
+        umma_gemm<D / 16>(tdP, do_km, hi, 2, kQB, v_km, hi, 2, kKB, idesc_s, 0);
         umma_commit(&bar_p);
       };
       bool ok = have;
+      if (ok) ok = mbar_wait(&bar_kv, 0, p.status, 6);
       if (ok) ok = mbar_wait(&bar_fullq[0], 0, p.status, 6);
       if (ok) { tc_fence_after_sync(); issue_s(0); ok = mbar_wait(&bar_fulldo, 0, p.status, 6); }
       if (ok) { tc_fence_after_sync(); issue_dp(); }
@@ -489,48 +501,52 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
       for (; ok; ++i) {
         const bool more = next_tile(it);
         const uint32_t acc = i > 0 ? 1u : 0u;
-        const uint32_t q_a = sQ_a + (i & 1) * kQTile;
         // dV += P^T.dO : M = keys, N = d, K = the 128 gathered rows
+        FMB_TICK_AT(41, 256);
         if (!(ok = mbar_wait(&bar_pready, i & 1, p.status, 1))) break;
         tc_fence_after_sync();
-#pragma unroll
-        for (int ks = 0; ks < kTcM / 16; ++ks) {
-          umma_ss(tdV, make_desc_sw128(sP_a + ks * 2048, kQBlock, 1024),
-                  make_desc_sw128(sdO_a + ks * 2048, kQBlock, 1024), idesc_kv, acc | (ks > 0));
-        }
+        FMB_TICK_AT(34, 256);
+        umma_gemm<kTcM / 16>(tdV, p_mn, hi, 128, 512, do_mn, hi, 128, 512, idesc_kv, acc);
         umma_commit(&bar_dv);        // dO is free once this completes: the dO loader's signal
+        FMB_TICK_AT(35, 256);
+#if FMB_BWD_S_EARLY
+        if (more) {                  // S(i+1): its columns are free since P_ready(i); runs under the dS phase
+          if (!(ok = mbar_wait(&bar_fullq[(i + 1) & 1], ((i + 1) >> 1) & 1, p.status, 6))) break;
+          tc_fence_after_sync();
+          issue_s(i + 1);
+        }
+        FMB_TICK_AT(38, 256);
+#endif
         if (!(ok = mbar_wait(&bar_dsready, i & 1, p.status, 2))) break;
         tc_fence_after_sync();
+        FMB_TICK_AT(36, 256);
         // dQ partial = dS.K : M = rows, N = d, K = keys
-#pragma unroll
-        for (int ks = 0; ks < C / 16; ++ks) {
-          umma_ss(tdQ, make_desc_sw128(sdS_a + (ks >> 2) * kQBlock + (ks & 3) * 32, 16, 1024),
-                  make_desc_sw128(sK_a + ks * 2048, kKBlock, 1024), idesc_dq, ks > 0);
-        }
+        umma_gemm<C / 16>(tdQ, ds_km, hi, 2, kQB, k_mn, hi, 128, 512, idesc_dq, 0);
         umma_commit(&bar_dq);
         // dK += dS^T.Q
-#pragma unroll
-        for (int ks = 0; ks < kTcM / 16; ++ks) {
-          umma_ss(tdK, make_desc_sw128(sdS_a + ks * 2048, kQBlock, 1024),
-                  make_desc_sw128(q_a + ks * 2048, kQBlock, 1024), idesc_kv, acc | (ks > 0));
-        }
+        umma_gemm<kTcM / 16>(tdK, ds_mn, hi, 128, 512, q_mn + (i & 1) * kQBuf, hi, 128, 512, idesc_kv, acc);
         umma_commit(&bar_dk[i & 1]); // this Q buffer is free once it completes: the Q loader's signal
+        FMB_TICK_AT(37, 256);
         if (!more) { ++i; break; }
+#if !FMB_BWD_S_EARLY
         if (!(ok = mbar_wait(&bar_fullq[(i + 1) & 1], ((i + 1) >> 1) & 1, p.status, 6))) break;
         tc_fence_after_sync();
         issue_s(i + 1);              // S's columns are free since P_ready(i)
+        FMB_TICK_AT(38, 256);
+#endif
         if (!(ok = mbar_wait(&bar_fulldo, (i + 1) & 1, p.status, 6))) break;
         if (!(ok = mbar_wait(&bar_dqfree, i & 1, p.status, 6))) break;
         tc_fence_after_sync();
         issue_dp();
+        FMB_TICK_AT(40, 256);
       }
       if (ok && i > 0) umma_commit(&bar_fin);
     }
   } else if (warp >= 9) {
     // =============================================================== loader warps
-    const bool q_side = warp == 9;
+    const bool q_side = warp < 9 + kBwdQLoaders / 32;
     const int nt = q_side ? kBwdQLoaders : kBwdOLoaders;
-    const int t = q_side ? lane : tid - (kBwdCompute + 32 + kBwdQLoaders);
+    const int t = q_side ? tid - (kBwdCompute + 32) : tid - (kBwdCompute + 32 + kBwdQLoaders);
     int* sRow = q_side ? sRowQ : sRowO;
     const int bar_id = q_side ? 3 : 4;
 #pragma unroll 1
@@ -550,7 +566,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
       for (int k = 0; k < 4; ++k)
         if (t + k * nt < kTcM) sRow[t + k * nt] = rid[k];
       ok = bar_and(bar_id, nt, ok);                // also publishes the row ids to the group
-      FMB_TICK_AT(24, 288); FMB_TICK_AT(26, 320);  // loaders: row ids + waiting for the buffer
+      FMB_TICK_AT(24, 288); FMB_TICK_AT(26, 288 + kBwdQLoaders);  // loaders: row ids + waiting for the buffer
       if (!ok) break;
       if (q_side) {
         const T* qbase = static_cast<const T*>(p.q) + (int64_t)q0 * p.q_rs + (int64_t)h * p.q_hs;
@@ -563,7 +579,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
       fence_async_smem();        // the copies are generic-proxy writes; the MMAs read through the async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(q_side ? &bar_fullq[m & 1] : &bar_fulldo);
-      FMB_TICK_AT(25, 288); FMB_TICK_AT(27, 320);  // loaders: gather
+      FMB_TICK_AT(25, 288); FMB_TICK_AT(27, 288 + kBwdQLoaders);  // loaders: gather
       bar_sync(bar_id, nt);                        // every thread has read the row ids
       have = next_tile(it);
     }
@@ -605,21 +621,27 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
       }
 
       // ---- P of row `lt`, this thread's 64 keys
-      if (!(good = mbar_wait(&bar_s, i & 1, p.status, 3))) break;
+      if (good) good = mbar_wait(&bar_s, i & 1, p.status, 3);   // on failure: run on to the barriers, leave there
       tc_fence_after_sync();
       FMB_TICK(17);   // waiting for S
       const int lim = r_cur < 0 ? 0 : (p.causal ? min(keys_valid, r_cur + shift - key0 + 1) : keys_valid);
       float pr[64];
+      tmem_ld32(tS + lane_sel + hf * 64, pr);
+      tmem_ld32(tS + lane_sel + hf * 64 + 32, pr + 32);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      FMB_TICK(31);
 #pragma unroll
       for (int i2 = 0; i2 < 2; ++i2) {
         const int col0 = hf * 64 + i2 * 32;
-        tmem_ld32(tS + lane_sel + col0, pr + i2 * 32);
-        tmem_ld_wait();
-        FMB_TICK(31);
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj)
           pr[i2 * 32 + jj] = (col0 + jj < lim) ? exp2f(pr[i2 * 32 + jj] * scale_log2 - lse_cur) : 0.f;
         FMB_TICK(32);
+        if (i2 == 0 && i > 0) {      // the previous tile's dQ staging (in the P tile) has been read out
+          if (warp < 4 && lane == 0) bulk_wait_read();
+          good = bar_and(2, kBwdCompute, good);
+        }
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj)
           *reinterpret_cast<uint4*>(sP + sw128_offset(lt, col0 / 8 + jj, kQBlock)) = pack8<T>(pr + i2 * 32 + jj * 8);
@@ -632,7 +654,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
       FMB_TICK(18);   // P
 
       // ---- dS
-      if (!(good = mbar_wait(&bar_p, i & 1, p.status, 3))) break;
+      if (good) good = mbar_wait(&bar_p, i & 1, p.status, 3);
       tc_fence_after_sync();
       FMB_TICK(19);   // waiting for dP
 #pragma unroll
@@ -656,7 +678,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
 
       // ---- dQ partial of row `lt`, this thread's half of the head dim: scaled, rounded to the I/O
       // dtype, stored at the entry's slot (16-byte chunks permuted like the forward partials)
-      if (!(good = mbar_wait(&bar_dq, i & 1, p.status, 4))) break;
+      if (good) good = mbar_wait(&bar_dq, i & 1, p.status, 4);
       tc_fence_after_sync();
       FMB_TICK(21);   // waiting for dQ
       {
@@ -668,41 +690,26 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
         FMB_TICK(29);
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_dqfree);    // dQ has been read out of dP's columns
+        // staged in the P tile (free: dV(i) completed before dQ(i)), 16-byte chunks permuted like the
+        // forward partials; one bulk copy per 32 rows, whose reads are waited for before P(i+1) is stored
         constexpr int NCH = DH / 8;               // 16-byte chunks of this thread's half row
-        uint4 ch[NCH];
+        const int key = (int)((it.slot + it.t0 + lt) & 7);
+        unsigned char* srow = sP + lt * (D * 2);
 #pragma unroll
         for (int jj = 0; jj < NCH; ++jj) {
 #pragma unroll
           for (int e = 0; e < 8; ++e) o[jj * 8 + e] *= p.scale;
-          ch[jj] = pack8<T>(o + jj * 8);
+          *reinterpret_cast<uint4*>(srow + (((hf * NCH + jj) ^ key) << 4)) = pack8<T>(o + jj * 8);
         }
-        // transpose inside groups of NCH lanes: afterwards lane j of a group holds chunk j of each of
-        // the group's NCH rows, so one store instruction writes whole half rows (full memory lines)
-#pragma unroll
-        for (int m = 1; m < NCH; m <<= 1) {
-          const bool up = (lane & m) != 0;
-#pragma unroll
-          for (int a = 0; a < NCH; ++a) {
-            if (a & m) continue;
-            uint4 snd = up ? ch[a] : ch[a | m];
-            uint4 rcv;
-            rcv.x = __shfl_xor_sync(0xffffffffu, snd.x, m);
-            rcv.y = __shfl_xor_sync(0xffffffffu, snd.y, m);
-            rcv.z = __shfl_xor_sync(0xffffffffu, snd.z, m);
-            rcv.w = __shfl_xor_sync(0xffffffffu, snd.w, m);
-            if (up) ch[a] = rcv; else ch[a | m] = rcv;
-          }
-        }
+        fence_async_smem();
         FMB_TICK(30);
-        const int gl = lane & (NCH - 1);          // this lane's chunk
-        const int row_g = lt - gl;                // first row of the lane group
-#pragma unroll
-        for (int k = 0; k < NCH; ++k) {
-          const int row = row_g + k;
-          if (row < rows) {
-            const int64_t slot = it.slot + it.t0 + row;
-            T* dst = part_dq + (plane + slot) * D;
-            *reinterpret_cast<uint4*>(dst + (((hf * NCH + gl) ^ (int)(slot & 7)) << 3)) = ch[k];
+        good = bar_and(2, kBwdCompute, good);     // both halves of every row staged
+        if (good && warp < 4 && lane == 0) {
+          const int wrows = min(32, rows - warp * 32);
+          if (wrows > 0) {
+            bulk_store(part_dq + (plane + it.slot + it.t0 + warp * 32) * D, sP + warp * 32 * (D * 2),
+                       (uint32_t)wrows * D * 2);
+            bulk_commit();
           }
         }
       }
@@ -716,6 +723,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
     }
 
     // ---- all GEMMs done -> dK and dV of key `lt`, this thread's half of the head dim
+    if (warp < 4 && lane == 0) bulk_wait_read();
     if (any_tile && good) good = mbar_wait(&bar_fin, 0, p.status, 4);
     good = bar_and(2, kBwdCompute, good);
     if (good) {

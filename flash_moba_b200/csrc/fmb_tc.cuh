@@ -149,6 +149,42 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64
       : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
+// The same instruction with the two descriptors given as 32-bit halves.  The low word holds the
+// start address (in 16-byte units) and the leading-dimension offset, the high word the stride
+// offset, version and swizzle mode: stepping through the K dimension only adds to the low word,
+// which keeps the issuing thread's instruction count per MMA small (it is a single thread whose
+// issue latency is on the kernel's critical path).
+__device__ __forceinline__ uint32_t desc_lo_sw128(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr & 0x3ffffu) >> 4) | (((lbo_bytes >> 4) & 0x3fffu) << 16);
+}
+__device__ __forceinline__ uint32_t desc_hi_sw128(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3fffu) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ void umma_ss_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                             uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, {%7, %7, %7, %7}, p;\n\t}"
+      :
+      : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// One GEMM of NK k-steps (16 elements each).  Operand offsets per k-step, in 16-byte units:
+// K-major tiles advance 2 inside a 64-element block and `blk` between blocks; MN-major tiles
+// advance 128 per step (blk = 512).
+template <int NK>
+__device__ __forceinline__ void umma_gemm(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t a_step,
+                                          uint32_t a_blk, uint32_t b_lo, uint32_t b_hi, uint32_t b_step,
+                                          uint32_t b_blk, uint32_t idesc, uint32_t accumulate) {
+#pragma unroll
+  for (int ks = 0; ks < NK; ++ks) {
+    umma_ss_lohi(d_tmem, a_lo + (ks >> 2) * a_blk + (ks & 3) * a_step, a_hi,
+                 b_lo + (ks >> 2) * b_blk + (ks & 3) * b_step, b_hi, idesc, accumulate | (ks > 0));
+  }
+}
 // the mbarrier receives one arrival when every MMA issued so far by this thread has completed
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
