@@ -352,8 +352,12 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
       tc_fence_after_sync();
       constexpr int kCols = kGateN / NQ;        // columns of a tile examined by this thread
       const uint32_t taddr = tmem_base + buf * 128 + qd * kCols + ((uint32_t)((warp & 3) * 32) << 16);
-      // 16 scores per step keeps the unrolled insertion code small enough for the instruction
-      // cache; the next 16 are fetched while these are examined
+      // 16 scores per step; the next 16 are fetched while these are examined.  A step first marks,
+      // without branching, the scores that reach the row's current k-th best (a superset of the
+      // scores that enter the list: the threshold is not updated inside the step).  Then every lane
+      // works through ITS OWN marked scores, so the (long) insertion code runs max-over-lanes of
+      // the marked counts times per step instead of once per position that any lane marked.
+      const bool tail = n0 + kGateN > nlim;     // this tile crosses the row's candidate limit
       float v[2][16];
       tmem_ld16(taddr, v[0]);
 #pragma unroll 1
@@ -363,21 +367,38 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
           tmem_ld_wait();
           if (i + half + 1 < kCols / 16) tmem_ld16(taddr + (i + half + 1) * 16, v[half ^ 1]);
           const int nb = n0 + qd * kCols + (i + half) * 16;
+          const float thr = ordered_to_score((uint32_t)(key[KMAX - 1] >> 32));
+          uint32_t m = 0;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int n = nb + j;
-            const float x = v[half][j];
-            const uint64_t cand = ((uint64_t)score_to_ordered(x) << 32) | (uint32_t)n;
-            if (n < nlim && x > -CUDART_INF_F && cand > key[KMAX - 1]) {
-              // insertion with independent compares and selects (no dependent swap chain):
-              // slot y takes its upper neighbour if the candidate outranks that one, else the
-              // candidate if it outranks the slot, else keeps its key
-              bool gt[KMAX];
+          for (int j = 0; j < 16; ++j) m |= (v[half][j] >= thr) ? (1u << j) : 0u;
+          if (tail) {
+            const int left = nlim - nb;           // candidates are n < nlim
+            m = left <= 0 ? 0u : (left >= 16 ? m : (m & ((1u << left) - 1u)));
+          }
+          while (__any_sync(0xffffffffu, m != 0u)) {
+            if (m != 0u) {
+              const int j = __ffs(m) - 1;
+              m &= m - 1u;
+              // v[half][j] for a run-time j: a 4-level select tree (the array must stay in registers)
+              float a8[8], a4[4];
 #pragma unroll
-              for (int y = 0; y < KMAX; ++y) gt[y] = cand > key[y];
+              for (int e = 0; e < 8; ++e) a8[e] = (j & 8) ? v[half][8 + e] : v[half][e];
 #pragma unroll
-              for (int y = KMAX - 1; y > 0; --y) key[y] = gt[y - 1] ? key[y - 1] : (gt[y] ? cand : key[y]);
-              key[0] = gt[0] ? cand : key[0];
+              for (int e = 0; e < 4; ++e) a4[e] = (j & 4) ? a8[4 + e] : a8[e];
+              const float a2a = (j & 2) ? a4[2] : a4[0], a2b = (j & 2) ? a4[3] : a4[1];
+              const float x = (j & 1) ? a2b : a2a;
+              const uint64_t cand = ((uint64_t)score_to_ordered(x) << 32) | (uint32_t)(nb + j);
+              if (x > -CUDART_INF_F && cand > key[KMAX - 1]) {
+                // insertion with independent compares and selects (no dependent swap chain):
+                // slot y takes its upper neighbour if the candidate outranks that one, else the
+                // candidate if it outranks the slot, else keeps its key
+                bool gt[KMAX];
+#pragma unroll
+                for (int y = 0; y < KMAX; ++y) gt[y] = cand > key[y];
+#pragma unroll
+                for (int y = KMAX - 1; y > 0; --y) key[y] = gt[y - 1] ? key[y - 1] : (gt[y] ? cand : key[y]);
+                key[0] = gt[0] ? cand : key[0];
+              }
             }
           }
         }
