@@ -252,14 +252,15 @@ __device__ __forceinline__ int64_t next_slot(const uint32_t* rp, int n, int64_t 
   return best;
 }
 
+// The combine kernels walk "virtual blocks" of 256 threads with a grid-stride loop, so that the
+// later stages of the cascade can be launched with a small grid: they usually find their flag
+// clear and must cost microseconds, not a scan of the whole block range.
 template <typename T>
-__global__ void __launch_bounds__(256) fwd_combine_kernel(const T* __restrict__ part_o,
-                                                          const float* __restrict__ part_lse, CombineParams c,
-                                                          T* out, int64_t o_rs, int64_t o_hs, float* lse,
-                                                          const int* only_if, int min_n) {
+__device__ __forceinline__ void fwd_combine_body(int64_t vblock, const T* __restrict__ part_o,
+                                                 const float* __restrict__ part_lse, const CombineParams& c,
+                                                 T* out, int64_t o_rs, int64_t o_hs, float* lse, int min_n) {
   using T2 = typename Elem<T>::T2;
-  if (only_if && *only_if == 0) return;   // the earlier stages met no row they had to leave
-  const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t wid = (vblock * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (wid >= c.total_q * c.nh) return;
   const int64_t t = wid / c.nh;
@@ -310,13 +311,21 @@ __global__ void __launch_bounds__(256) fwd_combine_kernel(const T* __restrict__ 
   }
   if (lane == 0) lse[(int64_t)h * c.total_q + t] = ssum > 0.f ? m + logf(ssum) : CUDART_INF_F;
 }
+template <typename T>
+__global__ void __launch_bounds__(256) fwd_combine_kernel(const T* __restrict__ part_o,
+                                                          const float* __restrict__ part_lse, CombineParams c,
+                                                          T* out, int64_t o_rs, int64_t o_hs, float* lse,
+                                                          const int* only_if, int min_n, int64_t nvb) {
+  if (only_if && *only_if == 0) return;   // the earlier stages met no row they had to leave
+  for (int64_t vb = blockIdx.x; vb < nvb; vb += gridDim.x)
+    fwd_combine_body<T>(vb, part_o, part_lse, c, out, o_rs, o_hs, lse, min_n);
+}
 
 template <typename T>
-__global__ void __launch_bounds__(256) bwd_combine_kernel(const T* __restrict__ part_dq, CombineParams c, T* dq,
-                                                          int64_t rs, int64_t hs, const int* only_if, int min_n) {
+__device__ __forceinline__ void bwd_combine_body(int64_t vblock, const T* __restrict__ part_dq, const CombineParams& c,
+                                                 T* dq, int64_t rs, int64_t hs, int min_n) {
   using T2 = typename Elem<T>::T2;
-  if (only_if && *only_if == 0) return;
-  const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t wid = (vblock * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (wid >= c.total_q * c.nh) return;
   const int64_t t = wid / c.nh;
@@ -353,6 +362,13 @@ __global__ void __launch_bounds__(256) bwd_combine_kernel(const T* __restrict__ 
     if (col < c.d) *reinterpret_cast<T2*>(dst + col) = Elem<T>::from_f2(acc[i].x, acc[i].y);
   }
 }
+template <typename T>
+__global__ void __launch_bounds__(256) bwd_combine_kernel(const T* __restrict__ part_dq, CombineParams c, T* dq,
+                                                          int64_t rs, int64_t hs, const int* only_if, int min_n,
+                                                          int64_t nvb) {
+  if (only_if && *only_if == 0) return;
+  for (int64_t vb = blockIdx.x; vb < nvb; vb += gridDim.x) bwd_combine_body<T>(vb, part_dq, c, dq, rs, hs, min_n);
+}
 
 // ------------------------------------------------------------------ fast combine (rows of <= G partials)
 // G lanes per (token, head) row, 32/G rows per warp.  Lane j of a group first fetches the plane
@@ -372,10 +388,10 @@ struct GroupRow {
   int64_t t; int hr; int64_t rid; int n; bool mine; bool valid; uint32_t pos; uint32_t slot;
 };
 template <int G>
-__device__ __forceinline__ GroupRow group_row(const CombineParams& c, int min_n, int* overflow) {
+__device__ __forceinline__ GroupRow group_row(int64_t vblock, const CombineParams& c, int min_n, int* overflow) {
   GroupRow g;
   const int lane = threadIdx.x & 31, gl = lane & (G - 1);
-  const int64_t gid = (((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * (32 / G) + (lane / G);
+  const int64_t gid = ((vblock * blockDim.x + threadIdx.x) >> 5) * (32 / G) + (lane / G);
   const bool row_ok = gid < c.total_q * c.nh;
   g.t = row_ok ? gid / c.nh : 0;
   g.hr = row_ok ? (int)(gid - g.t * c.nh) : 0;
@@ -400,18 +416,16 @@ __device__ __forceinline__ GroupRow group_row(const CombineParams& c, int min_n,
 }
 
 template <typename T, int G, int EPL>
-__global__ void __launch_bounds__(256) fwd_combine_group_kernel(const T* __restrict__ part_o,
-                                                                const float* __restrict__ part_lse,
-                                                                CombineParams c, T* out, int64_t o_rs, int64_t o_hs,
-                                                                float* lse, int min_n, const int* only_if,
-                                                                int* overflow) {
+__device__ __forceinline__ void fwd_combine_group_body(int64_t vblock, const T* __restrict__ part_o,
+                                                       const float* __restrict__ part_lse, const CombineParams& c,
+                                                       T* out, int64_t o_rs, int64_t o_hs, float* lse, int min_n,
+                                                       int* overflow) {
   constexpr int d = G * EPL;
   constexpr int NV = EPL / 8;                 // 16-byte loads per partial row per lane
   static_assert(EPL % 8 == 0, "a lane owns whole 16-byte chunks");
-  if (only_if && *only_if == 0) return;
   const int lane = threadIdx.x & 31, gl = lane & (G - 1);
   const unsigned gm = group_mask<G>(lane);
-  const GroupRow g = group_row<G>(c, min_n, overflow);
+  const GroupRow g = group_row<G>(vblock, c, min_n, overflow);
   const float l = g.valid ? part_lse[g.pos] : -CUDART_INF_F;
   float m = l;
 #pragma unroll
@@ -471,18 +485,27 @@ __global__ void __launch_bounds__(256) fwd_combine_group_kernel(const T* __restr
     if (gl == 0) lse[(int64_t)h * c.total_q + g.t] = ssum > 0.f ? m + logf(ssum) : CUDART_INF_F;
   }
 }
+template <typename T, int G, int EPL>
+__global__ void __launch_bounds__(256, 2) fwd_combine_group_kernel(const T* __restrict__ part_o,
+                                                                const float* __restrict__ part_lse,
+                                                                CombineParams c, T* out, int64_t o_rs, int64_t o_hs,
+                                                                float* lse, int min_n, const int* only_if,
+                                                                int* overflow, int64_t nvb) {
+  if (only_if && *only_if == 0) return;
+  for (int64_t vb = blockIdx.x; vb < nvb; vb += gridDim.x)
+    fwd_combine_group_body<T, G, EPL>(vb, part_o, part_lse, c, out, o_rs, o_hs, lse, min_n, overflow);
+}
 
 template <typename T, int G, int EPL>
-__global__ void __launch_bounds__(256) bwd_combine_group_kernel(const T* __restrict__ part_dq, CombineParams c,
-                                                                T* dq, int64_t rs, int64_t hs, int min_n,
-                                                                const int* only_if, int* overflow) {
+__device__ __forceinline__ void bwd_combine_group_body(int64_t vblock, const T* __restrict__ part_dq,
+                                                       const CombineParams& c, T* dq, int64_t rs, int64_t hs,
+                                                       int min_n, int* overflow) {
   constexpr int d = G * EPL;
   constexpr int NV = EPL / 8;                 // 16-byte loads per partial row per lane
   static_assert(EPL % 8 == 0, "a lane owns whole 16-byte chunks");
-  if (only_if && *only_if == 0) return;
   const int lane = threadIdx.x & 31, gl = lane & (G - 1);
   const unsigned gm = group_mask<G>(lane);
-  const GroupRow g = group_row<G>(c, min_n, overflow);
+  const GroupRow g = group_row<G>(vblock, c, min_n, overflow);
   int rank = 0;
 #pragma unroll
   for (int i = 0; i < G; ++i) rank += (__shfl_sync(gm, g.pos, i, G) < g.pos) ? 1 : 0;
@@ -525,6 +548,14 @@ __global__ void __launch_bounds__(256) bwd_combine_group_kernel(const T* __restr
     for (int v = 0; v < NV; ++v) *reinterpret_cast<uint4*>(dst + 8 * v) = pack8<T>(acc + 8 * v);
   }
 }
+template <typename T, int G, int EPL>
+__global__ void __launch_bounds__(256) bwd_combine_group_kernel(const T* __restrict__ part_dq, CombineParams c,
+                                                                T* dq, int64_t rs, int64_t hs, int min_n,
+                                                                const int* only_if, int* overflow, int64_t nvb) {
+  if (only_if && *only_if == 0) return;
+  for (int64_t vb = blockIdx.x; vb < nvb; vb += gridDim.x)
+    bwd_combine_group_body<T, G, EPL>(vb, part_dq, c, dq, rs, hs, min_n, overflow);
+}
 
 template <typename T>
 __global__ void __launch_bounds__(256) dot_do_o_kernel(const T* __restrict__ dout, int64_t do_rs, int64_t do_hs,
@@ -550,11 +581,13 @@ __global__ void __launch_bounds__(256) dot_do_o_kernel(const T* __restrict__ dou
   if (lane == 0) softmax_d[(int64_t)h * total_q + t] = s;
 }
 
-static unsigned warp_grid(int64_t warps) { return (unsigned)ceil_div64(warps, 8); }
+static int64_t warp_grid(int64_t warps) { return ceil_div64(warps, 8); }
 
 // Cascade: G = 8 (rows of <= 8 partials), 16, then the generic kernel; each later stage runs only
 // the rows the earlier ones left and exits at once if there were none.
-static unsigned group_grid(int64_t rows, int G) { return (unsigned)ceil_div64(ceil_div64(rows, 32 / G), 8); }
+static int64_t group_grid(int64_t rows, int G) { return ceil_div64(ceil_div64(rows, 32 / G), 8); }
+// grid of a later cascade stage: enough CTAs to fill the GPU if it does have work
+static unsigned late_grid(int64_t nvb) { return (unsigned)(nvb < 148 * 8 ? (nvb > 0 ? nvb : 1) : 148 * 8); }
 
 static CombineParams make_combine(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps) {
   CombineParams c;
@@ -570,13 +603,14 @@ static int fwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const
   int* ovf = w.status + 1;   // words 1..3 of the status block, zeroed with it
   const T* po = (const T*)w.part_o;
   T* out = (T*)a.o;
-  fwd_combine_group_kernel<T, 8, D / 8><<<group_grid(rows, 8), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs,
-                                                                            a.lse, 0, nullptr, ovf);
+  const int64_t nb8 = group_grid(rows, 8), nb16 = group_grid(rows, 16), nbw = warp_grid(rows);
+  fwd_combine_group_kernel<T, 8, D / 8><<<(unsigned)nb8, 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, 0,
+                                                                      nullptr, ovf, nb8);
   FMB_LAUNCH_CHECK("fwd_combine_group_kernel<8>");
-  fwd_combine_group_kernel<T, 16, D / 16><<<group_grid(rows, 16), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs,
-                                                                              a.o_hs, a.lse, 9, ovf, ovf + 1);
+  fwd_combine_group_kernel<T, 16, D / 16><<<late_grid(nb16), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs,
+                                                                         a.lse, 9, ovf, ovf + 1, nb16);
   FMB_LAUNCH_CHECK("fwd_combine_group_kernel<16>");
-  fwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, ovf + 1, 17);
+  fwd_combine_kernel<T><<<late_grid(nbw), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, ovf + 1, 17, nbw);
   FMB_LAUNCH_CHECK("fwd_combine_kernel");
   return FMB_OK;
 }
@@ -587,7 +621,7 @@ static int fwd_combine_any(const AttnArgs& a, const AttnWorkspace& w, const Pass
   if (a.d == 256) return fwd_combine_dispatch<T, 256>(a, w, ps, s);
   const int64_t rows = a.total_q * ps.nh;
   fwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>((const T*)w.part_o, w.part_lse, make_combine(a, w, ps),
-                                                        (T*)a.o, a.o_rs, a.o_hs, a.lse, nullptr, 0);
+                                                        (T*)a.o, a.o_rs, a.o_hs, a.lse, nullptr, 0, warp_grid(rows));
   FMB_LAUNCH_CHECK("fwd_combine_kernel");
   return FMB_OK;
 }
@@ -604,13 +638,13 @@ static int bwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const
   int* ovf = w.status + 1;
   const T* pd = (const T*)w.part_o;
   T* dq = (T*)a.dq;
-  bwd_combine_group_kernel<T, 8, D / 8><<<group_grid(rows, 8), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 0, nullptr,
-                                                                            ovf);
+  const int64_t nb8 = group_grid(rows, 8), nb16 = group_grid(rows, 16), nbw = warp_grid(rows);
+  bwd_combine_group_kernel<T, 8, D / 8><<<(unsigned)nb8, 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 0, nullptr, ovf, nb8);
   FMB_LAUNCH_CHECK("bwd_combine_group_kernel<8>");
-  bwd_combine_group_kernel<T, 16, D / 16><<<group_grid(rows, 16), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 9, ovf,
-                                                                              ovf + 1);
+  bwd_combine_group_kernel<T, 16, D / 16><<<late_grid(nb16), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 9, ovf, ovf + 1,
+                                                                         nb16);
   FMB_LAUNCH_CHECK("bwd_combine_group_kernel<16>");
-  bwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, ovf + 1, 17);
+  bwd_combine_kernel<T><<<late_grid(nbw), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, ovf + 1, 17, nbw);
   FMB_LAUNCH_CHECK("bwd_combine_kernel");
   return FMB_OK;
 }
@@ -621,7 +655,7 @@ static int bwd_combine_any(const AttnArgs& a, const AttnWorkspace& w, const Pass
   if (a.d == 256) return bwd_combine_dispatch<T, 256>(a, w, ps, s);
   const int64_t rows = a.total_q * ps.nh;
   bwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>((const T*)w.part_o, make_combine(a, w, ps), (T*)a.dq,
-                                                        a.dq_rs, a.dq_hs, nullptr, 0);
+                                                        a.dq_rs, a.dq_hs, nullptr, 0, warp_grid(rows));
   FMB_LAUNCH_CHECK("bwd_combine_kernel");
   return FMB_OK;
 }
