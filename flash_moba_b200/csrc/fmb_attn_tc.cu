@@ -58,29 +58,36 @@ struct TcParams {
   void* part_o; float* part_lse; int* status;
   int heads, heads_k; int64_t total_q;
   float scale; int causal;
+  // persistent CTAs: work items (key block, head or kv head, sequence) are handed out through a
+  // counter in the workspace status block, key blocks in ascending order (under a causal mask the
+  // early key blocks have the longest columns, so the long items start first)
+  int* work; int n_items, items_y, items_z;
 };
 
 __host__ __device__ constexpr int next_pow2_cols(int x) { return x <= 32 ? 32 : x <= 64 ? 64 : x <= 128 ? 128 : x <= 256 ? 256 : 512; }
 
 // ======================================================================== forward
-// CTA = key chunk c of one (sequence, head); K and V are staged once and shared by two compute
-// warpgroups that take alternate 128-row tiles of the chunk's CSC column; a third group of four
-// warps gathers the query rows one tile ahead with 16-byte cp.async copies (straight into the
-// swizzled UMMA tile, no registers).  384 threads, one CTA per SM:
-//   warps 0-3 / 4-7  compute group 0 / 1: own Q tile, own P/O-staging tile, own 256 TMEM
-//                    columns (S | O), own mbarriers; thread 0 of the group issues its MMAs.
-//                    Per tile:  S = Q.K^T  ->  chunk-local softmax, one thread per row (two
-//                    passes over TMEM: row maximum, then exponentials)  ->  P (bf16) to shared
-//                    memory  ->  O = P.V (V consumed MN-major)  ->  O / l staged and written
-//                    with one bulk copy per warp, log-sum-exp beside it.
-//   warps 8-11       loaders: row ids of the next tile, then its Q rows as soon as the group's
-//                    previous S GEMM has released the Q tile.
-// While one group is in its softmax the other group's MMAs and the loaders' copies proceed.
+// CTA = key block c of one (sequence, head); 672 threads, warp-specialised, one CTA per SM:
+//   warps 0-7 / 8-15  compute group 0 / 1 (two threads per row, each owns half of the columns).
+//                     The groups take alternate 128-row tiles of the block's CSC column; each has
+//                     its own Q tile, P/O-staging tile, 256 TMEM columns (S | O) and mbarriers.
+//                     Per tile: wait S -> chunk-local softmax (row maximum, then exponentials) ->
+//                     P (bf16) to shared memory -> P_ready;  wait O -> O / l staged and written
+//                     with one bulk copy per warp, log-sum-exp beside it.
+//   warp 16           one thread issues every MMA of both groups.  It polls the groups' barriers in
+//                     turn (P_ready -> O = P.V; Q tile landed -> next S = Q.K^T), so that a late
+//                     gather never stalls a compute warp.
+//   warps 17-18 / 19-20  loaders of group 0 / 1: row ids of the next tile, then its Q rows with
+//                     16-byte cp.async copies straight into the swizzled UMMA tile, as soon as
+//                     the group's previous S GEMM has released the Q tile.
+// K and V are staged once per work item and shared.  While one group is in its softmax the other
+// group's MMAs and the loaders' copies proceed.  CTAs are persistent (one per SM): TMEM is
+// allocated once, and a CTA keeps taking work items until the counter runs out.
 constexpr int kFwdGroups = 2;
-constexpr int kFwdGroupThreads = 256;          // two threads per row: each owns half of the columns
-constexpr int kFwdLoaders = 128;
-constexpr int kFwdLoaderSet = kFwdLoaders / kFwdGroups;   // loader threads per compute group
-constexpr int kFwdThreads = kFwdGroups * kFwdGroupThreads + kFwdLoaders;
+constexpr int kFwdGroupThreads = 256;
+constexpr int kFwdLoaderSet = 64;               // loader threads per compute group
+constexpr int kFwdIssuerWarp = kFwdGroups * kFwdGroupThreads / 32;
+constexpr int kFwdThreads = kFwdGroups * kFwdGroupThreads + 32 + kFwdGroups * kFwdLoaderSet;
 
 template <typename T, int C, int D>
 __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
@@ -91,7 +98,9 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
   constexpr int CH = C / 2, DH = D / 2;        // columns per thread in the softmax / epilogue
   extern __shared__ unsigned char smem_raw[];
   __shared__ uint64_t bar_s[kFwdGroups], bar_o[kFwdGroups], bar_full[kFwdGroups], bar_qfree[kFwdGroups];
+  __shared__ uint64_t bar_pready[kFwdGroups], bar_kv;
   __shared__ uint32_t tmem_base_s;
+  __shared__ int s_item;
   __shared__ int sRow[kFwdGroups][2][kTcM];
   __shared__ float sMax[kFwdGroups][2][kTcM], sSum[kFwdGroups][2][kTcM];
 
@@ -101,11 +110,51 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
   unsigned char* sQg = sV + C * D * 2;                         // [group][128][D]
   unsigned char* sPOg = sQg + kFwdGroups * kTcM * D * 2;       // [group][128][max(C,D)]
 
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const float scale_log2 = p.scale * kLog2eTc;
+  FMB_T0();
+  if (warp == 0) tmem_alloc(&tmem_base_s, NCOLS);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+
+  bool first_item = true;
+#pragma unroll 1
+  for (;;) {
+  // ---- next work item; the barriers start every item in phase 0
+  if (tid == 0) {
+    s_item = atomicAdd(p.work, 1);
+    if (!first_item) {
+      for (int i = 0; i < kFwdGroups; ++i) {
+        mbar_inval(&bar_s[i]); mbar_inval(&bar_o[i]); mbar_inval(&bar_full[i]); mbar_inval(&bar_qfree[i]);
+        mbar_inval(&bar_pready[i]);
+      }
+      mbar_inval(&bar_kv);
+    }
+    for (int i = 0; i < kFwdGroups; ++i) {
+      mbar_init(&bar_s[i], 1);
+      mbar_init(&bar_o[i], 1);
+      mbar_init(&bar_full[i], kFwdLoaderSet / 32);       // one arrival per loader warp
+      mbar_init(&bar_qfree[i], 1);
+      mbar_init(&bar_pready[i], kFwdGroupThreads / 32);  // one arrival per compute warp
+    }
+    mbar_init(&bar_kv, kFwdGroups * kFwdGroupThreads / 32);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  first_item = false;
+  const int item = s_item;
+  if (item >= p.n_items) break;
   // C is the key block: chunk c of the pattern is covered by nsub blocks of C keys
-  const int c = blockIdx.x / p.ps.nsub, sb = blockIdx.x % p.ps.nsub, h = p.ps.h0 + blockIdx.y, b = blockIdx.z;
+  const int bx = item / (p.items_y * p.items_z), rem = item - bx * (p.items_y * p.items_z);
+  const int c = bx / p.ps.nsub, sb = bx % p.ps.nsub, h = p.ps.h0 + rem % p.items_y, b = rem / p.items_y;
   const ColRef col = column_of(p.ps, b, h, c);
   const int nnz = col.nnz;
-  if (nnz <= 0) return;
+  if (nnz <= 0) {          // CTA-uniform
+    __syncthreads();
+    continue;
+  }
   const int64_t off = col.off;                                   // first entry in `indices`
   const int64_t slot0 = col.slot;                                // first slot of the column in the pass
   const int64_t plane = (int64_t)sb * p.ps.cap;                  // this key block's plane of slots
@@ -115,55 +164,69 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
   const int keys_valid = max(0, min(C, len_k - key0));
   const int hk = h / (p.heads / p.heads_k);
   const int shift = len_k - len_q;
-  const float scale_log2 = p.scale * kLog2eTc;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool loader = tid >= kFwdGroups * kFwdGroupThreads;
-  const int g = loader ? 0 : tid / kFwdGroupThreads;   // compute group
-  const int gt = tid % kFwdGroupThreads;               // thread inside the group
-  const int lt = tid & (kTcM - 1);                     // row (TMEM lane); for loaders: index in the role
-  const int hf = (gt >> 7) & 1;                        // column half of a compute thread
   const int ntiles = (nnz + kTcM - 1) / kTcM;
+  FMB_TICK(1);   // item hand-out, column lookup
 
-  FMB_T0();
-  if (warp == 0) tmem_alloc(&tmem_base_s, NCOLS);
-  if (tid == 0) {
-    for (int i = 0; i < kFwdGroups; ++i) {
-      mbar_init(&bar_s[i], 1);
-      mbar_init(&bar_o[i], 1);
-      mbar_init(&bar_full[i], kFwdLoaderSet);
-      mbar_init(&bar_qfree[i], 1);
+  if (warp == kFwdIssuerWarp) {
+    // =============================================================== MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc(FmtOf<T>::v, kTcM, C, 0, 0);
+      constexpr uint32_t idesc_o = make_idesc(FmtOf<T>::v, kTcM, D, 0, 1);
+      const uint32_t hi = desc_hi_sw128(1024);
+      const uint32_t k_km = desc_lo_sw128(smem_u32(sK), 16), v_mn = desc_lo_sw128(smem_u32(sV), kKBlock);
+      constexpr uint32_t kQB = kQBlock >> 4, kKB = kKBlock >> 4;
+      int ts[kFwdGroups], tp[kFwdGroups];     // next tile whose S / P.V GEMM is to be issued
+#pragma unroll
+      for (int g = 0; g < kFwdGroups; ++g) { ts[g] = g; tp[g] = g; }
+      bool ok = mbar_wait(&bar_kv, 0, p.status, 6);
+      uint32_t idle = 0;
+      while (ok && (tp[0] < ntiles || tp[1] < ntiles)) {
+        bool progress = false;
+#pragma unroll
+        for (int g = 0; g < kFwdGroups; ++g) {
+          const uint32_t tS = tmem_base + g * 256, tO = tS + 128;
+          const uint32_t q_km = desc_lo_sw128(smem_u32(sQg + g * (kTcM * D * 2)), 16);
+          const uint32_t p_km = desc_lo_sw128(smem_u32(sPOg + g * (kTcM * QP * 2)), 16);
+          // O = P.V of tile tp: P is in shared memory and S has been read
+          if (tp[g] < ntiles && tp[g] < ts[g] && mbar_test(&bar_pready[g], ((tp[g] - g) / kFwdGroups) & 1)) {
+            tc_fence_after_sync();
+            umma_gemm<C / 16>(tO, p_km, hi, 2, kQB, v_mn, hi, 128, 512, idesc_o, 0);
+            umma_commit(&bar_o[g]);
+            tp[g] += kFwdGroups;
+            progress = true;
+          }
+          // S = Q.K^T of tile ts: its Q rows have landed, and S of the group's previous tile has been read
+          if (ts[g] < ntiles && ts[g] < tp[g] + kFwdGroups &&
+              mbar_test(&bar_full[g], ((ts[g] - g) / kFwdGroups) & 1)) {
+            tc_fence_after_sync();
+            umma_gemm<D / 16>(tS, q_km, hi, 2, kQB, k_km, hi, 2, kKB, idesc_s, 0);
+            umma_commit(&bar_qfree[g]);   // the loaders may refill the Q tile
+            umma_commit(&bar_s[g]);
+            ts[g] += kFwdGroups;
+            progress = true;
+          }
+        }
+        if (progress) idle = 0;
+        else if (++idle > (kSpinLimit << 4)) {   // bounded like every other wait
+          atomicCAS(p.status, 0, 6);
+          ok = false;
+        }
+      }
     }
-    mbar_fence_init();
-  }
-  if (!loader && hf == 0) {   // 2 x 128 threads stage K and V
-    const T* kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + key0) * p.k_rs + (int64_t)hk * p.k_hs;
-    const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
-    if (g == 0) stage_dense_sw128_t<T, D / 8, C>(lt, sK, kKBlock, kbase, p.k_rs, keys_valid);
-    else stage_dense_sw128_t<T, D / 8, C>(lt, sV, kKBlock, vbase, p.v_rs, keys_valid);
-    fence_async_smem();
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  FMB_TICK(0);   // prologue: TMEM alloc + K/V staging
-  const uint32_t tmem_base = tmem_base_s;
-
-  if (loader) {
+  } else if (warp > kFwdIssuerWarp) {
     // =============================================================== loader warps
     // two independent sets of 64 threads, one per compute group
     const T* qbase = static_cast<const T*>(p.q) + (int64_t)q0 * p.q_rs + (int64_t)h * p.q_hs;
-    const int gi = (tid - kFwdGroups * kFwdGroupThreads) / kFwdLoaderSet;   // the group this set serves
-    const int st = tid % kFwdLoaderSet;
+    const int lt0 = tid - (kFwdIssuerWarp + 1) * 32;
+    const int gi = lt0 / kFwdLoaderSet;        // the group this set serves
+    const int st = lt0 % kFwdLoaderSet;
     uint32_t ph_free = 0;
-    auto row_of = [&](int tile, int e) {
-      int r = -1;
-      if (tile < ntiles && tile * kTcM + e < nnz) {
-        r = p.ps.indices[off + tile * kTcM + e];
-        if (r < 0 || r >= len_q) r = -1;
-      }
-      return r;
+    // row id of entry e of a tile (-1 = none): the load only; the range check happens at the use
+    auto row_raw = [&](int tile, int e) {
+      return (tile < ntiles && tile * kTcM + e < nnz) ? p.ps.indices[off + tile * kTcM + e] : -1;
     };
-    int r_a = row_of(gi, st), r_b = row_of(gi, st + kFwdLoaderSet);   // the set's first tile
+    int r_a = row_raw(gi, st), r_b = row_raw(gi, st + kFwdLoaderSet);   // the set's first tile
+#pragma unroll 1
     for (int i = gi, n = 0; i < ntiles; i += kFwdGroups, ++n) {
       int* rows = sRow[gi][n & 1];
       bool ok = true;
@@ -172,118 +235,105 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
         ok = mbar_wait(&bar_qfree[gi], ph_free, p.status, 5);
         ph_free ^= 1;
       }
-      rows[st] = r_a;
-      rows[st + kFwdLoaderSet] = r_b;
-      r_a = row_of(i + kFwdGroups, st);                   // next tile's row ids, in flight meanwhile
-      r_b = row_of(i + kFwdGroups, st + kFwdLoaderSet);
+      rows[st] = (r_a < 0 || r_a >= len_q) ? -1 : r_a;
+      rows[st + kFwdLoaderSet] = (r_b < 0 || r_b >= len_q) ? -1 : r_b;
+      r_a = row_raw(i + kFwdGroups, st);                  // next tile's row ids, in flight meanwhile
+      r_b = row_raw(i + kFwdGroups, st + kFwdLoaderSet);
       ok = bar_and(4 + gi, kFwdLoaderSet, ok);   // also publishes the row ids inside the set
       if (!ok) break;
       gather_cp_async<T, D / 8, kFwdLoaderSet>(st, sQg + gi * (kTcM * D * 2), kQBlock, qbase, p.q_rs, rows);
       cp_async_wait_all();
       fence_async_smem();   // the copies are generic-proxy writes; the MMAs read through the async proxy
-      mbar_arrive(&bar_full[gi]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_full[gi]);
     }
   } else {
     // =============================================================== compute groups
-    unsigned char* sQ = sQg + g * (kTcM * D * 2);
+    const int g = tid / kFwdGroupThreads;      // compute group
+    const int gt = tid % kFwdGroupThreads;     // thread inside the group
+    const int lt = tid & (kTcM - 1);           // row (TMEM lane)
+    const int hf = (gt >> 7) & 1;              // column half
+    const int gw = gt >> 5;                    // warp inside the group (0..7)
+    {   // group 0 stages K, group 1 stages V (the loaders fetch the first Q tiles meanwhile)
+      const T* kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + key0) * p.k_rs + (int64_t)hk * p.k_hs;
+      const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
+      if (g == 0) dense_cp_async<T, D / 8, C, kFwdGroupThreads>(gt, sK, kKBlock, kbase, p.k_rs, keys_valid);
+      else dense_cp_async<T, D / 8, C, kFwdGroupThreads>(gt, sV, kKBlock, vbase, p.v_rs, keys_valid);
+      cp_async_wait_all();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_kv);
+    }
+    FMB_TICK(0);   // prologue
     unsigned char* sPO = sPOg + g * (kTcM * QP * 2);
     const uint32_t tS = tmem_base + g * 256, tO = tS + 128;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t sK_a = smem_u32(sK), sV_a = smem_u32(sV), sQ_a = smem_u32(sQ), sPO_a = smem_u32(sPO);
-    constexpr uint32_t idesc_s = make_idesc(FmtOf<T>::v, kTcM, C, 0, 0);
-    constexpr uint32_t idesc_o = make_idesc(FmtOf<T>::v, kTcM, D, 0, 1);
     T* part_o = static_cast<T*>(p.part_o);
     const int bar_id = 2 + g;
-    const int gw = gt >> 5;                    // warp inside the group (0..7)
-    // S and O completions use separate mbarriers: the next S GEMM is issued behind this tile's
-    // P.V GEMM, and a single barrier must never run two phases ahead of its waiters
-    uint32_t phase_s = 0, phase_o = 0, phase_full = 0;
     bool good = true;
 
-    // S = Q.K^T of a tile: waits for its Q rows, then issues (thread 0 of the group)
-    auto issue_s = [&]() {
-      if (mbar_wait(&bar_full[g], phase_full, p.status, 6)) {   // the tile's Q rows have landed
-        tc_fence_after_sync();
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint64_t a = make_desc_sw128(sQ_a + (ks >> 2) * kQBlock + (ks & 3) * 32, 16, 1024);
-          const uint64_t bd = make_desc_sw128(sK_a + (ks >> 2) * kKBlock + (ks & 3) * 32, 16, 1024);
-          umma_ss(tS, a, bd, idesc_s, ks > 0);
-        }
-        umma_commit(&bar_qfree[g]);   // the loaders may refill the Q tile
-        umma_commit(&bar_s[g]);
-      }
-      phase_full ^= 1;
-    };
-    if (gt == 0 && g < ntiles) issue_s();   // first tile; later ones are issued one tile ahead
-
-    for (int i = g, n = 0; i < ntiles && good; i += kFwdGroups, ++n) {
+#pragma unroll 1
+    for (int i = g, n = 0; i < ntiles; i += kFwdGroups, ++n) {
       const int t0 = i * kTcM;
       const int rows = min(kTcM, nnz - t0);
       if (gw < 4 && lane == 0) bulk_wait_read();   // the previous tile's O staging has been read out
-      good = bar_and(bar_id, kFwdGroupThreads, mbar_wait(&bar_s[g], phase_s, p.status, 1));
-      phase_s ^= 1;
+      if (good) good = mbar_wait(&bar_s[g], n & 1, p.status, 1);   // on failure: run on to the barrier
       tc_fence_after_sync();
-      if (!good) break;
-      if (tid == 0) FMB_TICK(2);   // operands + S = Q.K^T
+      if (tid == 0) FMB_TICK(2);   // waiting for S
 
       // ---- chunk-local softmax of row `lt`, this thread's half of the keys
       const int r = sRow[g][n & 1][lt];
       const int lim = r < 0 ? 0 : (p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid);
-      float s[CH];
-#pragma unroll
-      for (int q4 = 0; q4 < CH / 32; ++q4) tmem_ld32(tS + lane_sel + hf * CH + q4 * 32, s + q4 * 32);
-      tmem_ld_wait();
+      // two passes over the row's scores in TMEM (maximum, then exponentials), 32 at a time: keeps
+      // the thread at 32 live scores, which is what the register budget of 21 warps allows
       float mx = -CUDART_INF_F;
-      if (lim >= C) {   // nothing masked: the common case away from the causal diagonal
 #pragma unroll
-        for (int jj = 0; jj < CH; ++jj) mx = fmaxf(mx, s[jj]);
-      } else {
+      for (int q4 = 0; q4 < CH / 32; ++q4) {
+        float s[32];
+        tmem_ld32(tS + lane_sel + hf * CH + q4 * 32, s);
+        tmem_ld_wait();
+        if (lim >= C) {   // nothing masked: the common case away from the causal diagonal
 #pragma unroll
-        for (int jj = 0; jj < CH; ++jj) {
-          s[jj] = hf * CH + jj < lim ? s[jj] : -CUDART_INF_F;
-          mx = fmaxf(mx, s[jj]);
+          for (int jj = 0; jj < 32; ++jj) mx = fmaxf(mx, s[jj]);
+        } else {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) mx = fmaxf(mx, hf * CH + q4 * 32 + jj < lim ? s[jj] : -CUDART_INF_F);
         }
       }
       sMax[g][hf][lt] = mx;
-      tc_fence_before_sync();
-      bar_sync(bar_id, kFwdGroupThreads);
+      good = bar_and(bar_id, kFwdGroupThreads, good);   // also: the previous bulk reads are done
+      if (!good) break;
       mx = fmaxf(mx, sMax[g][hf ^ 1][lt]);
       const float mref = lim > 0 ? mx * scale_log2 : 0.f;
       float sum = 0.f;
 #pragma unroll
-      for (int jj = 0; jj < CH; ++jj) {
-        s[jj] = exp2f(s[jj] * scale_log2 - mref);   // exp2(-inf) = 0 for masked keys
-        sum += s[jj];
-      }
+      for (int q4 = 0; q4 < CH / 32; ++q4) {
+        float s[32];
+        tmem_ld32(tS + lane_sel + hf * CH + q4 * 32, s);
+        tmem_ld_wait();
 #pragma unroll
-      for (int jj = 0; jj < CH / 8; ++jj)
-        *reinterpret_cast<uint4*>(sPO + sw128_offset(lt, hf * (CH / 8) + jj, kQBlock)) = pack8<T>(s + jj * 8);
+        for (int jj = 0; jj < 32; ++jj) {
+          const float e = exp2f(s[jj] * scale_log2 - mref);
+          s[jj] = (lim >= C || hf * CH + q4 * 32 + jj < lim) ? e : 0.f;
+          sum += s[jj];
+        }
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+          *reinterpret_cast<uint4*>(sPO + sw128_offset(lt, hf * (CH / 8) + q4 * 4 + jj, kQBlock)) = pack8<T>(s + jj * 8);
+      }
+      tc_fence_before_sync();
       sSum[g][hf][lt] = sum;
       fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_pready[g]);   // S has been read, P is in shared memory
       if (tid == 0) FMB_TICK(3);   // softmax
-      bar_sync(bar_id, kFwdGroupThreads);
-      if (gt == 0) {
-        tc_fence_after_sync();
-#pragma unroll
-        for (int ks = 0; ks < C / 16; ++ks) {
-          const uint64_t a = make_desc_sw128(sPO_a + (ks >> 2) * kQBlock + (ks & 3) * 32, 16, 1024);
-          const uint64_t bd = make_desc_sw128(sV_a + ks * 2048, kKBlock, 1024);
-          umma_ss(tO, a, bd, idesc_o, ks > 0);
-        }
-        umma_commit(&bar_o[g]);
-        // the group's next S GEMM goes out right behind: S has been consumed, and the result
-        // is ready by the time this tile's epilogue is done
-        if (i + kFwdGroups < ntiles) issue_s();
-      }
+      bar_sync(bar_id, kFwdGroupThreads);           // the other half's sum
       sum += sSum[g][hf ^ 1][lt];
       const float inv = sum > 0.f ? 1.f / sum : 0.f;
       if (hf == 0 && lt < rows) p.part_lse[plane + slot0 + t0 + lt] = sum > 0.f ? mx * p.scale + logf(sum) : -CUDART_INF_F;
-      good = bar_and(bar_id, kFwdGroupThreads, mbar_wait(&bar_o[g], phase_o, p.status, 2));
-      phase_o ^= 1;
+      if (good) good = mbar_wait(&bar_o[g], n & 1, p.status, 2);
       tc_fence_after_sync();
-      if (!good) break;
-      if (tid == 0) FMB_TICK(5);   // O = P.V
+      if (tid == 0) FMB_TICK(5);   // waiting for O = P.V
 
       // ---- epilogue: normalised partial O of row `lt`, this thread's half of the head dim,
       // staged in the P tile (its MMAs have completed); one bulk copy per 32 rows
@@ -302,18 +352,24 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
         tc_fence_before_sync();
         fence_async_smem();
       }
-      bar_sync(bar_id, kFwdGroupThreads);   // both halves of every row staged
+      good = bar_and(bar_id, kFwdGroupThreads, good);   // both halves of every row staged
+      if (!good) break;
       if (gw < 4) {
         const int wrows = min(32, rows - gw * 32);   // a warp's rows are contiguous in the workspace
         if (lane == 0 && wrows > 0) {
           bulk_store(part_o + (plane + slot0 + t0 + gw * 32) * D, sPO + gw * 32 * (D * 2), (uint32_t)wrows * D * 2);
-          bulk_commit();   // its reads are waited for under the next tile's S GEMM
+          bulk_commit();   // its reads are waited for before the next tile's P is stored
         }
       }
       if (tid == 0) FMB_TICK(6);   // epilogue
     }
     if (gw < 4 && lane == 0) bulk_wait_read();
   }
+  tc_fence_before_sync();
+  __syncthreads();         // every role is done with the item's tiles, barriers and TMEM columns
+  tc_fence_after_sync();
+  FMB_TICK(7);             // waiting for the other roles
+  }  // work items
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, NCOLS);
 }
@@ -926,6 +982,13 @@ static TcParams make_tc_params(const AttnArgs& a, const AttnWorkspace& w, const 
   return p;
 }
 
+static int sm_count() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+    n = 148;
+  return n;
+}
+
 template <typename T, int C, int D>
 static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   TcParams p = make_tc_params(a, w, ps);
@@ -936,7 +999,12 @@ static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassPa
   if (smem < 120 * 1024) smem = 120 * 1024;
   auto kern = fwd_main_tc_kernel<T, C, D>;
   FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<dim3(a.ncol * ps.nsub, ps.nh, a.batch), kFwdThreads, smem, s>>>(p);
+  // persistent CTAs, one per SM; items in ascending key-block order
+  p.work = w.status + 4;
+  p.items_y = ps.nh; p.items_z = a.batch;
+  p.n_items = a.ncol * ps.nsub * ps.nh * a.batch;
+  FMB_CUDA(cudaMemsetAsync(p.work, 0, sizeof(int), s));
+  kern<<<min(p.n_items, sm_count()), kFwdThreads, smem, s>>>(p);
   FMB_LAUNCH_CHECK("fwd_main_tc_kernel");
   return FMB_OK;
 }

@@ -15,6 +15,10 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
+// an mbarrier has to be invalidated before its memory is initialised again
+__device__ __forceinline__ void mbar_inval(uint64_t* bar) {
+  asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void mbar_fence_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
@@ -26,6 +30,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// non-blocking test of a phase (for a thread that serves several barriers in turn)
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)
@@ -262,6 +278,22 @@ __device__ __forceinline__ void gather_cp_async(int t, unsigned char* tile, uint
     const int src = rows[r];
     cp_async_16(tile + sw128_offset(r, j, block_stride), base + (int64_t)(src < 0 ? 0 : src) * row_stride + j * 8,
                 src >= 0);
+  }
+}
+
+// NROWS x NCHUNK*16-byte dense tile (rows `row_stride` apart, rows >= rows_valid zero-filled) copied
+// by a group of NT threads with 16-byte cp.async copies
+template <typename T, int NCHUNK, int NROWS, int NT>
+__device__ __forceinline__ void dense_cp_async(int t, unsigned char* tile, uint32_t block_stride, const T* base,
+                                               int64_t row_stride, int rows_valid) {
+  constexpr int RPP = NT / NCHUNK;           // rows per pass
+  static_assert(NT % NCHUNK == 0 && NROWS % RPP == 0, "thread group does not tile the rows");
+  const int j = t % NCHUNK, rb = t / NCHUNK;
+#pragma unroll 4
+  for (int i = 0; i < NROWS / RPP; ++i) {
+    const int r = rb + RPP * i;
+    const bool ok = r < rows_valid;
+    cp_async_16(tile + sw128_offset(r, j, block_stride), base + (int64_t)(ok ? r : 0) * row_stride + j * 8, ok);
   }
 }
 
