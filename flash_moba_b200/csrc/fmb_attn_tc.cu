@@ -59,9 +59,11 @@ struct TcParams {
   int heads, heads_k; int64_t total_q;
   float scale; int causal;
   // persistent CTAs: work items (key block, head or kv head, sequence) are handed out through a
-  // counter in the workspace status block, key blocks in ascending order (under a causal mask the
-  // early key blocks have the longest columns, so the long items start first)
-  int* work; int n_items, items_y, items_z;
+  // counter in the workspace status block.  Order: one (head, sequence) after the other, so that
+  // the CTAs running at the same time gather rows of few heads (their Q / dO rows stay in L2);
+  // inside a head the key blocks ascend (under a causal mask the early key blocks have the
+  // longest columns, so a head's long items start first and its short ones fill the end).
+  int* work; int n_items, items_x, items_y, items_z;
 };
 
 __host__ __device__ constexpr int next_pow2_cols(int x) { return x <= 32 ? 32 : x <= 64 ? 64 : x <= 128 ? 128 : x <= 256 ? 256 : 512; }
@@ -147,7 +149,7 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
   const int item = s_item;
   if (item >= p.n_items) break;
   // C is the key block: chunk c of the pattern is covered by nsub blocks of C keys
-  const int bx = item / (p.items_y * p.items_z), rem = item - bx * (p.items_y * p.items_z);
+  const int rem = item / p.items_x, bx = item - rem * p.items_x;
   const int c = bx / p.ps.nsub, sb = bx % p.ps.nsub, h = p.ps.h0 + rem % p.items_y, b = rem / p.items_y;
   const ColRef col = column_of(p.ps, b, h, c);
   const int nnz = col.nnz;
@@ -464,36 +466,35 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   unsigned char* sP = sdO + kQTile;               // [128][C]
   unsigned char* sdS = sP + kTcM * C * 2;         // [128][C]
 
+  __shared__ int s_item;
   const int group = p.heads / p.heads_k;
-  const int c = blockIdx.x / p.ps.nsub, sb = blockIdx.x % p.ps.nsub, hk = p.ps.h0 / group + blockIdx.y, b = blockIdx.z;
-  const int64_t plane = (int64_t)sb * p.ps.cap;
-  const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
-  const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
-  const int key0 = c * p.ps.chunk + sb * C;
-  if (key0 >= len_k) {
-    zero_dq_partials<T>(p.ps, static_cast<T*>(p.part_o), plane, b, hk, group, c, D);
-    return;
-  }
-  const int keys_valid = min(C, len_k - key0);
-  const int shift = len_k - len_q;
   const float scale_log2 = p.scale * kLog2eTc;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int lt = tid & (kTcM - 1);                // row (TMEM lane) of a compute thread
   const int hf = (tid >> 7) & 1;                  // column half of a compute thread
 
-  // ---- the CTA's tile sequence
-  auto seek_head = [&](BwdTile& it) { return bwd_seek_head(p.ps, b, hk, group, c, it); };
-  auto next_tile = [&](BwdTile& it) { return bwd_next_tile(p.ps, b, hk, group, c, it); };
-  // sequence-local query row of entry i of the tile (-1 = none).  row_raw() only issues the load;
-  // row_checked() is applied where the value is used, so that a prefetch does not wait for it.
-  auto row_raw = [&](const BwdTile& it, int i) {
-    return (it.t0 + i < it.nnz) ? p.ps.indices[it.off + it.t0 + i] : -1;
-  };
-  auto row_checked = [&](int r) { return (r < 0 || r >= len_q) ? -1 : r; };
-
   FMB_T0();
   if (warp == 0) tmem_alloc(&tmem_base_s, NCOLS);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+  const uint32_t tS = tmem_base, tdP = tmem_base + C, tdV = tmem_base + 2 * C, tdK = tmem_base + 2 * C + D;
+  const uint32_t tdQ = tdP;
+
+  // persistent CTA: work items (key block, kv head, sequence) from a counter; the barriers are
+  // invalidated and initialised again for every item, so each item starts in phase 0
+  bool first_item = true;
+#pragma unroll 1
+  for (;;) {
   if (tid == 0) {
+    s_item = atomicAdd(p.work, 1);
+    if (!first_item) {
+      mbar_inval(&bar_s); mbar_inval(&bar_p); mbar_inval(&bar_dq); mbar_inval(&bar_dv); mbar_inval(&bar_fin);
+      mbar_inval(&bar_dk[0]); mbar_inval(&bar_dk[1]); mbar_inval(&bar_fullq[0]); mbar_inval(&bar_fullq[1]);
+      mbar_inval(&bar_fulldo); mbar_inval(&bar_pready); mbar_inval(&bar_dsready); mbar_inval(&bar_dqfree);
+      mbar_inval(&bar_kv);
+    }
     mbar_init(&bar_s, 1); mbar_init(&bar_p, 1); mbar_init(&bar_dq, 1); mbar_init(&bar_dv, 1); mbar_init(&bar_fin, 1);
     mbar_init(&bar_dk[0], 1); mbar_init(&bar_dk[1], 1);
     mbar_init(&bar_fullq[0], kBwdQLoaders / 32); mbar_init(&bar_fullq[1], kBwdQLoaders / 32);
@@ -503,22 +504,45 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
     mbar_init(&bar_kv, kBwdCompute / 32);
     mbar_fence_init();
   }
-  tc_fence_before_sync();
-  __syncthreads();                 // barriers initialised, TMEM allocated
-  tc_fence_after_sync();
+  __syncthreads();
+  first_item = false;
+  const int item = s_item;
+  if (item >= p.n_items) break;
+  const int rem = item / p.items_x, bx = item - rem * p.items_x;
+  const int c = bx / p.ps.nsub, sb = bx % p.ps.nsub, hk = p.ps.h0 / group + rem % p.items_y, b = rem / p.items_y;
+  const int64_t plane = (int64_t)sb * p.ps.cap;
+  const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
+  const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
+  const int key0 = c * p.ps.chunk + sb * C;
+  if (key0 >= len_k) {     // CTA-uniform
+    zero_dq_partials<T>(p.ps, static_cast<T*>(p.part_o), plane, b, hk, group, c, D);
+    __syncthreads();
+    continue;
+  }
+  const int keys_valid = min(C, len_k - key0);
+  const int shift = len_k - len_q;
+
+  // ---- the item's tile sequence
+  auto seek_head = [&](BwdTile& it) { return bwd_seek_head(p.ps, b, hk, group, c, it); };
+  auto next_tile = [&](BwdTile& it) { return bwd_next_tile(p.ps, b, hk, group, c, it); };
+  // sequence-local query row of entry i of the tile (-1 = none).  row_raw() only issues the load;
+  // row_checked() is applied where the value is used, so that a prefetch does not wait for it.
+  auto row_raw = [&](const BwdTile& it, int i) {
+    return (it.t0 + i < it.nnz) ? p.ps.indices[it.off + it.t0 + i] : -1;
+  };
+  auto row_checked = [&](int r) { return (r < 0 || r >= len_q) ? -1 : r; };
+
   if (warp < 8) {                  // K and V tiles; the loaders fetch the first row tiles meanwhile
     const T* kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + key0) * p.k_rs + (int64_t)hk * p.k_hs;
     const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
-    if (hf == 0) stage_dense_sw128_t<T, D / 8, C>(lt, sK, kKBlock, kbase, p.k_rs, keys_valid);
-    else stage_dense_sw128_t<T, D / 8, C>(lt, sV, kKBlock, vbase, p.v_rs, keys_valid);
+    if (hf == 0) dense_cp_async<T, D / 8, C, kTcM>(lt, sK, kKBlock, kbase, p.k_rs, keys_valid);
+    else dense_cp_async<T, D / 8, C, kTcM>(lt, sV, kKBlock, vbase, p.v_rs, keys_valid);
+    cp_async_wait_all();
     fence_async_smem();
     __syncwarp();
     if (lane == 0) mbar_arrive(&bar_kv);
   }
-  FMB_TICK(16);   // prologue
-  const uint32_t tmem_base = tmem_base_s;
-  const uint32_t tS = tmem_base, tdP = tmem_base + C, tdV = tmem_base + 2 * C, tdK = tmem_base + 2 * C + D;
-  const uint32_t tdQ = tdP;
+  FMB_TICK(16);   // item hand-out, K/V staging
 
   BwdTile it{0, 0, 0, 0, 0};
   bool have = seek_head(it);
@@ -814,6 +838,10 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
       tc_fence_before_sync();
     }
   }
+  tc_fence_before_sync();
+  __syncthreads();         // every role is done with the item's tiles, barriers and TMEM columns
+  tc_fence_after_sync();
+  }  // work items
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, NCOLS);
 }
@@ -999,10 +1027,10 @@ static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassPa
   if (smem < 120 * 1024) smem = 120 * 1024;
   auto kern = fwd_main_tc_kernel<T, C, D>;
   FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  // persistent CTAs, one per SM; items in ascending key-block order
+  // persistent CTAs, one per SM
   p.work = w.status + 4;
-  p.items_y = ps.nh; p.items_z = a.batch;
-  p.n_items = a.ncol * ps.nsub * ps.nh * a.batch;
+  p.items_x = a.ncol * ps.nsub; p.items_y = ps.nh; p.items_z = a.batch;
+  p.n_items = p.items_x * p.items_y * p.items_z;
   FMB_CUDA(cudaMemsetAsync(p.work, 0, sizeof(int), s));
   kern<<<min(p.n_items, sm_count()), kFwdThreads, smem, s>>>(p);
   FMB_LAUNCH_CHECK("fwd_main_tc_kernel");
@@ -1017,7 +1045,12 @@ static int bwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassPa
   auto kern = bwd_main_tc_kernel<T, C, D>;
   FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int nchunk = max(a.ncol, ceil_div(a.max_k, a.chunk));
-  kern<<<dim3(nchunk * ps.nsub, ps.nh / (a.heads / a.heads_k), a.batch), kBwdThreads, smem, s>>>(p);
+  // persistent CTAs, one per SM
+  p.work = w.status + 4;
+  p.items_x = nchunk * ps.nsub; p.items_y = ps.nh / (a.heads / a.heads_k); p.items_z = a.batch;
+  p.n_items = p.items_x * p.items_y * p.items_z;
+  FMB_CUDA(cudaMemsetAsync(p.work, 0, sizeof(int), s));
+  kern<<<min(p.n_items, sm_count()), kBwdThreads, smem, s>>>(p);
   FMB_LAUNCH_CHECK("bwd_main_tc_kernel");
   return FMB_OK;
 }
