@@ -63,8 +63,23 @@ struct TcParams {
   // the CTAs running at the same time gather rows of few heads (their Q / dO rows stay in L2);
   // inside a head the key blocks ascend (under a causal mask the early key blocks have the
   // longest columns, so a head's long items start first and its short ones fill the end).
-  int* work; int n_items, items_x, items_y, items_z;
+  // The first `items_heavy` key blocks of every head (the longest columns) come before all of
+  // that, so that no long item starts late in the launch.
+  int* work; int n_items, items_x, items_y, items_z, items_heavy;
 };
+
+// work item -> (key block index, head/sequence index)
+__device__ __forceinline__ void decode_item(const TcParams& p, int item, int& bx, int& rem) {
+  const int yz = p.items_y * p.items_z, n_a = p.items_heavy * yz;
+  if (item < n_a) {
+    bx = item / yz;
+    rem = item - bx * yz;
+  } else {
+    const int j = item - n_a, rest = p.items_x - p.items_heavy;
+    rem = j / rest;
+    bx = p.items_heavy + (j - rem * rest);
+  }
+}
 
 __host__ __device__ constexpr int next_pow2_cols(int x) { return x <= 32 ? 32 : x <= 64 ? 64 : x <= 128 ? 128 : x <= 256 ? 256 : 512; }
 
@@ -149,7 +164,8 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
   const int item = s_item;
   if (item >= p.n_items) break;
   // C is the key block: chunk c of the pattern is covered by nsub blocks of C keys
-  const int rem = item / p.items_x, bx = item - rem * p.items_x;
+  int bx, rem;
+  decode_item(p, item, bx, rem);
   const int c = bx / p.ps.nsub, sb = bx % p.ps.nsub, h = p.ps.h0 + rem % p.items_y, b = rem / p.items_y;
   const ColRef col = column_of(p.ps, b, h, c);
   const int nnz = col.nnz;
@@ -508,7 +524,8 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   first_item = false;
   const int item = s_item;
   if (item >= p.n_items) break;
-  const int rem = item / p.items_x, bx = item - rem * p.items_x;
+  int bx, rem;
+  decode_item(p, item, bx, rem);
   const int c = bx / p.ps.nsub, sb = bx % p.ps.nsub, hk = p.ps.h0 / group + rem % p.items_y, b = rem / p.items_y;
   const int64_t plane = (int64_t)sb * p.ps.cap;
   const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
@@ -1030,6 +1047,7 @@ static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassPa
   // persistent CTAs, one per SM
   p.work = w.status + 4;
   p.items_x = a.ncol * ps.nsub; p.items_y = ps.nh; p.items_z = a.batch;
+  p.items_heavy = a.causal ? min(p.items_x, 16 * ps.nsub) : 0;
   p.n_items = p.items_x * p.items_y * p.items_z;
   FMB_CUDA(cudaMemsetAsync(p.work, 0, sizeof(int), s));
   kern<<<min(p.n_items, sm_count()), kFwdThreads, smem, s>>>(p);
@@ -1048,6 +1066,7 @@ static int bwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassPa
   // persistent CTAs, one per SM
   p.work = w.status + 4;
   p.items_x = nchunk * ps.nsub; p.items_y = ps.nh / (a.heads / a.heads_k); p.items_z = a.batch;
+  p.items_heavy = a.causal ? min(p.items_x, 16 * ps.nsub) : 0;
   p.n_items = p.items_x * p.items_y * p.items_z;
   FMB_CUDA(cudaMemsetAsync(p.work, 0, sizeof(int), s));
   kern<<<min(p.n_items, sm_count()), kBwdThreads, smem, s>>>(p);

@@ -89,11 +89,17 @@ __global__ void __launch_bounds__(1024) csc_col_scan_kernel(CscParams p) {
     const int c = c0 + threadIdx.x;
     int run = 0;
     if (c < p.ncol) {
-      for (int t = 0; t < ntiles_b; ++t) {     // tiles beyond the sequence hold zeros
-        int32_t* cell = hist + (int64_t)t * p.ncol + c;
-        const int x = *cell;
-        *cell = run;
-        run += x;
+      // tiles beyond the sequence hold zeros.  Sixteen counters are fetched at a time so that the
+      // loads overlap: one dependent load-add-store chain per tile would cost a memory latency each
+      for (int t0 = 0; t0 < ntiles_b; t0 += 16) {
+        int x[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) x[u] = (t0 + u < ntiles_b) ? hist[(int64_t)(t0 + u) * p.ncol + c] : 0;
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          if (t0 + u < ntiles_b) hist[(int64_t)(t0 + u) * p.ncol + c] = run;
+          run += x[u];
+        }
       }
     }
     // block-wide exclusive scan of `run` over this group of columns

@@ -155,7 +155,8 @@ __global__ void __launch_bounds__(kGateThreads) gate_topk_kernel(GateParams p) {
   float* sTV = sS + kGateM * kGateSStride;                         // [128][topk]
   int* sTI = reinterpret_cast<int*>(sTV + kGateM * p.topk);        // [128][topk]
 
-  const int mt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // late row tiles see the most candidate chunks under a causal mask: they are scheduled first
+  const int mt = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
   const int len_k = p.cu_k[b + 1] - p.cu_k[b];
   const int km0 = p.cu_km[b], nchunks = p.cu_km[b + 1] - km0;
@@ -265,7 +266,8 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
   unsigned char* sQ = smem;
   unsigned char* sKM = sQ + kTile;             // two buffers
 
-  const int mt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // late row tiles see the most candidate chunks under a causal mask: they are scheduled first
+  const int mt = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
   const int len_k = p.cu_k[b + 1] - p.cu_k[b];
   const int km0 = p.cu_km[b], nchunks = p.cu_km[b + 1] - km0;
