@@ -53,14 +53,58 @@ ACC = _load_accounting()
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """SM clock and throttle reasons of one GPU while the timed region runs.
+
+    Polled in-process through NVML every few milliseconds (the timed region of a multi-GPU run
+    lasts only tens of milliseconds, shorter than nvidia-smi's loop interval); nvidia-smi is the
+    fallback when the NVML binding is missing.  Reading only: nothing is set."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
-    def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index, period_s=0.004):
+        self.index, self.rows, self.proc, self.period = index, [], None, period_s
+        self.stop = threading.Event()
+        self.nvml = None
+        self.error = None
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            h = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+        except Exception:
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+        return pynvml, h
+
+    def _poll(self):
+        pynvml, h = self.nvml
+        try:
+            mx = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            mx = None
+        get_reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(pynvml, "nvmlDeviceGetCurrentClocksThrottleReasons", None)
+        while not self.stop.is_set():
+            try:
+                sm = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+                bits = int(get_reasons(h)) if get_reasons else 0
+                self.rows.append((float(sm), float(mx) if mx else None, bits))
+            except Exception as e:      # reported in the summary, never fatal
+                self.error = repr(e)
+            self.stop.wait(self.period)
 
     def __enter__(self):
+        try:
+            self.nvml = self._nvml_handle()
+            self.t = threading.Thread(target=self._poll, daemon=True)
+            self.t.start()
+            return self
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
@@ -73,9 +117,19 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            r = [x.strip() for x in line.split(",")]
+            try:
+                bits = sum(b for (name, b), v in zip((("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40),
+                                                      ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4)), r[2:6])
+                           if v.lower().startswith("active"))
+                self.rows.append((float(r[0]), float(r[1]), bits))
+            except (ValueError, IndexError):
+                continue
 
     def __exit__(self, *a):
+        self.stop.set()
+        if self.nvml is not None:
+            self.t.join(timeout=1)
         if self.proc:
             self.proc.terminate()
             try:
@@ -84,18 +138,16 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "error": self.error}
+        sm = [r[0] for r in self.rows]
+        mx = [r[1] for r in self.rows if r[1]]
+        bits = 0
         for r in self.rows:
-            try:
-                sm.append(float(r[0])); mx.append(float(r[1]))
-            except (ValueError, IndexError):
-                continue
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+            bits |= r[2]
+        reasons = sorted(n for n, b in self.REASON_BITS.items() if bits & b)
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm), "source": "nvml" if self.nvml is not None else "nvidia-smi"}
 
 
 def cpu_sample(seqlens, d, chunk, topk, rows=4096, threads=None):

@@ -450,7 +450,10 @@ __device__ __forceinline__ void fwd_combine_group_body(int64_t vblock, const T* 
       const int src = hit ? (__ffs(hit) - 1) : lane;
       const uint32_t pk = __shfl_sync(0xffffffffu, g.pos, src);
       const uint32_t sk = __shfl_sync(0xffffffffu, g.slot, src);
-      wk[k] = hit ? __shfl_sync(0xffffffffu, w, src) : 0.f;
+      // the shuffle must be executed by every lane: groups of one warp differ in `hit` when their
+      // rows have different numbers of partials
+      const float w_src = __shfl_sync(0xffffffffu, w, src);
+      wk[k] = hit ? w_src : 0.f;
       if (hit && wk[k] > 0.f) {
         const T* row = part_o + (int64_t)pk * d;
 #pragma unroll
@@ -617,8 +620,10 @@ static int fwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const
 
 template <typename T>
 static int fwd_combine_any(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
+#ifndef FMB_COMBINE_GENERIC
   if (a.d == 128) return fwd_combine_dispatch<T, 128>(a, w, ps, s);
   if (a.d == 256) return fwd_combine_dispatch<T, 256>(a, w, ps, s);
+#endif
   const int64_t rows = a.total_q * ps.nh;
   fwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>((const T*)w.part_o, w.part_lse, make_combine(a, w, ps),
                                                         (T*)a.o, a.o_rs, a.o_hs, a.lse, nullptr, 0, warp_grid(rows));

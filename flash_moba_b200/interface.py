@@ -193,6 +193,17 @@ def _flash_moba_attn_varlen_backward_fake(dout, q, k, v, out, softmax_lse, dq, d
     return torch.empty((heads, total_q), device=q.device, dtype=torch.float32)
 
 
+def _attention_head_dim(d: int) -> int:
+    """Head dimension the attention kernels run at: they are built for 64 and 128, and any smaller
+    head dimension is zero-padded up to the next of the two (the reference pads to a multiple
+    of 8 and dispatches on 32 ... 256, flash_moba/flash_moba_interface.py:433-436)."""
+    if d <= 64:
+        return 64
+    if d <= 128:
+        return 128
+    return d + (-d) % 8          # above 128: multiple of 8, rejected by the library with its message
+
+
 # ======================================================================================
 # autograd
 # ======================================================================================
@@ -205,8 +216,9 @@ class FlashMobaAttnVarlenFunc(torch.autograd.Function):
         if softmax_scale is None:
             softmax_scale = q.shape[-1] ** (-0.5)
         d_og = q.size(2)
-        if d_og % 8 != 0:
-            pad = [0, 8 - d_og % 8]
+        d_pad = _attention_head_dim(d_og)
+        if d_pad != d_og:      # zero columns change neither the scores nor the first d_og outputs
+            pad = [0, d_pad - d_og]
             q, k, v = (torch.nn.functional.pad(x, pad) for x in (q, k, v))
         out_padded, lse, s_dmask, rng_state = torch.ops.flash_moba._flash_moba_attn_varlen_forward(
             q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, moba_col_offsets, moba_col_nnz,
@@ -227,7 +239,7 @@ class FlashMobaAttnVarlenFunc(torch.autograd.Function):
          lg_block_m, lg_block_n) = ctx.meta
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         d_og = dout.size(2)
-        dout_padded = dout if d_og % 8 == 0 else torch.nn.functional.pad(dout, [0, 8 - d_og % 8])
+        dout_padded = dout if q.size(2) == d_og else torch.nn.functional.pad(dout, [0, q.size(2) - d_og])
         torch.ops.flash_moba._flash_moba_attn_varlen_backward(
             dout_padded, q, k, v, out, lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
             col_offsets, col_nnz, row_indices, lg_block_m, lg_block_n, dropout_p, softmax_scale, causal, softcap,

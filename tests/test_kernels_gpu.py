@@ -249,8 +249,8 @@ def test_attention_golden_patterns(case, engine):
     q, k, v, do = unpad(q, lq), unpad(k, lk), unpad(v, lk), unpad(do, lq)
     mask = torch.from_numpy(g[f"attn{i}_mask"])
     pattern = tuple(torch.from_numpy(g[f"attn{i}_{n}"]) for n in ("col_offsets", "col_nnz", "indices"))
-    if d not in (64, 128):
-        pytest.skip("head_dim outside {64,128} is not built yet")
+    if d > 128:
+        pytest.skip("head_dim above 128 is not built")
     _attn_check(q, k, v, do, cu_of(lq), cu_of(lk), mask, c, bool(causal), engine, pattern=pattern)
     # the reference's golden outputs themselves
     import flash_moba_b200 as F
@@ -376,6 +376,20 @@ def test_attention_fp16(engine):
     idx, co, cn, ind = O.moba_pattern(q.float(), k.float(), cq, cq, max(lens), 2, chunk, True)
     mask = O.csc_to_mask(co, cn, ind, cq, max(lens))
     _attn_check(q, k, v, do, cq, cq, mask, chunk, True, engine, pattern=(co, cn, ind))
+
+
+@pytest.mark.parametrize("d", [32, 40, 96, 100, 128])
+def test_attention_head_dims_padded_to_64_or_128(d):
+    """Head dimensions below 128 that the kernels are not built for run zero-padded to 64 / 128
+    (the reference's grid has 32, 96, ...: tests/test_moba_attn.py); softmax scale from the true d."""
+    torch.manual_seed(d)
+    lens = [333, 128]
+    T, H, chunk = sum(lens), 2, 64
+    q, k, v, do = [torch.randn(T, H, d).bfloat16() for _ in range(4)]
+    cq = cu_of(lens)
+    idx, co, cn, ind = O.moba_pattern(q.float(), k.float(), cq, cq, max(lens), 3, chunk, True)
+    mask = O.csc_to_mask(co, cn, ind, cq, max(lens))
+    _attn_check(q, k, v, do, cq, cq, mask, chunk, True, 1, pattern=(co, cn, ind))
 
 
 # ----------------------------------------------------------------------------- whole path
