@@ -95,6 +95,17 @@ int fmb_profile_read(int kind, float* ms, int max_entries) {
   return n;
 }
 
+int fmb_copy_rows_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                        size_t rows, int direction, void* stream) {
+  if (rows == 0 || width_bytes == 0) return FMB_OK;
+  if (!dst || !src || width_bytes > dst_pitch || width_bytes > src_pitch || (direction != 0 && direction != 1))
+    return fail(FMB_ERR_BAD_ARG, "copy_rows: bad pointers, pitches (%zu, %zu) narrower than the width %zu, or direction %d",
+                dst_pitch, src_pitch, width_bytes, direction);
+  FMB_CUDA(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows,
+                             direction == 0 ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  return FMB_OK;
+}
+
 int fmb_attn_engine(int chunk, int head_dim, int backward) {
   AttnArgs a;
   memset(&a, 0, sizeof(a));

@@ -235,6 +235,14 @@ unsigned long long fmb_launch_count(void);
 int fmb_profile_enable(int on);
 int fmb_profile_read(int kind, float* ms, int max_entries);
 
+/* Strided host<->device copy of a head range: `rows` rows of `width_bytes` bytes, `src_pitch` /
+ * `dst_pitch` bytes apart, enqueued on `stream` (cudaMemcpy2DAsync; the host side should be
+ * pinned).  direction: 0 host->device, 1 device->host.  Used by the host pipeline that overlaps
+ * the copies of one head group with the kernels of another.  No counterpart in the reference,
+ * whose operands are device tensors. */
+int fmb_copy_rows_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                        size_t rows, int direction, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
