@@ -530,13 +530,16 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   const int64_t plane = (int64_t)sb * p.ps.cap;
   const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
   const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
-  const int key0 = c * p.ps.chunk + sb * C;
+  // The kernel always works on 128 key lanes; with 64-key blocks (chunks that are not a multiple of
+  // 128) the upper 64 lanes are zero-filled and masked: twice the tensor work per key, still several
+  // times faster than the CUDA-core backward, and the tensor pipe is mostly idle anyway.
+  const int key0 = c * p.ps.chunk + sb * p.ps.kb;
   if (key0 >= len_k) {     // CTA-uniform
     zero_dq_partials<T>(p.ps, static_cast<T*>(p.part_o), plane, b, hk, group, c, D);
     __syncthreads();
     continue;
   }
-  const int keys_valid = min(C, len_k - key0);
+  const int keys_valid = min(p.ps.kb, len_k - key0);
   const int shift = len_k - len_q;
 
   // ---- the item's tile sequence
@@ -1076,7 +1079,6 @@ static int bwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassPa
 
 bool tc_supported(const AttnArgs& a, bool backward) {
   // key block = 128 keys when the chunk is a multiple of 128, else 64
-  if (backward) return a.chunk % 128 == 0 && (a.d == 64 || a.d == 128);
   return a.chunk % 64 == 0 && (a.d == 64 || a.d == 128);
 }
 
@@ -1094,10 +1096,11 @@ int launch_fwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, const PassPara
 
 int launch_bwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   if (a.batch == 0 || a.heads == 0) return FMB_OK;
-  if (w.kb == 128 && a.d == 64)
+  // 64-key blocks run on the same 128-lane kernel with the upper lanes masked
+  if ((w.kb == 128 || w.kb == 64) && a.d == 64)
     return a.dtype == FMB_BF16 ? bwd_tc_launch<__nv_bfloat16, 128, 64>(a, w, ps, s)
                                : bwd_tc_launch<__half, 128, 64>(a, w, ps, s);
-  if (w.kb == 128 && a.d == 128)
+  if ((w.kb == 128 || w.kb == 64) && a.d == 128)
     return a.dtype == FMB_BF16 ? bwd_tc_launch<__nv_bfloat16, 128, 128>(a, w, ps, s)
                                : bwd_tc_launch<__half, 128, 128>(a, w, ps, s);
   return fail(FMB_ERR_UNSUPPORTED, "tensor-core backward: key block %d / head_dim %d not built", w.kb, a.d);
