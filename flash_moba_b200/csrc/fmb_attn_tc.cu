@@ -102,7 +102,10 @@ __host__ __device__ constexpr int next_pow2_cols(int x) { return x <= 32 ? 32 : 
 // allocated once, and a CTA keeps taking work items until the counter runs out.
 constexpr int kFwdGroups = 2;
 constexpr int kFwdGroupThreads = 256;
-constexpr int kFwdLoaderSet = 64;               // loader threads per compute group
+#ifndef FMB_FWD_LW
+#define FMB_FWD_LW 2          // loader warps per compute group
+#endif
+constexpr int kFwdLoaderSet = 32 * FMB_FWD_LW;  // loader threads per compute group
 constexpr int kFwdIssuerWarp = kFwdGroups * kFwdGroupThreads / 32;
 constexpr int kFwdThreads = kFwdGroups * kFwdGroupThreads + 32 + kFwdGroups * kFwdLoaderSet;
 
@@ -241,7 +244,7 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
     uint32_t ph_free = 0;
     // row id of entry e of a tile (-1 = none): the load only; the range check happens at the use
     auto row_raw = [&](int tile, int e) {
-      return (tile < ntiles && tile * kTcM + e < nnz) ? p.ps.indices[off + tile * kTcM + e] : -1;
+      return (e < kTcM && tile < ntiles && tile * kTcM + e < nnz) ? p.ps.indices[off + tile * kTcM + e] : -1;
     };
     int r_a = row_raw(gi, st), r_b = row_raw(gi, st + kFwdLoaderSet);   // the set's first tile
 #pragma unroll 1
@@ -254,7 +257,7 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
         ph_free ^= 1;
       }
       rows[st] = (r_a < 0 || r_a >= len_q) ? -1 : r_a;
-      rows[st + kFwdLoaderSet] = (r_b < 0 || r_b >= len_q) ? -1 : r_b;
+      if (st + kFwdLoaderSet < kTcM) rows[st + kFwdLoaderSet] = (r_b < 0 || r_b >= len_q) ? -1 : r_b;
       r_a = row_raw(i + kFwdGroups, st);                  // next tile's row ids, in flight meanwhile
       r_b = row_raw(i + kFwdGroups, st + kFwdLoaderSet);
       ok = bar_and(4 + gi, kFwdLoaderSet, ok);   // also publishes the row ids inside the set
@@ -420,11 +423,16 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
 //             dS_ready(i) -> dQ(i) over dP's columns, dK(i) [its completion frees this Q buffer]
 //             dO(i+1) landed and dQ_free(i) -> dP(i+1)
 constexpr int kBwdCompute = 256;
+// Loader warps.  Measured at 64K tokens (backward main kernel): 1 + 2 warps 5.14 ms, 2 + 2 warps
+// 4.98 ms, 2 + 4 warps 4.63 ms, 1 + 4 warps 5.2 ms: the gathers are latency bound per warp.
 #ifndef FMB_BWD_QW
-#define FMB_BWD_QW 1          // warps gathering Q rows
+#define FMB_BWD_QW 2          // warps gathering Q rows
 #endif
 #ifndef FMB_BWD_OW
-#define FMB_BWD_OW 2          // warps gathering dO rows
+#define FMB_BWD_OW 4          // warps gathering dO rows
+#endif
+#ifndef FMB_BWD_PACKED_P
+#define FMB_BWD_PACKED_P 1    // 1: P kept as packed I/O-dtype values between the P and dS phases
 #endif
 #ifndef FMB_BWD_S_EARLY
 #define FMB_BWD_S_EARLY 0     // 1: S(i+1) is issued before dQ(i), dK(i) instead of after them
@@ -725,6 +733,30 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
       tc_fence_after_sync();
       FMB_TICK(17);   // waiting for S
       const int lim = r_cur < 0 ? 0 : (p.causal ? min(keys_valid, r_cur + shift - key0 + 1) : keys_valid);
+#if FMB_BWD_PACKED_P
+      // P is kept as the rounded values the dV GEMM uses (32 registers instead of 64 fp32): the
+      // registers saved let the CTA run more loader warps without spilling
+      uint4 pp[8];
+#pragma unroll
+      for (int i2 = 0; i2 < 2; ++i2) {
+        const int col0 = hf * 64 + i2 * 32;
+        float pr[32];
+        tmem_ld32(tS + lane_sel + col0, pr);
+        tmem_ld_wait();
+        if (i2 == 1) tc_fence_before_sync();
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) pr[jj] = (col0 + jj < lim) ? exp2f(pr[jj] * scale_log2 - lse_cur) : 0.f;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) pp[i2 * 4 + jj] = pack8<T>(pr + jj * 8);
+        if (i2 == 0 && i > 0) {      // the previous tile's dQ staging (in the P tile) has been read out
+          if (warp < 4 && lane == 0) bulk_wait_read();
+          good = bar_and(2, kBwdCompute, good);
+        }
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+          *reinterpret_cast<uint4*>(sP + sw128_offset(lt, col0 / 8 + jj, kQBlock)) = pp[i2 * 4 + jj];
+      }
+#else
       float pr[64];
       tmem_ld32(tS + lane_sel + hf * 64, pr);
       tmem_ld32(tS + lane_sel + hf * 64 + 32, pr + 32);
@@ -747,6 +779,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
           *reinterpret_cast<uint4*>(sP + sw128_offset(lt, col0 / 8 + jj, kQBlock)) = pack8<T>(pr + i2 * 32 + jj * 8);
         FMB_TICK(33);
       }
+#endif
       tc_fence_before_sync();
       fence_async_smem();
       __syncwarp();
@@ -764,7 +797,16 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
         tmem_ld32(tdP + lane_sel + col0, dp);
         tmem_ld_wait();
 #pragma unroll
+#if FMB_BWD_PACKED_P
+        for (int j8 = 0; j8 < 4; ++j8) {
+          float pf[8];
+          unpack8<T>(pp[i2 * 4 + j8], pf);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) dp[j8 * 8 + e] = pf[e] * (dp[j8 * 8 + e] - dd_cur);
+        }
+#else
         for (int jj = 0; jj < 32; ++jj) dp[jj] = pr[i2 * 32 + jj] * (dp[jj] - dd_cur);
+#endif
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj)
           *reinterpret_cast<uint4*>(sdS + sw128_offset(lt, col0 / 8 + jj, kQBlock)) = pack8<T>(dp + jj * 8);
@@ -782,25 +824,28 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
       tc_fence_after_sync();
       FMB_TICK(21);   // waiting for dQ
       {
-        float o[DH];
-#pragma unroll
-        for (int i2 = 0; i2 < DH / 32; ++i2) tmem_ld32(tdQ + lane_sel + hf * DH + i2 * 32, o + i2 * 32);
-        tmem_ld_wait();
-        tc_fence_before_sync();
-        FMB_TICK(29);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bar_dqfree);    // dQ has been read out of dP's columns
         // staged in the P tile (free: dV(i) completed before dQ(i)), 16-byte chunks permuted like the
-        // forward partials; one bulk copy per 32 rows, whose reads are waited for before P(i+1) is stored
+        // forward partials; one bulk copy per 32 rows, whose reads are waited for before P(i+1) is
+        // stored.  32 columns at a time keep the register footprint small.
         constexpr int NCH = DH / 8;               // 16-byte chunks of this thread's half row
         const int key = (int)((it.slot + it.t0 + lt) & 7);
         unsigned char* srow = sP + lt * (D * 2);
 #pragma unroll
-        for (int jj = 0; jj < NCH; ++jj) {
+        for (int i2 = 0; i2 < DH / 32; ++i2) {
+          float o[32];
+          tmem_ld32(tdQ + lane_sel + hf * DH + i2 * 32, o);
+          tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 8; ++e) o[jj * 8 + e] *= p.scale;
-          *reinterpret_cast<uint4*>(srow + (((hf * NCH + jj) ^ key) << 4)) = pack8<T>(o + jj * 8);
+          for (int jj = 0; jj < 4; ++jj) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[jj * 8 + e] *= p.scale;
+            *reinterpret_cast<uint4*>(srow + (((hf * NCH + i2 * 4 + jj) ^ key) << 4)) = pack8<T>(o + jj * 8);
+          }
         }
+        tc_fence_before_sync();
+        FMB_TICK(29);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_dqfree);    // dQ has been read out of dP's columns
         fence_async_smem();
         FMB_TICK(30);
         good = bar_and(2, kBwdCompute, good);     // both halves of every row staged

@@ -268,13 +268,16 @@ __device__ __forceinline__ void cp_async_wait_all() {
 template <typename T, int NCHUNK, int NT = 128>
 __device__ __forceinline__ void gather_cp_async(int t, unsigned char* tile, uint32_t block_stride, const T* base,
                                                 int64_t row_stride, const int* rows) {
+  static_assert(NT % NCHUNK == 0, "a thread keeps one 16-byte chunk column");
   constexpr int RPP = NT / NCHUNK;           // rows per pass
+  constexpr int PASSES = (128 + RPP - 1) / RPP;
   const int j = t % NCHUNK, rb = t / NCHUNK;
   // partly unrolled on purpose: the loader warps run beside other roles and the kernel's code has
   // to stay small enough for the instruction cache
 #pragma unroll 4
-  for (int i = 0; i < 128 / RPP; ++i) {
+  for (int i = 0; i < PASSES; ++i) {
     const int r = rb + RPP * i;
+    if (128 % RPP != 0 && r >= 128) break;   // thread groups that do not tile the 128 rows evenly
     const int src = rows[r];
     cp_async_16(tile + sw128_offset(r, j, block_stride), base + (int64_t)(src < 0 ? 0 : src) * row_stride + j * 8,
                 src >= 0);
