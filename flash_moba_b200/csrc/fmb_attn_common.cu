@@ -426,11 +426,9 @@ __device__ __forceinline__ void fwd_combine_group_body(int64_t vblock, const T* 
   const int lane = threadIdx.x & 31, gl = lane & (G - 1);
   const unsigned gm = group_mask<G>(lane);
   const GroupRow g = group_row<G>(vblock, c, min_n, overflow);
+  // the log-sum-exp of this lane's partial: requested first, used last (the partial rows are
+  // requested before anything waits for it, so that there is ONE round trip to memory, not two)
   const float l = g.valid ? part_lse[g.pos] : -CUDART_INF_F;
-  float m = l;
-#pragma unroll
-  for (int o = G / 2; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(gm, m, o, G));
-  const float w = (g.valid && m > -CUDART_INF_F) ? __expf(l - m) : 0.f;
   int rank = 0;
 #pragma unroll
   for (int i = 0; i < G; ++i) rank += (__shfl_sync(gm, g.pos, i, G) < g.pos) ? 1 : 0;
@@ -438,23 +436,23 @@ __device__ __forceinline__ void fwd_combine_group_body(int64_t vblock, const T* 
 #pragma unroll
   for (int i = 0; i < EPL; ++i) acc[i] = 0.f;
   float ssum = 0.f;
+  float m = -CUDART_INF_F, w = 0.f;
   constexpr int B = G < 8 ? G : 8;            // partial rows in flight per step
 #pragma unroll
   for (int r0 = 0; r0 < G; r0 += B) {
     uint4 x[B][NV];
-    float wk[B];
+    int srcs[B];
 #pragma unroll
     for (int k = 0; k < B; ++k) {
-      // the lane of this group whose partial has rank r0+k (none if the row is shorter)
+      // the lane of this group whose partial has rank r0+k (none if the row is shorter).  Every
+      // partial row of a listed slot has been written (zeros for a row that saw no key), so it is
+      // fetched whatever its weight turns out to be.
       const unsigned hit = __ballot_sync(0xffffffffu, g.valid && rank == r0 + k) & gm;
       const int src = hit ? (__ffs(hit) - 1) : lane;
+      srcs[k] = hit ? src : -1;
       const uint32_t pk = __shfl_sync(0xffffffffu, g.pos, src);
       const uint32_t sk = __shfl_sync(0xffffffffu, g.slot, src);
-      // the shuffle must be executed by every lane: groups of one warp differ in `hit` when their
-      // rows have different numbers of partials
-      const float w_src = __shfl_sync(0xffffffffu, w, src);
-      wk[k] = hit ? w_src : 0.f;
-      if (hit && wk[k] > 0.f) {
+      if (hit) {
         const T* row = part_o + (int64_t)pk * d;
 #pragma unroll
         for (int v = 0; v < NV; ++v) x[k][v] = *reinterpret_cast<const uint4*>(row + part_col(sk, gl * EPL + 8 * v, 8));
@@ -463,15 +461,25 @@ __device__ __forceinline__ void fwd_combine_group_body(int64_t vblock, const T* 
         for (int v = 0; v < NV; ++v) x[k][v] = make_uint4(0, 0, 0, 0);
       }
     }
+    if (r0 == 0) {   // weights: the row maximum of the partial log-sum-exps
+      m = l;
+#pragma unroll
+      for (int o = G / 2; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(gm, m, o, G));
+      w = (g.valid && m > -CUDART_INF_F) ? __expf(l - m) : 0.f;
+    }
 #pragma unroll
     for (int k = 0; k < B; ++k) {
-      ssum += wk[k];
+      // executed by every lane: groups of one warp differ in srcs[k] when their rows have
+      // different numbers of partials
+      const float w_src = __shfl_sync(0xffffffffu, w, srcs[k] < 0 ? lane : srcs[k]);
+      const float wk = srcs[k] < 0 ? 0.f : w_src;
+      ssum += wk;
 #pragma unroll
       for (int v = 0; v < NV; ++v) {
         float f[8];
         unpack8<T>(x[k][v], f);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[8 * v + e] = fmaf(wk[k], f[e], acc[8 * v + e]);
+        for (int e = 0; e < 8; ++e) acc[8 * v + e] = fmaf(wk, f[e], acc[8 * v + e]);
       }
     }
   }
@@ -560,13 +568,37 @@ __global__ void __launch_bounds__(256) bwd_combine_group_kernel(const T* __restr
     bwd_combine_group_body<T, G, EPL>(vb, part_dq, c, dq, rs, hs, min_n, overflow);
 }
 
-template <typename T>
+// D[h, t] = sum_d dO.O.  LPR lanes per row, each with one 16-byte load of dO and of O (LPR = d / 8
+// when that is a power of two); LPR = 0 selects the generic warp-per-row form.
+template <typename T, int LPR>
 __global__ void __launch_bounds__(256) dot_do_o_kernel(const T* __restrict__ dout, int64_t do_rs, int64_t do_hs,
                                                        const T* __restrict__ o, int64_t o_rs, int64_t o_hs,
                                                        float* softmax_d, int64_t total_q, int heads, int d) {
   using T2 = typename Elem<T>::T2;
-  const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
+  const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (LPR > 0) {
+    constexpr int L = LPR > 0 ? LPR : 32;
+    const int64_t row = wid * (32 / L) + lane / L;
+    float s = 0.f;
+    if (row < total_q * heads) {
+      const int64_t t = row / heads;
+      const int h = (int)(row - t * heads);
+      const int c = (lane % L) * 8;
+      float x[8], y[8];
+      unpack8<T>(ldg_nc_16(dout + t * do_rs + (int64_t)h * do_hs + c), x);
+      unpack8<T>(ldg_nc_16(o + t * o_rs + (int64_t)h * o_hs + c), y);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s = fmaf(x[e], y[e], s);
+    }
+#pragma unroll
+    for (int o2 = L / 2; o2; o2 >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o2);
+    if (row < total_q * heads && lane % L == 0) {
+      const int64_t t = row / heads;
+      softmax_d[(int64_t)(row - t * heads) * total_q + t] = s;
+    }
+    return;
+  }
   if (wid >= total_q * heads) return;
   const int64_t t = wid / heads;
   const int h = (int)(wid - t * heads);
@@ -670,19 +702,26 @@ int launch_bwd_combine(const AttnArgs& a, const AttnWorkspace& w, const PassPara
   return a.dtype == FMB_BF16 ? bwd_combine_any<__nv_bfloat16>(a, w, ps, s) : bwd_combine_any<__half>(a, w, ps, s);
 }
 
-int launch_dot_do_o(const AttnArgs& a, cudaStream_t s) {
+template <typename T>
+static int dot_do_o_dispatch(const AttnArgs& a, cudaStream_t s) {
   const int64_t rows = a.total_q * a.heads;
-  if (rows == 0) return FMB_OK;
-  if (a.dtype == FMB_BF16)
-    dot_do_o_kernel<__nv_bfloat16><<<warp_grid(rows), 256, 0, s>>>(
-        (const __nv_bfloat16*)a.dout, a.do_rs, a.do_hs, (const __nv_bfloat16*)a.o, a.o_rs, a.o_hs, a.softmax_d,
-        a.total_q, a.heads, a.d);
-  else
-    dot_do_o_kernel<__half><<<warp_grid(rows), 256, 0, s>>>((const __half*)a.dout, a.do_rs, a.do_hs,
-                                                           (const __half*)a.o, a.o_rs, a.o_hs, a.softmax_d,
-                                                           a.total_q, a.heads, a.d);
+  const T* dout = (const T*)a.dout;
+  const T* o = (const T*)a.o;
+#define FMB_DOT(LPR_)                                                                                        \
+  dot_do_o_kernel<T, LPR_><<<(unsigned)warp_grid(ceil_div64(rows, LPR_ ? 32 / (LPR_ ? LPR_ : 1) : 1)), 256, 0, s>>>( \
+      dout, a.do_rs, a.do_hs, o, a.o_rs, a.o_hs, a.softmax_d, a.total_q, a.heads, a.d)
+  if (a.d == 128) FMB_DOT(16);
+  else if (a.d == 64) FMB_DOT(8);
+  else if (a.d == 256) FMB_DOT(32);
+  else FMB_DOT(0);
+#undef FMB_DOT
   FMB_LAUNCH_CHECK("dot_do_o_kernel");
   return FMB_OK;
+}
+
+int launch_dot_do_o(const AttnArgs& a, cudaStream_t s) {
+  if (a.total_q * a.heads == 0) return FMB_OK;
+  return a.dtype == FMB_BF16 ? dot_do_o_dispatch<__nv_bfloat16>(a, s) : dot_do_o_dispatch<__half>(a, s);
 }
 
 // ------------------------------------------------------------------ drivers
