@@ -345,10 +345,10 @@ def main():
     dom_flops = (bwd_f if backward else fwd_f) * h_loc / H      # rank 0's launch
     roof = None
     # DRAM bytes per (row, chunk) entry of the dominant kernel, from one ncu capture of a 16K-token,
-    # 16-head case (dram__bytes_read.sum + dram__bytes_write.sum = 1,035.0 MB over its 2,039,808
+    # 16-head case (dram__bytes_read.sum + dram__bytes_write.sum = 1,038.1 MB over its 2,039,808
     # entries); the traffic is per-entry work (gathered rows in, partial rows out), so it scales
     # with the entries.
-    entry_bytes = {"bwd_main": 507.4}.get(dom) if (d == 128 and chunk == 128) else None
+    entry_bytes = {"bwd_main": 508.9}.get(dom) if (d == 128 and chunk == 128) else None
     entries = ACC.selected_entries(seqlens, chunk, topk) * h_loc
     if kern_ms.get(dom):
         ach = dom_flops / (kern_ms[dom] * 1e-3) / 1e12

@@ -206,8 +206,8 @@ static int inclusive_scan(uint32_t* data, int64_t n, uint32_t* tmp, cudaStream_t
 int build_row_lists(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   const int64_t rows = a.total_q * ps.nh;
   const int64_t ncols = (int64_t)a.batch * ps.nh * a.ncol;
-  FMB_CUDA(cudaMemsetAsync(w.row_ptr, 0, (size_t)(rows + 1) * sizeof(uint32_t), s));
-  FMB_CUDA(cudaMemsetAsync(w.row_fill, 0, (size_t)rows * sizeof(uint32_t), s));
+  // row_ptr and row_fill are neighbours in the workspace: one clear for both
+  FMB_CUDA(cudaMemsetAsync(w.row_ptr, 0, (size_t)((char*)(w.row_fill + rows) - (char*)w.row_ptr), s));
   if (ncols == 0) return FMB_OK;
   slot_count_kernel<<<(unsigned)ceil_div64(ncols + 1, 256), 256, 0, s>>>(ps, w.slot_base, a.batch);
   FMB_LAUNCH_CHECK("slot_count_kernel");

@@ -1097,7 +1097,7 @@ static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassPa
   p.items_x = a.ncol * ps.nsub; p.items_y = ps.nh; p.items_z = a.batch;
   p.items_heavy = a.causal ? min(p.items_x, 16 * ps.nsub) : 0;
   p.n_items = p.items_x * p.items_y * p.items_z;
-  FMB_CUDA(cudaMemsetAsync(p.work, 0, sizeof(int), s));
+  if (ps.h0 > 0) FMB_CUDA(cudaMemsetAsync(p.work, 0, sizeof(int), s));   // first pass: cleared with the status block
   kern<<<min(p.n_items, sm_count()), kFwdThreads, smem, s>>>(p);
   FMB_LAUNCH_CHECK("fwd_main_tc_kernel");
   return FMB_OK;
@@ -1116,7 +1116,7 @@ static int bwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassPa
   p.items_x = nchunk * ps.nsub; p.items_y = ps.nh / (a.heads / a.heads_k); p.items_z = a.batch;
   p.items_heavy = a.causal ? min(p.items_x, 16 * ps.nsub) : 0;
   p.n_items = p.items_x * p.items_y * p.items_z;
-  FMB_CUDA(cudaMemsetAsync(p.work, 0, sizeof(int), s));
+  if (ps.h0 > 0) FMB_CUDA(cudaMemsetAsync(p.work, 0, sizeof(int), s));   // first pass: cleared with the status block
   kern<<<min(p.n_items, sm_count()), kBwdThreads, smem, s>>>(p);
   FMB_LAUNCH_CHECK("bwd_main_tc_kernel");
   return FMB_OK;
