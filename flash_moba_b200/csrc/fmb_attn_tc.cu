@@ -617,7 +617,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
         umma_gemm<kTcM / 16>(tdV, p_mn, hi, 128, 512, do_mn, hi, 128, 512, idesc_kv, acc);
         umma_commit(&bar_dv);        // dO is free once this completes: the dO loader's signal
         FMB_TICK_AT(35, 256);
-#if FMB_BWD_S_EARLY
+#if FMB_BWD_S_EARLY == 1
         if (more) {                  // S(i+1): its columns are free since P_ready(i); runs under the dS phase
           if (!(ok = mbar_wait(&bar_fullq[(i + 1) & 1], ((i + 1) >> 1) & 1, p.status, 6))) break;
           tc_fence_after_sync();
@@ -631,12 +631,19 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
         // dQ partial = dS.K : M = rows, N = d, K = keys
         umma_gemm<C / 16>(tdQ, ds_km, hi, 2, kQB, k_mn, hi, 128, 512, idesc_dq, 0);
         umma_commit(&bar_dq);
+#if FMB_BWD_S_EARLY == 2
+        if (more) {                  // S(i+1) between dQ(i) and dK(i): the next tile's P phase can start sooner
+          if (!(ok = mbar_wait(&bar_fullq[(i + 1) & 1], ((i + 1) >> 1) & 1, p.status, 6))) break;
+          tc_fence_after_sync();
+          issue_s(i + 1);
+        }
+#endif
         // dK += dS^T.Q
         umma_gemm<kTcM / 16>(tdK, ds_mn, hi, 128, 512, q_mn + (i & 1) * kQBuf, hi, 128, 512, idesc_kv, acc);
         umma_commit(&bar_dk[i & 1]); // this Q buffer is free once it completes: the Q loader's signal
         FMB_TICK_AT(37, 256);
         if (!more) { ++i; break; }
-#if !FMB_BWD_S_EARLY
+#if FMB_BWD_S_EARLY == 0
         if (!(ok = mbar_wait(&bar_fullq[(i + 1) & 1], ((i + 1) >> 1) & 1, p.status, 6))) break;
         tc_fence_after_sync();
         issue_s(i + 1);              // S's columns are free since P_ready(i)

@@ -228,29 +228,6 @@ __device__ __forceinline__ void stage_tile_sw128(unsigned char* tile, uint32_t b
   }
 }
 
-// Gather of a 128-row tile by a 128-thread CTA, split in two so that the global loads can
-// be in flight while the CTA waits on something else: gather_load() issues NCHUNK
-// independent 16-byte loads per thread into registers (row ids from sRow, -1 = zero fill),
-// gather_store() writes them to the swizzled tile.
-template <typename T, int NCHUNK>
-__device__ __forceinline__ void gather_load(uint4 (&u)[NCHUNK], const T* base, int64_t row_stride,
-                                            const int* sRow) {
-  const int j = threadIdx.x % NCHUNK, rb = threadIdx.x / NCHUNK;
-#pragma unroll
-  for (int i = 0; i < NCHUNK; ++i) {
-    const int src = sRow[rb + (128 / NCHUNK) * i];
-    u[i] = make_uint4(0, 0, 0, 0);
-    if (src >= 0) u[i] = ldg_nc_16(base + (int64_t)src * row_stride + j * 8);
-  }
-}
-template <int NCHUNK>
-__device__ __forceinline__ void gather_store(const uint4 (&u)[NCHUNK], unsigned char* tile, uint32_t block_stride) {
-  const int j = threadIdx.x % NCHUNK, rb = threadIdx.x / NCHUNK;
-#pragma unroll
-  for (int i = 0; i < NCHUNK; ++i)
-    *reinterpret_cast<uint4*>(tile + sw128_offset(rb + (128 / NCHUNK) * i, j, block_stride)) = u[i];
-}
-
 // ---- cp.async (16-byte global -> shared copies that bypass registers) ------------------
 // Measured on B200: a 128-thread group gathers random 256-byte rows about four times faster
 // with these than with loads into registers (whose number in flight per warp is small).
@@ -311,64 +288,6 @@ __device__ __forceinline__ void bulk_store(void* gdst, const void* ssrc, uint32_
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-
-// rows x NCHUNK 16-byte chunks of a dense (row_stride) matrix into a swizzled tile, with all
-// of a thread's loads in flight at once.  nrows * NCHUNK must be a multiple of 128 * PER.
-template <typename T, int NCHUNK, int NROWS>
-__device__ __forceinline__ void stage_dense_sw128(unsigned char* tile, uint32_t block_stride, const T* base,
-                                                  int64_t row_stride, int rows_valid) {
-  constexpr int PER = NROWS * NCHUNK / 128;
-  const int j = threadIdx.x % NCHUNK, rb = threadIdx.x / NCHUNK;
-  uint4 u[PER];
-#pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    const int r = rb + (128 / NCHUNK) * i;
-    u[i] = make_uint4(0, 0, 0, 0);
-    if (r < rows_valid) u[i] = ldg_nc_16(base + (int64_t)r * row_stride + j * 8);
-  }
-#pragma unroll
-  for (int i = 0; i < PER; ++i)
-    *reinterpret_cast<uint4*>(tile + sw128_offset(rb + (128 / NCHUNK) * i, j, block_stride)) = u[i];
-}
-
-// The same three helpers for kernels whose 128-thread groups have different roles: `t` is the
-// thread's index inside its group (0..127).
-template <typename T, int NCHUNK>
-__device__ __forceinline__ void gather_load_t(int t, uint4 (&u)[NCHUNK], const T* base, int64_t row_stride,
-                                              const int* rows) {
-  const int j = t % NCHUNK, rb = t / NCHUNK;
-#pragma unroll
-  for (int i = 0; i < NCHUNK; ++i) {
-    const int src = rows[rb + (128 / NCHUNK) * i];
-    u[i] = make_uint4(0, 0, 0, 0);
-    if (src >= 0) u[i] = ldg_nc_16(base + (int64_t)src * row_stride + j * 8);
-  }
-}
-template <int NCHUNK>
-__device__ __forceinline__ void gather_store_t(int t, const uint4 (&u)[NCHUNK], unsigned char* tile,
-                                               uint32_t block_stride) {
-  const int j = t % NCHUNK, rb = t / NCHUNK;
-#pragma unroll
-  for (int i = 0; i < NCHUNK; ++i)
-    *reinterpret_cast<uint4*>(tile + sw128_offset(rb + (128 / NCHUNK) * i, j, block_stride)) = u[i];
-}
-template <typename T, int NCHUNK, int NROWS>
-__device__ __forceinline__ void stage_dense_sw128_t(int t, unsigned char* tile, uint32_t block_stride, const T* base,
-                                                    int64_t row_stride, int rows_valid) {
-  constexpr int PER = NROWS * NCHUNK / 128;
-  const int j = t % NCHUNK, rb = t / NCHUNK;
-  uint4 u[PER];
-#pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    const int r = rb + (128 / NCHUNK) * i;
-    u[i] = make_uint4(0, 0, 0, 0);
-    if (r < rows_valid) u[i] = ldg_nc_16(base + (int64_t)r * row_stride + j * 8);
-  }
-#pragma unroll
-  for (int i = 0; i < PER; ++i)
-    *reinterpret_cast<uint4*>(tile + sw128_offset(rb + (128 / NCHUNK) * i, j, block_stride)) = u[i];
-}
-
 
 template <typename T> struct FmtOf;
 template <> struct FmtOf<__nv_bfloat16> { static constexpr int v = 1; };
