@@ -184,7 +184,9 @@ def make_c1(utils, topk_mod, out):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to a checkout of mit-han-lab/flash-moba>")
+    ref_root = sys.argv[1]
     utils, topk_mod, epi, pool = _load_reference(ref_root)
     for name, fn, args in (("pool", make_pool, (pool,)), ("gate", make_gate, (topk_mod, epi)),
                            ("attn", make_attn, (utils,)), ("c1", make_c1, (utils, topk_mod))):

@@ -333,7 +333,7 @@ def _random_mask(lens_q, lens_k, H, chunk, causal, picks, seed=1):
 @pytest.mark.parametrize("chunk,d", [(256, 128), (192, 128), (256, 64), (320, 64)])
 def test_attention_chunks_wider_than_a_key_block(chunk, d, engine):
     """Chunks of 192..320 keys are processed as several 64- or 128-key blocks per column
-    (BASELINE configuration 5 uses chunk 256)."""
+    (the 512K-token benchmark configuration uses chunk 256)."""
     torch.manual_seed(0)
     lens, H, Hk = [700, 301], 4, 2
     T = sum(lens)
@@ -394,7 +394,7 @@ def test_attention_head_dims_padded_to_64_or_128(d):
 
 # ----------------------------------------------------------------------------- whole path
 def test_c1_end_to_end():
-    """BASELINE configuration 1 through the public API: top-k indices against the reference's
+    """The reference's CPU-runnable configuration (sequences of 1024 and 2048 tokens, 8 heads, d 64, chunk 128, top-k 4) through the public API: top-k indices against the reference's
     golden lists (mismatch < 0.5 %), forward output against the oracle run on the kernel's
     own pattern (so a flipped near-tie does not pose as numeric error)."""
     import flash_moba_b200 as F
