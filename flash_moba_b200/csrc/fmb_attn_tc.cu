@@ -1082,13 +1082,6 @@ static TcParams make_tc_params(const AttnArgs& a, const AttnWorkspace& w, const 
   return p;
 }
 
-static int sm_count() {
-  int dev = 0, n = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-    n = 148;
-  return n;
-}
-
 template <typename T, int C, int D>
 static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   TcParams p = make_tc_params(a, w, ps);
