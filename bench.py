@@ -38,6 +38,7 @@ WORKLOADS = {
     "small": ([4096], 8, 8, 128, 128, 8, True, 1.0),
     "mid": ([16384], 16, 16, 128, 128, 8, True, 1.0),
     "64k_h4": ([65536], 4, 4, 128, 128, 8, True, 1.0),      # one rank's share of "64k" at 8 GPUs
+    "c5s": ([524288], 4, 4, 128, 256, 16, True, 0.5),       # configuration 5 (512K tokens, chunk 256, top-k 16) with 4 of its 32 heads
     "c4s": ([8192, 16384, 4096, 12288, 2048, 24576], 32, 8, 128, 64, 16, True, 1.0),   # configuration 4 at a sixth of its size
 }
 
