@@ -568,6 +568,96 @@ __global__ void __launch_bounds__(256) bwd_combine_group_kernel(const T* __restr
     bwd_combine_group_body<T, G, EPL>(vb, part_dq, c, dq, rs, hs, min_n, overflow);
 }
 
+// ------------------------------------------------------------------ wide combine (rows of <= 32 partials)
+// A warp per (token, head) row.  Lane j fetches the position and log-sum-exp of the row's j-th
+// partial and the warp ranks the positions, as above.  A partial row is D/8 16-byte chunks, so D/8
+// lanes fetch one partial row and the warp fetches 32/(D/8) partial rows per step, eight steps in
+// flight; lane group s accumulates the partials of rank s, s + 32/(D/8), ... in ascending order and
+// the groups are added at the end in a fixed order.  FWD weights the partials by
+// exp(lse_j - max lse) and writes the row's log-sum-exp; the backward form is a plain sum.
+template <typename T, int D, bool FWD>
+__device__ __forceinline__ void combine_wide_body(int64_t vblock, const T* __restrict__ part,
+                                                  const float* __restrict__ part_lse, const CombineParams& c,
+                                                  T* out, int64_t rs, int64_t hs, float* lse, int min_n,
+                                                  int* overflow) {
+  constexpr int LPR = D / 8;                  // lanes per partial row
+  constexpr int PPS = 32 / LPR;               // partial rows per step
+  constexpr int B = 8;                        // steps in flight
+  static_assert(D == 64 || D == 128 || D == 256, "a partial row is 8, 16 or 32 chunks");
+  const int lane = threadIdx.x & 31, sub = lane / LPR, ch = lane % LPR;
+  const GroupRow g = group_row<32>(vblock, c, min_n, overflow);
+  if (!g.mine) return;                        // the same for every lane of the warp
+  float l = -CUDART_INF_F;
+  if (FWD && g.valid) l = part_lse[g.pos];
+  int rank = 0;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) rank += (__shfl_sync(0xffffffffu, g.pos, i) < g.pos) ? 1 : 0;
+  int inv = 0;                                // the lane that holds the partial of rank `lane`
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int ri = __shfl_sync(0xffffffffu, rank, i);
+    if (i < g.n && ri == lane) inv = i;
+  }
+  float m = 0.f, w = 1.f, ssum = 1.f;
+  if (FWD) {
+    m = l;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    w = (g.valid && m > -CUDART_INF_F) ? __expf(l - m) : 0.f;
+    ssum = w;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
+  }
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  for (int r0 = 0; r0 < g.n; r0 += PPS * B) {
+    uint4 x[B];
+    float wk[B];
+#pragma unroll
+    for (int k = 0; k < B; ++k) {
+      const int want = r0 + k * PPS + sub;
+      const bool hit = want < g.n;
+      const int src = __shfl_sync(0xffffffffu, inv, want & 31);
+      const uint32_t pk = __shfl_sync(0xffffffffu, g.pos, src);
+      const uint32_t sk = __shfl_sync(0xffffffffu, g.slot, src);
+      const float ws = __shfl_sync(0xffffffffu, w, src);
+      wk[k] = hit ? ws : 0.f;
+      x[k] = hit ? *reinterpret_cast<const uint4*>(part + (int64_t)pk * D + part_col(sk, ch * 8, 8))
+                 : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int k = 0; k < B; ++k) {
+      float f[8];
+      unpack8<T>(x[k], f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = FWD ? fmaf(wk[k], f[e], acc[e]) : acc[e] + f[e];   // x is 0 past the row's end
+    }
+  }
+#pragma unroll
+  for (int o = LPR; o < 32; o <<= 1) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
+  }
+  const int h = c.h0 + g.hr;
+  if (sub == 0) {
+    const float inv_s = FWD ? (ssum > 0.f ? 1.f / ssum : 0.f) : 1.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] *= inv_s;
+    *reinterpret_cast<uint4*>(out + g.t * rs + (int64_t)h * hs + ch * 8) = pack8<T>(acc);
+  }
+  if (FWD && lane == 0) lse[(int64_t)h * c.total_q + g.t] = ssum > 0.f ? m + logf(ssum) : CUDART_INF_F;
+}
+template <typename T, int D, bool FWD>
+__global__ void __launch_bounds__(256) combine_wide_kernel(const T* __restrict__ part,
+                                                           const float* __restrict__ part_lse, CombineParams c,
+                                                           T* out, int64_t rs, int64_t hs, float* lse, int min_n,
+                                                           const int* only_if, int* overflow, int64_t nvb) {
+  if (only_if && *only_if == 0) return;
+  for (int64_t vb = blockIdx.x; vb < nvb; vb += gridDim.x)
+    combine_wide_body<T, D, FWD>(vb, part, part_lse, c, out, rs, hs, lse, min_n, overflow);
+}
+
 // D[h, t] = sum_d dO.O.  LPR lanes per row, each with one 16-byte load of dO and of O (LPR = d / 8
 // when that is a power of two); LPR = 0 selects the generic warp-per-row form.
 template <typename T, int LPR>
@@ -618,8 +708,9 @@ __global__ void __launch_bounds__(256) dot_do_o_kernel(const T* __restrict__ dou
 
 static int64_t warp_grid(int64_t warps) { return ceil_div64(warps, 8); }
 
-// Cascade: G = 8 (rows of <= 8 partials), 16, then the generic kernel; each later stage runs only
-// the rows the earlier ones left and exits at once if there were none.
+// Cascade: lane groups of 8 (rows of <= 8 partials), the warp-per-row wide kernel (<= 32), then the
+// generic kernel; each later stage runs only the rows the earlier ones left and exits at once if
+// there were none.
 static int64_t group_grid(int64_t rows, int G) { return ceil_div64(ceil_div64(rows, 32 / G), 8); }
 int sm_count() {
   int dev = 0, n = 0;
@@ -659,14 +750,14 @@ static int fwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const
   int* ovf = w.status + 1;   // words 1..3 of the status block, zeroed with it
   const T* po = (const T*)w.part_o;
   T* out = (T*)a.o;
-  const int64_t nb8 = group_grid(rows, 8), nb16 = group_grid(rows, 16), nbw = warp_grid(rows);
+  const int64_t nb8 = group_grid(rows, 8), nbw = warp_grid(rows);
   fwd_combine_group_kernel<T, 8, D / 8><<<first_grid(nb8), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, 0,
                                                                       nullptr, ovf, nb8);
   FMB_LAUNCH_CHECK("fwd_combine_group_kernel<8>");
-  fwd_combine_group_kernel<T, 16, D / 16><<<late_grid(nb16), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs,
-                                                                         a.lse, 9, ovf, ovf + 1, nb16);
-  FMB_LAUNCH_CHECK("fwd_combine_group_kernel<16>");
-  fwd_combine_kernel<T><<<late_grid(nbw), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, ovf + 1, 17, nbw);
+  combine_wide_kernel<T, D, true><<<late_grid(nbw), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, 9, ovf,
+                                                                 ovf + 1, nbw);
+  FMB_LAUNCH_CHECK("combine_wide_kernel<fwd>");
+  fwd_combine_kernel<T><<<late_grid(nbw), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, ovf + 1, 33, nbw);
   FMB_LAUNCH_CHECK("fwd_combine_kernel");
   return FMB_OK;
 }
@@ -674,6 +765,7 @@ static int fwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const
 template <typename T>
 static int fwd_combine_any(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
 #ifndef FMB_COMBINE_GENERIC
+  if (a.d == 64) return fwd_combine_dispatch<T, 64>(a, w, ps, s);
   if (a.d == 128) return fwd_combine_dispatch<T, 128>(a, w, ps, s);
   if (a.d == 256) return fwd_combine_dispatch<T, 256>(a, w, ps, s);
 #endif
@@ -696,19 +788,20 @@ static int bwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const
   int* ovf = w.status + 1;
   const T* pd = (const T*)w.part_o;
   T* dq = (T*)a.dq;
-  const int64_t nb8 = group_grid(rows, 8), nb16 = group_grid(rows, 16), nbw = warp_grid(rows);
+  const int64_t nb8 = group_grid(rows, 8), nbw = warp_grid(rows);
   bwd_combine_group_kernel<T, 8, D / 8><<<first_grid(nb8), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 0, nullptr, ovf, nb8);
   FMB_LAUNCH_CHECK("bwd_combine_group_kernel<8>");
-  bwd_combine_group_kernel<T, 16, D / 16><<<late_grid(nb16), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 9, ovf, ovf + 1,
-                                                                         nb16);
-  FMB_LAUNCH_CHECK("bwd_combine_group_kernel<16>");
-  bwd_combine_kernel<T><<<late_grid(nbw), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, ovf + 1, 17, nbw);
+  combine_wide_kernel<T, D, false><<<late_grid(nbw), 256, 0, s>>>(pd, nullptr, c, dq, a.dq_rs, a.dq_hs, nullptr, 9, ovf,
+                                                                  ovf + 1, nbw);
+  FMB_LAUNCH_CHECK("combine_wide_kernel<bwd>");
+  bwd_combine_kernel<T><<<late_grid(nbw), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, ovf + 1, 33, nbw);
   FMB_LAUNCH_CHECK("bwd_combine_kernel");
   return FMB_OK;
 }
 
 template <typename T>
 static int bwd_combine_any(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
+  if (a.d == 64) return bwd_combine_dispatch<T, 64>(a, w, ps, s);
   if (a.d == 128) return bwd_combine_dispatch<T, 128>(a, w, ps, s);
   if (a.d == 256) return bwd_combine_dispatch<T, 256>(a, w, ps, s);
   const int64_t rows = a.total_q * ps.nh;

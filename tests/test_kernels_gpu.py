@@ -329,6 +329,31 @@ def _random_mask(lens_q, lens_k, H, chunk, causal, picks, seed=1):
     return mask
 
 
+@pytest.mark.parametrize("chunk,d,max_picks", [(64, 64, 31), (64, 128, 31), (128, 128, 20), (256, 128, 15), (256, 64, 15)])
+def test_attention_rows_with_9_to_32_partials(chunk, d, max_picks):
+    """Rows with every count of selected chunks from 1 to max_picks + 1 next to each other: the merge
+    of a row's partials goes through the 8-lane stage, the warp-per-row stage (9..32 partials; a
+    256-key chunk gives two partials per selected chunk) or the generic stage, row by row."""
+    torch.manual_seed(0)
+    lens, H, Hk = [chunk * (max_picks + 3) + 17], 2, 1
+    T = sum(lens)
+    q = torch.randn(T, H, d).bfloat16()
+    k = torch.randn(T, Hk, d).bfloat16()
+    v = torch.randn(T, Hk, d).bfloat16()
+    do = torch.randn(T, H, d).bfloat16()
+    ncol = (T + chunk - 1) // chunk
+    mask = torch.zeros(1, H, T, ncol, dtype=torch.bool)
+    g = torch.Generator().manual_seed(5)
+    for h in range(H):
+        for r in range(T):
+            own = r // chunk
+            picks = int(torch.randint(0, max_picks + 1, (1,), generator=g))
+            if own > 0 and picks > 0:
+                mask[0, h, r, torch.randperm(own, generator=g)[:picks]] = True
+            mask[0, h, r, own] = True
+    _attn_check(q, k, v, do, cu_of(lens), cu_of(lens), mask, chunk, True, 1)
+
+
 @pytest.mark.parametrize("engine", [0, 1])
 @pytest.mark.parametrize("chunk,d", [(256, 128), (192, 128), (256, 64), (320, 64)])
 def test_attention_chunks_wider_than_a_key_block(chunk, d, engine):
