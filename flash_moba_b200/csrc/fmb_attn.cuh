@@ -77,17 +77,22 @@ __device__ __forceinline__ ColRef column_of(const PassParams& r, int b, int h, i
 }
 
 // A key block that starts beyond the sequence's keys contributes nothing: its dQ partials are
-// zero (the combine still reads them).  Called by a whole CTA of the backward kernels.
+// zero (the combine still reads them).  Called by a whole CTA of the backward kernels (or, _by, by `nthreads` threads numbered `tid`).
 template <typename T>
-__device__ __forceinline__ void zero_dq_partials(const PassParams& r, T* part_dq, int64_t plane, int b, int hk,
-                                                 int group, int c, int d) {
+__device__ __forceinline__ void zero_dq_partials_by(const PassParams& r, T* part_dq, int64_t plane, int b, int hk,
+                                                    int group, int c, int d, int tid, int nthreads) {
   for (int hg = 0; hg < group; ++hg) {
     const ColRef col = column_of(r, b, hk * group + hg, c);
     if (col.nnz <= 0) continue;
     uint4* dst = reinterpret_cast<uint4*>(part_dq + (plane + col.slot) * d);
     const int64_t n16 = (int64_t)col.nnz * d * (int64_t)sizeof(T) / 16;
-    for (int64_t i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+    for (int64_t i = tid; i < n16; i += nthreads) dst[i] = make_uint4(0, 0, 0, 0);
   }
+}
+template <typename T>
+__device__ __forceinline__ void zero_dq_partials(const PassParams& r, T* part_dq, int64_t plane, int b, int hk,
+                                                 int group, int c, int d) {
+  zero_dq_partials_by<T>(r, part_dq, plane, b, hk, group, c, d, threadIdx.x, blockDim.x);
 }
 
 AttnWorkspace carve_attn_workspace(void* base, size_t bytes_available, const AttnArgs& a, size_t part_elem_bytes,

@@ -23,9 +23,12 @@ constexpr int kTcM = 128;   // gathered rows per tile = TMEM lanes
 // deltas per phase into 64-bit counters that start 64 bytes into the workspace status block.
 #ifdef FMB_TC_TIMING
 #define FMB_T0() long long t_prev_ = clock64()
+#ifndef FMB_TICK_TID
+#define FMB_TICK_TID 0
+#endif
 #define FMB_TICK(slot)                                                                          \
   do {                                                                                          \
-    if (threadIdx.x == 0) {                                                                     \
+    if (threadIdx.x == FMB_TICK_TID) {                                                                     \
       const long long t_now_ = clock64();                                                       \
       atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (slot),                   \
                 (unsigned long long)(t_now_ - t_prev_));                                        \
@@ -439,7 +442,8 @@ constexpr int kBwdCompute = 256;
 #endif
 constexpr int kBwdQLoaders = 32 * FMB_BWD_QW;
 constexpr int kBwdOLoaders = 32 * FMB_BWD_OW;
-constexpr int kBwdThreads = kBwdCompute + 32 + kBwdQLoaders + kBwdOLoaders;
+constexpr int kBwdScoutWarp = (kBwdCompute + 32 + kBwdQLoaders + kBwdOLoaders) / 32;   // K/V loader and item scout
+constexpr int kBwdThreads = kBwdCompute + 32 + kBwdQLoaders + kBwdOLoaders + 32;
 
 struct BwdTile {
   int hg;        // head within the group
@@ -468,6 +472,33 @@ __device__ __forceinline__ bool bwd_next_tile(const PassParams& ps, int b, int h
   return bwd_seek_head(ps, b, hk, group, c, it);
 }
 
+// One work item's geometry, derived by every role from the item number alone
+struct BwdItem {
+  int c, hk, b, q0, len_q, k0, len_k, key0, keys_valid, shift;
+  int64_t plane;
+  bool skip;       // the key block starts past the sequence's last key
+};
+__device__ __forceinline__ void bwd_decode_item(const TcParams& p, int item, int group, BwdItem& I) {
+  int bx, rem;
+  decode_item(p, item, bx, rem);
+  const int sb = bx % p.ps.nsub;
+  I.c = bx / p.ps.nsub;
+  I.hk = p.ps.h0 / group + rem % p.items_y;
+  I.b = rem / p.items_y;
+  I.plane = (int64_t)sb * p.ps.cap;
+  I.q0 = p.cu_q[I.b];
+  I.len_q = p.cu_q[I.b + 1] - I.q0;
+  I.k0 = p.cu_k[I.b];
+  I.len_k = p.cu_k[I.b + 1] - I.k0;
+  // The kernel always works on 128 key lanes; with 64-key blocks (chunks that are not a multiple of
+  // 128) the upper 64 lanes are zero-filled and masked: twice the tensor work per key, still several
+  // times faster than the CUDA-core backward, and the tensor pipe is mostly idle anyway.
+  I.key0 = I.c * p.ps.chunk + sb * p.ps.kb;
+  I.skip = I.key0 >= I.len_k;
+  I.keys_valid = min(p.ps.kb, I.len_k - I.key0);
+  I.shift = I.len_k - I.len_q;
+}
+
 template <typename T, int C, int D>
 __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   static_assert(C == 128, "tensor-core backward keeps one key per TMEM lane");
@@ -476,13 +507,25 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   constexpr uint32_t kQTile = kTcM * D * 2;
   constexpr int NCOLS = 512;
   constexpr int DH = D / 2;                       // head-dim columns per thread in the epilogues
-  extern __shared__ unsigned char smem_raw[];
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ uint64_t bar_s, bar_p, bar_dq, bar_dv, bar_fin, bar_fulldo, bar_dk[2], bar_fullq[2];
-  __shared__ uint64_t bar_pready, bar_dsready, bar_dqfree, bar_kv;
+  __shared__ uint64_t bar_pready, bar_dsready, bar_dqfree, bar_kv, bar_item[4];
+  __shared__ float sLse[kTcM], sDsum[kTcM];        // log-sum-exp and dO.O of the rows of the dO tile
+  __shared__ int s_tile[4];                       // that tile's valid rows, first slot (64 bit), "another tile follows"
   __shared__ uint32_t tmem_base_s;
+  __shared__ uint64_t bar_info[4];
+  __shared__ int s_items[4];                      // ring of work items, fetched two ahead
+  __shared__ int s_info[4][20];                   // ring of decoded work items (geometry, first tile)
+  __shared__ int s_prev[4];                       // key row, kv head, valid keys of the item whose dK / dV are in TMEM
   __shared__ int sRowQ[kTcM], sRowO[kTcM];        // row ids of the tile a loader group is fetching
 
-  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  // the swizzled tiles need a 1024-byte aligned base; static and dynamic shared memory together use
+  // the whole 227 KB, so there is no room for padding: checked here, reported through the status word
+  unsigned char* smem = smem_raw;
+  if ((smem_u32(smem_raw) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, 9);
+    return;
+  }
   unsigned char* sK = smem;                       // [C][D]
   unsigned char* sV = sK + C * D * 2;             // [C][D]
   unsigned char* sQ = sV + C * D * 2;             // 2 x [128][D]
@@ -490,7 +533,6 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   unsigned char* sP = sdO + kQTile;               // [128][C]
   unsigned char* sdS = sP + kTcM * C * 2;         // [128][C]
 
-  __shared__ int s_item;
   const int group = p.heads / p.heads_k;
   const float scale_log2 = p.scale * kLog2eTc;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -499,6 +541,22 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
 
   FMB_T0();
   if (warp == 0) tmem_alloc(&tmem_base_s, NCOLS);
+  if (tid == 0) {
+    mbar_init(&bar_s, 1); mbar_init(&bar_p, 1); mbar_init(&bar_dq, 1); mbar_init(&bar_dv, 1); mbar_init(&bar_fin, 1);
+    mbar_init(&bar_dk[0], 1); mbar_init(&bar_dk[1], 1);
+    mbar_init(&bar_fullq[0], kBwdQLoaders / 32); mbar_init(&bar_fullq[1], kBwdQLoaders / 32);
+    mbar_init(&bar_fulldo, kBwdOLoaders / 32);   // one arrival per loader warp
+    mbar_init(&bar_pready, kBwdCompute / 32); mbar_init(&bar_dsready, kBwdCompute / 32);
+    mbar_init(&bar_dqfree, kBwdCompute / 32);   // one arrival per compute warp
+    mbar_init(&bar_kv, 1);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { mbar_init(&bar_item[k], 1); mbar_init(&bar_info[k], 1); }
+    mbar_fence_init();
+    s_items[0] = atomicAdd(p.work, 1);
+    s_items[1] = atomicAdd(p.work, 1);
+    mbar_arrive(&bar_item[0]);
+    mbar_arrive(&bar_item[1]);
+  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -506,74 +564,43 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   const uint32_t tS = tmem_base, tdP = tmem_base + C, tdV = tmem_base + 2 * C, tdK = tmem_base + 2 * C + D;
   const uint32_t tdQ = tdP;
 
-  // persistent CTA: work items (key block, kv head, sequence) from a counter; the barriers are
-  // invalidated and initialised again for every item, so each item starts in phase 0
-  bool first_item = true;
-#pragma unroll 1
-  for (;;) {
-  if (tid == 0) {
-    s_item = atomicAdd(p.work, 1);
-    if (!first_item) {
-      mbar_inval(&bar_s); mbar_inval(&bar_p); mbar_inval(&bar_dq); mbar_inval(&bar_dv); mbar_inval(&bar_fin);
-      mbar_inval(&bar_dk[0]); mbar_inval(&bar_dk[1]); mbar_inval(&bar_fullq[0]); mbar_inval(&bar_fullq[1]);
-      mbar_inval(&bar_fulldo); mbar_inval(&bar_pready); mbar_inval(&bar_dsready); mbar_inval(&bar_dqfree);
-      mbar_inval(&bar_kv);
+  // The CTA is persistent and its roles run through the work items as ONE stream of tiles: no
+  // role waits for another at an item boundary except through the data it needs.  Every barrier
+  // is initialised once; phases are counted with stream-wide counters (n: items, nk: items with
+  // keys, g / m: tiles) that every role advances in the same way.
+  // n-th item of this CTA (p.n_items or more: the counter has run out); read by the scout warp only
+  auto get_item = [&](uint32_t n, int& item) -> bool {
+    if (!mbar_wait(&bar_item[n & 3], (n >> 2) & 1, p.status, 7)) {
+      item = p.n_items;
+      return false;
     }
-    mbar_init(&bar_s, 1); mbar_init(&bar_p, 1); mbar_init(&bar_dq, 1); mbar_init(&bar_dv, 1); mbar_init(&bar_fin, 1);
-    mbar_init(&bar_dk[0], 1); mbar_init(&bar_dk[1], 1);
-    mbar_init(&bar_fullq[0], kBwdQLoaders / 32); mbar_init(&bar_fullq[1], kBwdQLoaders / 32);
-    mbar_init(&bar_fulldo, kBwdOLoaders / 32);   // one arrival per loader warp
-    mbar_init(&bar_pready, kBwdCompute / 32); mbar_init(&bar_dsready, kBwdCompute / 32);
-    mbar_init(&bar_dqfree, kBwdCompute / 32);   // one arrival per compute warp
-    mbar_init(&bar_kv, kBwdCompute / 32);
-    mbar_fence_init();
-  }
-  __syncthreads();
-  first_item = false;
-  const int item = s_item;
-  if (item >= p.n_items) break;
-  int bx, rem;
-  decode_item(p, item, bx, rem);
-  const int c = bx / p.ps.nsub, sb = bx % p.ps.nsub, hk = p.ps.h0 / group + rem % p.items_y, b = rem / p.items_y;
-  const int64_t plane = (int64_t)sb * p.ps.cap;
-  const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
-  const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
-  // The kernel always works on 128 key lanes; with 64-key blocks (chunks that are not a multiple of
-  // 128) the upper 64 lanes are zero-filled and masked: twice the tensor work per key, still several
-  // times faster than the CUDA-core backward, and the tensor pipe is mostly idle anyway.
-  const int key0 = c * p.ps.chunk + sb * p.ps.kb;
-  if (key0 >= len_k) {     // CTA-uniform
-    zero_dq_partials<T>(p.ps, static_cast<T*>(p.part_o), plane, b, hk, group, c, D);
-    __syncthreads();
-    continue;
-  }
-  const int keys_valid = min(p.ps.kb, len_k - key0);
-  const int shift = len_k - len_q;
-
-  // ---- the item's tile sequence
-  auto seek_head = [&](BwdTile& it) { return bwd_seek_head(p.ps, b, hk, group, c, it); };
-  auto next_tile = [&](BwdTile& it) { return bwd_next_tile(p.ps, b, hk, group, c, it); };
+    item = *reinterpret_cast<volatile int*>(&s_items[n & 3]);
+    return true;
+  };
+  // The scout warp decodes every item ahead of the other roles (the geometry and the first tile
+  // cost a chain of three dependent global loads) and publishes it in s_info.
+  // state: 0 = the stream has ended, 1 = item with tiles or keys, 2 = key block past the sequence's end
+  auto read_info = [&](uint32_t n, BwdItem& I, BwdTile& it, bool& have) -> int {
+    if (!mbar_wait(&bar_info[n & 3], (n >> 2) & 1, p.status, 7)) return -1;
+    const volatile int* f = s_info[n & 3];
+    const int state = f[0];
+    I.c = f[1]; I.hk = f[2]; I.b = f[3]; I.q0 = f[4]; I.len_q = f[5]; I.k0 = f[6]; I.len_k = f[7];
+    I.key0 = f[8]; I.keys_valid = f[9]; I.shift = f[10]; I.plane = (int64_t)f[11] * p.ps.cap; I.skip = state == 2;
+    have = f[12] != 0;
+    it.hg = f[13]; it.t0 = 0; it.nnz = f[14];
+    it.off = (int64_t)(((uint64_t)(uint32_t)f[16] << 32) | (uint32_t)f[15]);
+    it.slot = (int64_t)(((uint64_t)(uint32_t)f[18] << 32) | (uint32_t)f[17]);
+    return state;
+  };
+  // ---- an item's tile sequence
+  auto seek_head = [&](const BwdItem& I, BwdTile& it) { return bwd_seek_head(p.ps, I.b, I.hk, group, I.c, it); };
+  auto next_tile = [&](const BwdItem& I, BwdTile& it) { return bwd_next_tile(p.ps, I.b, I.hk, group, I.c, it); };
   // sequence-local query row of entry i of the tile (-1 = none).  row_raw() only issues the load;
   // row_checked() is applied where the value is used, so that a prefetch does not wait for it.
   auto row_raw = [&](const BwdTile& it, int i) {
-    return (it.t0 + i < it.nnz) ? p.ps.indices[it.off + it.t0 + i] : -1;
+    return (it.t0 + i < it.nnz) ? ldg_s32_here(p.ps.indices + it.off + it.t0 + i) : -1;
   };
-  auto row_checked = [&](int r) { return (r < 0 || r >= len_q) ? -1 : r; };
-
-  if (warp < 8) {                  // K and V tiles; the loaders fetch the first row tiles meanwhile
-    const T* kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + key0) * p.k_rs + (int64_t)hk * p.k_hs;
-    const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
-    if (hf == 0) dense_cp_async<T, D / 8, C, kTcM>(lt, sK, kKBlock, kbase, p.k_rs, keys_valid);
-    else dense_cp_async<T, D / 8, C, kTcM>(lt, sV, kKBlock, vbase, p.v_rs, keys_valid);
-    cp_async_wait_all();
-    fence_async_smem();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&bar_kv);
-  }
-  FMB_TICK(16);   // item hand-out, K/V staging
-
-  BwdTile it{0, 0, 0, 0, 0};
-  bool have = seek_head(it);
+  auto row_checked = [&](const BwdItem& I, int r) { return (r < 0 || r >= I.len_q) ? -1 : r; };
 
   if (warp == 8) {
     // =============================================================== MMA issuer
@@ -591,71 +618,132 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
       const uint32_t ds_km = desc_lo_sw128(smem_u32(sdS), 16), ds_mn = desc_lo_sw128(smem_u32(sdS), kQBlock);
       constexpr uint32_t kQBuf = kQTile >> 4;        // second Q buffer, in descriptor address units
       constexpr uint32_t kQB = kQBlock >> 4, kKB = kKBlock >> 4;
-      auto issue_s = [&](int i) {      // S(i) = Q(i).K^T
-        umma_gemm<D / 16>(tS, q_km + (i & 1) * kQBuf, hi, 2, kQB, k_km, hi, 2, kKB, idesc_s, 0);
+      uint32_t g = 0, nk = 0;          // tiles and items with keys so far
+      bool ok = true;
+      // S(g) = Q(g).K^T once Q(g) has landed; S's columns are free since P_ready(g-1)
+      auto issue_s = [&]() {
+        if (!(ok = mbar_wait(&bar_fullq[g & 1], (g >> 1) & 1, p.status, 6))) return;
+        tc_fence_after_sync();
+        umma_gemm<D / 16>(tS, q_km + (g & 1) * kQBuf, hi, 2, kQB, k_km, hi, 2, kKB, idesc_s, 0);
         umma_commit(&bar_s);
       };
-      auto issue_dp = [&]() {          // dP = dO.V^T
+      // dP(g) = dO(g).V^T once dO(g) has landed and dQ(g-1) has been read out of these columns
+      auto issue_dp = [&]() {
+        if (!(ok = mbar_wait(&bar_fulldo, g & 1, p.status, 6))) return;
+        if (g > 0 && !(ok = mbar_wait(&bar_dqfree, (g - 1) & 1, p.status, 6))) return;
+        tc_fence_after_sync();
         umma_gemm<D / 16>(tdP, do_km, hi, 2, kQB, v_km, hi, 2, kKB, idesc_s, 0);
         umma_commit(&bar_p);
       };
-      bool ok = have;
-      if (ok) ok = mbar_wait(&bar_kv, 0, p.status, 6);
-      if (ok) ok = mbar_wait(&bar_fullq[0], 0, p.status, 6);
-      if (ok) { tc_fence_after_sync(); issue_s(0); ok = mbar_wait(&bar_fulldo, 0, p.status, 6); }
-      if (ok) { tc_fence_after_sync(); issue_dp(); }
-      int i = 0;
 #pragma unroll 1
-      for (; ok; ++i) {
-        const bool more = next_tile(it);
-        const uint32_t acc = i > 0 ? 1u : 0u;
-        // dV += P^T.dO : M = keys, N = d, K = the 128 gathered rows
-        FMB_TICK_AT(41, 256);
-        if (!(ok = mbar_wait(&bar_pready, i & 1, p.status, 1))) break;
-        tc_fence_after_sync();
-        FMB_TICK_AT(34, 256);
-        umma_gemm<kTcM / 16>(tdV, p_mn, hi, 128, 512, do_mn, hi, 128, 512, idesc_kv, acc);
-        umma_commit(&bar_dv);        // dO is free once this completes: the dO loader's signal
-        FMB_TICK_AT(35, 256);
-#if FMB_BWD_S_EARLY == 1
-        if (more) {                  // S(i+1): its columns are free since P_ready(i); runs under the dS phase
-          if (!(ok = mbar_wait(&bar_fullq[(i + 1) & 1], ((i + 1) >> 1) & 1, p.status, 6))) break;
-          tc_fence_after_sync();
-          issue_s(i + 1);
+      for (uint32_t n = 0; ok; ++n) {
+        BwdItem I;
+        BwdTile it;
+        bool have;
+        const int state = read_info(n, I, it, have);
+        if (state < 0) ok = false;
+        if (state <= 0) break;
+        if (I.skip) continue;
+        // K and V of this item are in place (the scout warp loads them once every GEMM of the
+        // previous item has completed)
+        FMB_TICK_AT(45, 256);          // item boundary: column data of the next item
+        if (!(ok = mbar_wait(&bar_kv, nk & 1, p.status, 6))) break;
+        FMB_TICK_AT(42, 256);          // waiting for K and V
+        if (have) {
+          issue_s();
+          FMB_TICK_AT(43, 256);        // waiting for the first Q tile
+          if (ok) issue_dp();
+          FMB_TICK_AT(44, 256);        // waiting for the first dO tile
+          uint32_t acc = 0;
+#pragma unroll 1
+          while (ok) {
+            const bool more = next_tile(I, it);
+            // dV += P^T.dO : M = keys, N = d, K = the 128 gathered rows
+            FMB_TICK_AT(41, 256);
+            if (!(ok = mbar_wait(&bar_pready, g & 1, p.status, 1))) break;
+            tc_fence_after_sync();
+            FMB_TICK_AT(34, 256);
+            umma_gemm<kTcM / 16>(tdV, p_mn, hi, 128, 512, do_mn, hi, 128, 512, idesc_kv, acc);
+            umma_commit(&bar_dv);        // dO is free once this completes: the dO loader's signal
+            FMB_TICK_AT(35, 256);
+            if (!(ok = mbar_wait(&bar_dsready, g & 1, p.status, 2))) break;
+            tc_fence_after_sync();
+            FMB_TICK_AT(36, 256);
+            // dQ partial = dS.K : M = rows, N = d, K = keys
+            umma_gemm<C / 16>(tdQ, ds_km, hi, 2, kQB, k_mn, hi, 128, 512, idesc_dq, 0);
+            umma_commit(&bar_dq);
+            // dK += dS^T.Q
+            umma_gemm<kTcM / 16>(tdK, ds_mn, hi, 128, 512, q_mn + (g & 1) * kQBuf, hi, 128, 512, idesc_kv, acc);
+            umma_commit(&bar_dk[g & 1]); // this Q buffer is free once it completes: the Q loader's signal
+            FMB_TICK_AT(37, 256);
+            ++g;
+            acc = 1;
+            if (!more) break;
+            issue_s();
+            FMB_TICK_AT(38, 256);
+#ifdef FMB_TC_TIMING_S
+            mbar_wait(&bar_s, g & 1, p.status, 6);   // timing experiment: how long after its issue does S complete
+            FMB_TICK_AT(46, 256);
+#endif
+            if (ok) issue_dp();
+            FMB_TICK_AT(40, 256);
+          }
         }
-        FMB_TICK_AT(38, 256);
-#endif
-        if (!(ok = mbar_wait(&bar_dsready, i & 1, p.status, 2))) break;
-        tc_fence_after_sync();
-        FMB_TICK_AT(36, 256);
-        // dQ partial = dS.K : M = rows, N = d, K = keys
-        umma_gemm<C / 16>(tdQ, ds_km, hi, 2, kQB, k_mn, hi, 128, 512, idesc_dq, 0);
-        umma_commit(&bar_dq);
-#if FMB_BWD_S_EARLY == 2
-        if (more) {                  // S(i+1) between dQ(i) and dK(i): the next tile's P phase can start sooner
-          if (!(ok = mbar_wait(&bar_fullq[(i + 1) & 1], ((i + 1) >> 1) & 1, p.status, 6))) break;
-          tc_fence_after_sync();
-          issue_s(i + 1);
-        }
-#endif
-        // dK += dS^T.Q
-        umma_gemm<kTcM / 16>(tdK, ds_mn, hi, 128, 512, q_mn + (i & 1) * kQBuf, hi, 128, 512, idesc_kv, acc);
-        umma_commit(&bar_dk[i & 1]); // this Q buffer is free once it completes: the Q loader's signal
-        FMB_TICK_AT(37, 256);
-        if (!more) { ++i; break; }
-#if FMB_BWD_S_EARLY == 0
-        if (!(ok = mbar_wait(&bar_fullq[(i + 1) & 1], ((i + 1) >> 1) & 1, p.status, 6))) break;
-        tc_fence_after_sync();
-        issue_s(i + 1);              // S's columns are free since P_ready(i)
-        FMB_TICK_AT(38, 256);
-#endif
-        if (!(ok = mbar_wait(&bar_fulldo, (i + 1) & 1, p.status, 6))) break;
-        if (!(ok = mbar_wait(&bar_dqfree, i & 1, p.status, 6))) break;
-        tc_fence_after_sync();
-        issue_dp();
-        FMB_TICK_AT(40, 256);
+        if (ok) umma_commit(&bar_fin);   // every GEMM of the item has completed: K, V, dK, dV may be reused
+        ++nk;
       }
-      if (ok && i > 0) umma_commit(&bar_fin);
+    }
+  } else if (warp == kBwdScoutWarp) {
+    // =============================================================== scout: items and K / V tiles
+    // Decodes item n + 1 and publishes it while item n is being worked on, and loads an item's K
+    // and V tiles as soon as every GEMM of the item before it has completed.
+    BwdItem I;
+    BwdTile it{0, 0, 0, 0, 0};
+    bool ok = true;
+    // returns 1 if item n exists (I, it describe it), 0 at the end of the stream
+    auto scout_item = [&](uint32_t n) -> int {
+      int item;
+      if (!get_item(n, item)) { ok = false; return 0; }
+      int state = 0, have = 0;
+      it = BwdTile{0, 0, 0, 0, 0};
+      I.skip = true;
+      if (item < p.n_items) {
+        bwd_decode_item(p, item, group, I);
+        state = I.skip ? 2 : 1;
+        if (!I.skip) have = seek_head(I, it) ? 1 : 0;
+      }
+      if (lane == 0) {
+        volatile int* f = s_info[n & 3];
+        f[1] = I.c; f[2] = I.hk; f[3] = I.b; f[4] = I.q0; f[5] = I.len_q; f[6] = I.k0; f[7] = I.len_k;
+        f[8] = I.key0; f[9] = I.keys_valid; f[10] = I.shift; f[11] = (int)(p.ps.cap ? I.plane / p.ps.cap : 0);
+        f[12] = have; f[13] = it.hg; f[14] = it.nnz;
+        f[15] = (int)(uint32_t)((uint64_t)it.off & 0xffffffffu); f[16] = (int)(uint32_t)((uint64_t)it.off >> 32);
+        f[17] = (int)(uint32_t)((uint64_t)it.slot & 0xffffffffu); f[18] = (int)(uint32_t)((uint64_t)it.slot >> 32);
+        f[0] = state;
+        mbar_arrive(&bar_info[n & 3]);
+      }
+      return state != 0;
+    };
+    int more = scout_item(0);
+    uint32_t nk = 0;                 // items with keys so far
+#pragma unroll 1
+    for (uint32_t n = 0; more && ok; ++n) {
+      const bool skip = I.skip;
+      if (!skip) {
+        const T* kbase = static_cast<const T*>(p.k) + (int64_t)(I.k0 + I.key0) * p.k_rs + (int64_t)I.hk * p.k_hs;
+        const T* vbase = static_cast<const T*>(p.v) + (int64_t)(I.k0 + I.key0) * p.v_rs + (int64_t)I.hk * p.v_hs;
+        dense_cp_async<T, D / 8, C, 32>(lane, sK, kKBlock, kbase, p.k_rs, I.keys_valid);
+        dense_cp_async<T, D / 8, C, 32>(lane, sV, kKBlock, vbase, p.v_rs, I.keys_valid);
+        cp_async_wait_all();
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_kv);
+      }
+      more = scout_item(n + 1);
+      if (!skip) {                   // every GEMM of item n has completed: its K and V tiles are free
+        if (ok) ok = mbar_wait(&bar_fin, nk & 1, p.status, 7);
+        ++nk;
+      }
     }
   } else if (warp >= 9) {
     // =============================================================== loader warps
@@ -664,257 +752,281 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
     const int t = q_side ? tid - (kBwdCompute + 32) : tid - (kBwdCompute + 32 + kBwdQLoaders);
     int* sRow = q_side ? sRowQ : sRowO;
     const int bar_id = q_side ? 3 : 4;
+    uint32_t m = 0;                  // tiles so far
+    bool ok = true;
 #pragma unroll 1
-    for (int m = 0; have; ++m) {
-      // the tile's row ids, fetched before the wait for the buffer
-      int rid[4];
+    for (uint32_t n = 0; ok; ++n) {
+      BwdItem I;
+      BwdTile it;
+      bool have;
+      const int state = read_info(n, I, it, have);
+      ok = bar_and(bar_id, nt, state >= 0);  // the group goes on, or leaves, together
+      if (!ok || state == 0) break;
+      if (I.skip) continue;
+#pragma unroll 1
+      for (; have; ++m) {
+        // the tile's row ids, fetched before the wait for the buffer
+        int rid[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) rid[k] = (t + k * nt < kTcM) ? row_checked(row_raw(it, t + k * nt)) : -1;
-      const int h = hk * group + it.hg;
-      bool ok = true;
-      if (q_side) {
-        if (m >= 2) ok = mbar_wait(&bar_dk[m & 1], ((m >> 1) - 1) & 1, p.status, 5);   // dK(m-2) has read Q
-      } else {
-        if (m >= 1) ok = mbar_wait(&bar_dv, (m - 1) & 1, p.status, 5);                 // dV(m-1) has read dO
-      }
+        for (int k = 0; k < 4; ++k) rid[k] = (t + k * nt < kTcM) ? row_checked(I, row_raw(it, t + k * nt)) : -1;
+        const int h = I.hk * group + it.hg;
+        BwdTile nx = it;
+        const bool more = next_tile(I, nx);
+        if (q_side) {
+          if (m >= 2) ok = mbar_wait(&bar_dk[m & 1], ((m >> 1) - 1) & 1, p.status, 5);   // dK(m-2) has read Q
+        } else {
+          if (m >= 1) ok = mbar_wait(&bar_dv, (m - 1) & 1, p.status, 5);                 // dV(m-1) has read dO
+        }
 #pragma unroll
-      for (int k = 0; k < 4; ++k)
-        if (t + k * nt < kTcM) sRow[t + k * nt] = rid[k];
-      ok = bar_and(bar_id, nt, ok);                // also publishes the row ids to the group
-      FMB_TICK_AT(24, 288); FMB_TICK_AT(26, 288 + kBwdQLoaders);  // loaders: row ids + waiting for the buffer
-      if (!ok) break;
-      if (q_side) {
-        const T* qbase = static_cast<const T*>(p.q) + (int64_t)q0 * p.q_rs + (int64_t)h * p.q_hs;
-        gather_cp_async<T, D / 8, kBwdQLoaders>(t, sQ + (m & 1) * kQTile, kQBlock, qbase, p.q_rs, sRow);
-      } else {
-        const T* dobase = static_cast<const T*>(p.dout) + (int64_t)q0 * p.do_rs + (int64_t)h * p.do_hs;
-        gather_cp_async<T, D / 8, kBwdOLoaders>(t, sdO, kQBlock, dobase, p.do_rs, sRow);
+        for (int k = 0; k < 4; ++k)
+          if (t + k * nt < kTcM) sRow[t + k * nt] = rid[k];
+        ok = bar_and(bar_id, nt, ok);                // also publishes the row ids to the group
+        FMB_TICK_AT(24, 288); FMB_TICK_AT(26, 288 + kBwdQLoaders);  // loaders: row ids + waiting for the buffer
+        if (!ok) break;
+        if (q_side) {
+          const T* qbase = static_cast<const T*>(p.q) + (int64_t)I.q0 * p.q_rs + (int64_t)h * p.q_hs;
+          gather_cp_async<T, D / 8, kBwdQLoaders>(t, sQ + (m & 1) * kQTile, kQBlock, qbase, p.q_rs, sRow);
+        } else {
+          const T* dobase = static_cast<const T*>(p.dout) + (int64_t)I.q0 * p.do_rs + (int64_t)h * p.do_hs;
+          gather_cp_async<T, D / 8, kBwdOLoaders>(t, sdO, kQBlock, dobase, p.do_rs, sRow);
+          // while the copies fly: what the compute warps need to know about the tile's rows, so that
+          // they issue no global loads of their own (the previous tile's values were copied to
+          // registers before P_ready, which precedes the dV GEMM this loader has waited for)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            if (t + k * nt < kTcM) {
+              float l = CUDART_INF_F, dd = 0.f;
+              if (rid[k] >= 0) {
+                const int64_t at = (int64_t)h * p.total_q + I.q0 + rid[k];
+                l = p.lse[at];
+                dd = p.softmax_d[at];
+              }
+              sLse[t + k * nt] = l;
+              sDsum[t + k * nt] = dd;
+            }
+          }
+          if (t == 0) {
+            const int64_t slot = it.slot + it.t0;
+            s_tile[0] = min(kTcM, it.nnz - it.t0);
+            s_tile[1] = (int)(uint32_t)((uint64_t)slot & 0xffffffffu);
+            s_tile[2] = (int)(uint32_t)((uint64_t)slot >> 32);
+            s_tile[3] = more ? 1 : 0;
+          }
+        }
+        cp_async_wait_all();
+        fence_async_smem();        // the copies are generic-proxy writes; the MMAs read through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(q_side ? &bar_fullq[m & 1] : &bar_fulldo);
+        FMB_TICK_AT(25, 288); FMB_TICK_AT(27, 288 + kBwdQLoaders);  // loaders: gather
+        bar_sync(bar_id, nt);                        // every thread has read the row ids
+        it = nx;
+        have = more;
       }
-      cp_async_wait_all();
-      fence_async_smem();        // the copies are generic-proxy writes; the MMAs read through the async proxy
-      __syncwarp();
-      if (lane == 0) mbar_arrive(q_side ? &bar_fullq[m & 1] : &bar_fulldo);
-      FMB_TICK_AT(25, 288); FMB_TICK_AT(27, 288 + kBwdQLoaders);  // loaders: gather
-      bar_sync(bar_id, nt);                        // every thread has read the row ids
-      have = next_tile(it);
     }
   } else {
     // =============================================================== compute warps
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
     T* part_dq = static_cast<T*>(p.part_o);
-    bool any_tile = false, good = true;
-
-    // row data (query row, LSE, D) of the tiles are fetched into registers ahead of their use: the
-    // row id two tiles ahead, LSE and D (which need the row id) one tile ahead
-    BwdTile n1 = it, n2;
-    bool have1 = have && next_tile(n1);
-    n2 = n1;
-    bool have2 = have1 && next_tile(n2);
-    int r_cur = -1, r_n1 = -1, r_n2 = -1;
-    float lse_cur = CUDART_INF_F, dd_cur = 0.f, lse_n1 = CUDART_INF_F, dd_n1 = 0.f;
-    auto row_stats = [&](const BwdTile& tl, int r, float& l2, float& dd) {
-      l2 = CUDART_INF_F; dd = 0.f;
-      if (r >= 0) {
-        const int64_t at = (int64_t)(hk * group + tl.hg) * p.total_q + q0 + r;
-        l2 = p.lse[at] * kLog2eTc;
-        dd = p.softmax_d[at];
-      }
-    };
-    if (have) {
-      r_cur = row_checked(row_raw(it, lt));
-      if (have1) r_n1 = row_raw(n1, lt);
-      row_stats(it, r_cur, lse_cur, dd_cur);
-    }
+    bool good = true;
+    uint32_t g = 0, nk = 0;          // tiles and items with keys so far
+    // the item whose dK / dV are still in TMEM
+    bool prev = false, prev_any = false;
 
 #pragma unroll 1
-    for (int i = 0; have && good; ++i) {
-      const int rows = min(kTcM, it.nnz - it.t0);
-      if (have2) r_n2 = row_raw(n2, lt);
-      if (have1) {
-        r_n1 = row_checked(r_n1);
-        row_stats(n1, r_n1, lse_n1, dd_n1);
-      }
+    for (uint32_t n = 0;; ++n) {
+      BwdItem I;
+      BwdTile it;
+      bool have;
+      const int state = read_info(n, I, it, have);
+      good = bar_and(2, kBwdCompute, good && state >= 0);
+      const bool done = !good || state == 0;
+      int fetched = 0;
+      if (tid == 0 && !done) fetched = atomicAdd(p.work, 1);      // item n + 2, published below
+      const bool run = !done && !I.skip;
+      have = have && run;
+      FMB_TICK(16);   // item hand-out, column data, first row data
 
-      // ---- P of row `lt`, this thread's 64 keys
-      if (good) good = mbar_wait(&bar_s, i & 1, p.status, 3);   // on failure: run on to the barriers, leave there
-      tc_fence_after_sync();
-      FMB_TICK(17);   // waiting for S
-      const int lim = r_cur < 0 ? 0 : (p.causal ? min(keys_valid, r_cur + shift - key0 + 1) : keys_valid);
-#if FMB_BWD_PACKED_P
-      // P is kept as the rounded values the dV GEMM uses (32 registers instead of 64 fp32): the
-      // registers saved let the CTA run more loader warps without spilling
-      uint4 pp[8];
-#pragma unroll
-      for (int i2 = 0; i2 < 2; ++i2) {
-        const int col0 = hf * 64 + i2 * 32;
-        float pr[32];
-        tmem_ld32(tS + lane_sel + col0, pr);
-        tmem_ld_wait();
-        if (i2 == 1) tc_fence_before_sync();
-#pragma unroll
-        for (int jj = 0; jj < 32; ++jj) pr[jj] = (col0 + jj < lim) ? exp2f(pr[jj] * scale_log2 - lse_cur) : 0.f;
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) pp[i2 * 4 + jj] = pack8<T>(pr + jj * 8);
-        if (i2 == 0 && i > 0) {      // the previous tile's dQ staging (in the P tile) has been read out
-          if (warp < 4 && lane == 0) bulk_wait_read();
-          good = bar_and(2, kBwdCompute, good);
-        }
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj)
-          *reinterpret_cast<uint4*>(sP + sw128_offset(lt, col0 / 8 + jj, kQBlock)) = pp[i2 * 4 + jj];
+      // ---- the previous item's GEMMs have completed: its dK and dV are final
+      if (prev) {
+        if (warp < 4 && lane == 0) bulk_wait_read();
+        if (good) good = mbar_wait(&bar_fin, (nk - 1) & 1, p.status, 4);
+        good = bar_and(2, kBwdCompute, good);
+        tc_fence_after_sync();
       }
-#else
-      float pr[64];
-      tmem_ld32(tS + lane_sel + hf * 64, pr);
-      tmem_ld32(tS + lane_sel + hf * 64 + 32, pr + 32);
-      tmem_ld_wait();
-      tc_fence_before_sync();
-      FMB_TICK(31);
-#pragma unroll
-      for (int i2 = 0; i2 < 2; ++i2) {
-        const int col0 = hf * 64 + i2 * 32;
-#pragma unroll
-        for (int jj = 0; jj < 32; ++jj)
-          pr[i2 * 32 + jj] = (col0 + jj < lim) ? exp2f(pr[i2 * 32 + jj] * scale_log2 - lse_cur) : 0.f;
-        FMB_TICK(32);
-        if (i2 == 0 && i > 0) {      // the previous tile's dQ staging (in the P tile) has been read out
-          if (warp < 4 && lane == 0) bulk_wait_read();
-          good = bar_and(2, kBwdCompute, good);
-        }
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj)
-          *reinterpret_cast<uint4*>(sP + sw128_offset(lt, col0 / 8 + jj, kQBlock)) = pack8<T>(pr + i2 * 32 + jj * 8);
-        FMB_TICK(33);
-      }
-#endif
-      tc_fence_before_sync();
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar_pready);      // S has been read, P is in shared memory
-      FMB_TICK(18);   // P
-
-      // ---- dS
-      if (good) good = mbar_wait(&bar_p, i & 1, p.status, 3);
-      tc_fence_after_sync();
-      FMB_TICK(19);   // waiting for dP
-#pragma unroll
-      for (int i2 = 0; i2 < 2; ++i2) {
-        const int col0 = hf * 64 + i2 * 32;
-        float dp[32];
-        tmem_ld32(tdP + lane_sel + col0, dp);
-        tmem_ld_wait();
-#pragma unroll
-#if FMB_BWD_PACKED_P
-        for (int j8 = 0; j8 < 4; ++j8) {
-          float pf[8];
-          unpack8<T>(pp[i2 * 4 + j8], pf);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) dp[j8 * 8 + e] = pf[e] * (dp[j8 * 8 + e] - dd_cur);
-        }
-#else
-        for (int jj = 0; jj < 32; ++jj) dp[jj] = pr[i2 * 32 + jj] * (dp[jj] - dd_cur);
-#endif
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj)
-          *reinterpret_cast<uint4*>(sdS + sw128_offset(lt, col0 / 8 + jj, kQBlock)) = pack8<T>(dp + jj * 8);
-      }
-      tc_fence_before_sync();
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar_dsready);     // dP has been read, dS is in shared memory
-      FMB_TICK(20);   // dS
-      any_tile = true;
-
-      // ---- dQ partial of row `lt`, this thread's half of the head dim: scaled, rounded to the I/O
-      // dtype, stored at the entry's slot (16-byte chunks permuted like the forward partials)
-      if (good) good = mbar_wait(&bar_dq, i & 1, p.status, 4);
-      tc_fence_after_sync();
-      FMB_TICK(21);   // waiting for dQ
+      // ---- dK and dV of key `lt` of the previous item, this thread's half of the head dim
       {
-        // staged in the P tile (free: dV(i) completed before dQ(i)), 16-byte chunks permuted like the
-        // forward partials; one bulk copy per 32 rows, whose reads are waited for before P(i+1) is
-        // stored.  32 columns at a time keep the register footprint small.
-        constexpr int NCH = DH / 8;               // 16-byte chunks of this thread's half row
-        const int key = (int)((it.slot + it.t0 + lt) & 7);
-        unsigned char* srow = sP + lt * (D * 2);
+        // (written by thread 0 after the item's last tile; the barrier at the top of this iteration orders the read)
+        const int64_t prev_row = s_prev[0];
+        const int prev_hk = s_prev[1], prev_keys = s_prev[2];
+        T* dkp = static_cast<T*>(p.dk) + (prev_row + lt) * p.dk_rs + (int64_t)prev_hk * p.dk_hs + hf * DH;
+        T* dvp = static_cast<T*>(p.dv) + (prev_row + lt) * p.dv_rs + (int64_t)prev_hk * p.dv_hs + hf * DH;
 #pragma unroll
         for (int i2 = 0; i2 < DH / 32; ++i2) {
-          float o[32];
-          tmem_ld32(tdQ + lane_sel + hf * DH + i2 * 32, o);
-          tmem_ld_wait();
+          if (prev && good) {
+            float o[32];
+            if (prev_any) {
+              tmem_ld32(tdK + lane_sel + hf * DH + i2 * 32, o);
+              tmem_ld_wait();
+            } else {
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
+              for (int j = 0; j < 32; ++j) o[j] = 0.f;
+            }
+            if (lt < prev_keys) {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) o[jj * 8 + e] *= p.scale;
-            *reinterpret_cast<uint4*>(srow + (((hf * NCH + i2 * 4 + jj) ^ key) << 4)) = pack8<T>(o + jj * 8);
+              for (int j = 0; j < 32; ++j) o[j] *= p.scale;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(dkp + i2 * 32 + j * 8) = pack8<T>(o + j * 8);
+            }
+            if (prev_any) {
+              tmem_ld32(tdV + lane_sel + hf * DH + i2 * 32, o);
+              tmem_ld_wait();
+            }
+            if (lt < prev_keys) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(dvp + i2 * 32 + j * 8) = pack8<T>(o + j * 8);
+            }
           }
         }
         tc_fence_before_sync();
-        FMB_TICK(29);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bar_dqfree);    // dQ has been read out of dP's columns
+      }
+      FMB_TICK(23);   // wait for the previous item's last GEMMs, dK/dV epilogue
+      if (tid == 0 && !done) {
+        *reinterpret_cast<volatile int*>(&s_items[(n + 2) & 3]) = fetched;
+        mbar_arrive(&bar_item[(n + 2) & 3]);
+      }
+      prev = false;
+      prev_any = false;
+      if (done) break;
+      if (I.skip) {
+        zero_dq_partials_by<T>(p.ps, part_dq, I.plane, I.b, I.hk, group, I.c, D, tid, kBwdCompute);
+        continue;
+      }
+
+      // The compute warps issue no global loads inside an item: the dO loader leaves the rows' query
+      // positions, log-sum-exps and dO.O sums and the tile's slot range in shared memory.
+      bool more = have;
+#pragma unroll 1
+      for (; more && good; ++g) {
+        // ---- P of row `lt`, this thread's 64 keys
+        FMB_TICK(47);   // loop back
+        if (good) good = mbar_wait(&bar_s, g & 1, p.status, 3);   // on failure: run on to the barriers, leave there
+        if (good) good = mbar_wait(&bar_fulldo, g & 1, p.status, 3);   // row data of the tile (long landed)
+        tc_fence_after_sync();
+        if (!prev_any) FMB_TICK(39);   // waiting for S, first tile of an item
+        FMB_TICK(17);   // waiting for S
+        const int r_cur = sRowO[lt];
+        const float lse2 = sLse[lt] * kLog2eTc, dd_cur = sDsum[lt];
+        const int rows = s_tile[0];
+        const int64_t slot0 = (int64_t)(((uint64_t)(uint32_t)s_tile[2] << 32) | (uint32_t)s_tile[1]);
+        more = s_tile[3] != 0;
+        const int lim = r_cur < 0 ? 0 : (p.causal ? min(I.keys_valid, r_cur + I.shift - I.key0 + 1) : I.keys_valid);
+        // P is kept as the rounded values the dV GEMM uses (32 registers instead of 64 fp32): the
+        // registers saved let the CTA run more loader warps without spilling
+        uint4 pp[8];
+#pragma unroll
+        for (int i2 = 0; i2 < 2; ++i2) {
+          const int col0 = hf * 64 + i2 * 32;
+          float pr[32];
+          tmem_ld32(tS + lane_sel + col0, pr);
+          tmem_ld_wait();
+          if (i2 == 1) tc_fence_before_sync();
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) pr[jj] = (col0 + jj < lim) ? exp2f(pr[jj] * scale_log2 - lse2) : 0.f;
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) pp[i2 * 4 + jj] = pack8<T>(pr + jj * 8);
+          if (i2 == 0) {               // the previous tile's dQ staging (in the P tile) has been read out
+            if (warp < 4 && lane == 0) bulk_wait_read();
+            good = bar_and(2, kBwdCompute, good);
+          }
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj)
+            *reinterpret_cast<uint4*>(sP + sw128_offset(lt, col0 / 8 + jj, kQBlock)) = pp[i2 * 4 + jj];
+        }
+        tc_fence_before_sync();
         fence_async_smem();
-        FMB_TICK(30);
-        good = bar_and(2, kBwdCompute, good);     // both halves of every row staged
-        if (good && warp < 4 && lane == 0) {
-          const int wrows = min(32, rows - warp * 32);
-          if (wrows > 0) {
-            bulk_store(part_dq + (plane + it.slot + it.t0 + warp * 32) * D, sP + warp * 32 * (D * 2),
-                       (uint32_t)wrows * D * 2);
-            bulk_commit();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_pready);      // S has been read, P is in shared memory
+        FMB_TICK(18);   // P
+
+        // ---- dS
+        if (good) good = mbar_wait(&bar_p, g & 1, p.status, 3);
+        tc_fence_after_sync();
+        FMB_TICK(19);   // waiting for dP
+#pragma unroll
+        for (int i2 = 0; i2 < 2; ++i2) {
+          const int col0 = hf * 64 + i2 * 32;
+          float dp[32];
+          tmem_ld32(tdP + lane_sel + col0, dp);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j8 = 0; j8 < 4; ++j8) {
+            float pf[8];
+            unpack8<T>(pp[i2 * 4 + j8], pf);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) dp[j8 * 8 + e] = pf[e] * (dp[j8 * 8 + e] - dd_cur);
+          }
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj)
+            *reinterpret_cast<uint4*>(sdS + sw128_offset(lt, col0 / 8 + jj, kQBlock)) = pack8<T>(dp + jj * 8);
+        }
+        tc_fence_before_sync();
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_dsready);     // dP has been read, dS is in shared memory
+        FMB_TICK(20);   // dS
+
+        // ---- dQ partial of row `lt`, this thread's half of the head dim: scaled, rounded to the I/O
+        // dtype, stored at the entry's slot (16-byte chunks permuted like the forward partials)
+        if (good) good = mbar_wait(&bar_dq, g & 1, p.status, 4);
+        tc_fence_after_sync();
+        FMB_TICK(21);   // waiting for dQ
+        {
+          // staged in the P tile (free: dV(g) completed before dQ(g)), 16-byte chunks permuted like the
+          // forward partials; one bulk copy per 32 rows, whose reads are waited for before the next P
+          // is stored.  32 columns at a time keep the register footprint small.
+          constexpr int NCH = DH / 8;               // 16-byte chunks of this thread's half row
+          const int key = (int)((slot0 + lt) & 7);
+          unsigned char* srow = sP + lt * (D * 2);
+#pragma unroll
+          for (int i2 = 0; i2 < DH / 32; ++i2) {
+            float o[32];
+            tmem_ld32(tdQ + lane_sel + hf * DH + i2 * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) o[jj * 8 + e] *= p.scale;
+              *reinterpret_cast<uint4*>(srow + (((hf * NCH + i2 * 4 + jj) ^ key) << 4)) = pack8<T>(o + jj * 8);
+            }
+          }
+          tc_fence_before_sync();
+          FMB_TICK(29);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bar_dqfree);    // dQ has been read out of dP's columns
+          fence_async_smem();
+          FMB_TICK(30);
+          good = bar_and(2, kBwdCompute, good);     // both halves of every row staged
+          if (good && warp < 4 && lane == 0) {
+            const int wrows = min(32, rows - warp * 32);
+            if (wrows > 0) {
+              bulk_store(part_dq + (I.plane + slot0 + warp * 32) * D, sP + warp * 32 * (D * 2),
+                         (uint32_t)wrows * D * 2);
+              bulk_commit();
+            }
           }
         }
+        FMB_TICK(22);   // dQ epilogue
+        prev_any = true;
       }
-      FMB_TICK(22);   // dQ epilogue
-
-      it = n1; have = have1;
-      n1 = n2; have1 = have2;
-      if (have2) have2 = next_tile(n2);
-      r_cur = r_n1; lse_cur = lse_n1; dd_cur = dd_n1;
-      r_n1 = r_n2;
+      prev = true;
+      if (tid == 0) { s_prev[0] = I.k0 + I.key0; s_prev[1] = I.hk; s_prev[2] = I.keys_valid; }
+      ++nk;
     }
-
-    // ---- all GEMMs done -> dK and dV of key `lt`, this thread's half of the head dim
     if (warp < 4 && lane == 0) bulk_wait_read();
-    if (any_tile && good) good = mbar_wait(&bar_fin, 0, p.status, 4);
-    good = bar_and(2, kBwdCompute, good);
-    if (good) {
-      tc_fence_after_sync();
-      T* dkp = static_cast<T*>(p.dk) + (int64_t)(k0 + key0 + lt) * p.dk_rs + (int64_t)hk * p.dk_hs + hf * DH;
-      T* dvp = static_cast<T*>(p.dv) + (int64_t)(k0 + key0 + lt) * p.dv_rs + (int64_t)hk * p.dv_hs + hf * DH;
-#pragma unroll
-      for (int i2 = 0; i2 < DH / 32; ++i2) {
-        float o[32];
-        if (any_tile) {
-          tmem_ld32(tdK + lane_sel + hf * DH + i2 * 32, o);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = 0.f;
-        }
-        if (lt < keys_valid) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] *= p.scale;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(dkp + i2 * 32 + j * 8) = pack8<T>(o + j * 8);
-        }
-        if (any_tile) {
-          tmem_ld32(tdV + lane_sel + hf * DH + i2 * 32, o);
-          tmem_ld_wait();
-        }
-        if (lt < keys_valid) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(dvp + i2 * 32 + j * 8) = pack8<T>(o + j * 8);
-        }
-      }
-      tc_fence_before_sync();
-    }
   }
   tc_fence_before_sync();
-  __syncthreads();         // every role is done with the item's tiles, barriers and TMEM columns
+  __syncthreads();         // every role is done with its tiles, barriers and TMEM columns
   tc_fence_after_sync();
-  }  // work items
-  __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, NCOLS);
 }
 
@@ -1106,8 +1218,9 @@ static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassPa
 template <typename T, int C, int D>
 static int bwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   TcParams p = make_tc_params(a, w, ps);
-  // K, V, two Q tiles, one dO tile, P and dS
-  const size_t smem = (size_t)2 * C * D * 2 + (size_t)3 * kTcM * D * 2 + (size_t)2 * kTcM * C * 2 + 1024;
+  // K, V, two Q tiles, one dO tile, P and dS: with d = 128 that and the kernel's 3 KB of static shared
+  // memory are exactly the 227 KB a CTA may have (the dynamic part is declared 1024-byte aligned)
+  const size_t smem = (size_t)2 * C * D * 2 + (size_t)3 * kTcM * D * 2 + (size_t)2 * kTcM * C * 2;
   auto kern = bwd_main_tc_kernel<T, C, D>;
   FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int nchunk = max(a.ncol, ceil_div(a.max_k, a.chunk));

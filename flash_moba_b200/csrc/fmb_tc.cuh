@@ -62,6 +62,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
 }
 
 
+// ---- loads that are issued where they are written
+// A plain load of read-only data may be moved by the compiler down to its first use (it does so
+// under register pressure), which turns a prefetch into a full-latency stall.  These are volatile
+// asm statements: they keep their place among the other volatile statements (barrier waits).
+__device__ __forceinline__ int ldg_s32_here(const int* ptr) {
+  int v;
+  asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(v) : "l"(ptr));
+  return v;
+}
+__device__ __forceinline__ float ldg_f32_here(const float* ptr) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(ptr));
+  return v;
+}
+
 // ---- named barriers for groups of warps inside a CTA (id 1..15; count a multiple of 32)
 __device__ __forceinline__ void bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
