@@ -87,10 +87,11 @@ __device__ __forceinline__ void decode_item(const TcParams& p, int item, int& bx
 __host__ __device__ constexpr int next_pow2_cols(int x) { return x <= 32 ? 32 : x <= 64 ? 64 : x <= 128 ? 128 : x <= 256 ? 256 : 512; }
 
 // ======================================================================== forward
-// CTA = key block c of one (sequence, head); 672 threads, warp-specialised, one CTA per SM:
+// Work item = key block c of one (sequence, head); 704 threads, warp-specialised, one persistent
+// CTA per SM that runs through its work items as ONE stream of 128-row tiles:
 //   warps 0-7 / 8-15  compute group 0 / 1 (two threads per row, each owns half of the columns).
-//                     The groups take alternate 128-row tiles of the block's CSC column; each has
-//                     its own Q tile, P/O-staging tile, 256 TMEM columns (S | O) and mbarriers.
+//                     The groups take alternate tiles of an item's CSC column; each has its own Q
+//                     tile, P/O-staging tile, 256 TMEM columns (S | O) and mbarriers.
 //                     Per tile: wait S -> chunk-local softmax (row maximum, then exponentials) ->
 //                     P (bf16) to shared memory -> P_ready;  wait O -> O / l staged and written
 //                     with one bulk copy per warp, log-sum-exp beside it.
@@ -100,9 +101,12 @@ __host__ __device__ constexpr int next_pow2_cols(int x) { return x <= 32 ? 32 : 
 //   warps 17-18 / 19-20  loaders of group 0 / 1: row ids of the next tile, then its Q rows with
 //                     16-byte cp.async copies straight into the swizzled UMMA tile, as soon as
 //                     the group's previous S GEMM has released the Q tile.
-// K and V are staged once per work item and shared.  While one group is in its softmax the other
-// group's MMAs and the loaders' copies proceed.  CTAs are persistent (one per SM): TMEM is
-// allocated once, and a CTA keeps taking work items until the counter runs out.
+//   warp 21           scout: takes work items from the counter, decodes them (a chain of dependent
+//                     global loads) one item ahead and publishes them in shared memory; stages an
+//                     item's K tile once the S GEMMs of the item before it have completed and its V
+//                     tile once the P.V GEMMs have.
+// No role waits for another at an item boundary except through the data it needs: the barriers are
+// initialised once and their phases counted per group across items.
 constexpr int kFwdGroups = 2;
 constexpr int kFwdGroupThreads = 256;
 #ifndef FMB_FWD_LW
@@ -110,7 +114,17 @@ constexpr int kFwdGroupThreads = 256;
 #endif
 constexpr int kFwdLoaderSet = 32 * FMB_FWD_LW;  // loader threads per compute group
 constexpr int kFwdIssuerWarp = kFwdGroups * kFwdGroupThreads / 32;
-constexpr int kFwdThreads = kFwdGroups * kFwdGroupThreads + 32 + kFwdGroups * kFwdLoaderSet;
+constexpr int kFwdScoutWarp = kFwdIssuerWarp + 1 + kFwdGroups * FMB_FWD_LW;
+constexpr int kFwdThreads = kFwdGroups * kFwdGroupThreads + 32 + kFwdGroups * kFwdLoaderSet + 32;
+
+// a decoded work item as the scout publishes it
+struct FwdItem {
+  int nnz;            // entries of the column (0: the stream has ended)
+  int64_t off;        // first entry in `indices`
+  int64_t slot;       // first slot of the column, plane included
+  int q0, len_q, h;   // the sequence's first query token and length, the head
+  int key0, keys_valid, shift;
+};
 
 template <typename T, int C, int D>
 __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
@@ -121,9 +135,9 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
   constexpr int CH = C / 2, DH = D / 2;        // columns per thread in the softmax / epilogue
   extern __shared__ unsigned char smem_raw[];
   __shared__ uint64_t bar_s[kFwdGroups], bar_o[kFwdGroups], bar_full[kFwdGroups], bar_qfree[kFwdGroups];
-  __shared__ uint64_t bar_pready[kFwdGroups], bar_kv;
+  __shared__ uint64_t bar_pready[kFwdGroups], bar_k, bar_v, bar_sfin, bar_fin, bar_info[4];
   __shared__ uint32_t tmem_base_s;
-  __shared__ int s_item;
+  __shared__ int s_info[4][12];
   __shared__ int sRow[kFwdGroups][2][kTcM];
   __shared__ float sMax[kFwdGroups][2][kTcM], sSum[kFwdGroups][2][kTcM];
 
@@ -137,24 +151,7 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
   const float scale_log2 = p.scale * kLog2eTc;
   FMB_T0();
   if (warp == 0) tmem_alloc(&tmem_base_s, NCOLS);
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = tmem_base_s;
-
-  bool first_item = true;
-#pragma unroll 1
-  for (;;) {
-  // ---- next work item; the barriers start every item in phase 0
   if (tid == 0) {
-    s_item = atomicAdd(p.work, 1);
-    if (!first_item) {
-      for (int i = 0; i < kFwdGroups; ++i) {
-        mbar_inval(&bar_s[i]); mbar_inval(&bar_o[i]); mbar_inval(&bar_full[i]); mbar_inval(&bar_qfree[i]);
-        mbar_inval(&bar_pready[i]);
-      }
-      mbar_inval(&bar_kv);
-    }
     for (int i = 0; i < kFwdGroups; ++i) {
       mbar_init(&bar_s[i], 1);
       mbar_init(&bar_o[i], 1);
@@ -162,36 +159,94 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
       mbar_init(&bar_qfree[i], 1);
       mbar_init(&bar_pready[i], kFwdGroupThreads / 32);  // one arrival per compute warp
     }
-    mbar_init(&bar_kv, kFwdGroups * kFwdGroupThreads / 32);
+    mbar_init(&bar_k, 1); mbar_init(&bar_v, 1); mbar_init(&bar_sfin, 1); mbar_init(&bar_fin, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&bar_info[i], 1);
     mbar_fence_init();
   }
+  tc_fence_before_sync();
   __syncthreads();
-  first_item = false;
-  const int item = s_item;
-  if (item >= p.n_items) break;
-  // C is the key block: chunk c of the pattern is covered by nsub blocks of C keys
-  int bx, rem;
-  decode_item(p, item, bx, rem);
-  const int c = bx / p.ps.nsub, sb = bx % p.ps.nsub, h = p.ps.h0 + rem % p.items_y, b = rem / p.items_y;
-  const ColRef col = column_of(p.ps, b, h, c);
-  const int nnz = col.nnz;
-  if (nnz <= 0) {          // CTA-uniform
-    __syncthreads();
-    continue;
-  }
-  const int64_t off = col.off;                                   // first entry in `indices`
-  const int64_t slot0 = col.slot;                                // first slot of the column in the pass
-  const int64_t plane = (int64_t)sb * p.ps.cap;                  // this key block's plane of slots
-  const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
-  const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
-  const int key0 = c * p.ps.chunk + sb * C;
-  const int keys_valid = max(0, min(C, len_k - key0));
-  const int hk = h / (p.heads / p.heads_k);
-  const int shift = len_k - len_q;
-  const int ntiles = (nnz + kTcM - 1) / kTcM;
-  FMB_TICK(1);   // item hand-out, column lookup
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
 
-  if (warp == kFwdIssuerWarp) {
+  // n-th item of this CTA's stream; false: the wait gave up (error recorded).  it.nnz == 0: the end.
+  auto read_info = [&](uint32_t n, FwdItem& it) -> bool {
+    if (!mbar_wait(&bar_info[n & 3], (n >> 2) & 1, p.status, 7)) {
+      it.nnz = 0;
+      return false;
+    }
+    const volatile int* f = s_info[n & 3];
+    it.nnz = f[0];
+    it.off = (int64_t)(((uint64_t)(uint32_t)f[2] << 32) | (uint32_t)f[1]);
+    it.slot = (int64_t)(((uint64_t)(uint32_t)f[4] << 32) | (uint32_t)f[3]);
+    it.q0 = f[5]; it.len_q = f[6]; it.h = f[7]; it.key0 = f[8]; it.keys_valid = f[9]; it.shift = f[10];
+    return true;
+  };
+
+  if (warp == kFwdScoutWarp) {
+    // =============================================================== scout: items, K and V tiles
+    bool ok = true;
+    const T* kbase = nullptr;
+    const T* vbase = nullptr;
+    int keys_valid = 0;
+    // takes items from the counter until one has entries, publishes it as item n of the stream
+    auto scout_item = [&](uint32_t n) -> bool {
+      FwdItem it;
+      it.nnz = 0;
+      for (;;) {
+        int item = 0;
+        if (lane == 0) item = atomicAdd(p.work, 1);
+        item = __shfl_sync(0xffffffffu, item, 0);
+        if (item >= p.n_items) { it.nnz = 0; break; }
+        int bx, rem;
+        decode_item(p, item, bx, rem);
+        // C is the key block: chunk c of the pattern is covered by nsub blocks of C keys
+        const int c = bx / p.ps.nsub, sb = bx % p.ps.nsub, h = p.ps.h0 + rem % p.items_y, b = rem / p.items_y;
+        const ColRef col = column_of(p.ps, b, h, c);
+        if (col.nnz <= 0) continue;
+        const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
+        const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
+        const int hk = h / (p.heads / p.heads_k);
+        it.nnz = col.nnz; it.off = col.off; it.slot = (int64_t)sb * p.ps.cap + col.slot;
+        it.q0 = q0; it.len_q = len_q; it.h = h;
+        it.key0 = c * p.ps.chunk + sb * C;
+        it.keys_valid = max(0, min(C, len_k - it.key0));
+        it.shift = len_k - len_q;
+        kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + it.key0) * p.k_rs + (int64_t)hk * p.k_hs;
+        vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + it.key0) * p.v_rs + (int64_t)hk * p.v_hs;
+        keys_valid = it.keys_valid;
+        break;
+      }
+      if (lane == 0) {
+        volatile int* f = s_info[n & 3];
+        f[1] = (int)(uint32_t)((uint64_t)it.off & 0xffffffffu); f[2] = (int)(uint32_t)((uint64_t)it.off >> 32);
+        f[3] = (int)(uint32_t)((uint64_t)it.slot & 0xffffffffu); f[4] = (int)(uint32_t)((uint64_t)it.slot >> 32);
+        f[5] = it.q0; f[6] = it.len_q; f[7] = it.h; f[8] = it.key0; f[9] = it.keys_valid; f[10] = it.shift;
+        f[0] = it.nnz;
+        mbar_arrive(&bar_info[n & 3]);
+      }
+      return it.nnz > 0;
+    };
+    bool more = scout_item(0);
+#pragma unroll 1
+    for (uint32_t n = 0; more && ok; ++n) {
+      // K of item n: every S GEMM of item n - 1 has completed; V: every P.V GEMM has
+      if (n > 0) ok = mbar_wait(&bar_sfin, (n - 1) & 1, p.status, 7);
+      if (!ok) break;
+      dense_cp_async<T, D / 8, C, 32>(lane, sK, kKBlock, kbase, p.k_rs, keys_valid);
+      cp_async_wait_all();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_k);
+      if (n > 0) ok = mbar_wait(&bar_fin, (n - 1) & 1, p.status, 7);
+      if (!ok) break;
+      dense_cp_async<T, D / 8, C, 32>(lane, sV, kKBlock, vbase, p.v_rs, keys_valid);
+      cp_async_wait_all();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_v);
+      more = scout_item(n + 1);
+    }
+  } else if (warp == kFwdIssuerWarp) {
     // =============================================================== MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(FmtOf<T>::v, kTcM, C, 0, 0);
@@ -199,77 +254,100 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
       const uint32_t hi = desc_hi_sw128(1024);
       const uint32_t k_km = desc_lo_sw128(smem_u32(sK), 16), v_mn = desc_lo_sw128(smem_u32(sV), kKBlock);
       constexpr uint32_t kQB = kQBlock >> 4, kKB = kKBlock >> 4;
-      int ts[kFwdGroups], tp[kFwdGroups];     // next tile whose S / P.V GEMM is to be issued
+      uint32_t cs[kFwdGroups] = {0, 0}, cp[kFwdGroups] = {0, 0};   // S / P.V GEMMs issued per group so far
+      bool ok = true;
+#pragma unroll 1
+      for (uint32_t n = 0; ok; ++n) {
+        FwdItem it;
+        if (!(ok = read_info(n, it)) || it.nnz <= 0) break;
+        const int ntiles = (it.nnz + kTcM - 1) / kTcM;
+        int ts[kFwdGroups], tp[kFwdGroups];     // next tile whose S / P.V GEMM is to be issued
 #pragma unroll
-      for (int g = 0; g < kFwdGroups; ++g) { ts[g] = g; tp[g] = g; }
-      bool ok = mbar_wait(&bar_kv, 0, p.status, 6);
-      uint32_t idle = 0;
-      while (ok && (tp[0] < ntiles || tp[1] < ntiles)) {
-        bool progress = false;
+        for (int g = 0; g < kFwdGroups; ++g) { ts[g] = g; tp[g] = g; }
+        if (!(ok = mbar_wait(&bar_k, n & 1, p.status, 6))) break;
+        bool have_v = false, s_open = true;
+        uint32_t idle = 0;
+        while (ok && (tp[0] < ntiles || tp[1] < ntiles)) {
+          bool progress = false;
+          if (!have_v && mbar_test(&bar_v, n & 1)) have_v = true;
 #pragma unroll
-        for (int g = 0; g < kFwdGroups; ++g) {
-          const uint32_t tS = tmem_base + g * 256, tO = tS + 128;
-          const uint32_t q_km = desc_lo_sw128(smem_u32(sQg + g * (kTcM * D * 2)), 16);
-          const uint32_t p_km = desc_lo_sw128(smem_u32(sPOg + g * (kTcM * QP * 2)), 16);
-          // O = P.V of tile tp: P is in shared memory and S has been read
-          if (tp[g] < ntiles && tp[g] < ts[g] && mbar_test(&bar_pready[g], ((tp[g] - g) / kFwdGroups) & 1)) {
-            tc_fence_after_sync();
-            umma_gemm<C / 16>(tO, p_km, hi, 2, kQB, v_mn, hi, 128, 512, idesc_o, 0);
-            umma_commit(&bar_o[g]);
-            tp[g] += kFwdGroups;
-            progress = true;
+          for (int g = 0; g < kFwdGroups; ++g) {
+            const uint32_t tS = tmem_base + g * 256, tO = tS + 128;
+            const uint32_t q_km = desc_lo_sw128(smem_u32(sQg + g * (kTcM * D * 2)), 16);
+            const uint32_t p_km = desc_lo_sw128(smem_u32(sPOg + g * (kTcM * QP * 2)), 16);
+            // O = P.V of tile tp: P is in shared memory and S has been read
+            if (have_v && tp[g] < ntiles && tp[g] < ts[g] && mbar_test(&bar_pready[g], cp[g] & 1)) {
+              tc_fence_after_sync();
+              umma_gemm<C / 16>(tO, p_km, hi, 2, kQB, v_mn, hi, 128, 512, idesc_o, 0);
+              umma_commit(&bar_o[g]);
+              tp[g] += kFwdGroups;
+              ++cp[g];
+              progress = true;
+            }
+            // S = Q.K^T of tile ts: its Q rows have landed, and S of the group's previous tile has been read
+            if (ts[g] < ntiles && ts[g] < tp[g] + kFwdGroups && mbar_test(&bar_full[g], cs[g] & 1)) {
+              tc_fence_after_sync();
+              umma_gemm<D / 16>(tS, q_km, hi, 2, kQB, k_km, hi, 2, kKB, idesc_s, 0);
+              umma_commit(&bar_qfree[g]);   // the loaders may refill the Q tile
+              umma_commit(&bar_s[g]);
+              ts[g] += kFwdGroups;
+              ++cs[g];
+              progress = true;
+            }
           }
-          // S = Q.K^T of tile ts: its Q rows have landed, and S of the group's previous tile has been read
-          if (ts[g] < ntiles && ts[g] < tp[g] + kFwdGroups &&
-              mbar_test(&bar_full[g], ((ts[g] - g) / kFwdGroups) & 1)) {
-            tc_fence_after_sync();
-            umma_gemm<D / 16>(tS, q_km, hi, 2, kQB, k_km, hi, 2, kKB, idesc_s, 0);
-            umma_commit(&bar_qfree[g]);   // the loaders may refill the Q tile
-            umma_commit(&bar_s[g]);
-            ts[g] += kFwdGroups;
-            progress = true;
+          if (s_open && ts[0] >= ntiles && ts[1] >= ntiles) {   // the item's last S GEMM has been issued
+            umma_commit(&bar_sfin);
+            s_open = false;
+          }
+          if (progress) idle = 0;
+          else if (++idle > (kSpinLimit << 4)) {   // bounded like every other wait
+            atomicCAS(p.status, 0, 6);
+            ok = false;
           }
         }
-        if (progress) idle = 0;
-        else if (++idle > (kSpinLimit << 4)) {   // bounded like every other wait
-          atomicCAS(p.status, 0, 6);
-          ok = false;
-        }
+        if (ok) umma_commit(&bar_fin);             // the item's last P.V GEMM has been issued
       }
     }
   } else if (warp > kFwdIssuerWarp) {
     // =============================================================== loader warps
     // two independent sets of 64 threads, one per compute group
-    const T* qbase = static_cast<const T*>(p.q) + (int64_t)q0 * p.q_rs + (int64_t)h * p.q_hs;
     const int lt0 = tid - (kFwdIssuerWarp + 1) * 32;
     const int gi = lt0 / kFwdLoaderSet;        // the group this set serves
     const int st = lt0 % kFwdLoaderSet;
-    uint32_t ph_free = 0;
-    // row id of entry e of a tile (-1 = none): the load only; the range check happens at the use
-    auto row_raw = [&](int tile, int e) {
-      return (e < kTcM && tile < ntiles && tile * kTcM + e < nnz) ? p.ps.indices[off + tile * kTcM + e] : -1;
-    };
-    int r_a = row_raw(gi, st), r_b = row_raw(gi, st + kFwdLoaderSet);   // the set's first tile
+    uint32_t m = 0;                            // tiles of this group so far
+    bool ok = true;
 #pragma unroll 1
-    for (int i = gi, n = 0; i < ntiles; i += kFwdGroups, ++n) {
-      int* rows = sRow[gi][n & 1];
-      bool ok = true;
-      if (n > 0) {   // the group's previous S GEMM must have finished reading its Q tile; it is
-                     // issued after the softmax of the tile before, the last reader of rows[]
-        ok = mbar_wait(&bar_qfree[gi], ph_free, p.status, 5);
-        ph_free ^= 1;
+    for (uint32_t n = 0; ok; ++n) {
+      FwdItem it;
+      ok = read_info(n, it);
+      ok = bar_and(4 + gi, kFwdLoaderSet, ok);   // the set goes on, or leaves, together
+      if (!ok || it.nnz <= 0) break;
+      const int ntiles = (it.nnz + kTcM - 1) / kTcM;
+      const T* qbase = static_cast<const T*>(p.q) + (int64_t)it.q0 * p.q_rs + (int64_t)it.h * p.q_hs;
+      // row id of entry e of a tile (-1 = none): the load only; the range check happens at the use
+      auto row_raw = [&](int tile, int e) {
+        return (e < kTcM && tile < ntiles && tile * kTcM + e < it.nnz) ? p.ps.indices[it.off + tile * kTcM + e] : -1;
+      };
+      int r_a = row_raw(gi, st), r_b = row_raw(gi, st + kFwdLoaderSet);   // the set's first tile of the item
+#pragma unroll 1
+      for (int i = gi; i < ntiles; i += kFwdGroups, ++m) {
+        int* rows = sRow[gi][m & 1];
+        if (m > 0) {   // the group's previous S GEMM must have finished reading its Q tile; it is
+                       // issued after the softmax of the tile before, the last reader of rows[]
+          ok = mbar_wait(&bar_qfree[gi], (m - 1) & 1, p.status, 5);
+        }
+        rows[st] = (r_a < 0 || r_a >= it.len_q) ? -1 : r_a;
+        if (st + kFwdLoaderSet < kTcM) rows[st + kFwdLoaderSet] = (r_b < 0 || r_b >= it.len_q) ? -1 : r_b;
+        r_a = row_raw(i + kFwdGroups, st);                  // next tile's row ids, in flight meanwhile
+        r_b = row_raw(i + kFwdGroups, st + kFwdLoaderSet);
+        ok = bar_and(4 + gi, kFwdLoaderSet, ok);   // also publishes the row ids inside the set
+        if (!ok) break;
+        gather_cp_async<T, D / 8, kFwdLoaderSet>(st, sQg + gi * (kTcM * D * 2), kQBlock, qbase, p.q_rs, rows);
+        cp_async_wait_all();
+        fence_async_smem();   // the copies are generic-proxy writes; the MMAs read through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_full[gi]);
       }
-      rows[st] = (r_a < 0 || r_a >= len_q) ? -1 : r_a;
-      if (st + kFwdLoaderSet < kTcM) rows[st + kFwdLoaderSet] = (r_b < 0 || r_b >= len_q) ? -1 : r_b;
-      r_a = row_raw(i + kFwdGroups, st);                  // next tile's row ids, in flight meanwhile
-      r_b = row_raw(i + kFwdGroups, st + kFwdLoaderSet);
-      ok = bar_and(4 + gi, kFwdLoaderSet, ok);   // also publishes the row ids inside the set
-      if (!ok) break;
-      gather_cp_async<T, D / 8, kFwdLoaderSet>(st, sQg + gi * (kTcM * D * 2), kQBlock, qbase, p.q_rs, rows);
-      cp_async_wait_all();
-      fence_async_smem();   // the copies are generic-proxy writes; the MMAs read through the async proxy
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar_full[gi]);
     }
   } else {
     // =============================================================== compute groups
@@ -278,123 +356,119 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
     const int lt = tid & (kTcM - 1);           // row (TMEM lane)
     const int hf = (gt >> 7) & 1;              // column half
     const int gw = gt >> 5;                    // warp inside the group (0..7)
-    {   // group 0 stages K, group 1 stages V (the loaders fetch the first Q tiles meanwhile)
-      const T* kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + key0) * p.k_rs + (int64_t)hk * p.k_hs;
-      const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
-      if (g == 0) dense_cp_async<T, D / 8, C, kFwdGroupThreads>(gt, sK, kKBlock, kbase, p.k_rs, keys_valid);
-      else dense_cp_async<T, D / 8, C, kFwdGroupThreads>(gt, sV, kKBlock, vbase, p.v_rs, keys_valid);
-      cp_async_wait_all();
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar_kv);
-    }
-    FMB_TICK(0);   // prologue
     unsigned char* sPO = sPOg + g * (kTcM * QP * 2);
     const uint32_t tS = tmem_base + g * 256, tO = tS + 128;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
     T* part_o = static_cast<T*>(p.part_o);
     const int bar_id = 2 + g;
     bool good = true;
+    uint32_t m = 0;                            // tiles of this group so far
 
 #pragma unroll 1
-    for (int i = g, n = 0; i < ntiles; i += kFwdGroups, ++n) {
-      const int t0 = i * kTcM;
-      const int rows = min(kTcM, nnz - t0);
-      if (gw < 4 && lane == 0) bulk_wait_read();   // the previous tile's O staging has been read out
-      if (good) good = mbar_wait(&bar_s[g], n & 1, p.status, 1);   // on failure: run on to the barrier
-      tc_fence_after_sync();
-      if (tid == 0) FMB_TICK(2);   // waiting for S
+    for (uint32_t n = 0; good; ++n) {
+      FwdItem it;
+      good = read_info(n, it);
+      good = bar_and(bar_id, kFwdGroupThreads, good);   // the group goes on, or leaves, together
+      if (!good || it.nnz <= 0) break;
+      const int ntiles = (it.nnz + kTcM - 1) / kTcM;
+      if (tid == 0) FMB_TICK(1);   // item boundary
+#pragma unroll 1
+      for (int i = g; i < ntiles; i += kFwdGroups, ++m) {
+        const int t0 = i * kTcM;
+        const int rows = min(kTcM, it.nnz - t0);
+        if (gw < 4 && lane == 0) bulk_wait_read();   // the previous tile's O staging has been read out
+        if (good) good = mbar_wait(&bar_s[g], m & 1, p.status, 1);   // on failure: run on to the barrier
+        tc_fence_after_sync();
+        if (tid == 0) FMB_TICK(2);   // waiting for S
 
-      // ---- chunk-local softmax of row `lt`, this thread's half of the keys
-      const int r = sRow[g][n & 1][lt];
-      const int lim = r < 0 ? 0 : (p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid);
-      // two passes over the row's scores in TMEM (maximum, then exponentials), 32 at a time: keeps
-      // the thread at 32 live scores, which is what the register budget of 21 warps allows
-      float mx = -CUDART_INF_F;
+        // ---- chunk-local softmax of row `lt`, this thread's half of the keys
+        const int r = sRow[g][m & 1][lt];
+        const int lim = r < 0 ? 0 : (p.causal ? min(it.keys_valid, r + it.shift - it.key0 + 1) : it.keys_valid);
+        // two passes over the row's scores in TMEM (maximum, then exponentials), 32 at a time: keeps
+        // the thread at 32 live scores, which is what the register budget of 22 warps allows
+        float mx = -CUDART_INF_F;
 #pragma unroll
-      for (int q4 = 0; q4 < CH / 32; ++q4) {
-        float s[32];
-        tmem_ld32(tS + lane_sel + hf * CH + q4 * 32, s);
-        tmem_ld_wait();
-        if (lim >= C) {   // nothing masked: the common case away from the causal diagonal
+        for (int q4 = 0; q4 < CH / 32; ++q4) {
+          float s[32];
+          tmem_ld32(tS + lane_sel + hf * CH + q4 * 32, s);
+          tmem_ld_wait();
+          if (lim >= C) {   // nothing masked: the common case away from the causal diagonal
 #pragma unroll
-          for (int jj = 0; jj < 32; ++jj) mx = fmaxf(mx, s[jj]);
-        } else {
+            for (int jj = 0; jj < 32; ++jj) mx = fmaxf(mx, s[jj]);
+          } else {
 #pragma unroll
-          for (int jj = 0; jj < 32; ++jj) mx = fmaxf(mx, hf * CH + q4 * 32 + jj < lim ? s[jj] : -CUDART_INF_F);
+            for (int jj = 0; jj < 32; ++jj) mx = fmaxf(mx, hf * CH + q4 * 32 + jj < lim ? s[jj] : -CUDART_INF_F);
+          }
         }
-      }
-      sMax[g][hf][lt] = mx;
-      good = bar_and(bar_id, kFwdGroupThreads, good);   // also: the previous bulk reads are done
-      if (!good) break;
-      mx = fmaxf(mx, sMax[g][hf ^ 1][lt]);
-      const float mref = lim > 0 ? mx * scale_log2 : 0.f;
-      float sum = 0.f;
+        sMax[g][hf][lt] = mx;
+        good = bar_and(bar_id, kFwdGroupThreads, good);   // also: the previous bulk reads are done
+        if (!good) break;
+        mx = fmaxf(mx, sMax[g][hf ^ 1][lt]);
+        const float mref = lim > 0 ? mx * scale_log2 : 0.f;
+        float sum = 0.f;
 #pragma unroll
-      for (int q4 = 0; q4 < CH / 32; ++q4) {
-        float s[32];
-        tmem_ld32(tS + lane_sel + hf * CH + q4 * 32, s);
-        tmem_ld_wait();
+        for (int q4 = 0; q4 < CH / 32; ++q4) {
+          float s[32];
+          tmem_ld32(tS + lane_sel + hf * CH + q4 * 32, s);
+          tmem_ld_wait();
 #pragma unroll
-        for (int jj = 0; jj < 32; ++jj) {
-          const float e = exp2f(s[jj] * scale_log2 - mref);
-          s[jj] = (lim >= C || hf * CH + q4 * 32 + jj < lim) ? e : 0.f;
-          sum += s[jj];
+          for (int jj = 0; jj < 32; ++jj) {
+            const float e = exp2f(s[jj] * scale_log2 - mref);
+            s[jj] = (lim >= C || hf * CH + q4 * 32 + jj < lim) ? e : 0.f;
+            sum += s[jj];
+          }
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj)
+            *reinterpret_cast<uint4*>(sPO + sw128_offset(lt, hf * (CH / 8) + q4 * 4 + jj, kQBlock)) = pack8<T>(s + jj * 8);
         }
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj)
-          *reinterpret_cast<uint4*>(sPO + sw128_offset(lt, hf * (CH / 8) + q4 * 4 + jj, kQBlock)) = pack8<T>(s + jj * 8);
-      }
-      tc_fence_before_sync();
-      sSum[g][hf][lt] = sum;
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar_pready[g]);   // S has been read, P is in shared memory
-      if (tid == 0) FMB_TICK(3);   // softmax
-      bar_sync(bar_id, kFwdGroupThreads);           // the other half's sum
-      sum += sSum[g][hf ^ 1][lt];
-      const float inv = sum > 0.f ? 1.f / sum : 0.f;
-      if (hf == 0 && lt < rows) p.part_lse[plane + slot0 + t0 + lt] = sum > 0.f ? mx * p.scale + logf(sum) : -CUDART_INF_F;
-      if (good) good = mbar_wait(&bar_o[g], n & 1, p.status, 2);
-      tc_fence_after_sync();
-      if (tid == 0) FMB_TICK(5);   // waiting for O = P.V
-
-      // ---- epilogue: normalised partial O of row `lt`, this thread's half of the head dim,
-      // staged in the P tile (its MMAs have completed); one bulk copy per 32 rows
-      {
-        const int key = (int)((slot0 + t0 + lt) & 7);
-        unsigned char* srow = sPO + lt * (D * 2);
-        float o[DH];
-#pragma unroll
-        for (int q4 = 0; q4 < DH / 32; ++q4) tmem_ld32(tO + lane_sel + hf * DH + q4 * 32, o + q4 * 32);
-        tmem_ld_wait();
-#pragma unroll
-        for (int jj = 0; jj < DH; ++jj) o[jj] *= inv;
-#pragma unroll
-        for (int jj = 0; jj < DH / 8; ++jj)
-          *reinterpret_cast<uint4*>(srow + (((hf * (DH / 8) + jj) ^ key) << 4)) = pack8<T>(o + jj * 8);
         tc_fence_before_sync();
+        sSum[g][hf][lt] = sum;
         fence_async_smem();
-      }
-      good = bar_and(bar_id, kFwdGroupThreads, good);   // both halves of every row staged
-      if (!good) break;
-      if (gw < 4) {
-        const int wrows = min(32, rows - gw * 32);   // a warp's rows are contiguous in the workspace
-        if (lane == 0 && wrows > 0) {
-          bulk_store(part_o + (plane + slot0 + t0 + gw * 32) * D, sPO + gw * 32 * (D * 2), (uint32_t)wrows * D * 2);
-          bulk_commit();   // its reads are waited for before the next tile's P is stored
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_pready[g]);   // S has been read, P is in shared memory
+        if (tid == 0) FMB_TICK(3);   // softmax
+        bar_sync(bar_id, kFwdGroupThreads);           // the other half's sum
+        sum += sSum[g][hf ^ 1][lt];
+        const float inv = sum > 0.f ? 1.f / sum : 0.f;
+        if (hf == 0 && lt < rows) p.part_lse[it.slot + t0 + lt] = sum > 0.f ? mx * p.scale + logf(sum) : -CUDART_INF_F;
+        if (good) good = mbar_wait(&bar_o[g], m & 1, p.status, 2);
+        tc_fence_after_sync();
+        if (tid == 0) FMB_TICK(5);   // waiting for O = P.V
+
+        // ---- epilogue: normalised partial O of row `lt`, this thread's half of the head dim,
+        // staged in the P tile (its MMAs have completed); one bulk copy per 32 rows
+        {
+          const int key = (int)((it.slot + t0 + lt) & 7);
+          unsigned char* srow = sPO + lt * (D * 2);
+          float o[DH];
+#pragma unroll
+          for (int q4 = 0; q4 < DH / 32; ++q4) tmem_ld32(tO + lane_sel + hf * DH + q4 * 32, o + q4 * 32);
+          tmem_ld_wait();
+#pragma unroll
+          for (int jj = 0; jj < DH; ++jj) o[jj] *= inv;
+#pragma unroll
+          for (int jj = 0; jj < DH / 8; ++jj)
+            *reinterpret_cast<uint4*>(srow + (((hf * (DH / 8) + jj) ^ key) << 4)) = pack8<T>(o + jj * 8);
+          tc_fence_before_sync();
+          fence_async_smem();
         }
+        good = bar_and(bar_id, kFwdGroupThreads, good);   // both halves of every row staged
+        if (!good) break;
+        if (gw < 4) {
+          const int wrows = min(32, rows - gw * 32);   // a warp's rows are contiguous in the workspace
+          if (lane == 0 && wrows > 0) {
+            bulk_store(part_o + (it.slot + t0 + gw * 32) * D, sPO + gw * 32 * (D * 2), (uint32_t)wrows * D * 2);
+            bulk_commit();   // its reads are waited for before the next tile's P is stored
+          }
+        }
+        if (tid == 0) FMB_TICK(6);   // epilogue
       }
-      if (tid == 0) FMB_TICK(6);   // epilogue
     }
     if (gw < 4 && lane == 0) bulk_wait_read();
   }
   tc_fence_before_sync();
-  __syncthreads();         // every role is done with the item's tiles, barriers and TMEM columns
+  __syncthreads();         // every role is done with its tiles, barriers and TMEM columns
   tc_fence_after_sync();
-  FMB_TICK(7);             // waiting for the other roles
-  }  // work items
-  __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, NCOLS);
 }
 
@@ -509,7 +583,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   constexpr int DH = D / 2;                       // head-dim columns per thread in the epilogues
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ uint64_t bar_s, bar_p, bar_dq, bar_dv, bar_fin, bar_fulldo, bar_dk[2], bar_fullq[2];
-  __shared__ uint64_t bar_pready, bar_dsready, bar_dqfree, bar_kv, bar_item[4];
+  __shared__ uint64_t bar_pready, bar_dsready, bar_dqfree, bar_kv, bar_rows, bar_item[4];
   __shared__ float sLse[kTcM], sDsum[kTcM];        // log-sum-exp and dO.O of the rows of the dO tile
   __shared__ int s_tile[4];                       // that tile's valid rows, first slot (64 bit), "another tile follows"
   __shared__ uint32_t tmem_base_s;
@@ -549,6 +623,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
     mbar_init(&bar_pready, kBwdCompute / 32); mbar_init(&bar_dsready, kBwdCompute / 32);
     mbar_init(&bar_dqfree, kBwdCompute / 32);   // one arrival per compute warp
     mbar_init(&bar_kv, 1);
+    mbar_init(&bar_rows, kBwdOLoaders / 32);
 #pragma unroll
     for (int k = 0; k < 4; ++k) { mbar_init(&bar_item[k], 1); mbar_init(&bar_info[k], 1); }
     mbar_fence_init();
@@ -775,23 +850,10 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
         if (q_side) {
           if (m >= 2) ok = mbar_wait(&bar_dk[m & 1], ((m >> 1) - 1) & 1, p.status, 5);   // dK(m-2) has read Q
         } else {
-          if (m >= 1) ok = mbar_wait(&bar_dv, (m - 1) & 1, p.status, 5);                 // dV(m-1) has read dO
-        }
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          if (t + k * nt < kTcM) sRow[t + k * nt] = rid[k];
-        ok = bar_and(bar_id, nt, ok);                // also publishes the row ids to the group
-        FMB_TICK_AT(24, 288); FMB_TICK_AT(26, 288 + kBwdQLoaders);  // loaders: row ids + waiting for the buffer
-        if (!ok) break;
-        if (q_side) {
-          const T* qbase = static_cast<const T*>(p.q) + (int64_t)I.q0 * p.q_rs + (int64_t)h * p.q_hs;
-          gather_cp_async<T, D / 8, kBwdQLoaders>(t, sQ + (m & 1) * kQTile, kQBlock, qbase, p.q_rs, sRow);
-        } else {
-          const T* dobase = static_cast<const T*>(p.dout) + (int64_t)I.q0 * p.do_rs + (int64_t)h * p.do_hs;
-          gather_cp_async<T, D / 8, kBwdOLoaders>(t, sdO, kQBlock, dobase, p.do_rs, sRow);
-          // while the copies fly: what the compute warps need to know about the tile's rows, so that
-          // they issue no global loads of their own (the previous tile's values were copied to
-          // registers before P_ready, which precedes the dV GEMM this loader has waited for)
+          // What the compute warps need to know about the tile's rows (so that they issue no global
+          // loads of their own) goes ahead of the tile: it may be written as soon as they have copied
+          // the previous tile's values to registers, which they do before P_ready.
+          if (m >= 1) ok = mbar_wait(&bar_pready, (m - 1) & 1, p.status, 5);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             if (t + k * nt < kTcM) {
@@ -801,6 +863,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
                 l = p.lse[at];
                 dd = p.softmax_d[at];
               }
+              sRow[t + k * nt] = rid[k];
               sLse[t + k * nt] = l;
               sDsum[t + k * nt] = dd;
             }
@@ -812,6 +875,24 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
             s_tile[2] = (int)(uint32_t)((uint64_t)slot >> 32);
             s_tile[3] = more ? 1 : 0;
           }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bar_rows);
+          if (ok && m >= 1) ok = mbar_wait(&bar_dv, (m - 1) & 1, p.status, 5);           // dV(m-1) has read dO
+        }
+        if (q_side) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            if (t + k * nt < kTcM) sRow[t + k * nt] = rid[k];
+        }
+        ok = bar_and(bar_id, nt, ok);                // also publishes the row ids to the group
+        FMB_TICK_AT(24, 288); FMB_TICK_AT(26, 288 + kBwdQLoaders);  // loaders: row ids + waiting for the buffer
+        if (!ok) break;
+        if (q_side) {
+          const T* qbase = static_cast<const T*>(p.q) + (int64_t)I.q0 * p.q_rs + (int64_t)h * p.q_hs;
+          gather_cp_async<T, D / 8, kBwdQLoaders>(t, sQ + (m & 1) * kQTile, kQBlock, qbase, p.q_rs, sRow);
+        } else {
+          const T* dobase = static_cast<const T*>(p.dout) + (int64_t)I.q0 * p.do_rs + (int64_t)h * p.do_hs;
+          gather_cp_async<T, D / 8, kBwdOLoaders>(t, sdO, kQBlock, dobase, p.do_rs, sRow);
         }
         cp_async_wait_all();
         fence_async_smem();        // the copies are generic-proxy writes; the MMAs read through the async proxy
@@ -910,7 +991,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
         // ---- P of row `lt`, this thread's 64 keys
         FMB_TICK(47);   // loop back
         if (good) good = mbar_wait(&bar_s, g & 1, p.status, 3);   // on failure: run on to the barriers, leave there
-        if (good) good = mbar_wait(&bar_fulldo, g & 1, p.status, 3);   // row data of the tile (long landed)
+        if (good) good = mbar_wait(&bar_rows, g & 1, p.status, 3);   // row data of the tile (long landed)
         tc_fence_after_sync();
         if (!prev_any) FMB_TICK(39);   // waiting for S, first tile of an item
         FMB_TICK(17);   // waiting for S
