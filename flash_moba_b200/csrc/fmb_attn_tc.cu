@@ -516,6 +516,9 @@ constexpr int kBwdCompute = 256;
 #endif
 constexpr int kBwdQLoaders = 32 * FMB_BWD_QW;
 constexpr int kBwdOLoaders = 32 * FMB_BWD_OW;
+#ifndef FMB_BWD_BOUNDS
+#define FMB_BWD_BOUNDS __launch_bounds__(kBwdThreads)
+#endif
 constexpr int kBwdScoutWarp = (kBwdCompute + 32 + kBwdQLoaders + kBwdOLoaders) / 32;   // K/V loader and item scout
 constexpr int kBwdThreads = kBwdCompute + 32 + kBwdQLoaders + kBwdOLoaders + 32;
 
@@ -574,7 +577,7 @@ __device__ __forceinline__ void bwd_decode_item(const TcParams& p, int item, int
 }
 
 template <typename T, int C, int D>
-__global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
+__global__ void FMB_BWD_BOUNDS bwd_main_tc_kernel(TcParams p) {
   static_assert(C == 128, "tensor-core backward keeps one key per TMEM lane");
   constexpr uint32_t kKBlock = C * 128;
   constexpr uint32_t kQBlock = kTcM * 128;
@@ -918,8 +921,11 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
       BwdItem I;
       BwdTile it;
       bool have;
+      FMB_TICK(51);   // after the item's last tile
       const int state = read_info(n, I, it, have);
+      FMB_TICK(52);   // item info
       good = bar_and(2, kBwdCompute, good && state >= 0);
+      FMB_TICK(53);   // the other compute warps
       const bool done = !good || state == 0;
       int fetched = 0;
       if (tid == 0 && !done) fetched = atomicAdd(p.work, 1);      // item n + 2, published below
@@ -929,43 +935,55 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
 
       // ---- the previous item's GEMMs have completed: its dK and dV are final
       if (prev) {
-        if (warp < 4 && lane == 0) bulk_wait_read();
+        if (warp < 4) bulk_wait_read();
         if (good) good = mbar_wait(&bar_fin, (nk - 1) & 1, p.status, 4);
         good = bar_and(2, kBwdCompute, good);
         tc_fence_after_sync();
+        FMB_TICK(54);   // the previous item's last GEMMs
       }
-      // ---- dK and dV of key `lt` of the previous item, this thread's half of the head dim
-      {
+      // ---- dK and dV of key `lt` of the previous item, this thread's half of the head dim: staged in
+      // the P / dS tiles (free between items) with rows 16 bytes apart from a multiple of 128, which
+      // keeps the 16-byte stores of a warp off each other's banks, then one bulk copy per key row.
+      // dK first, then dV through the same staging area.
+      if (prev && good) {
         // (written by thread 0 after the item's last tile; the barrier at the top of this iteration orders the read)
         const int64_t prev_row = s_prev[0];
         const int prev_hk = s_prev[1], prev_keys = s_prev[2];
-        T* dkp = static_cast<T*>(p.dk) + (prev_row + lt) * p.dk_rs + (int64_t)prev_hk * p.dk_hs + hf * DH;
-        T* dvp = static_cast<T*>(p.dv) + (prev_row + lt) * p.dv_rs + (int64_t)prev_hk * p.dv_hs + hf * DH;
+        constexpr int kPitch = D * 2 + 16;
+        static_assert(kTcM * kPitch <= 2 * kTcM * C * 2, "staging area = the P and dS tiles");
+        unsigned char* srow = sP + lt * kPitch;
 #pragma unroll
-        for (int i2 = 0; i2 < DH / 32; ++i2) {
-          if (prev && good) {
+        for (int which = 0; which < 2; ++which) {
+          if (which == 1) {            // the dK rows have been read out of the staging area
+            if (hf == 0) bulk_wait_read();
+            good = bar_and(2, kBwdCompute, good);
+          }
+#pragma unroll
+          for (int i2 = 0; i2 < DH / 32; ++i2) {
             float o[32];
             if (prev_any) {
-              tmem_ld32(tdK + lane_sel + hf * DH + i2 * 32, o);
+              tmem_ld32((which == 0 ? tdK : tdV) + lane_sel + hf * DH + i2 * 32, o);
               tmem_ld_wait();
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j) o[j] = 0.f;
             }
-            if (lt < prev_keys) {
+            if (which == 0) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) o[j] *= p.scale;
+            }
 #pragma unroll
-              for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(dkp + i2 * 32 + j * 8) = pack8<T>(o + j * 8);
-            }
-            if (prev_any) {
-              tmem_ld32(tdV + lane_sel + hf * DH + i2 * 32, o);
-              tmem_ld_wait();
-            }
-            if (lt < prev_keys) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(dvp + i2 * 32 + j * 8) = pack8<T>(o + j * 8);
-            }
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint4*>(srow + (hf * DH + i2 * 32 + j * 8) * 2) = pack8<T>(o + j * 8);
+          }
+          fence_async_smem();
+          good = bar_and(2, kBwdCompute, good);   // both halves of every row staged
+          if (good && hf == 0 && lt < prev_keys) {
+            T* dst = which == 0
+                         ? static_cast<T*>(p.dk) + (prev_row + lt) * p.dk_rs + (int64_t)prev_hk * p.dk_hs
+                         : static_cast<T*>(p.dv) + (prev_row + lt) * p.dv_rs + (int64_t)prev_hk * p.dv_hs;
+            bulk_store(dst, srow, D * 2);
+            bulk_commit();
           }
         }
         tc_fence_before_sync();
@@ -1015,8 +1033,8 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
           for (int jj = 0; jj < 32; ++jj) pr[jj] = (col0 + jj < lim) ? exp2f(pr[jj] * scale_log2 - lse2) : 0.f;
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) pp[i2 * 4 + jj] = pack8<T>(pr + jj * 8);
-          if (i2 == 0) {               // the previous tile's dQ staging (in the P tile) has been read out
-            if (warp < 4 && lane == 0) bulk_wait_read();
+          if (i2 == 0) {               // the previous tile's dQ staging / the dK, dV staging has been read out
+            if (warp < 4) bulk_wait_read();
             good = bar_and(2, kBwdCompute, good);
           }
 #pragma unroll
@@ -1103,7 +1121,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
       if (tid == 0) { s_prev[0] = I.k0 + I.key0; s_prev[1] = I.hk; s_prev[2] = I.keys_valid; }
       ++nk;
     }
-    if (warp < 4 && lane == 0) bulk_wait_read();
+    if (warp < 4) bulk_wait_read();
   }
   tc_fence_before_sync();
   __syncthreads();         // every role is done with its tiles, barriers and TMEM columns
