@@ -94,7 +94,7 @@ class ClockSampler:
             try:
                 sm = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
                 bits = int(get_reasons(h)) if get_reasons else 0
-                self.rows.append((float(sm), float(mx) if mx else None, bits))
+                self.rows.append((float(sm), float(mx) if mx else None, bits, time.perf_counter()))
             except Exception as e:      # reported in the summary, never fatal
                 self.error = repr(e)
             self.stop.wait(self.period)
@@ -124,7 +124,7 @@ class ClockSampler:
                 bits = sum(b for (name, b), v in zip((("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40),
                                                       ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4)), r[2:6])
                            if v.lower().startswith("active"))
-                self.rows.append((float(r[0]), float(r[1]), bits))
+                self.rows.append((float(r[0]), float(r[1]), bits, time.perf_counter()))
             except (ValueError, IndexError):
                 continue
 
@@ -139,17 +139,30 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.proc.kill()
 
+    def mark(self, which):
+        """Host time stamps of the timed region's start and end (the sampler itself runs from the
+        warm-up on, so that a slow first NVML call does not eat the timed region)."""
+        setattr(self, "t_" + which, time.perf_counter())
+
     def summary(self):
-        if not self.rows:
+        t0, t1 = getattr(self, "t_start", None), getattr(self, "t_end", None)
+        rows, window = self.rows, "sampler lifetime"
+        if t0 is not None and t1 is not None:
+            inside = [r for r in self.rows if t0 <= r[3] <= t1]
+            if len(inside) >= 3:
+                rows, window = inside, "timed region"
+            else:   # a box whose NVML calls take tens of milliseconds: the warm-up steps are the same load
+                rows, window = [r for r in self.rows if r[3] <= t1], f"warm-up + timed region ({len(inside)} inside the timed region)"
+        if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "error": self.error}
-        sm = [r[0] for r in self.rows]
-        mx = [r[1] for r in self.rows if r[1]]
+        sm = [r[0] for r in rows]
+        mx = [r[1] for r in rows if r[1]]
         bits = 0
-        for r in self.rows:
+        for r in rows:
             bits |= r[2]
         reasons = sorted(n for n, b in self.REASON_BITS.items() if bits & b)
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
-                "samples": len(sm), "source": "nvml" if self.nvml is not None else "nvidia-smi"}
+                "samples": len(sm), "window": window, "source": "nvml" if self.nvml is not None else "nvidia-smi"}
 
 
 def cpu_sample(seqlens, d, chunk, topk, rows=4096, threads=None):
@@ -265,19 +278,21 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        step(q, k, v, do)
-    barrier()
-    launches0 = _lib.lib.fmb_launch_count()
-    _lib.lib.fmb_profile_enable(1)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clk:
+        for _ in range(args.warmup):
+            step(q, k, v, do)
         barrier()
+        launches0 = _lib.lib.fmb_launch_count()
+        _lib.lib.fmb_profile_enable(1)
+        barrier()
+        clk.mark("start")
         ev0.record()
         for _ in range(args.steps):
             step(q, k, v, do)
         ev1.record()
         barrier()
+        clk.mark("end")
     ms = ev0.elapsed_time(ev1) / args.steps
     launches = _lib.lib.fmb_launch_count() - launches0
     import ctypes
@@ -349,7 +364,7 @@ def main():
     # 16-head case (dram__bytes_read.sum + dram__bytes_write.sum = 1,038.1 MB over its 2,039,808
     # entries); the traffic is per-entry work (gathered rows in, partial rows out), so it scales
     # with the entries.
-    entry_bytes = {"bwd_main": 508.9}.get(dom) if (d == 128 and chunk == 128) else None
+    entry_bytes = {"bwd_main": 548.5}.get(dom) if (d == 128 and chunk == 128) else None
     entries = ACC.selected_entries(seqlens, chunk, topk) * h_loc
     if kern_ms.get(dom):
         ach = dom_flops / (kern_ms[dom] * 1e-3) / 1e12

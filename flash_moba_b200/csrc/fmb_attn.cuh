@@ -33,7 +33,7 @@ __host__ __device__ __forceinline__ int part_col(int64_t pos, int col, int elems
 // key block KB is handled as nsub = chunk / KB sub-blocks, each with its own plane of `cap`
 // slots: the partial of (entry j of the column, sub-block sb) lives at sb*cap + slot_base + j.
 struct AttnWorkspace {
-  int* status;          // first word: 0, or where a bounded device wait gave up / 7 = slot overflow
+  int* status;          // first word: 0, or where a bounded device wait gave up (1-6, 8) / 7 = slot overflow / 9 = misaligned shared memory
   void* part_o;         // nsub*cap*d elements of the I/O dtype (fwd: O partials, bwd: dQ partials)
   float* part_lse;      // fwd only: nsub*cap
   uint32_t* slot_base;  // batch*nh*ncol + 1

@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
 
   // n-th item of this CTA's stream; false: the wait gave up (error recorded).  it.nnz == 0: the end.
   auto read_info = [&](uint32_t n, FwdItem& it) -> bool {
-    if (!mbar_wait(&bar_info[n & 3], (n >> 2) & 1, p.status, 7)) {
+    if (!mbar_wait(&bar_info[n & 3], (n >> 2) & 1, p.status, 8)) {
       it.nnz = 0;
       return false;
     }
@@ -230,14 +230,14 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
 #pragma unroll 1
     for (uint32_t n = 0; more && ok; ++n) {
       // K of item n: every S GEMM of item n - 1 has completed; V: every P.V GEMM has
-      if (n > 0) ok = mbar_wait(&bar_sfin, (n - 1) & 1, p.status, 7);
+      if (n > 0) ok = mbar_wait(&bar_sfin, (n - 1) & 1, p.status, 8);
       if (!ok) break;
       dense_cp_async<T, D / 8, C, 32>(lane, sK, kKBlock, kbase, p.k_rs, keys_valid);
       cp_async_wait_all();
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar_k);
-      if (n > 0) ok = mbar_wait(&bar_fin, (n - 1) & 1, p.status, 7);
+      if (n > 0) ok = mbar_wait(&bar_fin, (n - 1) & 1, p.status, 8);
       if (!ok) break;
       dense_cp_async<T, D / 8, C, 32>(lane, sV, kKBlock, vbase, p.v_rs, keys_valid);
       cp_async_wait_all();
@@ -474,31 +474,41 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
 
 
 // ======================================================================== backward
-// CTA = key block c of (sequence b, kv head hk); 480 threads, warp-specialised:
+// Work item = key block c of (sequence b, kv head hk); 512 threads, warp-specialised, one
+// persistent CTA per SM that runs through its work items as ONE stream of 128-row tiles:
 //   warps 0-7   compute.  TMEM lane = gathered query row (at the end: key); warps w and w+4 share
-//               a lane quarter and split the columns in halves.
+//               a lane quarter and split the columns in halves.  They issue no global loads.
 //   warp 8      one thread issues every MMA; it alone waits for operand tiles, so a late gather
 //               never stalls a compute warp that still has work.
 //   warps 9-10  Q loader, warps 11-14 dO loader: 16-byte cp.async copies of the tile's rows
 //               straight into the swizzled UMMA tiles (no registers; measured ~4x the throughput
 //               of loads into registers, and ~3.5x that of TMA tile::gather4 row gathers for these
 //               isolated 256-byte rows).  Q is double buffered (its loader has two tiles of slack);
-//               dO is refilled as soon as the dV GEMM of the previous tile has completed.
-// The CTA walks the q heads of the kv head's group and the 128-row tiles of each head's CSC
-// column as one sequence of tiles.  Per tile, five GEMMs:
+//               dO is refilled as soon as the dV GEMM of the previous tile has completed.  Ahead of
+//               the dO tile its loader leaves the rows' query positions, log-sum-exps, dO.O sums
+//               and the tile's slot range in shared memory for the compute warps.
+//   warp 15     scout: decodes item n + 1 (geometry, first tile: a chain of dependent global
+//               loads) while item n runs and publishes it in a shared-memory ring; stages an
+//               item's K and V tiles as soon as every GEMM of the item before it has completed.
+// An item's tiles are the q heads of the kv head's group and the 128-row tiles of each head's CSC
+// column.  Per tile, five GEMMs:
 //     S  = Q.K^T          dP = dO.V^T                       (both K-major operands)
 //     dV += P^T.dO        dK += dS^T.Q   (A and B consumed MN-major from the row-major tiles)
 //     dQ_partial = dS.K   (K consumed MN-major)             -> workspace at the entry's slot
-// dK and dV stay in TMEM (fp32) for the CTA's whole life: no atomics, no cross-head reduction
-// pass.  TMEM columns: [0,C) S, [C,2C) dP then dQ, [2C,2C+D) dV, [2C+D,2C+2D) dK.
+// dK and dV stay in TMEM (fp32) for the whole item: no atomics, no cross-head reduction pass; they
+// are written out while the next item's first GEMMs run.  TMEM columns: [0,C) S, [C,2C) dP then
+// dQ, [2C,2C+D) dV, [2C+D,2C+2D) dK.
 //
-// All hand-offs are mbarriers.  Per tile i (the tensor pipe executes the GEMMs in issue order):
-//   compute:  wait S(i)  -> P = exp2(S.scale.log2e - LSE.log2e) -> shared (bf16) + registers (fp32) -> P_ready
-//             wait dP(i) -> dS = P.(dP - D) -> shared (bf16)                                        -> dS_ready
-//             wait dQ(i) -> dQ partial: TMEM -> registers -> global (scaled, I/O dtype)             -> dQ_free
-//   issuer:   P_ready(i)  -> dV(i) [its completion frees dO and P], S(i+1) once Q(i+1) has landed
-//             dS_ready(i) -> dQ(i) over dP's columns, dK(i) [its completion frees this Q buffer]
-//             dO(i+1) landed and dQ_free(i) -> dP(i+1)
+// All hand-offs are mbarriers, initialised once; their phases are counted over the stream.  Per
+// tile g (the tensor pipe executes the GEMMs in issue order):
+//   compute:  wait S(g)  -> P = exp2(S.scale.log2e - LSE.log2e) -> shared (bf16) + registers      -> P_ready
+//             wait dP(g) -> dS = P.(dP - D) -> shared (bf16)                                        -> dS_ready
+//             wait dQ(g) -> dQ partial: TMEM -> registers -> staging -> global (scaled, I/O dtype)  -> dQ_free
+//   issuer:   P_ready(g)  -> dV(g) [its completion frees dO and P], S(g+1) once Q(g+1) has landed
+//             dS_ready(g) -> dQ(g) over dP's columns, dK(g) [its completion frees this Q buffer]
+//             dO(g+1) landed and dQ_free(g) -> dP(g+1)
+//   at an item's end the issuer commits "item finished"; the scout then loads the next K, V, the
+//   compute warps read dK, dV out of TMEM.
 constexpr int kBwdCompute = 256;
 // Loader warps.  Measured at 64K tokens (backward main kernel): 1 + 2 warps 5.14 ms, 2 + 2 warps
 // 4.98 ms, 2 + 4 warps 4.63 ms, 1 + 4 warps 5.2 ms: the gathers are latency bound per warp.
@@ -648,7 +658,7 @@ __global__ void FMB_BWD_BOUNDS bwd_main_tc_kernel(TcParams p) {
   // keys, g / m: tiles) that every role advances in the same way.
   // n-th item of this CTA (p.n_items or more: the counter has run out); read by the scout warp only
   auto get_item = [&](uint32_t n, int& item) -> bool {
-    if (!mbar_wait(&bar_item[n & 3], (n >> 2) & 1, p.status, 7)) {
+    if (!mbar_wait(&bar_item[n & 3], (n >> 2) & 1, p.status, 8)) {
       item = p.n_items;
       return false;
     }
@@ -659,7 +669,7 @@ __global__ void FMB_BWD_BOUNDS bwd_main_tc_kernel(TcParams p) {
   // cost a chain of three dependent global loads) and publishes it in s_info.
   // state: 0 = the stream has ended, 1 = item with tiles or keys, 2 = key block past the sequence's end
   auto read_info = [&](uint32_t n, BwdItem& I, BwdTile& it, bool& have) -> int {
-    if (!mbar_wait(&bar_info[n & 3], (n >> 2) & 1, p.status, 7)) return -1;
+    if (!mbar_wait(&bar_info[n & 3], (n >> 2) & 1, p.status, 8)) return -1;
     const volatile int* f = s_info[n & 3];
     const int state = f[0];
     I.c = f[1]; I.hk = f[2]; I.b = f[3]; I.q0 = f[4]; I.len_q = f[5]; I.k0 = f[6]; I.len_k = f[7];
@@ -819,7 +829,7 @@ __global__ void FMB_BWD_BOUNDS bwd_main_tc_kernel(TcParams p) {
       }
       more = scout_item(n + 1);
       if (!skip) {                   // every GEMM of item n has completed: its K and V tiles are free
-        if (ok) ok = mbar_wait(&bar_fin, nk & 1, p.status, 7);
+        if (ok) ok = mbar_wait(&bar_fin, nk & 1, p.status, 8);
         ++nk;
       }
     }
