@@ -510,25 +510,19 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
 //   at an item's end the issuer commits "item finished"; the scout then loads the next K, V, the
 //   compute warps read dK, dV out of TMEM.
 constexpr int kBwdCompute = 256;
-// Loader warps.  Measured at 64K tokens (backward main kernel): 1 + 2 warps 5.14 ms, 2 + 2 warps
-// 4.98 ms, 2 + 4 warps 4.63 ms, 1 + 4 warps 5.2 ms: the gathers are latency bound per warp.
+// Loader warps.  Measured at 64K tokens (backward main kernel, before the item stream): 1 + 2 warps
+// 5.14 ms, 2 + 2 warps 4.98 ms, 2 + 4 warps 4.63 ms, 1 + 4 warps 5.2 ms: the gathers are latency
+// bound per warp; with the item stream 3 + 3 warps 4.14 ms against 4.08 ms for 2 + 4.  Sixteen
+// warps are the most that keep 128 registers per thread (registers are allocated to warps in
+// groups of four: a seventeenth warp would bring the limit down to 96).
 #ifndef FMB_BWD_QW
 #define FMB_BWD_QW 2          // warps gathering Q rows
 #endif
 #ifndef FMB_BWD_OW
 #define FMB_BWD_OW 4          // warps gathering dO rows
 #endif
-#ifndef FMB_BWD_PACKED_P
-#define FMB_BWD_PACKED_P 1    // 1: P kept as packed I/O-dtype values between the P and dS phases
-#endif
-#ifndef FMB_BWD_S_EARLY
-#define FMB_BWD_S_EARLY 0     // 1: S(i+1) is issued before dQ(i), dK(i) instead of after them
-#endif
 constexpr int kBwdQLoaders = 32 * FMB_BWD_QW;
 constexpr int kBwdOLoaders = 32 * FMB_BWD_OW;
-#ifndef FMB_BWD_BOUNDS
-#define FMB_BWD_BOUNDS __launch_bounds__(kBwdThreads)
-#endif
 constexpr int kBwdScoutWarp = (kBwdCompute + 32 + kBwdQLoaders + kBwdOLoaders) / 32;   // K/V loader and item scout
 constexpr int kBwdThreads = kBwdCompute + 32 + kBwdQLoaders + kBwdOLoaders + 32;
 
@@ -587,7 +581,7 @@ __device__ __forceinline__ void bwd_decode_item(const TcParams& p, int item, int
 }
 
 template <typename T, int C, int D>
-__global__ void FMB_BWD_BOUNDS bwd_main_tc_kernel(TcParams p) {
+__global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   static_assert(C == 128, "tensor-core backward keeps one key per TMEM lane");
   constexpr uint32_t kKBlock = C * 128;
   constexpr uint32_t kQBlock = kTcM * 128;
@@ -769,10 +763,6 @@ __global__ void FMB_BWD_BOUNDS bwd_main_tc_kernel(TcParams p) {
             if (!more) break;
             issue_s();
             FMB_TICK_AT(38, 256);
-#ifdef FMB_TC_TIMING_S
-            mbar_wait(&bar_s, g & 1, p.status, 6);   // timing experiment: how long after its issue does S complete
-            FMB_TICK_AT(46, 256);
-#endif
             if (ok) issue_dp();
             FMB_TICK_AT(40, 256);
           }

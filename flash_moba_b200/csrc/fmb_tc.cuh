@@ -15,10 +15,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
-// an mbarrier has to be invalidated before its memory is initialised again
-__device__ __forceinline__ void mbar_inval(uint64_t* bar) {
-  asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ void mbar_fence_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
@@ -62,18 +58,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
 }
 
 
-// ---- loads that are issued where they are written
+// ---- a load that is issued where it is written
 // A plain load of read-only data may be moved by the compiler down to its first use (it does so
-// under register pressure), which turns a prefetch into a full-latency stall.  These are volatile
-// asm statements: they keep their place among the other volatile statements (barrier waits).
+// under register pressure), which turns a prefetch into a full-latency stall.  This is a volatile
+// asm statement: it keeps its place among the other volatile statements (barrier waits).
 __device__ __forceinline__ int ldg_s32_here(const int* ptr) {
   int v;
   asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(v) : "l"(ptr));
-  return v;
-}
-__device__ __forceinline__ float ldg_f32_here(const float* ptr) {
-  float v;
-  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(ptr));
   return v;
 }
 
