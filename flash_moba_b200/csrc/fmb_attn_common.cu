@@ -708,8 +708,8 @@ __global__ void __launch_bounds__(256) dot_do_o_kernel(const T* __restrict__ dou
 
 static int64_t warp_grid(int64_t warps) { return ceil_div64(warps, 8); }
 
-// Cascade: lane groups of 8 (rows of <= 8 partials), the warp-per-row wide kernel (<= 32), then the
-// generic kernel; each later stage runs only the rows the earlier ones left and exits at once if
+// Cascade: lane groups of 8 (rows of <= 8 partials), of 16 (<= 16, head dims of 128 and more), the
+// warp-per-row wide kernel (<= 32), then the generic kernel; each later stage runs only the rows the earlier ones left and exits at once if
 // there were none.
 static int64_t group_grid(int64_t rows, int G) { return ceil_div64(ceil_div64(rows, 32 / G), 8); }
 int sm_count() {
@@ -754,10 +754,20 @@ static int fwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const
   fwd_combine_group_kernel<T, 8, D / 8><<<first_grid(nb8), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, 0,
                                                                       nullptr, ovf, nb8);
   FMB_LAUNCH_CHECK("fwd_combine_group_kernel<8>");
-  combine_wide_kernel<T, D, true><<<late_grid(nbw), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, 9, ovf,
-                                                                 ovf + 1, nbw);
+  int* left = ovf;            // flag set by the stage before; rows of at least min_n partials are left
+  int min_n = 9;
+  if constexpr (D >= 128) {   // 16 lanes of a row own whole 16-byte chunks: two rows per warp
+    const int64_t nb16 = group_grid(rows, 16);
+    fwd_combine_group_kernel<T, 16, D / 16><<<late_grid(nb16), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs,
+                                                                           a.lse, 9, ovf, ovf + 1, nb16);
+    FMB_LAUNCH_CHECK("fwd_combine_group_kernel<16>");
+    left = ovf + 1;
+    min_n = 17;
+  }
+  combine_wide_kernel<T, D, true><<<late_grid(nbw), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, min_n,
+                                                                 left, ovf + 2, nbw);
   FMB_LAUNCH_CHECK("combine_wide_kernel<fwd>");
-  fwd_combine_kernel<T><<<late_grid(nbw), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, ovf + 1, 33, nbw);
+  fwd_combine_kernel<T><<<late_grid(nbw), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, ovf + 2, 33, nbw);
   FMB_LAUNCH_CHECK("fwd_combine_kernel");
   return FMB_OK;
 }
@@ -791,10 +801,20 @@ static int bwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const
   const int64_t nb8 = group_grid(rows, 8), nbw = warp_grid(rows);
   bwd_combine_group_kernel<T, 8, D / 8><<<first_grid(nb8), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 0, nullptr, ovf, nb8);
   FMB_LAUNCH_CHECK("bwd_combine_group_kernel<8>");
-  combine_wide_kernel<T, D, false><<<late_grid(nbw), 256, 0, s>>>(pd, nullptr, c, dq, a.dq_rs, a.dq_hs, nullptr, 9, ovf,
-                                                                  ovf + 1, nbw);
+  int* left = ovf;
+  int min_n = 9;
+  if constexpr (D >= 128) {
+    const int64_t nb16 = group_grid(rows, 16);
+    bwd_combine_group_kernel<T, 16, D / 16><<<late_grid(nb16), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 9, ovf, ovf + 1,
+                                                                           nb16);
+    FMB_LAUNCH_CHECK("bwd_combine_group_kernel<16>");
+    left = ovf + 1;
+    min_n = 17;
+  }
+  combine_wide_kernel<T, D, false><<<late_grid(nbw), 256, 0, s>>>(pd, nullptr, c, dq, a.dq_rs, a.dq_hs, nullptr, min_n,
+                                                                  left, ovf + 2, nbw);
   FMB_LAUNCH_CHECK("combine_wide_kernel<bwd>");
-  bwd_combine_kernel<T><<<late_grid(nbw), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, ovf + 1, 33, nbw);
+  bwd_combine_kernel<T><<<late_grid(nbw), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, ovf + 2, 33, nbw);
   FMB_LAUNCH_CHECK("bwd_combine_kernel");
   return FMB_OK;
 }

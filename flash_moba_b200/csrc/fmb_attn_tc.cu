@@ -411,11 +411,19 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
           float s[32];
           tmem_ld32(tS + lane_sel + hf * CH + q4 * 32, s);
           tmem_ld_wait();
+          if (lim >= C) {
 #pragma unroll
-          for (int jj = 0; jj < 32; ++jj) {
-            const float e = exp2f(s[jj] * scale_log2 - mref);
-            s[jj] = (lim >= C || hf * CH + q4 * 32 + jj < lim) ? e : 0.f;
-            sum += s[jj];
+            for (int jj = 0; jj < 32; ++jj) {
+              s[jj] = exp2f(s[jj] * scale_log2 - mref);
+              sum += s[jj];
+            }
+          } else {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) {
+              const float e = exp2f(s[jj] * scale_log2 - mref);
+              s[jj] = (hf * CH + q4 * 32 + jj < lim) ? e : 0.f;
+              sum += s[jj];
+            }
           }
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj)
