@@ -310,11 +310,18 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
     const T* qbase = static_cast<const T*>(p.q) + (int64_t)(q0 + r0) * p.q_rs + (int64_t)h * p.q_hs;
     const T* kmbase = static_cast<const T*>(p.km) + ((int64_t)km0 * p.heads_k + hk) * p.d;
     const int64_t km_rs = (int64_t)p.heads_k * p.d;
-    stage_tile_sw128<T, D / 8>(sQ, kBlock, qbase, p.q_rs, kGateM, [&](int r) { return r < rows ? (int64_t)r : -1; });
-    {
-      const int ncols = min(kGateN, n_end);
-      stage_tile_sw128<T, D / 8>(sKM, kBlock, kmbase, km_rs, kGateN, [&](int r) { return r < ncols ? (int64_t)r : -1; });
-    }
+    // The Q tile and the first two centroid tiles are copied with cp.async (no registers, all in
+    // flight at once); inside the loop the tile two steps ahead is copied while this step's scores
+    // are examined, and its MMA is issued at the step's end, so that neither a copy nor an MMA is
+    // waited for in the steady state.
+    auto stage_km = [&](int t) {
+      const int n1 = t * kGateN, nc = min(kGateN, n_end - n1);
+      dense_cp_async<T, D / 8, kGateN, 128 * NQ>(tid, sKM + (t & 1) * kTile, kBlock, kmbase + (int64_t)n1 * km_rs, km_rs, nc);
+    };
+    dense_cp_async<T, D / 8, kGateM, 128 * NQ>(tid, sQ, kBlock, qbase, p.q_rs, rows);
+    stage_km(0);
+    if (ntiles > 1) stage_km(1);
+    cp_async_wait_all();
     fence_async_smem();
     tc_fence_before_sync();
     __syncthreads();
@@ -331,27 +338,21 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
       }
       umma_commit(&bar[buf]);
     };
-    if (tid == 0) issue(0);
+    if (tid == 0) {
+      issue(0);
+      if (ntiles > 1) issue(1);
+    }
     uint32_t phases = 0;   // bit b = parity to wait for on bar[b]
     for (int t = 0; t < ntiles; ++t) {
       const int buf = t & 1;
       const int n0 = t * kGateN;
-      if (t + 1 < ntiles) {   // stage the next centroid tile (its buffer was read by MMA t-1, long complete)
-        const int n1 = n0 + kGateN, nc1 = min(kGateN, n_end - n1);
-        stage_tile_sw128<T, D / 8>(sKM + (buf ^ 1) * kTile, kBlock, kmbase + (int64_t)n1 * km_rs, km_rs, kGateN,
-                                   [&](int r) { return r < nc1 ? (int64_t)r : -1; });
-        fence_async_smem();
-      }
-      tc_fence_before_sync();
-      __syncthreads();   // next tile staged; every thread has finished reading TMEM buffer buf^1
-      if (tid == 0 && t + 1 < ntiles) {
-        tc_fence_after_sync();
-        issue(buf ^ 1);
-      }
       const bool ok = mbar_wait(&bar[buf], (phases >> buf) & 1u, &g_gate_status, 1);
       phases ^= 1u << buf;
       if (!__syncthreads_and(ok)) break;
       tc_fence_after_sync();
+      // MMA t has completed: its centroid buffer takes the tile two steps ahead
+      const bool ahead = t + 2 < ntiles;
+      if (ahead) stage_km(t + 2);
       constexpr int kCols = kGateN / NQ;        // columns of a tile examined by this thread
       const uint32_t taddr = tmem_base + buf * 128 + qd * kCols + ((uint32_t)((warp & 3) * 32) << 16);
       // 16 scores per step; the next 16 are fetched while these are examined.  A step first marks,
@@ -403,6 +404,16 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
               }
             }
           }
+        }
+      }
+      if (ahead) {             // CTA-uniform
+        cp_async_wait_all();
+        fence_async_smem();
+        tc_fence_before_sync();
+        __syncthreads();       // tile t + 2 staged; every thread has finished reading TMEM buffer buf
+        if (tid == 0) {
+          tc_fence_after_sync();
+          issue(buf);
         }
       }
     }
