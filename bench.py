@@ -364,7 +364,7 @@ def main():
     # 16-head case (dram__bytes_read.sum + dram__bytes_write.sum = 1,038.1 MB over its 2,039,808
     # entries); the traffic is per-entry work (gathered rows in, partial rows out), so it scales
     # with the entries.
-    entry_bytes = {"bwd_main": 548.5}.get(dom) if (d == 128 and chunk == 128) else None
+    entry_bytes = {"bwd_main": 559.3}.get(dom) if (d == 128 and chunk == 128) else None
     entries = ACC.selected_entries(seqlens, chunk, topk) * h_loc
     if kern_ms.get(dom):
         ach = dom_flops / (kern_ms[dom] * 1e-3) / 1e12
