@@ -221,10 +221,33 @@ def run_reference(args, wl):
                                    "fp32 PyTorch oracle (oracle/moba_oracle.py), per step"},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    emit(json.dumps(line))
+
+
+_RESULT_FD = None
+
+
+def protect_stdout():
+    """The driver reads ONE JSON line from stdout; libraries print there too (NCCL its version line
+    when NCCL_DEBUG asks for it).  From here on everything written to file descriptor 1 goes to
+    stderr, and only emit() writes to the real stdout."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(text):
+    sys.stdout.flush()
+    if _RESULT_FD is None:
+        print(text, flush=True)
+    else:
+        os.write(_RESULT_FD, (text + "\n").encode())
 
 
 def main():
+    protect_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
@@ -392,7 +415,7 @@ def main():
         line["cpu_baseline"] = {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                                 "sample": f"pattern+fwd+bwd of the last {rows} query rows of 1 head vs all "
                                           f"{seqlens[0]} keys, fp32 PyTorch oracle, {dt:.1f} s"}
-    print(json.dumps(line))
+    emit(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
 
