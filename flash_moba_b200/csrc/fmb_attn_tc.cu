@@ -1301,6 +1301,15 @@ static TcParams make_tc_params(const AttnArgs& a, const AttnWorkspace& w, const 
   return p;
 }
 
+// When the gathered rows of the whole pass (Q, and dO in the backward pass) fit in L2 whatever the
+// order of the work items, the key blocks are handed out longest columns first throughout: a launch
+// of few items per CTA (one rank's share of a multi-GPU run) is balanced best that way.  Measured:
+// 64K tokens x 4 heads 1.69 -> 1.62 ms per step; 512K tokens x 4 heads (1 GB of rows) 1 % slower,
+// hence the size test.
+static bool rows_fit_l2(const AttnArgs& a, const PassParams& ps) {
+  return (int64_t)a.total_q * a.d * 2 * 2 * ps.nh <= (int64_t)160 << 20;
+}
+
 template <typename T, int C, int D>
 static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   TcParams p = make_tc_params(a, w, ps);
@@ -1314,7 +1323,7 @@ static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassPa
   // persistent CTAs, one per SM
   p.work = w.status + 4;
   p.items_x = a.ncol * ps.nsub; p.items_y = ps.nh; p.items_z = a.batch;
-  p.items_heavy = a.causal ? min(p.items_x, 16 * ps.nsub) : 0;
+  p.items_heavy = !a.causal ? 0 : (rows_fit_l2(a, ps) ? p.items_x : min(p.items_x, 16 * ps.nsub));
   p.n_items = p.items_x * p.items_y * p.items_z;
   if (ps.h0 > 0) FMB_CUDA(cudaMemsetAsync(p.work, 0, sizeof(int), s));   // first pass: cleared with the status block
   kern<<<min(p.n_items, sm_count()), kFwdThreads, smem, s>>>(p);
@@ -1334,7 +1343,7 @@ static int bwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassPa
   // persistent CTAs, one per SM
   p.work = w.status + 4;
   p.items_x = nchunk * ps.nsub; p.items_y = ps.nh / (a.heads / a.heads_k); p.items_z = a.batch;
-  p.items_heavy = a.causal ? min(p.items_x, 16 * ps.nsub) : 0;
+  p.items_heavy = !a.causal ? 0 : (rows_fit_l2(a, ps) ? p.items_x : min(p.items_x, 16 * ps.nsub));
   p.n_items = p.items_x * p.items_y * p.items_z;
   if (ps.h0 > 0) FMB_CUDA(cudaMemsetAsync(p.work, 0, sizeof(int), s));   // first pass: cleared with the status block
   kern<<<min(p.n_items, sm_count()), kBwdThreads, smem, s>>>(p);
