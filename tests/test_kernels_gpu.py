@@ -354,6 +354,29 @@ def test_attention_rows_with_9_to_32_partials(chunk, d, max_picks):
     _attn_check(q, k, v, do, cu_of(lens), cu_of(lens), mask, chunk, True, 1)
 
 
+@pytest.mark.parametrize("chunk,d,causal,hk", [(64, 64, True, 4), (128, 128, True, 2), (128, 128, False, 1),
+                                               (256, 128, True, 2), (192, 64, True, 4)])
+def test_attention_many_work_items_per_cta(chunk, d, causal, hk):
+    """Many short, ragged sequences (some empty, some ending inside a key block): the persistent
+    CTAs of the main kernels each run through several work items, among them items whose column is
+    empty and key blocks that start past a sequence's end, with the next item decoded and its K/V
+    staged while the current one is still being worked on."""
+    torch.manual_seed(3)
+    g = torch.Generator().manual_seed(11)
+    lens = [int(x) for x in torch.randint(0, 900, (40,), generator=g)]
+    lens[3] = 0
+    lens[17] = chunk            # ends exactly on a chunk boundary
+    lens[18] = chunk + 1
+    H = 4
+    T = sum(lens)
+    q = torch.randn(T, H, d).bfloat16()
+    k = torch.randn(T, hk, d).bfloat16()
+    v = torch.randn(T, hk, d).bfloat16()
+    do = torch.randn(T, H, d).bfloat16()
+    mask = _random_mask(lens, lens, H, chunk, causal, 2, seed=4)
+    _attn_check(q, k, v, do, cu_of(lens), cu_of(lens), mask, chunk, causal, 1)
+
+
 @pytest.mark.parametrize("engine", [0, 1])
 @pytest.mark.parametrize("chunk,d", [(256, 128), (192, 128), (256, 64), (320, 64)])
 def test_attention_chunks_wider_than_a_key_block(chunk, d, engine):
