@@ -217,9 +217,10 @@ int fmb_selftest_gather(const void* a, int a_rows, const int* idx, const void* b
                         int* status, fmb_stream_t stream);
 
 /* The first 4 bytes of the workspace given to fmb_attn_fwd / fmb_attn_bwd hold a device-side
- * status word after the call: 0 = ok; 1..6 = a bounded wait inside a kernel expired
+ * status word after the call: 0 = ok; 1..6 and 8 = a bounded wait inside a kernel expired
  * (FMB_ERR_TIMEOUT condition); 7 = the pattern's columns overlap or exceed the slots of a pass
- * (give a larger workspace).  Results are invalid when it is non-zero. */
+ * (give a larger workspace); 9 = the kernel found its shared memory misaligned (a build problem).
+ * Results are invalid when it is non-zero. */
 
 /* ------------------------------------------------------------------ measurement aids
  * No counterpart in the reference (it is timed from Python with torch.utils.benchmark,
