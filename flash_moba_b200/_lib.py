@@ -50,6 +50,9 @@ _SIGS = {
     "fmb_varlen_sort": (i32, [c_ptr, c_ptr, c_ptr, c_ptr, i64, i64, c_ptr]),
     "fmb_attn_fwd_workspace_bytes": (sz, [i64, i32, i32, i32, i64, i32, i32, i32, i32]),
     "fmb_attn_bwd_workspace_bytes": (sz, [i64, i32, i32, i32, i64, i32, i32, i32, i32]),
+    "fmb_attn_lists_bytes": (sz, [i64, i32, i32, i32, i64, i32, i32, i32]),
+    "fmb_attn_lists_save": (i32, [c_ptr, sz, i64, i32, i32, i32, i64, i32, i32, i32, c_ptr, sz, c_ptr]),
+    "fmb_attn_lists_load": (i32, [c_ptr, sz, i64, i32, i32, i32, i64, i32, i32, i32, c_ptr, sz, c_ptr]),
     "fmb_attn_fwd": (i32, [c_ptr, i64, i64, c_ptr, i64, i64, c_ptr, i64, i64, c_ptr, i64, i64, c_ptr,
                            c_ptr, c_ptr, c_ptr, i64, c_ptr, c_ptr, c_ptr, sz,
                            i32, i32, i32, i32, i64, i32, i32, i32, f32, i32, i32, c_ptr]),

@@ -239,6 +239,39 @@ size_t fmb_attn_bwd_workspace_bytes(int64_t total_q, int heads, int heads_k, int
                               heads_per_pass, true);
 }
 
+static AttnArgs lists_geometry(const void* ws, size_t ws_bytes, int64_t total_q, int heads, int heads_k,
+                               int head_dim, int64_t n_indices, int batch, int max_seqlen_k, int chunk) {
+  AttnArgs a;
+  memset(&a, 0, sizeof(a));
+  a.ws = const_cast<void*>(ws); a.ws_bytes = ws_bytes;
+  a.total_q = total_q; a.heads = heads; a.heads_k = heads_k > 0 ? heads_k : heads; a.d = head_dim;
+  a.n_indices = n_indices; a.batch = batch; a.chunk = chunk > 0 ? chunk : 128;
+  a.ncol = ceil_div(max_seqlen_k, a.chunk);
+  return a;
+}
+size_t fmb_attn_lists_bytes(int64_t total_q, int heads, int heads_k, int head_dim, int64_t n_indices, int batch,
+                            int max_seqlen_k, int chunk) {
+  if (heads <= 0) return 0;
+  return attn_lists_bytes(lists_geometry(nullptr, 0, total_q, heads, heads_k, head_dim, n_indices, batch,
+                                         max_seqlen_k, chunk));
+}
+int fmb_attn_lists_save(const void* fwd_workspace, size_t workspace_bytes, int64_t total_q, int heads, int heads_k,
+                        int head_dim, int64_t n_indices, int batch, int max_seqlen_k, int chunk, void* lists,
+                        size_t lists_bytes, fmb_stream_t stream) {
+  FMB_CHECK_ARG(heads > 0 && chunk > 0 && chunk % 64 == 0, "attn_lists_save: bad geometry");
+  return attn_lists_save(lists_geometry(fwd_workspace, workspace_bytes, total_q, heads, heads_k, head_dim, n_indices,
+                                        batch, max_seqlen_k, chunk),
+                         lists, lists_bytes, (cudaStream_t)stream);
+}
+int fmb_attn_lists_load(void* bwd_workspace, size_t workspace_bytes, int64_t total_q, int heads, int heads_k,
+                        int head_dim, int64_t n_indices, int batch, int max_seqlen_k, int chunk, const void* lists,
+                        size_t lists_bytes, fmb_stream_t stream) {
+  FMB_CHECK_ARG(heads > 0 && chunk > 0 && chunk % 64 == 0, "attn_lists_load: bad geometry");
+  return attn_lists_load(lists_geometry(bwd_workspace, workspace_bytes, total_q, heads, heads_k, head_dim, n_indices,
+                                        batch, max_seqlen_k, chunk),
+                         lists, lists_bytes, (cudaStream_t)stream);
+}
+
 static int check_attn(const char* op, const AttnArgs& a) {
   int rc = check_common(op, a.heads, a.heads_k, a.d, a.dtype);
   if (rc) return rc;

@@ -45,6 +45,7 @@ struct AttnWorkspace {
   int nsub, kb;         // sub-blocks per chunk, keys per sub-block
   int64_t cap;          // slots per plane
   size_t bytes;
+  size_t lists_off, lists_bytes;   // slot_base .. row_pos: what a backward call can take over from a forward call
 };
 
 // Pass geometry + pattern access shared by every attention kernel
@@ -98,6 +99,15 @@ __device__ __forceinline__ void zero_dq_partials(const PassParams& r, T* part_dq
 AttnWorkspace carve_attn_workspace(void* base, size_t bytes_available, const AttnArgs& a, size_t part_elem_bytes,
                                    bool with_lse, int heads_per_pass);
 PassParams make_pass(const AttnArgs& a, const AttnWorkspace& w, int h0, int nh);
+
+// The slot and row lists depend on the pattern alone, so a backward call can take over the lists
+// the forward call of the same pattern built, when both run in one pass over all heads.
+// attn_lists_save copies them out of a forward workspace; attn_lists_load copies them into a
+// backward workspace and arms the next launch_attn_bwd of this thread on that workspace to skip
+// its own build.  Both return 1 (and do nothing) when the workspace makes the call multi-pass.
+size_t attn_lists_bytes(const AttnArgs& geometry);
+int attn_lists_save(const AttnArgs& geometry_and_ws, void* dst, size_t dst_bytes, cudaStream_t s);
+int attn_lists_load(const AttnArgs& geometry_and_ws, const void* src, size_t src_bytes, cudaStream_t s);
 
 // Builds slot_base and row_ptr / row_pos (CSR transpose of the pass's part of the pattern).
 // Row id = (h - h0)*total_q + token.

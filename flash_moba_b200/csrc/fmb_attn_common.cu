@@ -26,10 +26,12 @@ static size_t layout(AttnWorkspace& w, void* base, const AttnArgs& a, size_t par
   w.status = static_cast<int*>(take(512));
   w.part_o = take((size_t)w.nsub * w.cap * a.d * part_elem_bytes);
   w.part_lse = static_cast<float*>(take(with_lse ? (size_t)w.nsub * w.cap * sizeof(float) : 0));
+  w.lists_off = off;
   w.slot_base = static_cast<uint32_t*>(take((size_t)(ncols + 1) * sizeof(uint32_t)));
   w.row_ptr = static_cast<uint32_t*>(take((size_t)(rows + 1) * sizeof(uint32_t)));
   w.row_fill = static_cast<uint32_t*>(take((size_t)rows * sizeof(uint32_t)));
   w.row_pos = static_cast<uint32_t*>(take((size_t)w.cap * sizeof(uint32_t)));
+  w.lists_bytes = off - w.lists_off;
   const int64_t longest = rows + 1 > ncols + 1 ? rows + 1 : ncols + 1;
   w.scan_tmp = static_cast<uint32_t*>(take(scan_tmp_elems(longest) * sizeof(uint32_t)));
   w.bytes = off;
@@ -888,15 +890,51 @@ int launch_attn_fwd(const AttnArgs& a, int engine, cudaStream_t s) {
   return FMB_OK;
 }
 
+// ------------------------------------------------------------------ lists handed from forward to backward
+struct ListsTicket {
+  const void* ws; int64_t total_q, n_indices; int heads, batch, ncol, chunk; bool armed;
+};
+static thread_local ListsTicket g_ticket = {nullptr, 0, 0, 0, 0, 0, 0, false};
+
+size_t attn_lists_bytes(const AttnArgs& a) {
+  return carve_attn_workspace(nullptr, 0, a, 2, false, a.heads).lists_bytes;
+}
+int attn_lists_save(const AttnArgs& a, void* dst, size_t dst_bytes, cudaStream_t s) {
+  const AttnWorkspace w = carve_attn_workspace(a.ws, a.ws_bytes, a, 2, true, 0);
+  if (a.ws == nullptr || a.ws_bytes < w.bytes || w.nh < a.heads) return 1;
+  if (dst == nullptr || dst_bytes < w.lists_bytes)
+    return fail(FMB_ERR_WORKSPACE, "attn_lists_save: buffer too small (%zu bytes given, %zu needed)", dst_bytes,
+                w.lists_bytes);
+  FMB_CUDA(cudaMemcpyAsync(dst, static_cast<const char*>(a.ws) + w.lists_off, w.lists_bytes,
+                           cudaMemcpyDeviceToDevice, s));
+  return FMB_OK;
+}
+int attn_lists_load(const AttnArgs& a, const void* src, size_t src_bytes, cudaStream_t s) {
+  const AttnWorkspace w = carve_attn_workspace(a.ws, a.ws_bytes, a, 2, false, 0);
+  if (a.ws == nullptr || a.ws_bytes < w.bytes || w.nh < a.heads) return 1;
+  if (src == nullptr || src_bytes < w.lists_bytes)
+    return fail(FMB_ERR_WORKSPACE, "attn_lists_load: buffer too small (%zu bytes given, %zu needed)", src_bytes,
+                w.lists_bytes);
+  FMB_CUDA(cudaMemcpyAsync(static_cast<char*>(a.ws) + w.lists_off, src, w.lists_bytes, cudaMemcpyDeviceToDevice, s));
+  g_ticket = ListsTicket{a.ws, a.total_q, a.n_indices, a.heads, a.batch, a.ncol, a.chunk, true};
+  return FMB_OK;
+}
+
 int launch_attn_bwd(const AttnArgs& a, int engine, cudaStream_t s) {
   AttnWorkspace w = carve_attn_workspace(a.ws, a.ws_bytes, a, 2, false, 0);
   int rc = check_pass_sizes("attn_bwd", a, w, w.bytes);
   if (rc) return rc;
+  // lists loaded into this very workspace for this very problem, one pass: no build of our own
+  const bool lists_given = g_ticket.armed && g_ticket.ws == a.ws && g_ticket.total_q == a.total_q &&
+                           g_ticket.n_indices == a.n_indices && g_ticket.heads == a.heads &&
+                           g_ticket.batch == a.batch && g_ticket.ncol == a.ncol && g_ticket.chunk == a.chunk &&
+                           w.nh >= a.heads;
+  g_ticket.armed = false;
   FMB_CUDA(cudaMemsetAsync(w.status, 0, 512, s));
   if ((rc = launch_dot_do_o(a, s))) return rc;
   for (int h0 = 0; h0 < a.heads; h0 += w.nh) {
     const PassParams ps = make_pass(a, w, h0, min(w.nh, a.heads - h0));
-    if ((rc = build_row_lists(a, w, ps, s))) return rc;
+    if (!lists_given && (rc = build_row_lists(a, w, ps, s))) return rc;
     prof_begin(1, s);
     if (engine == 1 && tc_supported(a, true)) rc = launch_bwd_main_tc(a, w, ps, s);
     else rc = launch_bwd_main_simt(a, w, ps, s);

@@ -224,7 +224,9 @@ class FlashMobaAttnVarlenFunc(torch.autograd.Function):
             q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, moba_col_offsets, moba_col_nnz,
             moba_row_indices, lg_block_m, lg_block_n, dropout_p, softmax_scale, causal=causal, softcap=softcap,
             alibi_slopes=alibi_slopes, return_softmax=return_softmax and dropout_p > 0)
+        lists = ops.take_lists()     # the pattern's row lists, kept by the forward call for the backward call
         if is_grad:
+            ctx.lists = lists
             ctx.save_for_backward(q, k, v, out_padded, lse, cu_seqlens_q, cu_seqlens_k, rng_state,
                                   moba_col_offsets, moba_col_nnz, moba_row_indices)
             ctx.meta = (dropout_p, max_seqlen_q, max_seqlen_k, softmax_scale, causal, softcap, alibi_slopes,
@@ -240,6 +242,7 @@ class FlashMobaAttnVarlenFunc(torch.autograd.Function):
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         d_og = dout.size(2)
         dout_padded = dout if q.size(2) == d_og else torch.nn.functional.pad(dout, [0, q.size(2) - d_og])
+        ops.offer_lists(getattr(ctx, "lists", None))
         torch.ops.flash_moba._flash_moba_attn_varlen_backward(
             dout_padded, q, k, v, out, lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
             col_offsets, col_nnz, row_indices, lg_block_m, lg_block_n, dropout_p, softmax_scale, causal, softcap,

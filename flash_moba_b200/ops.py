@@ -48,6 +48,39 @@ def ptr(t: Optional[torch.Tensor]) -> int:
     return 0 if t is None else t.data_ptr()
 
 
+# ---- the pattern's slot / row lists, handed from a forward call to its backward call
+# Both attention calls build the same CSR transpose of the pattern in their workspace.  attn_fwd
+# keeps a copy of it (a few bytes per pattern entry) that the autograd Function collects with
+# take_lists() right after its forward op and offers to the backward op with offer_lists(); the
+# custom ops' signatures stay the reference's.  FMB_SHARE_LISTS=0 turns the hand-over off.
+import threading as _threading
+
+_tls = _threading.local()
+
+
+def _share_lists() -> bool:
+    import os
+    return os.environ.get("FMB_SHARE_LISTS", "1") != "0"
+
+
+def _lists_key(col_offsets, col_nnz, indices, cu_seqlens_q, total_q, h, hk, d, batch, max_seqlen_k, chunk):
+    """What the lists depend on: the pattern tensors and the sequence bounds (storage and version), the geometry."""
+    ident = tuple((t.data_ptr(), t._version, t.numel()) for t in (col_offsets, col_nnz, indices, cu_seqlens_q))
+    return ident + (int(total_q), h, hk, d, batch, int(max_seqlen_k), int(chunk), str(indices.device))
+
+
+def take_lists():
+    """The lists kept by the last attn_fwd of this thread (None if it kept none); clears the slot."""
+    got = getattr(_tls, "kept", None)
+    _tls.kept = None
+    return got
+
+
+def offer_lists(lists) -> None:
+    """Lists for the next attn_bwd of this thread (used only if they belong to its pattern)."""
+    _tls.offered = lists
+
+
 def _workspace(query, total_q, h, hk, d, n_indices, batch, max_seqlen_k, chunk, device):
     """Workspace for one attention call: the single-pass size if it fits the cap
     (FMB_WORKSPACE_GB, default 24 GiB), otherwise the largest pass of whole kv-head groups that
@@ -236,6 +269,17 @@ def attn_fwd(q, k, v, col_offsets, col_nnz, indices, cu_seqlens_q, cu_seqlens_k,
                                ptr(ws), nbytes, batch, h, hk, d, total_q, int(max_seqlen_q), int(max_seqlen_k),
                                int(chunk), float(softmax_scale), int(bool(causal)), _dtype_code(q), _stream()))
         _check_status(ws, "attn_fwd")
+        _tls.kept = None
+        if _share_lists() and indices.numel() > 0:
+            geo = (total_q, h, hk, d, indices.numel(), batch, int(max_seqlen_k), int(chunk))
+            nlist = lib.fmb_attn_lists_bytes(*geo)
+            lists = torch.empty((max(nlist, 1),), dtype=torch.uint8, device=dev)
+            rc = lib.fmb_attn_lists_save(ptr(ws), nbytes, *geo, ptr(lists), nlist, _stream())
+            if rc == 0:
+                _tls.kept = (_lists_key(col_offsets, col_nnz, indices, cu_seqlens_q, total_q, h, hk, d, batch,
+                                        max_seqlen_k, chunk), lists)
+            elif rc != 1:      # 1: the call ran in several passes, nothing to keep
+                check(rc)
     return out, lse
 
 
@@ -257,6 +301,15 @@ def attn_bwd(dout, q, k, v, out, lse, dq, dk, dv, col_offsets, col_nnz, indices,
         softmax_d = torch.empty((h, total_q), dtype=torch.float32, device=dev)
         ws, nbytes = _workspace(lib.fmb_attn_bwd_workspace_bytes, total_q, h, hk, d, indices.numel(), batch,
                                 max_seqlen_k, chunk, dev)
+        offered = getattr(_tls, "offered", None)
+        _tls.offered = None
+        if offered is not None and _share_lists() and \
+                offered[0] == _lists_key(col_offsets, col_nnz, indices, cu_seqlens_q, total_q, h, hk, d, batch,
+                                         max_seqlen_k, chunk):
+            rc = lib.fmb_attn_lists_load(ptr(ws), nbytes, total_q, h, hk, d, indices.numel(), batch,
+                                         int(max_seqlen_k), int(chunk), ptr(offered[1]), offered[1].numel(), _stream())
+            if rc not in (0, 1):
+                check(rc)
         check(lib.fmb_attn_bwd(ptr(dout), dout.stride(0), dout.stride(1), ptr(q), q.stride(0), q.stride(1),
                                ptr(k), k.stride(0), k.stride(1), ptr(v), v.stride(0), v.stride(1),
                                ptr(out), out.stride(0), out.stride(1), ptr(lse),

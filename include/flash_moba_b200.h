@@ -216,6 +216,25 @@ int fmb_selftest_umma(const void* a, const void* b, float* d, int b_mn_major, in
 int fmb_selftest_gather(const void* a, int a_rows, const int* idx, const void* b, float* d, int dtype,
                         int* status, fmb_stream_t stream);
 
+/* Optional hand-over of the pattern's slot and row lists (the CSR transpose that both attention
+ * calls build in their workspace) from a forward call to the backward call of the same pattern.
+ * No counterpart in the reference, whose kernels walk the pattern query-block-major and need no
+ * transpose.  After fmb_attn_fwd: fmb_attn_lists_save copies the lists out of the forward
+ * workspace into `lists` (fmb_attn_lists_bytes of device memory).  Before fmb_attn_bwd, on the
+ * same host thread: fmb_attn_lists_load copies them into the backward workspace; the next
+ * fmb_attn_bwd of this thread on that workspace and geometry then skips its own build (64K
+ * tokens x 32 heads: 0.24 ms of 11).  Both return 0 when done, 1 when the workspace makes the
+ * call run in several passes over the heads (nothing copied, fmb_attn_bwd builds its own lists),
+ * an FMB_ERR_* code on bad arguments.  Same stream order as the attention calls. */
+size_t fmb_attn_lists_bytes(int64_t total_q, int heads, int heads_k, int head_dim, int64_t n_indices,
+                            int batch, int max_seqlen_k, int chunk);
+int fmb_attn_lists_save(const void* fwd_workspace, size_t workspace_bytes, int64_t total_q, int heads,
+                        int heads_k, int head_dim, int64_t n_indices, int batch, int max_seqlen_k,
+                        int chunk, void* lists, size_t lists_bytes, fmb_stream_t stream);
+int fmb_attn_lists_load(void* bwd_workspace, size_t workspace_bytes, int64_t total_q, int heads,
+                        int heads_k, int head_dim, int64_t n_indices, int batch, int max_seqlen_k,
+                        int chunk, const void* lists, size_t lists_bytes, fmb_stream_t stream);
+
 /* The first 4 bytes of the workspace given to fmb_attn_fwd / fmb_attn_bwd hold a device-side
  * status word after the call: 0 = ok; 1..6 and 8 = a bounded wait inside a kernel expired
  * (FMB_ERR_TIMEOUT condition); 7 = the pattern's columns overlap or exceed the slots of a pass

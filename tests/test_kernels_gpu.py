@@ -483,6 +483,39 @@ def test_c1_end_to_end():
     assert diff <= 0.05, diff
 
 
+def test_row_lists_handed_from_forward_to_backward(monkeypatch):
+    """The backward call takes over the pattern's slot / row lists from the forward call (single-pass
+    calls): same gradients bit for bit, fewer launches; a multi-pass workspace falls back to
+    building its own."""
+    import flash_moba_b200 as F
+    from flash_moba_b200 import _lib
+    torch.manual_seed(0)
+    lens, H, Hk, d, chunk, topk = [700, 333], 4, 2, 128, 128, 3
+    T = sum(lens)
+    cu = cu_of(lens).to(DEV)
+    q, k, v, do = (torch.randn(T, h, d, device=DEV).bfloat16() for h in (H, Hk, Hk, H))
+
+    def run():
+        qd, kd, vd = (t.clone().requires_grad_(True) for t in (q, k, v))
+        n0 = _lib.lib.fmb_launch_count()
+        out = F.flash_moba_varlen_func(qd, kd, vd, cu, cu, max(lens), max(lens), chunk, topk, causal=True)
+        grads = torch.autograd.grad(out, (qd, kd, vd), do)
+        torch.cuda.synchronize()
+        return (out.detach(),) + grads, _lib.lib.fmb_launch_count() - n0
+
+    monkeypatch.setenv("FMB_SHARE_LISTS", "0")
+    ref, n_ref = run()
+    monkeypatch.setenv("FMB_SHARE_LISTS", "1")
+    got, n_got = run()
+    for a, b in zip(ref, got):
+        assert torch.equal(a, b)
+    assert n_got < n_ref
+    monkeypatch.setenv("FMB_WORKSPACE_GB", "0.000001")     # forces one kv-head group per pass
+    multi, n_multi = run()
+    for a, b in zip(ref, multi):
+        assert torch.equal(a, b)
+
+
 def test_determinism_and_autograd_through_public_api():
     import flash_moba_b200 as F
     torch.manual_seed(0)
