@@ -606,7 +606,10 @@ __device__ __forceinline__ void combine_wide_body(int64_t vblock, const T* __res
 #pragma unroll
     for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     w = (g.valid && m > -CUDART_INF_F) ? __expf(l - m) : 0.f;
-    ssum = w;
+    // summed with the weights in rank order: the order in which the row's partials sit in the
+    // lanes is that of the row list, which the atomics of its build leave undefined
+    const float w_ranked = __shfl_sync(0xffffffffu, w, inv);
+    ssum = lane < g.n ? w_ranked : 0.f;
 #pragma unroll
     for (int o = 16; o; o >>= 1) ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
   }

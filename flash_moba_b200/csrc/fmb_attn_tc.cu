@@ -1,13 +1,13 @@
 // tcgen05 tensor-core engine of the block-sparse attention main kernels.
 //
-// Key-chunk-major, like the CUDA-core engine: a CTA owns key chunk c of one (sequence, head),
-// keeps the chunk's K and V in shared memory (128-byte-swizzled UMMA tiles) for its whole
-// life, and walks the chunk's CSC column in dense tiles of 128 gathered query rows:
-//     gather Q rows -> smem     S = Q.K^T   (tcgen05.mma, fp32 accumulator in TMEM)
-//     softmax of the tile, one thread per row (tcgen05.ld), P -> smem (bf16)
-//     O = P.V (tcgen05.mma, V consumed MN-major straight from its row-major tile)
-//     O / l -> workspace partial at the pair's CSC position, chunk-local log-sum-exp beside it
-// Two CTAs share an SM (256 TMEM columns each), so one CTA's softmax overlaps the other's MMAs.
+// Key-chunk-major: a work item is one key block of one (sequence, head) (backward: kv head); its
+// K and V tiles sit in shared memory (128-byte-swizzled UMMA tiles) while the item's CSC column,
+// i.e. the gathered list of query rows that selected the chunk, is walked in dense tiles of 128
+// rows.  One persistent CTA per SM (all 512 TMEM columns, nearly all shared memory) runs through
+// its work items as one stream of tiles; the roles (compute warps, one MMA-issuing thread, loader
+// warps that gather rows with 16-byte cp.async copies, a scout warp that decodes items ahead and
+// stages K / V) hand tiles to each other through mbarriers.  Forward and backward kernels are
+// described at their definitions below.
 // Every mbarrier wait is bounded; a wait that expires records where in the status word of the
 // workspace and the CTA leaves through the normal exit (TMEM released).
 #include "fmb_attn.cuh"
@@ -19,36 +19,6 @@ using namespace tc;
 
 constexpr int kTcM = 128;   // gathered rows per tile = TMEM lanes
 
-// Optional phase timing (build with -DFMB_TC_TIMING): thread 0 of every CTA accumulates clock64
-// deltas per phase into 64-bit counters that start 64 bytes into the workspace status block.
-#ifdef FMB_TC_TIMING
-#define FMB_T0() long long t_prev_ = clock64()
-#ifndef FMB_TICK_TID
-#define FMB_TICK_TID 0
-#endif
-#define FMB_TICK(slot)                                                                          \
-  do {                                                                                          \
-    if (threadIdx.x == FMB_TICK_TID) {                                                                     \
-      const long long t_now_ = clock64();                                                       \
-      atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (slot),                   \
-                (unsigned long long)(t_now_ - t_prev_));                                        \
-      t_prev_ = t_now_;                                                                         \
-    }                                                                                           \
-  } while (0)
-#define FMB_TICK_AT(slot, who)                                                                  \
-  do {                                                                                          \
-    if (threadIdx.x == (who)) {                                                                 \
-      const long long t_now_ = clock64();                                                       \
-      atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (slot),                   \
-                (unsigned long long)(t_now_ - t_prev_));                                        \
-      t_prev_ = t_now_;                                                                         \
-    }                                                                                           \
-  } while (0)
-#else
-#define FMB_T0() do {} while (0)
-#define FMB_TICK(slot) do {} while (0)
-#define FMB_TICK_AT(slot, who) do {} while (0)
-#endif
 constexpr float kLog2eTc = 1.4426950408889634f;
 
 struct TcParams {
@@ -109,12 +79,10 @@ __host__ __device__ constexpr int next_pow2_cols(int x) { return x <= 32 ? 32 : 
 // initialised once and their phases counted per group across items.
 constexpr int kFwdGroups = 2;
 constexpr int kFwdGroupThreads = 256;
-#ifndef FMB_FWD_LW
-#define FMB_FWD_LW 2          // loader warps per compute group
-#endif
-constexpr int kFwdLoaderSet = 32 * FMB_FWD_LW;  // loader threads per compute group
+constexpr int kFwdLoaderWarps = 2;              // loader warps per compute group
+constexpr int kFwdLoaderSet = 32 * kFwdLoaderWarps;  // loader threads per compute group
 constexpr int kFwdIssuerWarp = kFwdGroups * kFwdGroupThreads / 32;
-constexpr int kFwdScoutWarp = kFwdIssuerWarp + 1 + kFwdGroups * FMB_FWD_LW;
+constexpr int kFwdScoutWarp = kFwdIssuerWarp + 1 + kFwdGroups * kFwdLoaderWarps;
 constexpr int kFwdThreads = kFwdGroups * kFwdGroupThreads + 32 + kFwdGroups * kFwdLoaderSet + 32;
 
 // a decoded work item as the scout publishes it
@@ -149,7 +117,6 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const float scale_log2 = p.scale * kLog2eTc;
-  FMB_T0();
   if (warp == 0) tmem_alloc(&tmem_base_s, NCOLS);
   if (tid == 0) {
     for (int i = 0; i < kFwdGroups; ++i) {
@@ -371,7 +338,6 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
       good = bar_and(bar_id, kFwdGroupThreads, good);   // the group goes on, or leaves, together
       if (!good || it.nnz <= 0) break;
       const int ntiles = (it.nnz + kTcM - 1) / kTcM;
-      if (tid == 0) FMB_TICK(1);   // item boundary
 #pragma unroll 1
       for (int i = g; i < ntiles; i += kFwdGroups, ++m) {
         const int t0 = i * kTcM;
@@ -379,7 +345,6 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
         if (gw < 4 && lane == 0) bulk_wait_read();   // the previous tile's O staging has been read out
         if (good) good = mbar_wait(&bar_s[g], m & 1, p.status, 1);   // on failure: run on to the barrier
         tc_fence_after_sync();
-        if (tid == 0) FMB_TICK(2);   // waiting for S
 
         // ---- chunk-local softmax of row `lt`, this thread's half of the keys
         const int r = sRow[g][m & 1][lt];
@@ -434,14 +399,12 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
         fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_pready[g]);   // S has been read, P is in shared memory
-        if (tid == 0) FMB_TICK(3);   // softmax
         bar_sync(bar_id, kFwdGroupThreads);           // the other half's sum
         sum += sSum[g][hf ^ 1][lt];
         const float inv = sum > 0.f ? 1.f / sum : 0.f;
         if (hf == 0 && lt < rows) p.part_lse[it.slot + t0 + lt] = sum > 0.f ? mx * p.scale + logf(sum) : -CUDART_INF_F;
         if (good) good = mbar_wait(&bar_o[g], m & 1, p.status, 2);
         tc_fence_after_sync();
-        if (tid == 0) FMB_TICK(5);   // waiting for O = P.V
 
         // ---- epilogue: normalised partial O of row `lt`, this thread's half of the head dim,
         // staged in the P tile (its MMAs have completed); one bulk copy per 32 rows
@@ -469,7 +432,6 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
             bulk_commit();   // its reads are waited for before the next tile's P is stored
           }
         }
-        if (tid == 0) FMB_TICK(6);   // epilogue
       }
     }
     if (gw < 4 && lane == 0) bulk_wait_read();
@@ -523,14 +485,8 @@ constexpr int kBwdCompute = 256;
 // bound per warp; with the item stream 3 + 3 warps 4.14 ms against 4.08 ms for 2 + 4.  Sixteen
 // warps are the most that keep 128 registers per thread (registers are allocated to warps in
 // groups of four: a seventeenth warp would bring the limit down to 96).
-#ifndef FMB_BWD_QW
-#define FMB_BWD_QW 2          // warps gathering Q rows
-#endif
-#ifndef FMB_BWD_OW
-#define FMB_BWD_OW 4          // warps gathering dO rows
-#endif
-constexpr int kBwdQLoaders = 32 * FMB_BWD_QW;
-constexpr int kBwdOLoaders = 32 * FMB_BWD_OW;
+constexpr int kBwdQLoaders = 32 * 2;          // threads gathering Q rows
+constexpr int kBwdOLoaders = 32 * 4;          // threads gathering dO rows
 constexpr int kBwdScoutWarp = (kBwdCompute + 32 + kBwdQLoaders + kBwdOLoaders) / 32;   // K/V loader and item scout
 constexpr int kBwdThreads = kBwdCompute + 32 + kBwdQLoaders + kBwdOLoaders + 32;
 
@@ -628,7 +584,6 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   const int lt = tid & (kTcM - 1);                // row (TMEM lane) of a compute thread
   const int hf = (tid >> 7) & 1;                  // column half of a compute thread
 
-  FMB_T0();
   if (warp == 0) tmem_alloc(&tmem_base_s, NCOLS);
   if (tid == 0) {
     mbar_init(&bar_s, 1); mbar_init(&bar_p, 1); mbar_init(&bar_dq, 1); mbar_init(&bar_dv, 1); mbar_init(&bar_fin, 1);
@@ -736,43 +691,32 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
         if (I.skip) continue;
         // K and V of this item are in place (the scout warp loads them once every GEMM of the
         // previous item has completed)
-        FMB_TICK_AT(45, 256);          // item boundary: column data of the next item
         if (!(ok = mbar_wait(&bar_kv, nk & 1, p.status, 6))) break;
-        FMB_TICK_AT(42, 256);          // waiting for K and V
         if (have) {
           issue_s();
-          FMB_TICK_AT(43, 256);        // waiting for the first Q tile
           if (ok) issue_dp();
-          FMB_TICK_AT(44, 256);        // waiting for the first dO tile
           uint32_t acc = 0;
 #pragma unroll 1
           while (ok) {
             const bool more = next_tile(I, it);
             // dV += P^T.dO : M = keys, N = d, K = the 128 gathered rows
-            FMB_TICK_AT(41, 256);
             if (!(ok = mbar_wait(&bar_pready, g & 1, p.status, 1))) break;
             tc_fence_after_sync();
-            FMB_TICK_AT(34, 256);
             umma_gemm<kTcM / 16>(tdV, p_mn, hi, 128, 512, do_mn, hi, 128, 512, idesc_kv, acc);
             umma_commit(&bar_dv);        // dO is free once this completes: the dO loader's signal
-            FMB_TICK_AT(35, 256);
             if (!(ok = mbar_wait(&bar_dsready, g & 1, p.status, 2))) break;
             tc_fence_after_sync();
-            FMB_TICK_AT(36, 256);
             // dQ partial = dS.K : M = rows, N = d, K = keys
             umma_gemm<C / 16>(tdQ, ds_km, hi, 2, kQB, k_mn, hi, 128, 512, idesc_dq, 0);
             umma_commit(&bar_dq);
             // dK += dS^T.Q
             umma_gemm<kTcM / 16>(tdK, ds_mn, hi, 128, 512, q_mn + (g & 1) * kQBuf, hi, 128, 512, idesc_kv, acc);
             umma_commit(&bar_dk[g & 1]); // this Q buffer is free once it completes: the Q loader's signal
-            FMB_TICK_AT(37, 256);
             ++g;
             acc = 1;
             if (!more) break;
             issue_s();
-            FMB_TICK_AT(38, 256);
             if (ok) issue_dp();
-            FMB_TICK_AT(40, 256);
           }
         }
         if (ok) umma_commit(&bar_fin);   // every GEMM of the item has completed: K, V, dK, dV may be reused
@@ -896,7 +840,6 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
             if (t + k * nt < kTcM) sRow[t + k * nt] = rid[k];
         }
         ok = bar_and(bar_id, nt, ok);                // also publishes the row ids to the group
-        FMB_TICK_AT(24, 288); FMB_TICK_AT(26, 288 + kBwdQLoaders);  // loaders: row ids + waiting for the buffer
         if (!ok) break;
         if (q_side) {
           const T* qbase = static_cast<const T*>(p.q) + (int64_t)I.q0 * p.q_rs + (int64_t)h * p.q_hs;
@@ -909,7 +852,6 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
         fence_async_smem();        // the copies are generic-proxy writes; the MMAs read through the async proxy
         __syncwarp();
         if (lane == 0) mbar_arrive(q_side ? &bar_fullq[m & 1] : &bar_fulldo);
-        FMB_TICK_AT(25, 288); FMB_TICK_AT(27, 288 + kBwdQLoaders);  // loaders: gather
         bar_sync(bar_id, nt);                        // every thread has read the row ids
         it = nx;
         have = more;
@@ -929,17 +871,13 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
       BwdItem I;
       BwdTile it;
       bool have;
-      FMB_TICK(51);   // after the item's last tile
       const int state = read_info(n, I, it, have);
-      FMB_TICK(52);   // item info
       good = bar_and(2, kBwdCompute, good && state >= 0);
-      FMB_TICK(53);   // the other compute warps
       const bool done = !good || state == 0;
       int fetched = 0;
       if (tid == 0 && !done) fetched = atomicAdd(p.work, 1);      // item n + 2, published below
       const bool run = !done && !I.skip;
       have = have && run;
-      FMB_TICK(16);   // item hand-out, column data, first row data
 
       // ---- the previous item's GEMMs have completed: its dK and dV are final
       if (prev) {
@@ -947,7 +885,6 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
         if (good) good = mbar_wait(&bar_fin, (nk - 1) & 1, p.status, 4);
         good = bar_and(2, kBwdCompute, good);
         tc_fence_after_sync();
-        FMB_TICK(54);   // the previous item's last GEMMs
       }
       // ---- dK and dV of key `lt` of the previous item, this thread's half of the head dim: staged in
       // the P / dS tiles (free between items) with rows 16 bytes apart from a multiple of 128, which
@@ -996,7 +933,6 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
         }
         tc_fence_before_sync();
       }
-      FMB_TICK(23);   // wait for the previous item's last GEMMs, dK/dV epilogue
       if (tid == 0 && !done) {
         *reinterpret_cast<volatile int*>(&s_items[(n + 2) & 3]) = fetched;
         mbar_arrive(&bar_item[(n + 2) & 3]);
@@ -1015,12 +951,9 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
 #pragma unroll 1
       for (; more && good; ++g) {
         // ---- P of row `lt`, this thread's 64 keys
-        FMB_TICK(47);   // loop back
         if (good) good = mbar_wait(&bar_s, g & 1, p.status, 3);   // on failure: run on to the barriers, leave there
         if (good) good = mbar_wait(&bar_rows, g & 1, p.status, 3);   // row data of the tile (long landed)
         tc_fence_after_sync();
-        if (!prev_any) FMB_TICK(39);   // waiting for S, first tile of an item
-        FMB_TICK(17);   // waiting for S
         const int r_cur = sRowO[lt];
         const float lse2 = sLse[lt] * kLog2eTc, dd_cur = sDsum[lt];
         const int rows = s_tile[0];
@@ -1053,12 +986,10 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
         fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_pready);      // S has been read, P is in shared memory
-        FMB_TICK(18);   // P
 
         // ---- dS
         if (good) good = mbar_wait(&bar_p, g & 1, p.status, 3);
         tc_fence_after_sync();
-        FMB_TICK(19);   // waiting for dP
 #pragma unroll
         for (int i2 = 0; i2 < 2; ++i2) {
           const int col0 = hf * 64 + i2 * 32;
@@ -1080,13 +1011,11 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
         fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_dsready);     // dP has been read, dS is in shared memory
-        FMB_TICK(20);   // dS
 
         // ---- dQ partial of row `lt`, this thread's half of the head dim: scaled, rounded to the I/O
         // dtype, stored at the entry's slot (16-byte chunks permuted like the forward partials)
         if (good) good = mbar_wait(&bar_dq, g & 1, p.status, 4);
         tc_fence_after_sync();
-        FMB_TICK(21);   // waiting for dQ
         {
           // staged in the P tile (free: dV(g) completed before dQ(g)), 16-byte chunks permuted like the
           // forward partials; one bulk copy per 32 rows, whose reads are waited for before the next P
@@ -1107,11 +1036,9 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
             }
           }
           tc_fence_before_sync();
-          FMB_TICK(29);
           __syncwarp();
           if (lane == 0) mbar_arrive(&bar_dqfree);    // dQ has been read out of dP's columns
           fence_async_smem();
-          FMB_TICK(30);
           good = bar_and(2, kBwdCompute, good);     // both halves of every row staged
           if (good && warp < 4 && lane == 0) {
             const int wrows = min(32, rows - warp * 32);
@@ -1122,7 +1049,6 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
             }
           }
         }
-        FMB_TICK(22);   // dQ epilogue
         prev_any = true;
       }
       prev = true;

@@ -193,14 +193,11 @@ int launch_build_csc(const int32_t* topk_idx, int64_t idx_rs, int64_t idx_hs, co
   p.cols_per_cta = min(kMaxColsPerCta, ncol);
   const int ncr = ceil_div(ncol, p.cols_per_cta);
   const size_t smem = (size_t)p.cols_per_cta * kBmStride * sizeof(uint32_t);
-  static bool attr_done = false;   // per process; the attribute is idempotent
-  if (!attr_done) {
-    FMB_CUDA(cudaFuncSetAttribute(csc_tile_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  kMaxColsPerCta * kBmStride * 4));
-    FMB_CUDA(cudaFuncSetAttribute(csc_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  kMaxColsPerCta * kBmStride * 4));
-    attr_done = true;
-  }
+  // the attribute belongs to the current device: set on every call (cheap, idempotent, thread-safe)
+  FMB_CUDA(cudaFuncSetAttribute(csc_tile_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                kMaxColsPerCta * kBmStride * 4));
+  FMB_CUDA(cudaFuncSetAttribute(csc_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                kMaxColsPerCta * kBmStride * 4));
   dim3 grid(batch * heads, p.ntiles, ncr);
   csc_tile_hist_kernel<<<grid, kCscThreads, smem, s>>>(p);
   FMB_LAUNCH_CHECK("csc_tile_hist_kernel");

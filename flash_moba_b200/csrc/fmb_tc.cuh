@@ -44,9 +44,12 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after kSpinLimit polls (each poll may itself block for a short,
-// hardware-defined time), records `where` in *status and returns false.  The caller then
-// leaves the kernel through its normal exit path (TMEM is still released).
+// Bounded wait: gives up after kSpinLimit polls, records `where` in *status and returns false.
+// The caller then leaves the kernel through its normal exit path (TMEM is still released).
+// A poll blocks for a hardware-defined time, so the bound is one in time too: measured on a B200
+// by fmb_selftest_wait_expiry (an mbarrier nobody arrives at), which the GPU tests run.  The loop is
+// kept this small on purpose: the attention kernels have about twenty-five call sites, and a
+// second register in the loop (a clock-based bound) cost the backward kernel 7 % through spills.
 constexpr uint32_t kSpinLimit = 1u << 17;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int where) {
 #pragma unroll 1   // the compiler otherwise unrolls the poll 32 times at every call site
@@ -56,7 +59,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   if (status) atomicCAS(status, 0, where);
   return false;
 }
-
 
 // ---- a load that is issued where it is written
 // A plain load of read-only data may be moved by the compiler down to its first use (it does so
@@ -85,6 +87,15 @@ __device__ __forceinline__ bool bar_and(int id, int nthreads, bool pred) {
       : "memory");
   return r != 0;
 }
+
+// ---- register budget per warpgroup ------------------------------------------------------
+// A CTA is launched with one register count for every thread; warp-specialised kernels hand
+// registers from the warps that only copy or issue to the warps that compute.  Executed by all
+// four warps of a warpgroup (warps 4i..4i+3) with the same value, a multiple of 8.
+template <int N>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 
 // ---- fences --------------------------------------------------------------------------
 // generic-proxy writes to shared memory -> visible to the async proxy (tcgen05.mma, TMA)
