@@ -45,6 +45,9 @@ _SIGS = {
                             i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, c_ptr]),
     "fmb_build_csc_workspace_bytes": (sz, [i32, i32, i32, i32]),
     "fmb_build_csc": (i32, [c_ptr, i64, i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, sz, i32, i32, i32, i32, i32, c_ptr]),
+    "fmb_build_csc_rows": (i32, [c_ptr, i64, i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, sz, i32, i32, i32, i64, i32, i32,
+                                 c_ptr]),
+    "fmb_attn_rows_offer": (i32, [c_ptr, i64, i32, i32]),
     "fmb_build_csc_static_capacity": (sz, []),
     "fmb_build_csc_static": (i32, [c_ptr, i64, i64, c_ptr, c_ptr, c_ptr, c_ptr, i32, i32, i32, i32, i32, c_ptr]),
     "fmb_varlen_sort": (i32, [c_ptr, c_ptr, c_ptr, c_ptr, i64, i64, c_ptr]),

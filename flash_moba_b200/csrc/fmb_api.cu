@@ -206,6 +206,31 @@ int fmb_build_csc(const int32_t* topk_idx, int64_t topk_row_stride, int64_t topk
                           (cudaStream_t)stream);
 }
 
+int fmb_build_csc_rows(const int32_t* topk_idx, int64_t topk_row_stride, int64_t topk_head_stride,
+                       const int32_t* cu_seqlens_q, int64_t* col_offsets, int32_t* col_nnz, int32_t* indices,
+                       uint32_t* row_slots, void* workspace, size_t workspace_bytes, int batch, int heads, int topk,
+                       int64_t total_q, int max_seqlen_q, int ncol, fmb_stream_t stream) {
+  FMB_CHECK_ARG(batch >= 0 && heads >= 0 && topk >= 1 && max_seqlen_q >= 0 && ncol >= 0 && total_q >= 0,
+                "build_csc_rows: bad sizes");
+  FMB_CHECK_ARG(total_q * heads * topk < (int64_t)0xffffffffll, "build_csc_rows: more than 2^32 - 1 pattern entries");
+  if (batch == 0 || heads == 0) return FMB_OK;
+  FMB_CHECK_ARG(topk_idx && cu_seqlens_q && col_offsets && col_nnz && indices && row_slots, "build_csc_rows: null pointer");
+  FMB_CHECK_ARG(max_seqlen_q / 512 < 65535, "build_csc_rows: max_seqlen_q too large");
+  if (ncol == 0) {   // no columns at all: every place of every row list is empty
+    FMB_CUDA(cudaMemsetAsync(row_slots, 0xff, (size_t)total_q * heads * topk * sizeof(uint32_t), (cudaStream_t)stream));
+    return FMB_OK;
+  }
+  return launch_build_csc(topk_idx, topk_row_stride, topk_head_stride, cu_seqlens_q, col_offsets, col_nnz,
+                          indices, workspace, workspace_bytes, batch, heads, topk, max_seqlen_q, ncol,
+                          (cudaStream_t)stream, row_slots, total_q);
+}
+
+int fmb_attn_rows_offer(const uint32_t* row_slots, int64_t total_q, int heads, int topk) {
+  FMB_CHECK_ARG(row_slots == nullptr || (total_q >= 0 && heads > 0 && topk > 0), "attn_rows_offer: bad sizes");
+  attn_rows_offer(row_slots, total_q, heads, topk);
+  return FMB_OK;
+}
+
 size_t fmb_build_csc_static_capacity(void) { return csc_static_scratch_bytes(); }
 
 int fmb_build_csc_static(const int32_t* topk_idx, int64_t topk_row_stride, int64_t topk_head_stride,

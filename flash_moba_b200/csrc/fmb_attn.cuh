@@ -41,6 +41,7 @@ struct AttnWorkspace {
   uint32_t* row_fill;   // nh*total_q
   uint32_t* row_pos;    // cap: slots of a row's entries
   uint32_t* scan_tmp;   // block sums of the scans
+  int fixed_k;          // > 0: row lists handed over by the pattern builder (see attn_rows_offer)
   int nh;               // heads per pass
   int nsub, kb;         // sub-blocks per chunk, keys per sub-block
   int64_t cap;          // slots per plane
@@ -68,7 +69,9 @@ __device__ __forceinline__ ColRef column_of(const PassParams& r, int b, int h, i
   const int nnz = r.col_nnz[ci];
   const int64_t off = r.col_offsets[ci];
   if (nnz <= 0 || off < 0 || off + nnz > r.n_indices) return o;   // malformed: ignored, never read
-  const int64_t slot = r.slot_base[((int64_t)b * r.nh + (h - r.h0)) * r.ncol + c];
+  // no slot table: the pattern builder vouches for columns that do not overlap, and an entry's
+  // slot is simply its position in `indices`
+  const int64_t slot = r.slot_base ? (int64_t)r.slot_base[((int64_t)b * r.nh + (h - r.h0)) * r.ncol + c] : off;
   if (slot + nnz > r.cap) {          // cannot happen for a pattern whose columns do not overlap
     atomicCAS(r.status, 0, 7);
     return o;
@@ -108,6 +111,13 @@ PassParams make_pass(const AttnArgs& a, const AttnWorkspace& w, int h0, int nh);
 size_t attn_lists_bytes(const AttnArgs& geometry);
 int attn_lists_save(const AttnArgs& geometry_and_ws, void* dst, size_t dst_bytes, cudaStream_t s);
 int attn_lists_load(const AttnArgs& geometry_and_ws, const void* src, size_t src_bytes, cudaStream_t s);
+
+// The pattern builder can hand over the row-major view of its pattern (fmb_build_csc_rows): for
+// entry j of row (h, token)'s top-k list, the position in `indices` of that (row, chunk) pair, or
+// 0xffffffff.  attn_rows_offer arms the next attention call of this thread (forward or backward,
+// one pass over all heads, same geometry) to use positions in `indices` as slots and these rows
+// instead of building slot and row lists.
+void attn_rows_offer(const uint32_t* row_slots, int64_t total_q, int heads, int topk);
 
 // Builds slot_base and row_ptr / row_pos (CSR transpose of the pass's part of the pattern).
 // Row id = (h - h0)*total_q + token.

@@ -15,6 +15,7 @@ static size_t layout(AttnWorkspace& w, void* base, const AttnArgs& a, size_t par
     return p;
   };
   w.nh = nh;
+  w.fixed_k = 0;
   w.kb = (a.chunk % 128 == 0) ? 128 : 64;
   w.nsub = a.chunk / w.kb;
   // one pass over all heads can never need more slots than the pattern has entries; a pass over a
@@ -235,7 +236,20 @@ struct CombineParams {
   int64_t total_q, cap;
   int heads_out;   // heads of the output tensor's row (for nothing but documentation)
   int h0, nh, nsub, d;
+  int fixed_k;     // > 0: row lists handed over by the pattern builder: row `rid` owns the fixed_k places
+                   // row_pos[rid*fixed_k ..], empty places hold 0xffffffff; row_ptr is not used
 };
+// first place and number of places of row `rid` in row_pos
+__device__ __forceinline__ void row_span(const CombineParams& c, int64_t rid, int64_t& p0, int& n) {
+  if (c.fixed_k > 0) {
+    p0 = rid * c.fixed_k;
+    n = c.fixed_k;
+  } else {
+    p0 = c.row_ptr[rid];
+    n = (int)(c.row_ptr[rid + 1] - (uint32_t)p0);
+  }
+}
+constexpr uint32_t kNoSlot = 0xffffffffu;
 
 // Generic kernel: a warp per (token, head of the pass).  The row's partials are visited plane by
 // plane, inside a plane in ascending slot order = ascending (sb*cap + slot).
@@ -268,13 +282,15 @@ __device__ __forceinline__ void fwd_combine_body(int64_t vblock, const T* __rest
   const int64_t t = wid / c.nh;
   const int hr = (int)(wid - t * c.nh);
   const int64_t rid = (int64_t)hr * c.total_q + t;
-  const uint32_t p0 = c.row_ptr[rid];
-  const int n = (int)(c.row_ptr[rid + 1] - p0);
+  int64_t p0;
+  int n;
+  row_span(c, rid, p0, n);
   if (n * c.nsub < min_n) return;
   const uint32_t* rp = c.row_pos + p0;
   float m = -CUDART_INF_F;
   for (int sb = 0; sb < c.nsub; ++sb)
-    for (int j = lane; j < n; j += 32) m = fmaxf(m, part_lse[(int64_t)sb * c.cap + rp[j]]);
+    for (int j = lane; j < n; j += 32)
+      if (rp[j] != kNoSlot) m = fmaxf(m, part_lse[(int64_t)sb * c.cap + rp[j]]);
 #pragma unroll
   for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   float2 acc[4];
@@ -286,6 +302,7 @@ __device__ __forceinline__ void fwd_combine_body(int64_t vblock, const T* __rest
       int64_t last = -1;
       for (int r = 0; r < n; ++r) {
         const int64_t slot = next_slot(rp, n, last, lane);
+        if (slot >= (int64_t)kNoSlot) break;     // the remaining places of the row are empty
         last = slot;
         const int64_t pp = (int64_t)sb * c.cap + slot;
         const float wgt = __expf(part_lse[pp] - m);
@@ -333,8 +350,9 @@ __device__ __forceinline__ void bwd_combine_body(int64_t vblock, const T* __rest
   const int64_t t = wid / c.nh;
   const int hr = (int)(wid - t * c.nh);
   const int64_t rid = (int64_t)hr * c.total_q + t;
-  const uint32_t p0 = c.row_ptr[rid];
-  const int n = (int)(c.row_ptr[rid + 1] - p0);
+  int64_t p0;
+  int n;
+  row_span(c, rid, p0, n);
   if (n * c.nsub < min_n) return;
   const uint32_t* rp = c.row_pos + p0;
   float2 acc[4];
@@ -344,6 +362,7 @@ __device__ __forceinline__ void bwd_combine_body(int64_t vblock, const T* __rest
     int64_t last = -1;
     for (int r = 0; r < n; ++r) {
       const int64_t slot = next_slot(rp, n, last, lane);
+      if (slot >= (int64_t)kNoSlot) break;       // the remaining places of the row are empty
       last = slot;
       const T* src = part_dq + ((int64_t)sb * c.cap + slot) * c.d;
 #pragma unroll
@@ -398,12 +417,9 @@ __device__ __forceinline__ GroupRow group_row(int64_t vblock, const CombineParam
   g.t = row_ok ? gid / c.nh : 0;
   g.hr = row_ok ? (int)(gid - g.t * c.nh) : 0;
   g.rid = (int64_t)g.hr * c.total_q + g.t;
-  uint32_t p0 = 0;
+  int64_t p0 = 0;
   int n_e = 0;
-  if (row_ok) {
-    p0 = c.row_ptr[g.rid];
-    n_e = (int)(c.row_ptr[g.rid + 1] - p0);
-  }
+  if (row_ok) row_span(c, g.rid, p0, n_e);
   g.n = n_e * c.nsub;                       // partials of the row
   g.mine = row_ok && g.n >= min_n;          // rows below min_n were done by the previous kernel
   if (g.n > G) {
@@ -413,6 +429,7 @@ __device__ __forceinline__ GroupRow group_row(int64_t vblock, const CombineParam
   if (!g.mine) g.n = 0;
   g.valid = gl < g.n;
   g.slot = g.valid ? c.row_pos[p0 + gl / c.nsub] : 0u;
+  if (g.slot == kNoSlot) g.valid = false;      // an empty place of a handed-over row list
   g.pos = g.valid ? (uint32_t)((gl % c.nsub) * c.cap) + g.slot : 0xffffffffu;
   return g;
 }
@@ -594,11 +611,14 @@ __device__ __forceinline__ void combine_wide_body(int64_t vblock, const T* __res
   int rank = 0;
 #pragma unroll
   for (int i = 0; i < 32; ++i) rank += (__shfl_sync(0xffffffffu, g.pos, i) < g.pos) ? 1 : 0;
+  // the row's partials in use (a handed-over row list may have empty places: they rank last)
+  const int nv = __popc(__ballot_sync(0xffffffffu, g.valid));
   int inv = 0;                                // the lane that holds the partial of rank `lane`
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
     const int ri = __shfl_sync(0xffffffffu, rank, i);
-    if (i < g.n && ri == lane) inv = i;
+    const bool vi = (__shfl_sync(0xffffffffu, (int)g.valid, i) != 0);
+    if (vi && ri == lane) inv = i;
   }
   float m = 0.f, w = 1.f, ssum = 1.f;
   if (FWD) {
@@ -609,20 +629,20 @@ __device__ __forceinline__ void combine_wide_body(int64_t vblock, const T* __res
     // summed with the weights in rank order: the order in which the row's partials sit in the
     // lanes is that of the row list, which the atomics of its build leave undefined
     const float w_ranked = __shfl_sync(0xffffffffu, w, inv);
-    ssum = lane < g.n ? w_ranked : 0.f;
+    ssum = lane < nv ? w_ranked : 0.f;
 #pragma unroll
     for (int o = 16; o; o >>= 1) ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
   }
   float acc[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-  for (int r0 = 0; r0 < g.n; r0 += PPS * B) {
+  for (int r0 = 0; r0 < nv; r0 += PPS * B) {
     uint4 x[B];
     float wk[B];
 #pragma unroll
     for (int k = 0; k < B; ++k) {
       const int want = r0 + k * PPS + sub;
-      const bool hit = want < g.n;
+      const bool hit = want < nv;
       const int src = __shfl_sync(0xffffffffu, inv, want & 31);
       const uint32_t pk = __shfl_sync(0xffffffffu, g.pos, src);
       const uint32_t sk = __shfl_sync(0xffffffffu, g.slot, src);
@@ -745,6 +765,7 @@ static CombineParams make_combine(const AttnArgs& a, const AttnWorkspace& w, con
   CombineParams c;
   c.row_ptr = w.row_ptr; c.row_pos = w.row_pos; c.total_q = a.total_q; c.cap = w.cap; c.heads_out = a.heads;
   c.h0 = ps.h0; c.nh = ps.nh; c.nsub = w.nsub; c.d = a.d;
+  c.fixed_k = w.fixed_k;
   return c;
 }
 
@@ -756,6 +777,29 @@ static int fwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const
   const T* po = (const T*)w.part_o;
   T* out = (T*)a.o;
   const int64_t nb8 = group_grid(rows, 8), nbw = warp_grid(rows);
+  if (c.fixed_k > 0) {   // every row has fixed_k * nsub places: the stage is known on the host, one launch
+    const int places = c.fixed_k * c.nsub;
+    if (places <= 8) {
+      fwd_combine_group_kernel<T, 8, D / 8><<<first_grid(nb8), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse,
+                                                                          0, nullptr, ovf, nb8);
+      FMB_LAUNCH_CHECK("fwd_combine_group_kernel<8>");
+    } else if (D >= 128 && places <= 16) {
+      if constexpr (D >= 128) {
+        const int64_t nb16 = group_grid(rows, 16);
+        fwd_combine_group_kernel<T, 16, D / 16><<<first_grid(nb16), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs,
+                                                                                a.lse, 0, nullptr, ovf, nb16);
+        FMB_LAUNCH_CHECK("fwd_combine_group_kernel<16>");
+      }
+    } else if (places <= 32) {
+      combine_wide_kernel<T, D, true><<<late_grid(nbw), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, 0,
+                                                                     nullptr, ovf, nbw);
+      FMB_LAUNCH_CHECK("combine_wide_kernel<fwd>");
+    } else {
+      fwd_combine_kernel<T><<<late_grid(nbw), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, nullptr, 0, nbw);
+      FMB_LAUNCH_CHECK("fwd_combine_kernel");
+    }
+    return FMB_OK;
+  }
   fwd_combine_group_kernel<T, 8, D / 8><<<first_grid(nb8), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, 0,
                                                                       nullptr, ovf, nb8);
   FMB_LAUNCH_CHECK("fwd_combine_group_kernel<8>");
@@ -804,6 +848,28 @@ static int bwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const
   const T* pd = (const T*)w.part_o;
   T* dq = (T*)a.dq;
   const int64_t nb8 = group_grid(rows, 8), nbw = warp_grid(rows);
+  if (c.fixed_k > 0) {   // every row has fixed_k * nsub places: the stage is known on the host, one launch
+    const int places = c.fixed_k * c.nsub;
+    if (places <= 8) {
+      bwd_combine_group_kernel<T, 8, D / 8><<<first_grid(nb8), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 0, nullptr, ovf, nb8);
+      FMB_LAUNCH_CHECK("bwd_combine_group_kernel<8>");
+    } else if (D >= 128 && places <= 16) {
+      if constexpr (D >= 128) {
+        const int64_t nb16 = group_grid(rows, 16);
+        bwd_combine_group_kernel<T, 16, D / 16><<<first_grid(nb16), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 0, nullptr,
+                                                                                ovf, nb16);
+        FMB_LAUNCH_CHECK("bwd_combine_group_kernel<16>");
+      }
+    } else if (places <= 32) {
+      combine_wide_kernel<T, D, false><<<late_grid(nbw), 256, 0, s>>>(pd, nullptr, c, dq, a.dq_rs, a.dq_hs, nullptr, 0,
+                                                                      nullptr, ovf, nbw);
+      FMB_LAUNCH_CHECK("combine_wide_kernel<bwd>");
+    } else {
+      bwd_combine_kernel<T><<<late_grid(nbw), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, nullptr, 0, nbw);
+      FMB_LAUNCH_CHECK("bwd_combine_kernel");
+    }
+    return FMB_OK;
+  }
   bwd_combine_group_kernel<T, 8, D / 8><<<first_grid(nb8), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 0, nullptr, ovf, nb8);
   FMB_LAUNCH_CHECK("bwd_combine_group_kernel<8>");
   int* left = ovf;
@@ -875,14 +941,39 @@ static int check_pass_sizes(const char* op, const AttnArgs& a, const AttnWorkspa
   return FMB_OK;
 }
 
+// ------------------------------------------------------------------ rows handed over by the pattern builder
+struct RowsTicket {
+  const uint32_t* rows; int64_t total_q; int heads, topk; bool armed;
+};
+static thread_local RowsTicket g_rows = {nullptr, 0, 0, 0, false};
+
+void attn_rows_offer(const uint32_t* row_slots, int64_t total_q, int heads, int topk) {
+  g_rows = RowsTicket{row_slots, total_q, heads, topk, row_slots != nullptr && topk > 0};
+}
+// Consumes the ticket; true if this call (one pass over all heads, matching geometry) runs on it:
+// slots are positions in `indices`, the row lists are the builder's.
+static bool take_rows(const AttnArgs& a, AttnWorkspace& w) {
+  const RowsTicket t = g_rows;
+  g_rows.armed = false;
+  w.fixed_k = 0;
+  if (!t.armed || t.total_q != a.total_q || t.heads != a.heads || w.nh < a.heads ||
+      (int64_t)t.total_q * t.heads * t.topk != a.n_indices || a.n_indices >= (int64_t)0xffffffffll)
+    return false;
+  w.fixed_k = t.topk;
+  w.row_pos = const_cast<uint32_t*>(t.rows);
+  w.slot_base = nullptr;
+  return true;
+}
+
 int launch_attn_fwd(const AttnArgs& a, int engine, cudaStream_t s) {
   AttnWorkspace w = carve_attn_workspace(a.ws, a.ws_bytes, a, 2, true, 0);
   int rc = check_pass_sizes("attn_fwd", a, w, w.bytes);
   if (rc) return rc;
+  const bool rows_given = take_rows(a, w);
   FMB_CUDA(cudaMemsetAsync(w.status, 0, 512, s));
   for (int h0 = 0; h0 < a.heads; h0 += w.nh) {
     const PassParams ps = make_pass(a, w, h0, min(w.nh, a.heads - h0));
-    if ((rc = build_row_lists(a, w, ps, s))) return rc;
+    if (!rows_given && (rc = build_row_lists(a, w, ps, s))) return rc;
     prof_begin(0, s);
     if (engine == 1 && tc_supported(a, false)) rc = launch_fwd_main_tc(a, w, ps, s);
     else rc = launch_fwd_main_simt(a, w, ps, s);
@@ -933,11 +1024,12 @@ int launch_attn_bwd(const AttnArgs& a, int engine, cudaStream_t s) {
                            g_ticket.batch == a.batch && g_ticket.ncol == a.ncol && g_ticket.chunk == a.chunk &&
                            w.nh >= a.heads;
   g_ticket.armed = false;
+  const bool rows_given = take_rows(a, w);
   FMB_CUDA(cudaMemsetAsync(w.status, 0, 512, s));
   if ((rc = launch_dot_do_o(a, s))) return rc;
   for (int h0 = 0; h0 < a.heads; h0 += w.nh) {
     const PassParams ps = make_pass(a, w, h0, min(w.nh, a.heads - h0));
-    if (!lists_given && (rc = build_row_lists(a, w, ps, s))) return rc;
+    if (!lists_given && !rows_given && (rc = build_row_lists(a, w, ps, s))) return rc;
     prof_begin(1, s);
     if (engine == 1 && tc_supported(a, true)) rc = launch_bwd_main_tc(a, w, ps, s);
     else rc = launch_bwd_main_simt(a, w, ps, s);

@@ -120,7 +120,7 @@ int read_gate_status(int* out);
 size_t csc_workspace_bytes(int batch, int heads, int max_q, int ncol);
 int launch_build_csc(const int32_t* topk_idx, int64_t idx_rs, int64_t idx_hs, const int32_t* cu_q, int64_t* col_offsets, int32_t* col_nnz,
                      int32_t* indices, void* ws, size_t ws_bytes, int batch, int heads, int topk, int max_q,
-                     int ncol, cudaStream_t s);
+                     int ncol, cudaStream_t s, uint32_t* row_slots = nullptr, int64_t total_q = 0);
 size_t csc_static_scratch_bytes();
 int launch_build_csc_static(const int32_t* topk_idx, int64_t idx_rs, int64_t idx_hs, const int32_t* cu_q,
                             int64_t* col_offsets, int32_t* col_nnz, int32_t* indices, int batch, int heads,

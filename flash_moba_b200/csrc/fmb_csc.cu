@@ -13,7 +13,11 @@
 //                  zero of the region's unused tail
 //   3. scatter   : rebuild the bitmap; a half-warp per column walks its bits in row
 //                  order and writes them at col_offsets + cursor -> columns come out
-//                  ascending, bit-exact and run-to-run deterministic.
+//                  ascending, bit-exact and run-to-run deterministic.  On request the same
+//                  kernel also writes, for entry j of every row's top-k list, the position
+//                  in `indices` where that (row, chunk) pair landed (row_slots): the
+//                  row-major view of the pattern that the attention kernels' combine pass
+//                  needs, so that an attention call on this pattern builds no lists of its own.
 // HBM bound.  Algorithmic bytes: 4*nnz read + 4*nnz written + 12*B*H*ncol.
 #include <mutex>
 
@@ -32,6 +36,8 @@ struct CscParams {
   const int32_t* cu_q;
   int64_t* col_offsets; int32_t* col_nnz; int32_t* indices;
   int32_t* hist;                                      // [B*H][ntiles][ncol]
+  uint32_t* row_slots;                                // optional: [(h*total_q + token)*topk + j], 0xffffffff = no entry
+  int64_t total_q;
   int heads, topk, ncol, ntiles, cols_per_cta;
 };
 
@@ -168,6 +174,26 @@ __global__ void __launch_bounds__(kCscThreads) csc_scatter_kernel(CscParams p) {
       *dst++ = rbase + bit;
     }
   }
+  if (p.row_slots == nullptr) return;
+  // Row-major pass: entry (row r, list place j) with chunk c in this CTA's column range sits at
+  // col_offsets[c] + cursor[c] + (rows of this tile below r that also selected c).
+  const int r0 = tile * kTileRows;
+  const int rows = min(kTileRows, len_q - r0);
+  const int32_t* src = p.topk_idx + (int64_t)(seq0 + r0) * p.idx_rs + (int64_t)h * p.idx_hs;
+  uint32_t* out = p.row_slots + ((int64_t)h * p.total_q + seq0 + r0) * p.topk;
+  for (int e = threadIdx.x; e < rows * p.topk; e += blockDim.x) {
+    const int r = e / p.topk, j = e - r * p.topk;
+    const int cg = src[(int64_t)r * p.idx_rs + j];
+    const int c = cg - c0;
+    if (c >= 0 && c < ncols) {
+      const uint32_t* col = bm + c * kBmStride;
+      int below = __popc(col[r >> 5] & ((1u << (r & 31)) - 1u));
+      for (int w = 0; w < (r >> 5); ++w) below += __popc(col[w]);
+      out[e] = (uint32_t)(offs[c] + cursor[c] + below);
+    } else if (blockIdx.z == 0 && (cg < 0 || cg >= p.ncol)) {
+      out[e] = 0xffffffffu;     // empty place of the list (or a chunk id outside the pattern)
+    }
+  }
 }
 
 static int csc_ntiles(int max_q) { return max(1, ceil_div(max_q, kTileRows)); }
@@ -178,7 +204,7 @@ size_t csc_workspace_bytes(int batch, int heads, int max_q, int ncol) {
 
 int launch_build_csc(const int32_t* topk_idx, int64_t idx_rs, int64_t idx_hs, const int32_t* cu_q, int64_t* col_offsets, int32_t* col_nnz,
                      int32_t* indices, void* ws, size_t ws_bytes, int batch, int heads, int topk, int max_q,
-                     int ncol, cudaStream_t s) {
+                     int ncol, cudaStream_t s, uint32_t* row_slots, int64_t total_q) {
   if (batch == 0 || heads == 0 || ncol == 0) return FMB_OK;
   if (ws == nullptr || ws_bytes < csc_workspace_bytes(batch, heads, max_q, ncol))
     return fail(FMB_ERR_WORKSPACE, "build_csc: workspace too small (%zu < %zu)", ws_bytes,
@@ -189,6 +215,7 @@ int launch_build_csc(const int32_t* topk_idx, int64_t idx_rs, int64_t idx_hs, co
   p.idx_hs = idx_hs;
   p.cu_q = cu_q; p.col_offsets = col_offsets; p.col_nnz = col_nnz; p.indices = indices;
   p.hist = static_cast<int32_t*>(ws);
+  p.row_slots = row_slots; p.total_q = total_q;
   p.heads = heads; p.topk = topk; p.ncol = ncol; p.ntiles = csc_ntiles(max_q);
   p.cols_per_cta = min(kMaxColsPerCta, ncol);
   const int ncr = ceil_div(ncol, p.cols_per_cta);

@@ -72,7 +72,7 @@ def _moba_fused_topk(
     idx, _ = ops.gate_topk(q, km, cu_seqlens_q, cu_seqlens_k, cu_seqlens_km, max_seqlen_q, max_seqlen_k,
                            moba_topk, moba_chunk_size, causal)
     ncol = (max_seqlen_k + moba_chunk_size - 1) // moba_chunk_size
-    return ops.build_csc(idx, cu_seqlens_q, max_seqlen_q, ncol)
+    return ops.build_csc(idx, cu_seqlens_q, max_seqlen_q, ncol, keep_rows=True)
 
 
 @torch.library.register_fake("flash_moba::_moba_fused_topk")

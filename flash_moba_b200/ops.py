@@ -81,6 +81,42 @@ def offer_lists(lists) -> None:
     _tls.offered = lists
 
 
+# ---- the row-major view of a pattern, kept by the pattern builder for the attention calls
+# build_csc lets the library write, next to the pattern, where every (row, chunk) pair landed in
+# `indices` (fmb_build_csc_rows).  An attention call on exactly that pattern offers those rows to
+# the library (fmb_attn_rows_offer) and then launches no list-building kernels of its own.  The
+# cache holds the pattern tensors themselves, so a data pointer cannot be reused while its entry
+# lives; an in-place write to a pattern tensor changes its version and misses.
+import collections as _collections
+
+_rows_cache = _collections.OrderedDict()
+_ROWS_CACHE_ENTRIES = 4
+
+
+def _pattern_key(col_offsets, col_nnz, indices):
+    return tuple((t.data_ptr(), t._version, t.numel()) for t in (col_offsets, col_nnz, indices)) + (str(indices.device),)
+
+
+def _rows_remember(col_offsets, col_nnz, indices, row_slots, topk):
+    _rows_cache[_pattern_key(col_offsets, col_nnz, indices)] = (col_offsets, col_nnz, indices, row_slots, topk)
+    while len(_rows_cache) > _ROWS_CACHE_ENTRIES:
+        _rows_cache.popitem(last=False)
+
+
+def _rows_offer(col_offsets, col_nnz, indices, total_q, h) -> bool:
+    """Offers the builder's rows of this pattern to the next attention call; False if there are none."""
+    if not _share_lists():
+        return False
+    hit = _rows_cache.get(_pattern_key(col_offsets, col_nnz, indices))
+    if hit is None:
+        return False
+    row_slots, topk = hit[3], hit[4]
+    if row_slots.numel() != total_q * h * topk or indices.numel() != row_slots.numel():
+        return False
+    check(lib.fmb_attn_rows_offer(ptr(row_slots), total_q, h, topk))
+    return True
+
+
 def _workspace(query, total_q, h, hk, d, n_indices, batch, max_seqlen_k, chunk, device):
     """Workspace for one attention call: the single-pass size if it fits the cap
     (FMB_WORKSPACE_GB, default 24 GiB), otherwise the largest pass of whole kv-head groups that
@@ -192,8 +228,13 @@ def gate_topk(q, km, cu_seqlens_q, cu_seqlens_k, cu_seqlens_km, max_seqlen_q: in
 
 
 # --------------------------------------------------------------------------- stages O/E/S
-def build_csc(topk_idx: torch.Tensor, cu_seqlens_q: torch.Tensor, max_seqlen_q: int, ncol: int):
-    """(col_offsets i64 (B,H,ncol), col_nnz i32 (B,H,ncol), indices i32 (T*H*topk))."""
+def build_csc(topk_idx: torch.Tensor, cu_seqlens_q: torch.Tensor, max_seqlen_q: int, ncol: int,
+              keep_rows: bool = False):
+    """(col_offsets i64 (B,H,ncol), col_nnz i32 (B,H,ncol), indices i32 (T*H*topk)).
+
+    keep_rows: also let the library write the pattern's row-major view and keep it for attention
+    calls on the returned tensors (only for lists that name a chunk at most once per row, as the
+    lists of gate_topk do)."""
     _require_cuda(topk_idx)
     if topk_idx.dtype != torch.int32 or topk_idx.stride(-1) != 1:
         raise RuntimeError("topk_idx must be int32 with contiguous last dimension")
@@ -206,9 +247,17 @@ def build_csc(topk_idx: torch.Tensor, cu_seqlens_q: torch.Tensor, max_seqlen_q: 
         indices = torch.empty((total_q * h * topk,), dtype=torch.int32, device=dev)
         nbytes = lib.fmb_build_csc_workspace_bytes(batch, h, int(max_seqlen_q), ncol)
         ws = torch.empty((max(nbytes, 1),), dtype=torch.uint8, device=dev)
-        check(lib.fmb_build_csc(ptr(topk_idx), topk_idx.stride(0), topk_idx.stride(1),
-                                ptr(_i32c(cu_seqlens_q, "cu_seqlens_q")), ptr(col_offsets), ptr(col_nnz),
-                                ptr(indices), ptr(ws), nbytes, batch, h, topk, int(max_seqlen_q), ncol, _stream()))
+        if keep_rows and _share_lists() and 0 < indices.numel() < 0xffffffff:
+            row_slots = torch.empty((h, total_q, topk), dtype=torch.int32, device=dev)
+            check(lib.fmb_build_csc_rows(ptr(topk_idx), topk_idx.stride(0), topk_idx.stride(1),
+                                         ptr(_i32c(cu_seqlens_q, "cu_seqlens_q")), ptr(col_offsets), ptr(col_nnz),
+                                         ptr(indices), ptr(row_slots), ptr(ws), nbytes, batch, h, topk, total_q,
+                                         int(max_seqlen_q), ncol, _stream()))
+            _rows_remember(col_offsets, col_nnz, indices, row_slots, topk)
+        else:
+            check(lib.fmb_build_csc(ptr(topk_idx), topk_idx.stride(0), topk_idx.stride(1),
+                                    ptr(_i32c(cu_seqlens_q, "cu_seqlens_q")), ptr(col_offsets), ptr(col_nnz),
+                                    ptr(indices), ptr(ws), nbytes, batch, h, topk, int(max_seqlen_q), ncol, _stream()))
     return col_offsets, col_nnz, indices
 
 
@@ -262,6 +311,7 @@ def attn_fwd(q, k, v, col_offsets, col_nnz, indices, cu_seqlens_q, cu_seqlens_k,
         lse = torch.empty((h, total_q), dtype=torch.float32, device=dev)
         ws, nbytes = _workspace(lib.fmb_attn_fwd_workspace_bytes, total_q, h, hk, d, indices.numel(), batch,
                                 max_seqlen_k, chunk, dev)
+        rows_offered = _rows_offer(col_offsets, col_nnz, indices, total_q, h)
         check(lib.fmb_attn_fwd(ptr(q), q.stride(0), q.stride(1), ptr(k), k.stride(0), k.stride(1),
                                ptr(v), v.stride(0), v.stride(1), ptr(out), out.stride(0), out.stride(1), ptr(lse),
                                ptr(col_offsets), ptr(col_nnz), ptr(indices), indices.numel(),
@@ -270,7 +320,7 @@ def attn_fwd(q, k, v, col_offsets, col_nnz, indices, cu_seqlens_q, cu_seqlens_k,
                                int(chunk), float(softmax_scale), int(bool(causal)), _dtype_code(q), _stream()))
         _check_status(ws, "attn_fwd")
         _tls.kept = None
-        if _share_lists() and indices.numel() > 0:
+        if _share_lists() and indices.numel() > 0 and not rows_offered:
             geo = (total_q, h, hk, d, indices.numel(), batch, int(max_seqlen_k), int(chunk))
             nlist = lib.fmb_attn_lists_bytes(*geo)
             lists = torch.empty((max(nlist, 1),), dtype=torch.uint8, device=dev)
@@ -303,7 +353,9 @@ def attn_bwd(dout, q, k, v, out, lse, dq, dk, dv, col_offsets, col_nnz, indices,
                                 max_seqlen_k, chunk, dev)
         offered = getattr(_tls, "offered", None)
         _tls.offered = None
-        if offered is not None and _share_lists() and \
+        if _rows_offer(col_offsets, col_nnz, indices, total_q, h):
+            pass        # the pattern builder's rows: no lists to load, none to build
+        elif offered is not None and _share_lists() and \
                 offered[0] == _lists_key(col_offsets, col_nnz, indices, cu_seqlens_q, total_q, h, hk, d, batch,
                                          max_seqlen_k, chunk):
             rc = lib.fmb_attn_lists_load(ptr(ws), nbytes, total_q, h, hk, d, indices.numel(), batch,

@@ -105,6 +105,26 @@ int fmb_build_csc(const int32_t* topk_idx, int64_t topk_row_stride, int64_t topk
                   int batch, int heads, int topk, int max_seqlen_q, int ncol,
                   fmb_stream_t stream);
 
+/* fmb_build_csc that also writes the row-major view of the pattern it builds: row_slots
+ * (uint32, total_q*heads*topk, index ((h*total_q + token)*topk + j)) receives, for place j of the
+ * top-k list of (token, head h), the position in `indices` where that (row, chunk) pair was put, or
+ * 0xffffffff for an empty place (chunk id < 0 or >= ncol).  Rows of sequences shorter than
+ * max_seqlen_q and all tokens of the batch are covered; a list must not name a chunk twice (the
+ * lists of fmb_gate_topk never do).  fmb_attn_rows_offer hands row_slots to the next fmb_attn_fwd
+ * or fmb_attn_bwd call made by the same host thread: if that call's geometry matches (total_q,
+ * heads, n_indices = total_q*heads*topk) and its workspace holds all heads in one pass, it uses an
+ * entry's position in `indices` as its partial-result slot and these row lists, and launches none
+ * of its own list-building kernels (the reference rebuilds nothing either: its kernels are
+ * query-block-major, csrc/flash_moba/src/flash_fwd_kernel.h:232-769).  The offer is consumed by
+ * that one call whether it is used or not; passing NULL withdraws it.  The pattern must be the
+ * one fmb_build_csc_rows wrote together with row_slots (columns that do not overlap). */
+int fmb_build_csc_rows(const int32_t* topk_idx, int64_t topk_row_stride, int64_t topk_head_stride,
+                       const int32_t* cu_seqlens_q, int64_t* col_offsets, int32_t* col_nnz,
+                       int32_t* indices, uint32_t* row_slots, void* workspace, size_t workspace_bytes,
+                       int batch, int heads, int topk, int64_t total_q, int max_seqlen_q, int ncol,
+                       fmb_stream_t stream);
+int fmb_attn_rows_offer(const uint32_t* row_slots, int64_t total_q, int heads, int topk);
+
 /* fmb_build_csc for callers that cannot allocate device memory.  This entry point has no
  * counterpart in the reference (there the C++ side allocates with torch::empty).  It is for
  * hosts that may not call cudaMalloc once they are running — a serving runtime that took

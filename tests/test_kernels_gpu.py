@@ -516,6 +516,51 @@ def test_row_lists_handed_from_forward_to_backward(monkeypatch):
         assert torch.equal(a, b)
 
 
+def test_lists_of_a_caller_built_pattern_and_launch_counts(monkeypatch):
+    """A pattern that did not come from the library's own builder (here: rebuilt by the oracle from
+    the same lists) takes the general path: slot and row lists built by the forward call and handed
+    to the backward call.  Same results bit for bit as the library's own pattern, which needs no
+    list-building launches at all: a whole step (pool, gating, pattern, forward, backward) is at
+    most 12 launches."""
+    import flash_moba_b200 as F
+    from flash_moba_b200 import _lib
+    torch.manual_seed(1)
+    lens, H, Hk, d, chunk, topk = [900, 515], 4, 2, 128, 128, 4
+    T = sum(lens)
+    cu = cu_of(lens).to(DEV)
+    q, k, v, do = (torch.randn(T, h, d, device=DEV).bfloat16() for h in (H, Hk, Hk, H))
+    mx = max(lens)
+
+    def attn(pattern):
+        qd, kd, vd = (t.clone().requires_grad_(True) for t in (q, k, v))
+        n0 = _lib.lib.fmb_launch_count()
+        out = F.flash_moba_attn_varlen_func(qd, kd, vd, cu, cu, mx, mx, *pattern, 128, chunk, causal=True)
+        grads = torch.autograd.grad(out, (qd, kd, vd), do)
+        torch.cuda.synchronize()
+        return (out.detach(),) + grads, _lib.lib.fmb_launch_count() - n0
+
+    own = F.flash_topk_varlen_func(q, k, cu, cu, mx, mx, topk, chunk, causal=True)
+    got_own, n_own = attn(own)
+    copy = tuple(t.clone() for t in own)              # same pattern, unknown to the library
+    got_copy, n_copy = attn(copy)
+    for a, b in zip(got_own, got_copy):
+        assert torch.equal(a, b)
+    assert n_own == 5, n_own                          # forward main + combine, dO.O, backward main + combine
+    assert n_own < n_copy
+    monkeypatch.setenv("FMB_SHARE_LISTS", "0")
+    got_off, n_off = attn(copy)
+    for a, b in zip(got_own, got_off):
+        assert torch.equal(a, b)
+    assert n_copy < n_off
+    monkeypatch.setenv("FMB_SHARE_LISTS", "1")
+    n0 = _lib.lib.fmb_launch_count()
+    qd, kd, vd = (t.clone().requires_grad_(True) for t in (q, k, v))
+    out = F.flash_moba_varlen_func(qd, kd, vd, cu, cu, mx, mx, chunk, topk, causal=True)
+    torch.autograd.grad(out, (qd, kd, vd), do)
+    torch.cuda.synchronize()
+    assert _lib.lib.fmb_launch_count() - n0 <= 12
+
+
 def test_determinism_and_autograd_through_public_api():
     import flash_moba_b200 as F
     torch.manual_seed(0)
