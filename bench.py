@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the MoBA hot path (pattern + block-sparse forward + backward).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload 64k|c2|c3]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload 64k|c2|c3|c4|c5] [--heads H]
 
 A step = one pass of the hot path over one batch of synthetic input through the public API
 (`flash_moba_varlen_func` forward, autograd backward): mean-pool -> gating top-k -> pattern
@@ -30,16 +30,22 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+def _c4_lengths():
+    """Configuration 4's 16 sequence lengths: uniform in [2048, 32768], rounded up to multiples of 64, seed 0."""
+    import random
+    rnd = random.Random(0)
+    return [(rnd.randint(2048, 32768) + 63) // 64 * 64 for _ in range(16)]
+
+
 WORKLOADS = {
-    # name: (seqlens, heads, heads_k, d, chunk, topk, backward, input scale)
+    # name: (seqlens, heads, heads_k, d, chunk, topk, backward, input scale): the headline workload and
+    # the benchmark configurations 2-5 at their full shapes; --heads runs a stated share of the heads
+    # (same ratio of q to kv heads) and --tokens a shorter single sequence, for profiler captures
     "64k": ([65536], 32, 32, 128, 128, 8, True, 1.0),
     "c2": ([32768], 16, 16, 128, 128, 8, False, 0.5),
     "c3": ([8192] * 8, 32, 32, 128, 128, 8, True, 1.0),
-    "small": ([4096], 8, 8, 128, 128, 8, True, 1.0),
-    "mid": ([16384], 16, 16, 128, 128, 8, True, 1.0),
-    "64k_h4": ([65536], 4, 4, 128, 128, 8, True, 1.0),      # one rank's share of "64k" at 8 GPUs
-    "c5s": ([524288], 4, 4, 128, 256, 16, True, 0.5),       # configuration 5 (512K tokens, chunk 256, top-k 16) with 4 of its 32 heads
-    "c4s": ([8192, 16384, 4096, 12288, 2048, 24576], 32, 8, 128, 64, 16, True, 1.0),   # configuration 4 at a sixth of its size
+    "c4": (_c4_lengths(), 32, 8, 128, 64, 16, True, 1.0),
+    "c5": ([524288], 32, 32, 128, 256, 16, True, 0.5),
 }
 
 
@@ -52,6 +58,7 @@ def _load_accounting():
 
 
 ACC = _load_accounting()
+BWD_MAIN_DRAM_BYTES_PER_ENTRY = 653.7
 
 
 class ClockSampler:
@@ -196,8 +203,26 @@ def cpu_sample(seqlens, d, chunk, topk, rows=4096, threads=None):
     return dt, 3.5 * 4 * d * pairs, rows, threads
 
 
+def workload_of(args):
+    """(seqlens, H, Hk, d, chunk, topk, backward, scale) of the run, after --heads / --tokens."""
+    seqlens, H, Hk, d, chunk, topk, backward, scale = WORKLOADS[args.workload]
+    if args.heads:
+        assert args.heads % (H // Hk) == 0 and args.heads <= H, "--heads must keep whole kv-head groups"
+        H, Hk = args.heads, args.heads // (H // Hk)
+    if args.tokens:
+        assert len(seqlens) == 1, "--tokens is for single-sequence workloads"
+        seqlens = [args.tokens]
+    return seqlens, H, Hk, d, chunk, topk, backward, scale
+
+
+def config_of(wl, seqlens, H, Hk, d, chunk, topk, backward):
+    """What defines the workload: the same dict in both arms' lines."""
+    return {"workload": wl, "seqlens": seqlens, "heads": H, "heads_k": Hk, "head_dim": d, "chunk": chunk,
+            "topk": topk, "causal": True, "step": "pattern(pool+gate+csc) + fwd" + (" + bwd" if backward else "")}
+
+
 def run_reference(args, wl):
-    seqlens, H, Hk, d, chunk, topk, backward, scale = WORKLOADS[wl]
+    seqlens, H, Hk, d, chunk, topk, backward, scale = workload_of(args)
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -214,8 +239,7 @@ def run_reference(args, wl):
         "impl": "reference", "metric": "moba_fwd_bwd_selected_block_tflops", "value": val, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": wl, "seqlens": seqlens, "heads": H, "heads_k": Hk, "head_dim": d, "chunk": chunk,
-                   "topk": topk, "causal": True},
+        "config": config_of(wl, seqlens, H, Hk, d, chunk, topk, backward),
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                          "sample": f"pattern+fwd+bwd of the last {rows} query rows of 1 head vs all {seqlens[0]} keys, "
                                    "fp32 PyTorch oracle (oracle/moba_oracle.py), per step"},
@@ -228,7 +252,7 @@ _RESULT_FD = None
 
 
 def protect_stdout():
-    """The driver reads ONE JSON line from stdout; libraries print there too (NCCL its version line
+    """The result is ONE JSON line on stdout; libraries print there too (NCCL its version line
     when NCCL_DEBUG asks for it).  From here on everything written to file descriptor 1 goes to
     stderr, and only emit() writes to the real stdout."""
     global _RESULT_FD
@@ -254,6 +278,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="64k", choices=sorted(WORKLOADS))
+    ap.add_argument("--heads", type=int, default=0, help="run this many of the workload's q heads (same q:kv ratio)")
+    ap.add_argument("--tokens", type=int, default=0, help="single-sequence workloads: this many tokens instead")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--e2e-groups", type=int, default=8, help="head groups of the host pipeline")
@@ -264,7 +290,7 @@ def main():
     if args.impl == "reference":
         return run_reference(args, wl)
 
-    seqlens, H, Hk, d, chunk, topk, backward, scale = WORKLOADS[wl]
+    seqlens, H, Hk, d, chunk, topk, backward, scale = workload_of(args)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -318,9 +344,25 @@ def main():
         clk.mark("end")
     ms = ev0.elapsed_time(ev1) / args.steps
     launches = _lib.lib.fmb_launch_count() - launches0
+    # device-side status words of every attention call so far, and of the gating launches
+    status = 0
+    try:
+        ops.check_pending_status()
+        gate_code = __import__("ctypes").c_int(0)
+        _lib.check(_lib.lib.fmb_gate_status(__import__("ctypes").addressof(gate_code)))
+    except RuntimeError as e:
+        status = str(e)
+    # host time per step: the same loop without waiting for the device (enqueue cost of a step)
+    barrier()
+    t_h0 = time.perf_counter()
+    for _ in range(args.steps):
+        step(q, k, v, do)
+    host_ms = (time.perf_counter() - t_h0) * 1e3 / args.steps
+    barrier()
     import ctypes
     kern_ms = {}
-    for kind, name in ((0, "fwd_main"), (1, "bwd_main"), (2, "gate"), (3, "pool")):
+    for kind, name in ((0, "fwd_main"), (1, "bwd_main"), (2, "gate"), (3, "pool"), (4, "fwd_combine"),
+                       (5, "bwd_combine"), (6, "pattern_build"), (7, "dot_do_o")):
         buf = (ctypes.c_float * 256)()
         n = _lib.lib.fmb_profile_read(kind, ctypes.cast(buf, ctypes.c_void_p), 256)
         kern_ms[name] = (sum(buf[:n]) / n) if n > 0 else None
@@ -377,22 +419,30 @@ def main():
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
     except OSError:
         pass
-    peak_tf = peaks.get("bf16_tflops_sustained", 1400.0)
-    peak_src = "measured (MEASURED_PEAKS.json bf16_tflops_sustained: kernel timed inside a long step)" if peaks else \
-        "fallback 1.4 PFLOP/s sustained"
+    clocks = clk.summary()
+    # the burst figure is the denominator as long as the clock stayed at its maximum with no power
+    # cap during the timed region (a step is milliseconds long); the sustained figure otherwise
+    at_max = bool(clocks.get("sm_mhz")) and clocks.get("sm_max_mhz") and \
+        clocks["sm_mhz"] >= 0.98 * clocks["sm_max_mhz"] and "sw_power_cap" not in clocks.get("reasons", [])
+    peak_burst, peak_sust = peaks.get("bf16_tflops", 1590.0), peaks.get("bf16_tflops_sustained", 1400.0)
+    peak_tf = peak_burst if at_max else peak_sust
+    peak_src = ("measured (MEASURED_PEAKS.json " if peaks else "fallback (") + \
+        ("bf16_tflops, burst: SM clock at its maximum and no power cap during the timed region)" if at_max else
+         "bf16_tflops_sustained: the clock dropped or the power cap was active)")
     dom = "bwd_main" if backward else "fwd_main"
     dom_flops = (bwd_f if backward else fwd_f) * h_loc / H      # rank 0's launch
     roof = None
     # DRAM bytes per (row, chunk) entry of the dominant kernel, from one ncu capture of a 16K-token,
-    # 16-head case (dram__bytes_read.sum + dram__bytes_write.sum = 1,038.1 MB over its 2,039,808
-    # entries); the traffic is per-entry work (gathered rows in, partial rows out), so it scales
-    # with the entries.
-    entry_bytes = {"bwd_main": 559.3}.get(dom) if (d == 128 and chunk == 128) else None
+    # 16-head case of this build (profiles/bwd_main_tc_kernel_16k.md: dram__bytes_read.sum +
+    # dram__bytes_write.sum over its 2,039,808 entries); the traffic is per-entry work (gathered
+    # rows in, partial rows out), so it scales with the entries.
+    entry_bytes = {"bwd_main": BWD_MAIN_DRAM_BYTES_PER_ENTRY}.get(dom) if (d == 128 and chunk == 128) else None
     entries = ACC.selected_entries(seqlens, chunk, topk) * h_loc
     if kern_ms.get(dom):
         ach = dom_flops / (kern_ms[dom] * 1e-3) / 1e12
         roof = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s",
-                "frac": ach / peak_tf, "traffic": (entry_bytes * entries if entry_bytes else None),
+                "frac": ach / peak_tf, "frac_of_burst": ach / peak_burst, "frac_of_sustained": ach / peak_sust,
+                "traffic": (entry_bytes * entries if entry_bytes else None),
                 "traffic_source": "ncu dram bytes of a 16K-token case, scaled by (row, chunk) entries" if entry_bytes else None,
                 "peak_source": peak_src,
                 "launch_ms": kern_ms[dom], "flops_per_launch": dom_flops,
@@ -402,13 +452,13 @@ def main():
         "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": wl, "seqlens": seqlens, "heads": H, "heads_k": Hk, "head_dim": d, "chunk": chunk,
-                   "topk": topk, "causal": True, "step": "pattern(pool+gate+csc) + fwd" + (" + bwd" if backward else ""),
-                   "sharding": f"query heads {h0}..{h1 - 1} of {H} on rank 0, whole kv-head groups per rank, no collective",
-                   "l2": f"inputs q,k,v,dO ({4 * T * h_loc * d * 2 >> 20} MB per rank) plus the per-pair partials exceed the 126 MB L2",
-                   "engine": {"fwd": ["cuda-core", "tcgen05"][_lib.lib.fmb_attn_engine(chunk, d, 0)],
-                              "bwd": ["cuda-core", "tcgen05"][_lib.lib.fmb_attn_engine(chunk, d, 1)]}},
-        "gpu_launches": int(launches), "clocks": clk.summary(), "e2e": e2e, "roofline": roof,
+        "config": config_of(wl, seqlens, H, Hk, d, chunk, topk, backward),
+        "run": {"sharding": f"query heads {h0}..{h1 - 1} of {H} on rank 0, whole kv-head groups per rank, no collective",
+                "l2": f"inputs q,k,v,dO ({4 * T * h_loc * d * 2 >> 20} MB per rank) plus the per-pair partials exceed the 126 MB L2",
+                "engine": {"fwd": ["cuda-core", "tcgen05"][_lib.lib.fmb_attn_engine(chunk, d, 0)],
+                           "bwd": ["cuda-core", "tcgen05"][_lib.lib.fmb_attn_engine(chunk, d, 1)]}},
+        "gpu_launches": int(launches), "launches_per_step": launches / args.steps, "host_ms_per_step": host_ms,
+        "status": status, "clocks": clocks, "e2e": e2e, "roofline": roof,
     }
     if world == 1 and not args.no_cpu_baseline:
         dt, fl, rows, threads = cpu_sample(seqlens, d, chunk, topk, rows=8192)

@@ -22,7 +22,7 @@ static unsigned long long g_launches = 0;
 void note_launch() { __atomic_fetch_add(&g_launches, 1ull, __ATOMIC_RELAXED); }
 
 // ---- optional event timing of the dominant kernels ------------------------------------
-constexpr int kProfKinds = 4, kProfRing = 256;
+constexpr int kProfKinds = 8, kProfRing = 256;
 struct ProfState {
   bool on = false;
   cudaEvent_t ev[kProfKinds][kProfRing][2] = {};
@@ -140,7 +140,34 @@ int fmb_gate_engine(int head_dim, int topk) { return (g_engine == 1 && gate_tc_s
 
 int fmb_gate_status(int* host_status) {
   FMB_CHECK_ARG(host_status, "gate_status: null pointer");
-  return read_gate_status(host_status);
+  const int rc = read_gate_status(host_status);
+  if (rc) return rc;
+  if (*host_status != 0)
+    return fail(FMB_ERR_TIMEOUT, "gate_topk: a bounded device-side wait expired (code %d)", *host_status);
+  return FMB_OK;
+}
+
+int fmb_attn_status(const void* workspace, int* host_status, fmb_stream_t stream) {
+  FMB_CHECK_ARG(workspace && host_status, "attn_status: null pointer");
+  FMB_CUDA(cudaMemcpyAsync(host_status, workspace, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  FMB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  const int code = *host_status;
+  if (code == 0) return FMB_OK;
+  if (code == 7)
+    return fail(FMB_ERR_WORKSPACE, "attention: the pattern does not fit the slots of a pass (columns that overlap, "
+                "or a workspace too small for this pattern)");
+  if (code == 9) return fail(FMB_ERR_CUDA, "attention: a kernel found its shared memory misaligned");
+  return fail(FMB_ERR_TIMEOUT, "attention: a bounded device-side wait expired (code %d)", code);
+}
+
+int fmb_attn_status_mirror(int* mirror) {
+  attn_status_mirror(mirror);
+  return FMB_OK;
+}
+
+int fmb_selftest_wait_expiry(int* status, unsigned long long* elapsed_ns, fmb_stream_t stream) {
+  FMB_CHECK_ARG(status && elapsed_ns, "selftest_wait_expiry: null pointer");
+  return launch_selftest_wait_expiry(status, elapsed_ns, (cudaStream_t)stream);
 }
 
 int fmb_chunk_offsets(const int32_t* cu_seqlens_k, int batch, int chunk, int32_t* cu_seqlens_km,

@@ -42,6 +42,7 @@ struct AttnWorkspace {
   uint32_t* row_pos;    // cap: slots of a row's entries
   uint32_t* scan_tmp;   // block sums of the scans
   int fixed_k;          // > 0: row lists handed over by the pattern builder (see attn_rows_offer)
+  int* mirror;          // where the call's status word is copied at its end (see attn_status_mirror), or nullptr
   int nh;               // heads per pass
   int nsub, kb;         // sub-blocks per chunk, keys per sub-block
   int64_t cap;          // slots per plane
@@ -118,6 +119,9 @@ int attn_lists_load(const AttnArgs& geometry_and_ws, const void* src, size_t src
 // one pass over all heads, same geometry) to use positions in `indices` as slots and these rows
 // instead of building slot and row lists.
 void attn_rows_offer(const uint32_t* row_slots, int64_t total_q, int heads, int topk);
+// One-shot, per host thread: the next attention call copies its status word to *mirror (memory the
+// device can write and the host can read, e.g. mapped pinned memory) when its main kernels are done.
+void attn_status_mirror(int* mirror);
 
 // Builds slot_base and row_ptr / row_pos (CSR transpose of the pass's part of the pattern).
 // Row id = (h - h0)*total_q + token.
@@ -139,6 +143,7 @@ bool tc_supported(const AttnArgs& a, bool backward);
 int sm_count();   // SMs of the current device
 int launch_selftest_gather(const void* a, int a_rows, const int* idx, const void* b, float* d, int dtype,
                            int* status, cudaStream_t s);
+int launch_selftest_wait_expiry(int* status, unsigned long long* elapsed_ns, cudaStream_t s);
 int launch_selftest_umma(const void* a, const void* b, float* d, int b_mn_major, int dtype, int* status,
                          cudaStream_t s);
 

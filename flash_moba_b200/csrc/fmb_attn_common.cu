@@ -16,6 +16,7 @@ static size_t layout(AttnWorkspace& w, void* base, const AttnArgs& a, size_t par
   };
   w.nh = nh;
   w.fixed_k = 0;
+  w.mirror = nullptr;
   w.kb = (a.chunk % 128 == 0) ? 128 : 64;
   w.nsub = a.chunk / w.kb;
   // one pass over all heads can never need more slots than the pattern has entries; a pass over a
@@ -238,7 +239,13 @@ struct CombineParams {
   int h0, nh, nsub, d;
   int fixed_k;     // > 0: row lists handed over by the pattern builder: row `rid` owns the fixed_k places
                    // row_pos[rid*fixed_k ..], empty places hold 0xffffffff; row_ptr is not used
+  const int* status; int* mirror;   // mirror != nullptr: the first combine kernel of the call's last pass copies
+                                    // the call's status word there (see attn_status_mirror)
 };
+// The main kernels, which set the status word, have completed when a combine kernel starts.
+__device__ __forceinline__ void mirror_status(const CombineParams& c) {
+  if (c.mirror != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *c.mirror = *c.status;
+}
 // first place and number of places of row `rid` in row_pos
 __device__ __forceinline__ void row_span(const CombineParams& c, int64_t rid, int64_t& p0, int& n) {
   if (c.fixed_k > 0) {
@@ -335,6 +342,7 @@ __global__ void __launch_bounds__(256) fwd_combine_kernel(const T* __restrict__ 
                                                           const float* __restrict__ part_lse, CombineParams c,
                                                           T* out, int64_t o_rs, int64_t o_hs, float* lse,
                                                           const int* only_if, int min_n, int64_t nvb) {
+  mirror_status(c);
   if (only_if && *only_if == 0) return;   // the earlier stages met no row they had to leave
   for (int64_t vb = blockIdx.x; vb < nvb; vb += gridDim.x)
     fwd_combine_body<T>(vb, part_o, part_lse, c, out, o_rs, o_hs, lse, min_n);
@@ -387,6 +395,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) bwd_combine_kernel(const T* __restrict__ part_dq, CombineParams c, T* dq,
                                                           int64_t rs, int64_t hs, const int* only_if, int min_n,
                                                           int64_t nvb) {
+  mirror_status(c);
   if (only_if && *only_if == 0) return;
   for (int64_t vb = blockIdx.x; vb < nvb; vb += gridDim.x) bwd_combine_body<T>(vb, part_dq, c, dq, rs, hs, min_n);
 }
@@ -516,11 +525,12 @@ __device__ __forceinline__ void fwd_combine_group_body(int64_t vblock, const T* 
   }
 }
 template <typename T, int G, int EPL>
-__global__ void __launch_bounds__(256, 2) fwd_combine_group_kernel(const T* __restrict__ part_o,
+__global__ void __launch_bounds__(256, EPL <= 8 ? 3 : 2) fwd_combine_group_kernel(const T* __restrict__ part_o,
                                                                 const float* __restrict__ part_lse,
                                                                 CombineParams c, T* out, int64_t o_rs, int64_t o_hs,
                                                                 float* lse, int min_n, const int* only_if,
                                                                 int* overflow, int64_t nvb) {
+  mirror_status(c);
   if (only_if && *only_if == 0) return;
   for (int64_t vb = blockIdx.x; vb < nvb; vb += gridDim.x)
     fwd_combine_group_body<T, G, EPL>(vb, part_o, part_lse, c, out, o_rs, o_hs, lse, min_n, overflow);
@@ -582,6 +592,7 @@ template <typename T, int G, int EPL>
 __global__ void __launch_bounds__(256) bwd_combine_group_kernel(const T* __restrict__ part_dq, CombineParams c,
                                                                 T* dq, int64_t rs, int64_t hs, int min_n,
                                                                 const int* only_if, int* overflow, int64_t nvb) {
+  mirror_status(c);
   if (only_if && *only_if == 0) return;
   for (int64_t vb = blockIdx.x; vb < nvb; vb += gridDim.x)
     bwd_combine_group_body<T, G, EPL>(vb, part_dq, c, dq, rs, hs, min_n, overflow);
@@ -678,6 +689,7 @@ __global__ void __launch_bounds__(256) combine_wide_kernel(const T* __restrict__
                                                            const float* __restrict__ part_lse, CombineParams c,
                                                            T* out, int64_t rs, int64_t hs, float* lse, int min_n,
                                                            const int* only_if, int* overflow, int64_t nvb) {
+  mirror_status(c);
   if (only_if && *only_if == 0) return;
   for (int64_t vb = blockIdx.x; vb < nvb; vb += gridDim.x)
     combine_wide_body<T, D, FWD>(vb, part, part_lse, c, out, rs, hs, lse, min_n, overflow);
@@ -746,13 +758,11 @@ int sm_count() {
 
 // First cascade stage: persistent CTAs, as many as are resident (2 per SM at 128 registers); measured
 // at 64K tokens 0.24 ms per step faster than one CTA per block of rows (65,536 short-lived CTAs).
-// (Prefetching the next blocks' row lists inside the loop was tried and lost 0.7 ms to spills.)
-#ifndef FMB_COMBINE_CTAS
-#define FMB_COMBINE_CTAS 2      // 0: one CTA per 256-thread block of rows; n: n persistent CTAs per SM
-#endif
-static unsigned first_grid(int64_t nvb) {
-  if (FMB_COMBINE_CTAS == 0) return (unsigned)nvb;
-  const int64_t cap = (int64_t)sm_count() * FMB_COMBINE_CTAS;
+// (Prefetching the next blocks' row lists inside the loop was tried and lost 0.7 ms to spills; with the
+// pattern builder's fixed-stride rows the prefetch is one register and changed nothing: 0.94 against
+// 0.92 ms in the backward combine, which reads its 4.8 GB at 80 % of the measured copy bandwidth.)
+static unsigned first_grid(int64_t nvb, int ctas_per_sm = 2) {
+  const int64_t cap = (int64_t)sm_count() * ctas_per_sm;
   return (unsigned)(nvb < cap ? nvb : cap);
 }
 // grid of a later cascade stage: enough CTAs to fill the GPU if it does have work
@@ -766,6 +776,8 @@ static CombineParams make_combine(const AttnArgs& a, const AttnWorkspace& w, con
   c.row_ptr = w.row_ptr; c.row_pos = w.row_pos; c.total_q = a.total_q; c.cap = w.cap; c.heads_out = a.heads;
   c.h0 = ps.h0; c.nh = ps.nh; c.nsub = w.nsub; c.d = a.d;
   c.fixed_k = w.fixed_k;
+  c.status = w.status;
+  c.mirror = (ps.h0 + ps.nh >= a.heads) ? w.mirror : nullptr;   // the call's last pass
   return c;
 }
 
@@ -779,15 +791,15 @@ static int fwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const
   const int64_t nb8 = group_grid(rows, 8), nbw = warp_grid(rows);
   if (c.fixed_k > 0) {   // every row has fixed_k * nsub places: the stage is known on the host, one launch
     const int places = c.fixed_k * c.nsub;
-    if (places <= 8) {
+    if (places <= 8) {   // (16 lanes per row instead of 8 for these rows: 1.57 ms against 1.21 ms at 64K)
       fwd_combine_group_kernel<T, 8, D / 8><<<first_grid(nb8), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse,
                                                                           0, nullptr, ovf, nb8);
       FMB_LAUNCH_CHECK("fwd_combine_group_kernel<8>");
     } else if (D >= 128 && places <= 16) {
       if constexpr (D >= 128) {
         const int64_t nb16 = group_grid(rows, 16);
-        fwd_combine_group_kernel<T, 16, D / 16><<<first_grid(nb16), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs,
-                                                                                a.lse, 0, nullptr, ovf, nb16);
+        fwd_combine_group_kernel<T, 16, D / 16><<<first_grid(nb16, D / 16 <= 8 ? 3 : 2), 256, 0, s>>>(
+            po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, 0, nullptr, ovf, nb16);
         FMB_LAUNCH_CHECK("fwd_combine_group_kernel<16>");
       }
     } else if (places <= 32) {
@@ -823,11 +835,9 @@ static int fwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const
 
 template <typename T>
 static int fwd_combine_any(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
-#ifndef FMB_COMBINE_GENERIC
   if (a.d == 64) return fwd_combine_dispatch<T, 64>(a, w, ps, s);
   if (a.d == 128) return fwd_combine_dispatch<T, 128>(a, w, ps, s);
   if (a.d == 256) return fwd_combine_dispatch<T, 256>(a, w, ps, s);
-#endif
   const int64_t rows = a.total_q * ps.nh;
   fwd_combine_kernel<T><<<warp_grid(rows), 256, 0, s>>>((const T*)w.part_o, w.part_lse, make_combine(a, w, ps),
                                                         (T*)a.o, a.o_rs, a.o_hs, a.lse, nullptr, 0, warp_grid(rows));
@@ -965,8 +975,18 @@ static bool take_rows(const AttnArgs& a, AttnWorkspace& w) {
   return true;
 }
 
+// ------------------------------------------------------------------ status word mirrored for the host
+static thread_local int* g_mirror = nullptr;
+void attn_status_mirror(int* mirror) { g_mirror = mirror; }
+static int* take_mirror() {
+  int* m = g_mirror;
+  g_mirror = nullptr;
+  return m;
+}
+
 int launch_attn_fwd(const AttnArgs& a, int engine, cudaStream_t s) {
   AttnWorkspace w = carve_attn_workspace(a.ws, a.ws_bytes, a, 2, true, 0);
+  w.mirror = take_mirror();
   int rc = check_pass_sizes("attn_fwd", a, w, w.bytes);
   if (rc) return rc;
   const bool rows_given = take_rows(a, w);
@@ -979,7 +999,10 @@ int launch_attn_fwd(const AttnArgs& a, int engine, cudaStream_t s) {
     else rc = launch_fwd_main_simt(a, w, ps, s);
     prof_end(0, s);
     if (rc) return rc;
-    if ((rc = launch_fwd_combine(a, w, ps, s))) return rc;
+    prof_begin(4, s);
+    rc = launch_fwd_combine(a, w, ps, s);
+    prof_end(4, s);
+    if (rc) return rc;
   }
   return FMB_OK;
 }
@@ -1016,6 +1039,7 @@ int attn_lists_load(const AttnArgs& a, const void* src, size_t src_bytes, cudaSt
 
 int launch_attn_bwd(const AttnArgs& a, int engine, cudaStream_t s) {
   AttnWorkspace w = carve_attn_workspace(a.ws, a.ws_bytes, a, 2, false, 0);
+  w.mirror = take_mirror();
   int rc = check_pass_sizes("attn_bwd", a, w, w.bytes);
   if (rc) return rc;
   // lists loaded into this very workspace for this very problem, one pass: no build of our own
@@ -1026,7 +1050,10 @@ int launch_attn_bwd(const AttnArgs& a, int engine, cudaStream_t s) {
   g_ticket.armed = false;
   const bool rows_given = take_rows(a, w);
   FMB_CUDA(cudaMemsetAsync(w.status, 0, 512, s));
-  if ((rc = launch_dot_do_o(a, s))) return rc;
+  prof_begin(7, s);
+  rc = launch_dot_do_o(a, s);
+  prof_end(7, s);
+  if (rc) return rc;
   for (int h0 = 0; h0 < a.heads; h0 += w.nh) {
     const PassParams ps = make_pass(a, w, h0, min(w.nh, a.heads - h0));
     if (!lists_given && !rows_given && (rc = build_row_lists(a, w, ps, s))) return rc;
@@ -1035,7 +1062,10 @@ int launch_attn_bwd(const AttnArgs& a, int engine, cudaStream_t s) {
     else rc = launch_bwd_main_simt(a, w, ps, s);
     prof_end(1, s);
     if (rc) return rc;
-    if ((rc = launch_bwd_combine(a, w, ps, s))) return rc;
+    prof_begin(5, s);
+    rc = launch_bwd_combine(a, w, ps, s);
+    prof_end(5, s);
+    if (rc) return rc;
   }
   return FMB_OK;
 }

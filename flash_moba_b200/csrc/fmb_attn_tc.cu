@@ -1063,6 +1063,28 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
   if (warp == 0) tmem_dealloc(tmem_base, NCOLS);
 }
 
+// ------------------------------------------------------------------ self test of the bounded wait
+__global__ void __launch_bounds__(32) selftest_wait_expiry_kernel(int* status, unsigned long long* elapsed_ns) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  unsigned long long t0, t1;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  const bool ok = mbar_wait(&bar, 0, status, 5);     // nobody arrives: gives up after kSpinLimit polls
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+  if (threadIdx.x == 0) *elapsed_ns = ok ? 0ull : t1 - t0;
+}
+
+int launch_selftest_wait_expiry(int* status, unsigned long long* elapsed_ns, cudaStream_t s) {
+  FMB_CUDA(cudaMemsetAsync(status, 0, sizeof(int), s));
+  selftest_wait_expiry_kernel<<<1, 32, 0, s>>>(status, elapsed_ns);
+  FMB_LAUNCH_CHECK("selftest_wait_expiry_kernel");
+  return FMB_OK;
+}
+
 // ------------------------------------------------------------------ self test of the MMA path
 // D[128][128] (fp32) = A[128][128] . B, with B given [N][K] (K contiguous) when b_mn_major == 0
 // or [K][N] (N contiguous) when 1.  Exercises exactly the descriptors the attention kernels use.

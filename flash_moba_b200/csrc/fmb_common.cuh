@@ -18,8 +18,9 @@ namespace fmb {
 char* error_buffer();          // defined in fmb_api.cu
 int fail(int code, const char* fmt, ...);
 void note_launch();            // counts kernel launches (fmb_launch_count)
-// optional CUDA-event timing of the dominant kernels (fmb_profile_*); kind 0 = forward
-// main kernel, 1 = backward main kernel, 2 = gating kernel, 3 = mean-pool kernel
+// optional CUDA-event timing of the kernels (fmb_profile_*); kind 0 = forward main kernel,
+// 1 = backward main kernel, 2 = gating kernel, 3 = mean-pool kernel, 4 = forward combine,
+// 5 = backward combine, 6 = pattern build (three kernels), 7 = dO.O
 void prof_begin(int kind, cudaStream_t s);
 void prof_end(int kind, cudaStream_t s);
 

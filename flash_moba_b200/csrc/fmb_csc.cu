@@ -226,11 +226,13 @@ int launch_build_csc(const int32_t* topk_idx, int64_t idx_rs, int64_t idx_hs, co
   FMB_CUDA(cudaFuncSetAttribute(csc_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 kMaxColsPerCta * kBmStride * 4));
   dim3 grid(batch * heads, p.ntiles, ncr);
+  prof_begin(6, s);
   csc_tile_hist_kernel<<<grid, kCscThreads, smem, s>>>(p);
   FMB_LAUNCH_CHECK("csc_tile_hist_kernel");
   csc_col_scan_kernel<<<batch * heads, 1024, 0, s>>>(p);
   FMB_LAUNCH_CHECK("csc_col_scan_kernel");
   csc_scatter_kernel<<<grid, kCscThreads, smem, s>>>(p);
+  prof_end(6, s);
   FMB_LAUNCH_CHECK("csc_scatter_kernel");
   return FMB_OK;
 }

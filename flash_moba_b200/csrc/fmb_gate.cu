@@ -2,14 +2,14 @@
 // per-row top-k, in one kernel; the score matrix never reaches HBM.
 //
 // Replaces csrc/flash_topk/src/flash_topk_kernel.h:31-357 of the reference (one thread per
-// row doing a serial insertion over every score of every tile).  Here a CTA owns 128 query
-// rows of one (sequence, head); for each tile of 128 centroids the score tile is produced
-// into shared memory and then a WARP owns a row: its 32 lanes test 32 scores at once
-// against the row's current k-th best (one compare + one ballot per 32 scores), and only
-// the rare survivors are inserted into the sorted list, which lives distributed across the
-// lanes (lane j holds rank j and rank j+32).  Ordering rule = the reference's: descending
-// score, and on equal scores the higher chunk id first
-// (csrc/flash_topk/src/flash_topk_kernel.h:261-285).
+// row doing a serial insertion over every score of every tile).  Two kernels:
+//   * gate_topk_tc_kernel (head dims 64 / 128, top-k <= 32): the score tile is a tcgen05 MMA with
+//     the accumulator in TMEM; TMEM lane = query row, so a thread reads its row's scores straight
+//     from TMEM and keeps the row's list in registers as 64-bit ordered keys;
+//   * gate_topk_kernel (other shapes, and the cross-check of the first): CUDA-core score tile in
+//     shared memory, a warp per row, the list distributed over the lanes.
+// Ordering rule = the reference's: descending score, and on equal scores the higher chunk id
+// first (csrc/flash_topk/src/flash_topk_kernel.h:261-285).
 #include "fmb_common.cuh"
 #include "fmb_tc.cuh"
 
@@ -460,8 +460,13 @@ static int g_gate_engine = 1;
 void set_gate_engine(int e) { g_gate_engine = e; }
 bool gate_tc_supported(int d, int topk) { return (d == 64 || d == 128) && topk <= 32; }
 
+// reads the word (synchronising) and clears it, so that one expired wait is reported once
 int read_gate_status(int* out) {
   FMB_CUDA(cudaMemcpyFromSymbol(out, g_gate_status, sizeof(int)));
+  if (*out != 0) {
+    const int zero = 0;
+    FMB_CUDA(cudaMemcpyToSymbol(g_gate_status, &zero, sizeof(int)));
+  }
   return FMB_OK;
 }
 

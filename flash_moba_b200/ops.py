@@ -132,17 +132,69 @@ def _workspace(query, total_q, h, hk, d, n_indices, batch, max_seqlen_k, chunk, 
     return torch.empty((max(nbytes, 1),), dtype=torch.uint8, device=device), nbytes
 
 
-def _check_status(ws: torch.Tensor, what: str) -> None:
-    """With FMB_CHECK_STATUS=1 every attention call synchronises and reads the device-side
-    status word (first 4 bytes of the workspace); a bounded wait that expired raises."""
+def _raise_for_status(code: int, what: str) -> None:
+    if code == 7:
+        raise RuntimeError(f"flash_moba_b200: {what}: the pattern does not fit the slots of a pass "
+                           "(overlapping columns, or raise FMB_WORKSPACE_GB)")
+    if code != 0:
+        raise RuntimeError(f"flash_moba_b200: {what}: a bounded device-side wait expired (code {code})")
+
+
+# Status words on their way to the host: (event behind the call, ring, slot, which call).  The
+# library stores a call's status word straight into mapped pinned memory (fmb_attn_status_mirror),
+# so no copy is queued in the stream.
+_pending_status = _collections.deque()
+_status_rings = {}
+_RING = 256
+_PENDING = -1
+
+
+def _drain_status(block: bool) -> None:
+    while _pending_status:
+        ev, ring, i, what = _pending_status[0]
+        if block:
+            ev.synchronize()
+        elif not ev.query():
+            return
+        _pending_status.popleft()
+        code = int(ring[i])
+        _raise_for_status(0 if code == _PENDING else code, what)    # still pending: the call had no rows
+
+
+def check_pending_status() -> None:
+    """Waits for the status words of all attention calls issued so far by this process and raises
+    for the first one that reports a failure (see _status_begin)."""
+    _drain_status(True)
+
+
+def _status_begin(dev):
+    """Every attention call leaves a device-side status word: 0, or which bounded wait gave up /
+    7 = the pattern did not fit the slots.  By default the library mirrors the word into pinned
+    host memory at the end of the call, without synchronising, and the attention calls that follow
+    (or check_pending_status()) look at it: a failure raises one call late, never silently.  With
+    FMB_CHECK_STATUS=1 every call synchronises and raises at once (the tests).  Returns the ticket
+    for _status_end."""
     import os
     if os.environ.get("FMB_CHECK_STATUS", "0") == "1":
-        code = int(ws[:4].view(torch.int32).item())
-        if code == 7:
-            raise RuntimeError(f"flash_moba_b200: {what}: the pattern does not fit the slots of a pass "
-                               "(overlapping columns, or raise FMB_WORKSPACE_GB)")
-        if code != 0:
-            raise RuntimeError(f"flash_moba_b200: {what}: a bounded device-side wait expired (code {code})")
+        return None
+    _drain_status(len(_pending_status) >= _RING - 8)
+    ring_state = _status_rings.get(dev.index)
+    if ring_state is None:
+        ring_state = _status_rings[dev.index] = [torch.zeros((_RING,), dtype=torch.int32).pin_memory(), 0]
+    ring, i = ring_state
+    ring_state[1] = (i + 1) % _RING
+    ring[i] = _PENDING
+    check(lib.fmb_attn_status_mirror(ring.data_ptr() + 4 * i))
+    return ring, i
+
+
+def _status_end(ticket, ws: torch.Tensor, what: str) -> None:
+    if ticket is None:
+        _raise_for_status(int(ws[:4].view(torch.int32).item()), what)
+        return
+    ev = torch.cuda.Event()
+    ev.record()
+    _pending_status.append((ev, ticket[0], ticket[1], what))
 
 
 def selftest_umma(a: torch.Tensor, b: torch.Tensor, b_mn_major: bool) -> torch.Tensor:
@@ -169,6 +221,18 @@ def selftest_gather(a: torch.Tensor, idx: torch.Tensor, b: torch.Tensor) -> torc
         if int(status.item()) != 0:
             raise RuntimeError(f"selftest_gather: bounded wait expired (code {int(status.item())})")
     return d
+
+
+def selftest_wait_expiry(device=None) -> Tuple[int, float]:
+    """Runs the library's bounded wait on an mbarrier nobody arrives at (see fmb_selftest_wait_expiry).
+    Returns (status code written by the kernel, seconds the wait lasted before it gave up)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        status = torch.full((1,), -1, dtype=torch.int32, device=dev)
+        ns = torch.zeros((1,), dtype=torch.int64, device=dev)
+        check(lib.fmb_selftest_wait_expiry(ptr(status), ptr(ns), _stream()))
+        torch.cuda.synchronize(dev)
+    return int(status.item()), int(ns.item()) * 1e-9
 
 
 def set_engine(engine: int) -> int:
@@ -312,13 +376,14 @@ def attn_fwd(q, k, v, col_offsets, col_nnz, indices, cu_seqlens_q, cu_seqlens_k,
         ws, nbytes = _workspace(lib.fmb_attn_fwd_workspace_bytes, total_q, h, hk, d, indices.numel(), batch,
                                 max_seqlen_k, chunk, dev)
         rows_offered = _rows_offer(col_offsets, col_nnz, indices, total_q, h)
+        ticket = _status_begin(dev)
         check(lib.fmb_attn_fwd(ptr(q), q.stride(0), q.stride(1), ptr(k), k.stride(0), k.stride(1),
                                ptr(v), v.stride(0), v.stride(1), ptr(out), out.stride(0), out.stride(1), ptr(lse),
                                ptr(col_offsets), ptr(col_nnz), ptr(indices), indices.numel(),
                                ptr(_i32c(cu_seqlens_q, "cu_seqlens_q")), ptr(_i32c(cu_seqlens_k, "cu_seqlens_k")),
                                ptr(ws), nbytes, batch, h, hk, d, total_q, int(max_seqlen_q), int(max_seqlen_k),
                                int(chunk), float(softmax_scale), int(bool(causal)), _dtype_code(q), _stream()))
-        _check_status(ws, "attn_fwd")
+        _status_end(ticket, ws, "attn_fwd")
         _tls.kept = None
         if _share_lists() and indices.numel() > 0 and not rows_offered:
             geo = (total_q, h, hk, d, indices.numel(), batch, int(max_seqlen_k), int(chunk))
@@ -362,6 +427,7 @@ def attn_bwd(dout, q, k, v, out, lse, dq, dk, dv, col_offsets, col_nnz, indices,
                                          int(max_seqlen_k), int(chunk), ptr(offered[1]), offered[1].numel(), _stream())
             if rc not in (0, 1):
                 check(rc)
+        ticket = _status_begin(dev)
         check(lib.fmb_attn_bwd(ptr(dout), dout.stride(0), dout.stride(1), ptr(q), q.stride(0), q.stride(1),
                                ptr(k), k.stride(0), k.stride(1), ptr(v), v.stride(0), v.stride(1),
                                ptr(out), out.stride(0), out.stride(1), ptr(lse),
@@ -372,5 +438,5 @@ def attn_bwd(dout, q, k, v, out, lse, dq, dk, dv, col_offsets, col_nnz, indices,
                                ptr(ws), nbytes, batch, h, hk, d, total_q, total_k, int(max_seqlen_q),
                                int(max_seqlen_k), int(chunk), float(softmax_scale), int(bool(causal)),
                                _dtype_code(q), _stream()))
-        _check_status(ws, "attn_bwd")
+        _status_end(ticket, ws, "attn_bwd")
     return softmax_d

@@ -2,10 +2,20 @@
  * flash_moba_b200 — C ABI of the B200 (sm_100a) MoBA sparse-attention kernels.
  *
  * One shared library, libflashmoba_b200.so.  Every entry point takes plain device
- * pointers, sizes and a CUDA stream; it never allocates or frees device memory, never
- * synchronises the host with the device and keeps no state between calls.  All outputs
- * and workspaces are allocated by the caller; `*_workspace_bytes` tells how much.
+ * pointers, sizes and a CUDA stream; it never allocates or frees device memory and, unless
+ * its description says "synchronising", never synchronises the host with the device.  All
+ * outputs and workspaces are allocated by the caller; `*_workspace_bytes` tells how much.
  * All work is enqueued on `stream` of the CURRENT device (the caller sets the device).
+ *
+ * State the library keeps (everything else lives in the caller's buffers):
+ *   - per host thread: the text behind fmb_last_error(); the one-shot offers made with
+ *     fmb_attn_rows_offer, fmb_attn_lists_load and fmb_attn_status_mirror, consumed by that
+ *     thread's next attention call;
+ *   - per process: the engine selected with fmb_set_engine, the launch counter and the event
+ *     records of fmb_launch_count / fmb_profile_*;
+ *   - per device: the gating kernel's status word (fmb_gate_status) and the 8 MiB scratch array
+ *     of fmb_build_csc_static.
+ * Calls on different streams or from different host threads are independent apart from these.
  *
  * Return value: 0 on success, otherwise one of FMB_ERR_*; `fmb_last_error()` then
  * returns a thread-local, human readable message.
@@ -218,9 +228,16 @@ int fmb_attn_engine(int chunk, int head_dim, int backward);
 /* Same for fmb_gate_topk (tcgen05 for head_dim 64/128 and topk <= 32). */
 int fmb_gate_engine(int head_dim, int topk);
 
-/* Synchronising read of the gating kernel's device-side status word into *host_status
- * (0 = ok, non-zero = a bounded wait expired at some point in this process). */
+/* Synchronising read of the gating kernel's device-side status word of the current device into
+ * *host_status: 0 = ok, non-zero = a bounded wait expired in some gating launch since the last
+ * read.  The word is cleared by the read.  Returns FMB_ERR_TIMEOUT when it was non-zero. */
 int fmb_gate_status(int* host_status);
+
+/* Synchronising read of the status word that fmb_attn_fwd / fmb_attn_bwd left in the first 4
+ * bytes of `workspace` (see below), after the work enqueued on `stream` so far has completed.
+ * *host_status receives the word; the return value is FMB_OK for 0, FMB_ERR_TIMEOUT for an
+ * expired wait (1..6, 8), FMB_ERR_WORKSPACE for 7 and FMB_ERR_CUDA for 9. */
+int fmb_attn_status(const void* workspace, int* host_status, fmb_stream_t stream);
 
 /* Self test of the tcgen05 path, no counterpart in the reference: d[128][128] (float) =
  * a[128][128] . b, where b is [n][k] (k contiguous) if b_mn_major == 0, or [k][n]
@@ -235,6 +252,12 @@ int fmb_selftest_umma(const void* a, const void* b, float* d, int b_mn_major, in
  * index < 0 or >= a_rows gives a zero row) and b is [128][128]; idx is a device int[128]. */
 int fmb_selftest_gather(const void* a, int a_rows, const int* idx, const void* b, float* d, int dtype,
                         int* status, fmb_stream_t stream);
+
+/* Self test of the bounded wait every kernel of this library uses: one warp waits on an mbarrier
+ * that nobody arrives at, gives up, records code 5 in *status (device int, set to 0 by the call
+ * first) and the nanoseconds the wait lasted in *elapsed_ns (device uint64), and exits normally.
+ * Nothing else runs in the kernel, so no copy or MMA is in flight when it gives up. */
+int fmb_selftest_wait_expiry(int* status, unsigned long long* elapsed_ns, fmb_stream_t stream);
 
 /* Optional hand-over of the pattern's slot and row lists (the CSR transpose that both attention
  * calls build in their workspace) from a forward call to the backward call of the same pattern.
@@ -261,6 +284,16 @@ int fmb_attn_lists_load(void* bwd_workspace, size_t workspace_bytes, int64_t tot
  * (give a larger workspace); 9 = the kernel found its shared memory misaligned (a build problem).
  * Results are invalid when it is non-zero. */
 
+/* Reading that word without a copy in the stream: fmb_attn_status_mirror(p) makes the next
+ * fmb_attn_fwd / fmb_attn_bwd call of this host thread store its status word to *p once its main
+ * kernels have completed (one store by one thread of its merge kernel; p must be writable by
+ * the device and readable by the host, typically mapped pinned host memory).  The caller sets *p
+ * to a "pending" value before the call and polls it, or looks at it after an event recorded
+ * behind the call.  One-shot; NULL withdraws it.  (A 4-byte device-to-host copy in the stream
+ * queues behind large copies of other streams on the same copy engine: measured 55 -> 61 ms per
+ * step in a pipeline that overlaps result copies with kernels.) */
+int fmb_attn_status_mirror(int* mirror);
+
 /* ------------------------------------------------------------------ measurement aids
  * No counterpart in the reference (it is timed from Python with torch.utils.benchmark,
  * flash_moba/utils/benchmark.py:120-156).
@@ -270,7 +303,8 @@ unsigned long long fmb_launch_count(void);
 /* CUDA-event timing of the dominant kernels on the launching stream.  While enabled, up to
  * 256 launches per kind are bracketed by events (no synchronisation is added); enabling
  * also clears the record.  kind: 0 forward main kernel, 1 backward main kernel, 2 gating
- * kernel, 3 mean-pool kernel.  After the caller has synchronised, fmb_profile_read stores
+ * kernel, 3 mean-pool kernel, 4 forward combine, 5 backward combine, 6 pattern build (its
+ * three kernels together), 7 dO.O.  After the caller has synchronised, fmb_profile_read stores
  * the elapsed milliseconds of each recorded launch and returns how many (or -1). */
 int fmb_profile_enable(int on);
 int fmb_profile_read(int kind, float* ms, int max_entries);
