@@ -284,6 +284,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--e2e-groups", type=int, default=8, help="head groups of the host pipeline")
     ap.add_argument("--engine", type=int, default=1)
+    ap.add_argument("--shard", default="heads", choices=["heads", "query-range"],
+                    help="N > 1: split the heads (no collective), or split one long sequence by query range "
+                         "(all-gather of centroids, K and V; reduce-scatter of dK and dV, inside the step)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     wl = args.workload
@@ -304,20 +307,31 @@ def main():
     from flash_moba_b200 import _lib, ops
     ops.set_engine(args.engine)
 
-    # shard: q heads (and their kv heads) split across ranks; no data-path collective
-    from flash_moba_b200.sharding import plan_head_shards
-    assert Hk >= world, "fewer kv heads than ranks: split the sequence by query range instead"
-    h0, h1 = plan_head_shards(H, Hk, world)[rank]
-    h_loc, hk_loc = h1 - h0, (h1 - h0) // (H // Hk)
-    T = sum(seqlens)
+    from flash_moba_b200 import sharding
+    by_range = args.shard == "query-range" and world > 1
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    if by_range:
+        # one long sequence split by query range: every rank holds S / world rows of all heads
+        assert len(seqlens) == 1 and seqlens[0] % (world * chunk) == 0, "query-range split: one sequence, whole chunks per rank"
+        h0, h1, h_loc, hk_loc = 0, H, H, Hk
+        T = seqlens[0] // world
+        args.no_e2e = True
+    else:
+        # q heads (and their kv heads) split across ranks; no data-path collective
+        assert Hk >= world, "fewer kv heads than ranks: split the sequence by query range instead (--shard query-range)"
+        h0, h1 = sharding.plan_head_shards(H, Hk, world)[rank]
+        h_loc, hk_loc = h1 - h0, (h1 - h0) // (H // Hk)
+        T = sum(seqlens)
     mk = lambda h: (torch.randn(T, h, d, generator=g, device=dev, dtype=torch.float32) * scale).to(torch.bfloat16)
     q, k, v, do = mk(h_loc).requires_grad_(True), mk(hk_loc).requires_grad_(True), mk(hk_loc).requires_grad_(True), mk(h_loc)
     cu = torch.tensor([0] + list(__import__("itertools").accumulate(seqlens)), dtype=torch.int32, device=dev)
     mx = max(seqlens)
 
     def step(qq, kk, vv, dd):
-        out = F.flash_moba_varlen_func(qq, kk, vv, cu, cu, mx, mx, chunk, topk, causal=True)
+        if by_range:
+            out = sharding.moba_query_range(qq, kk, vv, seqlens[0], chunk, topk)
+        else:
+            out = F.flash_moba_varlen_func(qq, kk, vv, cu, cu, mx, mx, chunk, topk, causal=True)
         if backward:
             return (out,) + torch.autograd.grad(out, (qq, kk, vv), dd)
         return (out,)
@@ -430,14 +444,14 @@ def main():
         ("bf16_tflops, burst: SM clock at its maximum and no power cap during the timed region)" if at_max else
          "bf16_tflops_sustained: the clock dropped or the power cap was active)")
     dom = "bwd_main" if backward else "fwd_main"
-    dom_flops = (bwd_f if backward else fwd_f) * h_loc / H      # rank 0's launch
+    dom_flops = (bwd_f if backward else fwd_f) * (1.0 / world if by_range else h_loc / H)      # rank 0's launch (about, under the range split)
     roof = None
     # DRAM bytes per (row, chunk) entry of the dominant kernel, from one ncu capture of a 16K-token,
     # 16-head case of this build (profiles/bwd_main_tc_kernel_16k.md: dram__bytes_read.sum +
     # dram__bytes_write.sum over its 2,039,808 entries); the traffic is per-entry work (gathered
     # rows in, partial rows out), so it scales with the entries.
     entry_bytes = {"bwd_main": BWD_MAIN_DRAM_BYTES_PER_ENTRY}.get(dom) if (d == 128 and chunk == 128) else None
-    entries = ACC.selected_entries(seqlens, chunk, topk) * h_loc
+    entries = ACC.selected_entries(seqlens, chunk, topk) * h_loc / (world if by_range else 1)
     if kern_ms.get(dom):
         ach = dom_flops / (kern_ms[dom] * 1e-3) / 1e12
         roof = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s",
@@ -453,7 +467,10 @@ def main():
         "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
         "config": config_of(wl, seqlens, H, Hk, d, chunk, topk, backward),
-        "run": {"sharding": f"query heads {h0}..{h1 - 1} of {H} on rank 0, whole kv-head groups per rank, no collective",
+        "run": {"sharding": (f"query rows split in {world} ranges, all heads on every rank" if by_range else
+                             f"query heads {h0}..{h1 - 1} of {H} on rank 0, whole kv-head groups per rank, no collective"),
+                "collective": ("all_gather(centroids, K, V) + reduce_scatter(dK, dV), NCCL, inside the step" if by_range
+                               else "none"),
                 "l2": f"inputs q,k,v,dO ({4 * T * h_loc * d * 2 >> 20} MB per rank) plus the per-pair partials exceed the 126 MB L2",
                 "engine": {"fwd": ["cuda-core", "tcgen05"][_lib.lib.fmb_attn_engine(chunk, d, 0)],
                            "bwd": ["cuda-core", "tcgen05"][_lib.lib.fmb_attn_engine(chunk, d, 1)]}},

@@ -8,10 +8,14 @@ pass, only inside a kv-head group (dK/dV are summed over the group's query heads
 * ``plan_head_shards`` / ``plan_work_items`` + ``shard_heads``: every rank runs the whole
   single-GPU pipeline on its own heads (or its own (sequence, kv head) items).  No collective.
 * ``moba_query_range``: one very long sequence, fewer heads than ranks.  Rank r owns the query
-  rows [r*S/R, (r+1)*S/R) and the matching slice of K and V; K and V are all-gathered (NCCL
-  over NVLink), the rank's queries attend the gathered keys [0, (r+1)*S/R) with the
-  bottom-right aligned causal mask the kernels already implement for len_q < len_k, and in the
-  backward pass the partial dK/dV are reduce-scattered back to their owners.
+  rows [r*S/R, (r+1)*S/R) and the matching slice of K and V.  Each rank pools the centroids of
+  its own key range; the centroids, K and V are all-gathered (NCCL over NVLink, issued in that
+  order without waiting); gating and the pattern build need only the rank's queries and the
+  (small) centroid table, so they run while K and V are still crossing the links; the rank's
+  queries then attend the gathered keys [0, (r+1)*S/R) with the bottom-right aligned causal
+  mask the kernels already implement for len_q < len_k, and in the backward pass the partial
+  dK/dV are reduce-scattered back to their owners.  The kernels only ever read the rank's own
+  memory: the collectives land in local buffers first.
 """
 from typing import Callable, List, Optional, Sequence, Tuple
 
@@ -100,6 +104,65 @@ def all_gather_rows(x: torch.Tensor, group=None) -> torch.Tensor:
     return _AllGatherRows.apply(x, group)
 
 
+class _MobaQueryRange(torch.autograd.Function):
+    """The query-range split with this package's kernels (see moba_query_range)."""
+
+    @staticmethod
+    def forward(ctx, q_local, k_local, v_local, seqlen, chunk, topk, group):
+        from . import interface, ops
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        share = seqlen // world
+        len_k = (rank + 1) * share        # causal: keys after the rank's last query are never used
+        dev = q_local.device
+        hk, d = k_local.shape[1], k_local.shape[2]
+        cu_q = torch.tensor([0, share], dtype=torch.int32, device=dev)
+        cu_k = torch.tensor([0, len_k], dtype=torch.int32, device=dev)
+        cu_local = torch.tensor([0, share], dtype=torch.int32, device=dev)
+        k_local, v_local = k_local.contiguous(), v_local.contiguous()
+        # centroids of the own key range (chunks never straddle ranks: share % chunk == 0), then the
+        # three gathers back to back; only the small one is waited for before gating
+        km_local, _ = ops.mean_pool(k_local, cu_local, share, chunk)
+        nloc = share // chunk
+        km_all = torch.empty((world * nloc, hk, d), dtype=k_local.dtype, device=dev)
+        k_all = torch.empty((seqlen, hk, d), dtype=k_local.dtype, device=dev)
+        v_all = torch.empty((seqlen, hk, d), dtype=v_local.dtype, device=dev)
+        w_km = dist.all_gather_into_tensor(km_all, km_local[:nloc].contiguous(), group=group, async_op=True)
+        w_k = dist.all_gather_into_tensor(k_all, k_local, group=group, async_op=True)
+        w_v = dist.all_gather_into_tensor(v_all, v_local, group=group, async_op=True)
+        w_km.wait()
+        nk = len_k // chunk
+        cu_km = torch.tensor([0, nk], dtype=torch.int32, device=dev)
+        pattern = torch.ops.flash_moba._moba_fused_topk(q_local, km_all[:nk], cu_q, cu_k, cu_km, share, len_k, topk,
+                                                        chunk, causal=True)
+        w_k.wait()
+        w_v.wait()
+        scale = q_local.shape[-1] ** (-0.5)
+        lg_m = interface.decide_lg_block_m(topk, chunk, len_k, True)
+        out, lse, _, _ = torch.ops.flash_moba._flash_moba_attn_varlen_forward(
+            q_local, k_all[:len_k], v_all[:len_k], cu_q, cu_k, share, len_k, *pattern, lg_m, chunk, 0.0, scale, True)
+        ctx.save_for_backward(q_local, k_all, v_all, out, lse, cu_q, cu_k, *pattern)
+        ctx.meta = (seqlen, share, len_k, chunk, scale, lg_m, group)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q_local, k_all, v_all, out, lse, cu_q, cu_k, co, cn, ind = ctx.saved_tensors
+        seqlen, share, len_k, chunk, scale, lg_m, group = ctx.meta
+        dq = torch.empty_like(q_local)
+        # the whole sequence's dK / dV: rows past this rank's last key get nothing from it
+        dk_all, dv_all = torch.zeros_like(k_all), torch.zeros_like(v_all)
+        torch.ops.flash_moba._flash_moba_attn_varlen_backward(
+            dout.contiguous(), q_local, k_all[:len_k], v_all[:len_k], out, lse, dq, dk_all[:len_k], dv_all[:len_k],
+            cu_q, cu_k, share, len_k, co, cn, ind, lg_m, chunk, 0.0, scale, True, 0.0, None, False)
+        dk = torch.empty((share,) + tuple(k_all.shape[1:]), dtype=k_all.dtype, device=k_all.device)
+        dv = torch.empty_like(dk)
+        w_k = dist.reduce_scatter_tensor(dk, dk_all, op=dist.ReduceOp.SUM, group=group, async_op=True)
+        w_v = dist.reduce_scatter_tensor(dv, dv_all, op=dist.ReduceOp.SUM, group=group, async_op=True)
+        w_k.wait()
+        w_v.wait()
+        return dq, dk, dv, None, None, None, None
+
+
 def moba_query_range(q_local, k_local, v_local, seqlen: int, chunk: int, topk: int, group=None,
                      attention: Optional[Callable] = None):
     """MoBA attention of ONE causal sequence of `seqlen` tokens split by query range.
@@ -107,8 +170,10 @@ def moba_query_range(q_local, k_local, v_local, seqlen: int, chunk: int, topk: i
     Every rank passes its own rows: q_local (S/R, H, d), k_local and v_local (S/R, Hk, d), ranks
     in sequence order, seqlen divisible by the world size.  Returns the rank's output rows
     (S/R, H, d); gradients flow to q_local, k_local and v_local (the key/value gradients through a
-    reduce-scatter).  `attention(q, k, v, cu_q, cu_k, max_q, max_k, chunk, topk, causal=True)`
-    defaults to this package's `flash_moba_varlen_func`.
+    reduce-scatter).  By default the package's own kernels run, with the centroids pooled per
+    rank and gathered with K and V, and gating overlapped with the K/V gathers.  Passing
+    `attention(q, k, v, cu_q, cu_k, max_q, max_k, chunk, topk, causal=True)` (e.g. a CPU
+    implementation under gloo) takes the plain route instead: gather K and V, call it.
     """
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
@@ -120,7 +185,7 @@ def moba_query_range(q_local, k_local, v_local, seqlen: int, chunk: int, topk: i
     if share % chunk != 0:
         raise ValueError("the per-rank share must be a whole number of chunks")
     if attention is None:
-        from .interface import flash_moba_varlen_func as attention
+        return _MobaQueryRange.apply(q_local, k_local, v_local, seqlen, chunk, topk, group)
     k_all = all_gather_rows(k_local, group)
     v_all = all_gather_rows(v_local, group)
     len_k = (rank + 1) * share            # causal: keys after the rank's last query are never used

@@ -122,11 +122,14 @@ def _rank_main(rank, world, port, ret):
 
 
 @pytest.mark.timeout(600)
-def test_query_range_two_ranks_nccl():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+@pytest.mark.parametrize("world", [2, 4])
+def test_query_range_ranks_nccl(world):
+    """The query-range split as NCCL ranks (centroids pooled per rank and gathered with K and V,
+    gating overlapped with the K/V gathers, dK/dV reduce-scattered): O and dQ bit-identical to the
+    unsplit call, dK/dV to bf16 rounding of the per-rank partial sums."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
-    world = 2
     ctx = mp.get_context("spawn")
     ret = ctx.Manager().dict()
     port = _free_port()
