@@ -16,6 +16,7 @@ from .interface import (  # noqa: F401
     flash_topk_mean_pool,
     flash_topk_varlen_func,
 )
+from .modules import CentroidCache, MobaAttention  # noqa: F401
 
 __all__ = [
     "flash_moba_varlen_func",
@@ -24,4 +25,6 @@ __all__ = [
     "flash_topk_mean_pool",
     "decide_lg_block_m",
     "FlashMobaAttnVarlenFunc",
+    "MobaAttention",
+    "CentroidCache",
 ]

@@ -35,6 +35,7 @@ _SIGS = {
     "fmb_gate_status": (i32, [c_ptr]),
     "fmb_attn_status": (i32, [c_ptr, c_ptr, c_ptr]),
     "fmb_attn_status_mirror": (i32, [c_ptr]),
+    "fmb_attn_key_spans": (i32, [c_ptr, c_ptr]),
     "fmb_selftest_wait_expiry": (i32, [c_ptr, c_ptr, c_ptr]),
     "fmb_selftest_umma": (i32, [c_ptr, c_ptr, c_ptr, i32, i32, c_ptr, c_ptr]),
     "fmb_selftest_gather": (i32, [c_ptr, i32, c_ptr, c_ptr, c_ptr, i32, c_ptr, c_ptr]),

@@ -340,6 +340,15 @@ static int check_attn(const char* op, const AttnArgs& a) {
   return FMB_OK;
 }
 
+static thread_local const int32_t* g_key_spans[2] = {nullptr, nullptr};
+
+int fmb_attn_key_spans(const int32_t* k_begin, const int32_t* k_end) {
+  FMB_CHECK_ARG((k_begin == nullptr) == (k_end == nullptr), "attn_key_spans: give both arrays or neither");
+  g_key_spans[0] = k_begin;
+  g_key_spans[1] = k_end;
+  return FMB_OK;
+}
+
 int fmb_attn_fwd(const void* q, int64_t q_row_stride, int64_t q_head_stride, const void* k,
                  int64_t k_row_stride, int64_t k_head_stride, const void* v, int64_t v_row_stride,
                  int64_t v_head_stride, void* out, int64_t o_row_stride, int64_t o_head_stride, float* lse,
@@ -355,6 +364,11 @@ int fmb_attn_fwd(const void* q, int64_t q_row_stride, int64_t q_head_stride, con
   a.v_rs = v_row_stride; a.v_hs = v_head_stride; a.o_rs = o_row_stride; a.o_hs = o_head_stride;
   a.lse = lse; a.col_offsets = col_offsets; a.col_nnz = col_nnz; a.indices = indices; a.n_indices = n_indices;
   a.cu_q = cu_seqlens_q; a.cu_k = cu_seqlens_k; a.ws = workspace; a.ws_bytes = workspace_bytes;
+  a.k_begin = cu_seqlens_k; a.k_end = cu_seqlens_k ? cu_seqlens_k + 1 : nullptr;
+  if (g_key_spans[0] != nullptr) {      // one-shot: spans given for this call (fmb_attn_key_spans)
+    a.k_begin = g_key_spans[0]; a.k_end = g_key_spans[1];
+    g_key_spans[0] = g_key_spans[1] = nullptr;
+  }
   a.batch = batch; a.heads = heads; a.heads_k = heads_k; a.d = head_dim; a.total_q = total_q;
   a.max_q = max_seqlen_q; a.max_k = max_seqlen_k; a.chunk = chunk;
   a.ncol = chunk > 0 ? ceil_div(max_seqlen_k, chunk) : 0;
@@ -395,6 +409,7 @@ int fmb_attn_bwd(const void* dout, int64_t do_row_stride, int64_t do_head_stride
   a.lse = const_cast<float*>(lse); a.softmax_d = softmax_d;
   a.col_offsets = col_offsets; a.col_nnz = col_nnz; a.indices = indices; a.n_indices = n_indices;
   a.cu_q = cu_seqlens_q; a.cu_k = cu_seqlens_k; a.ws = workspace; a.ws_bytes = workspace_bytes;
+  a.k_begin = cu_seqlens_k; a.k_end = cu_seqlens_k ? cu_seqlens_k + 1 : nullptr;
   a.batch = batch; a.heads = heads; a.heads_k = heads_k; a.d = head_dim; a.total_q = total_q;
   a.total_k = total_k; a.max_q = max_seqlen_q; a.max_k = max_seqlen_k; a.chunk = chunk;
   a.ncol = chunk > 0 ? ceil_div(max_seqlen_k, chunk) : 0;

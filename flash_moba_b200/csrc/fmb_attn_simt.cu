@@ -18,7 +18,7 @@ struct SimtParams {
   void *dk, *dv; int64_t dk_rs, dk_hs, dv_rs, dv_hs;
   const float *lse, *softmax_d;
   PassParams ps;
-  const int32_t *cu_q, *cu_k;
+  const int32_t *cu_q, *k_begin, *k_end;
   void* part_o; float* part_lse;
   int heads, heads_k; int64_t total_q;
   float scale; int causal;
@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(kSimtThreads) fwd_main_simt_kernel(SimtParams 
   const int64_t off = col.off;
   const int64_t slot0 = col.slot, plane = (int64_t)sb * p.ps.cap;
   const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
-  const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
+  const int k0 = p.k_begin[b], len_k = p.k_end[b] - k0;
   const int key0 = c * p.ps.chunk + sb * C;
   const int keys_valid = max(0, min(C, len_k - key0));
   const int hk = h / (p.heads / p.heads_k);
@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(kSimtThreads) bwd_main_simt_kernel(SimtParams 
   const int c = blockIdx.x / p.ps.nsub, sb = blockIdx.x % p.ps.nsub, hk = p.ps.h0 / group + blockIdx.y, b = blockIdx.z;
   const int64_t plane = (int64_t)sb * p.ps.cap;
   const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
-  const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
+  const int k0 = p.k_begin[b], len_k = p.k_end[b] - k0;
   const int key0 = c * p.ps.chunk + sb * C;
   if (key0 >= len_k) {
     zero_dq_partials<T>(p.ps, static_cast<T*>(p.part_o), plane, b, hk, group, c, D);
@@ -379,7 +379,7 @@ static SimtParams make_params(const AttnArgs& a, const AttnWorkspace& w, const P
   p.dk = a.dk; p.dv = a.dv; p.dk_rs = a.dk_rs; p.dk_hs = a.dk_hs; p.dv_rs = a.dv_rs; p.dv_hs = a.dv_hs;
   p.lse = a.lse; p.softmax_d = a.softmax_d;
   p.ps = ps;
-  p.cu_q = a.cu_q; p.cu_k = a.cu_k; p.part_o = w.part_o; p.part_lse = w.part_lse;
+  p.cu_q = a.cu_q; p.k_begin = a.k_begin; p.k_end = a.k_end; p.part_o = w.part_o; p.part_lse = w.part_lse;
   p.heads = a.heads; p.heads_k = a.heads_k; p.total_q = a.total_q;
   p.scale = a.scale; p.causal = a.causal;
   return p;

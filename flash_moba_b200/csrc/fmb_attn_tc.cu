@@ -27,7 +27,7 @@ struct TcParams {
   void *dk, *dv; int64_t dk_rs, dk_hs, dv_rs, dv_hs;
   const float *lse, *softmax_d;
   PassParams ps;
-  const int32_t *cu_q, *cu_k;
+  const int32_t *cu_q, *k_begin, *k_end;
   void* part_o; float* part_lse; int* status;
   int heads, heads_k; int64_t total_q;
   float scale; int causal;
@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
         const ColRef col = column_of(p.ps, b, h, c);
         if (col.nnz <= 0) continue;
         const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
-        const int k0 = p.cu_k[b], len_k = p.cu_k[b + 1] - k0;
+        const int k0 = p.k_begin[b], len_k = p.k_end[b] - k0;
         const int hk = h / (p.heads / p.heads_k);
         it.nnz = col.nnz; it.off = col.off; it.slot = (int64_t)sb * p.ps.cap + col.slot;
         it.q0 = q0; it.len_q = len_q; it.h = h;
@@ -533,8 +533,8 @@ __device__ __forceinline__ void bwd_decode_item(const TcParams& p, int item, int
   I.plane = (int64_t)sb * p.ps.cap;
   I.q0 = p.cu_q[I.b];
   I.len_q = p.cu_q[I.b + 1] - I.q0;
-  I.k0 = p.cu_k[I.b];
-  I.len_k = p.cu_k[I.b + 1] - I.k0;
+  I.k0 = p.k_begin[I.b];
+  I.len_k = p.k_end[I.b] - I.k0;
   // The kernel always works on 128 key lanes; with 64-key blocks (chunks that are not a multiple of
   // 128) the upper 64 lanes are zero-filled and masked: twice the tensor work per key, still several
   // times faster than the CUDA-core backward, and the tensor pipe is mostly idle anyway.
@@ -1243,7 +1243,8 @@ static TcParams make_tc_params(const AttnArgs& a, const AttnWorkspace& w, const 
   p.dk = a.dk; p.dv = a.dv; p.dk_rs = a.dk_rs; p.dk_hs = a.dk_hs; p.dv_rs = a.dv_rs; p.dv_hs = a.dv_hs;
   p.lse = a.lse; p.softmax_d = a.softmax_d;
   p.ps = ps;
-  p.cu_q = a.cu_q; p.cu_k = a.cu_k; p.part_o = w.part_o; p.part_lse = w.part_lse; p.status = w.status;
+  p.cu_q = a.cu_q; p.k_begin = a.k_begin; p.k_end = a.k_end;
+  p.part_o = w.part_o; p.part_lse = w.part_lse; p.status = w.status;
   p.heads = a.heads; p.heads_k = a.heads_k; p.total_q = a.total_q;
   p.scale = a.scale; p.causal = a.causal;
   return p;

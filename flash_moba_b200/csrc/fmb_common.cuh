@@ -138,6 +138,9 @@ struct AttnArgs {
   float* softmax_d;  // (heads, total_q)
   const int64_t* col_offsets; const int32_t* col_nnz; const int32_t* indices; int64_t n_indices;
   const int32_t *cu_q, *cu_k;
+  // first key row and one-past-last key row of every sequence: cu_k and cu_k + 1 unless the caller
+  // gave its own spans (left padding / fewer keys in use than stored; forward only)
+  const int32_t *k_begin, *k_end;
   void* ws; size_t ws_bytes;
   int batch, heads, heads_k, d; int64_t total_q, total_k; int max_q, max_k, chunk, ncol;
   float scale; int causal, dtype;

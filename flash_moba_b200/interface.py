@@ -11,8 +11,8 @@ Differences that do not change results:
   * the pattern comes out of `_moba_fused_topk` already sorted (the builder is ordered), so
     `flash_topk_varlen_func` does not call `_varlen_sort`; the op still exists and sorts;
   * `lg_block_m` is a partition hint of the reference kernel; it is validated and ignored;
-  * dropout, softcap, alibi, left-padding and `seqused_k` are rejected if non-default (the
-    reference documents them as unsupported for MoBA).
+  * dropout, softcap and alibi are rejected if non-default (the reference documents them as
+    unsupported for MoBA); `leftpad_k` and `seqused_k` of the forward op are honoured.
 """
 from typing import Optional, Tuple
 
@@ -41,15 +41,13 @@ def _fix_last_stride(x):
     return x.contiguous() if x is not None and x.stride(-1) != 1 else x
 
 
-def _reject_unsupported(dropout_p, softcap, alibi_slopes, leftpad_k=None, seqused_k=None):
+def _reject_unsupported(dropout_p, softcap, alibi_slopes):
     if dropout_p != 0.0:
         raise RuntimeError("FlashMoBA does not support dropout (dropout_p must be 0.0)")
     if softcap != 0.0:
         raise RuntimeError("FlashMoBA does not support softcap (softcap must be 0.0)")
     if alibi_slopes is not None:
         raise RuntimeError("FlashMoBA does not support ALiBi (alibi_slopes must be None)")
-    if leftpad_k is not None or seqused_k is not None:
-        raise RuntimeError("leftpad_k / seqused_k are not supported")
 
 
 # ======================================================================================
@@ -121,7 +119,7 @@ def _flash_moba_attn_varlen_forward(
     seqused_k: Optional[torch.Tensor] = None,
     zero_tensors: bool = False,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
-    _reject_unsupported(dropout_p, softcap, alibi_slopes, leftpad_k, seqused_k)
+    _reject_unsupported(dropout_p, softcap, alibi_slopes)
     if lg_block_n % 64 != 0:
         raise RuntimeError("lg_block_n must be divisible by 64")
     if lg_block_m % 64 != 0 or not (128 <= lg_block_m <= 1024):
@@ -129,7 +127,7 @@ def _flash_moba_attn_varlen_forward(
     q, k, v = [_fix_last_stride(x) for x in (q, k, v)]
     out, lse = ops.attn_fwd(q, k, v, moba_col_offsets.contiguous(), moba_col_nnz.contiguous(),
                             moba_row_indices.contiguous(), cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
-                            max_seqlen_k, lg_block_n, softmax_scale, causal)
+                            max_seqlen_k, lg_block_n, softmax_scale, causal, leftpad_k=leftpad_k, seqused_k=seqused_k)
     p = torch.empty((0,), dtype=q.dtype, device=q.device)
     rng_state = torch.zeros((2,), dtype=torch.int64, device=q.device)
     return out, lse, p, rng_state

@@ -351,8 +351,23 @@ def _check_pattern(col_offsets, col_nnz, indices):
         raise RuntimeError("moba_col_offsets / moba_col_nnz must both be (batch, heads, ncol)")
 
 
+def _key_spans(cu_seqlens_k, leftpad_k, seqused_k, batch):
+    """(first key row, one past the last key row) per sequence for the reference's leftpad_k /
+    seqused_k arguments (csrc/flash_moba/src/block_info.h:19-26): keys start leftpad_k[b] rows into
+    the sequence's storage and seqused_k[b] rows of the storage are in use."""
+    for t, n in ((leftpad_k, "leftpad_k"), (seqused_k, "seqused_k")):
+        if t is not None:
+            _require_cuda(t)
+            if tuple(_i32c(t, n).shape) != (batch,):
+                raise RuntimeError(f"{n} must have shape (batch_size,)")
+    begin = cu_seqlens_k[:-1] if leftpad_k is None else cu_seqlens_k[:-1] + leftpad_k
+    end = cu_seqlens_k[1:] if seqused_k is None else cu_seqlens_k[:-1] + seqused_k
+    return begin.contiguous(), end.contiguous()
+
+
 def attn_fwd(q, k, v, col_offsets, col_nnz, indices, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int,
-             max_seqlen_k: int, chunk: int, softmax_scale: float, causal: bool, out: Optional[torch.Tensor] = None):
+             max_seqlen_k: int, chunk: int, softmax_scale: float, causal: bool, out: Optional[torch.Tensor] = None,
+             leftpad_k: Optional[torch.Tensor] = None, seqused_k: Optional[torch.Tensor] = None):
     """Block-sparse forward.  Returns (out (T,H,d), lse (H,T) fp32)."""
     _require_cuda(q, k, v, col_offsets, col_nnz, indices)
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
@@ -377,6 +392,10 @@ def attn_fwd(q, k, v, col_offsets, col_nnz, indices, cu_seqlens_q, cu_seqlens_k,
                                 max_seqlen_k, chunk, dev)
         rows_offered = _rows_offer(col_offsets, col_nnz, indices, total_q, h)
         ticket = _status_begin(dev)
+        spans = None
+        if leftpad_k is not None or seqused_k is not None:
+            spans = _key_spans(_i32c(cu_seqlens_k, "cu_seqlens_k"), leftpad_k, seqused_k, batch)
+            check(lib.fmb_attn_key_spans(ptr(spans[0]), ptr(spans[1])))
         check(lib.fmb_attn_fwd(ptr(q), q.stride(0), q.stride(1), ptr(k), k.stride(0), k.stride(1),
                                ptr(v), v.stride(0), v.stride(1), ptr(out), out.stride(0), out.stride(1), ptr(lse),
                                ptr(col_offsets), ptr(col_nnz), ptr(indices), indices.numel(),

@@ -9,8 +9,8 @@
  *
  * State the library keeps (everything else lives in the caller's buffers):
  *   - per host thread: the text behind fmb_last_error(); the one-shot offers made with
- *     fmb_attn_rows_offer, fmb_attn_lists_load and fmb_attn_status_mirror, consumed by that
- *     thread's next attention call;
+ *     fmb_attn_rows_offer, fmb_attn_lists_load, fmb_attn_status_mirror and fmb_attn_key_spans,
+ *     consumed by that thread's next attention call;
  *   - per process: the engine selected with fmb_set_engine, the launch counter and the event
  *     records of fmb_launch_count / fmb_profile_*;
  *   - per device: the gating kernel's status word (fmb_gate_status) and the 8 MiB scratch array
@@ -193,6 +193,16 @@ int fmb_attn_fwd(const void* q, int64_t q_row_stride, int64_t q_head_stride,
                  void* workspace, size_t workspace_bytes, int batch, int heads, int heads_k,
                  int head_dim, int64_t total_q, int max_seqlen_q, int max_seqlen_k, int chunk,
                  float softmax_scale, int causal, int dtype, fmb_stream_t stream);
+
+/* Keys of a sequence that do not start at cu_seqlens_k[b] or end at cu_seqlens_k[b+1]: the next
+ * fmb_attn_fwd call of this host thread reads sequence b's keys from rows [k_begin[b], k_end[b]) of
+ * k and v (device int32[batch] each) instead; cu_seqlens_k is then only checked for NULL.  This is
+ * how the reference's `leftpad_k` (k_begin[b] = cu_seqlens_k[b] + leftpad_k[b]) and `seqused_k`
+ * (k_end[b] = cu_seqlens_k[b] + seqused_k[b]) arguments of its forward op are served
+ * (csrc/flash_moba/src/block_info.h:19-26, csrc/flash_moba/flash_moba_api.cpp:477-482,558-564);
+ * like there, the backward call has no such arguments.  max_seqlen_k must bound k_end - k_begin.
+ * One-shot; (NULL, NULL) withdraws it. */
+int fmb_attn_key_spans(const int32_t* k_begin, const int32_t* k_end);
 
 /* ------------------------------------------------------------------ stage B: backward
  * dq/dk/dv for the forward above (dk/dv summed over the q heads of a kv head).
