@@ -38,7 +38,6 @@ _SIGS = {
     "fmb_attn_key_spans": (i32, [c_ptr, c_ptr]),
     "fmb_selftest_wait_expiry": (i32, [c_ptr, c_ptr, c_ptr]),
     "fmb_selftest_umma": (i32, [c_ptr, c_ptr, c_ptr, i32, i32, c_ptr, c_ptr]),
-    "fmb_selftest_gather": (i32, [c_ptr, i32, c_ptr, c_ptr, c_ptr, i32, c_ptr, c_ptr]),
     "fmb_launch_count": (ctypes.c_ulonglong, []),
     "fmb_profile_enable": (i32, [i32]),
     "fmb_profile_read": (i32, [i32, c_ptr, i32]),

@@ -121,13 +121,6 @@ int fmb_selftest_umma(const void* a, const void* b, float* d, int b_mn_major, in
   return launch_selftest_umma(a, b, d, b_mn_major, dtype, status, (cudaStream_t)stream);
 }
 
-int fmb_selftest_gather(const void* a, int a_rows, const int* idx, const void* b, float* d, int dtype,
-                        int* status, fmb_stream_t stream) {
-  FMB_CHECK_ARG(a && idx && b && d && status && a_rows > 0, "selftest_gather: bad arguments");
-  FMB_CHECK_ARG(dtype == FMB_BF16 || dtype == FMB_FP16, "selftest_gather: only fp16 and bf16");
-  return launch_selftest_gather(a, a_rows, idx, b, d, dtype, status, (cudaStream_t)stream);
-}
-
 int fmb_set_engine(int engine) {
   if (engine == 0 || engine == 1) {
     g_engine = engine;

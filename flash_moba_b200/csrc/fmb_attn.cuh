@@ -141,8 +141,6 @@ int launch_fwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, const PassPara
 int launch_bwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s);
 bool tc_supported(const AttnArgs& a, bool backward);
 int sm_count();   // SMs of the current device
-int launch_selftest_gather(const void* a, int a_rows, const int* idx, const void* b, float* d, int dtype,
-                           int* status, cudaStream_t s);
 int launch_selftest_wait_expiry(int* status, unsigned long long* elapsed_ns, cudaStream_t s);
 int launch_selftest_umma(const void* a, const void* b, float* d, int b_mn_major, int dtype, int* status,
                          cudaStream_t s);

@@ -39,7 +39,22 @@ struct TcParams {
   // The first `items_heavy` key blocks of every head (the longest columns) come before all of
   // that, so that no long item starts late in the launch.
   int* work; int n_items, items_x, items_y, items_z, items_heavy;
+  // 1: whole key blocks are staged with TMA tensor-map loads (K and V laid out so that one 2-D map
+  // covers all kv heads of a token row); a sequence's short last block takes the cp.async path
+  int kv_tma;
 };
+
+// One key block (C rows x D columns of kv head `hk`, first row `row0`) -> the swizzled K-major
+// tile at `tile`, as D/64 tensor-map loads that complete `bar` (whose one arrival is the
+// expect_tx made here).  One thread.
+template <int C, int D>
+__device__ __forceinline__ void tma_stage_block(unsigned char* tile, const CUtensorMap* map, int64_t head_col, int row0,
+                                                uint64_t* bar, uint32_t expect_bytes) {
+  if (expect_bytes) mbar_expect_tx(bar, expect_bytes);
+#pragma unroll
+  for (int hb = 0; hb < D / 64; ++hb)
+    tma_load_2d(tile + hb * (C * 128), map, (int)head_col + hb * 64, row0, bar);
+}
 
 // work item -> (key block index, head/sequence index)
 __device__ __forceinline__ void decode_item(const TcParams& p, int item, int& bx, int& rem) {
@@ -95,7 +110,8 @@ struct FwdItem {
 };
 
 template <typename T, int C, int D>
-__global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
+__global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap map_k,
+                                                                  const __grid_constant__ CUtensorMap map_v) {
   constexpr int QP = (C > D ? C : D);
   constexpr uint32_t kKBlock = C * 128;        // bytes between 64-element blocks of the K / V tiles
   constexpr uint32_t kQBlock = kTcM * 128;     // same for the 128-row Q / P tiles
@@ -154,7 +170,8 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
     bool ok = true;
     const T* kbase = nullptr;
     const T* vbase = nullptr;
-    int keys_valid = 0;
+    int keys_valid = 0, key_row0 = 0;
+    int64_t k_col = 0, v_col = 0;
     // takes items from the counter until one has entries, publishes it as item n of the stream
     auto scout_item = [&](uint32_t n) -> bool {
       FwdItem it;
@@ -181,6 +198,9 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
         kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + it.key0) * p.k_rs + (int64_t)hk * p.k_hs;
         vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + it.key0) * p.v_rs + (int64_t)hk * p.v_hs;
         keys_valid = it.keys_valid;
+        key_row0 = k0 + it.key0;
+        k_col = (int64_t)hk * p.k_hs;
+        v_col = (int64_t)hk * p.v_hs;
         break;
       }
       if (lane == 0) {
@@ -199,18 +219,27 @@ __global__ void __launch_bounds__(kFwdThreads) fwd_main_tc_kernel(TcParams p) {
       // K of item n: every S GEMM of item n - 1 has completed; V: every P.V GEMM has
       if (n > 0) ok = mbar_wait(&bar_sfin, (n - 1) & 1, p.status, 8);
       if (!ok) break;
-      dense_cp_async<T, D / 8, C, 32>(lane, sK, kKBlock, kbase, p.k_rs, keys_valid);
-      cp_async_wait_all();
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar_k);
+      const bool by_tma = p.kv_tma && keys_valid == C;     // warp-uniform
+      if (by_tma) {
+        if (lane == 0) tma_stage_block<C, D>(sK, &map_k, k_col, key_row0, &bar_k, C * D * 2);
+      } else {
+        dense_cp_async<T, D / 8, C, 32>(lane, sK, kKBlock, kbase, p.k_rs, keys_valid);
+        cp_async_wait_all();
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_k);
+      }
       if (n > 0) ok = mbar_wait(&bar_fin, (n - 1) & 1, p.status, 8);
       if (!ok) break;
-      dense_cp_async<T, D / 8, C, 32>(lane, sV, kKBlock, vbase, p.v_rs, keys_valid);
-      cp_async_wait_all();
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar_v);
+      if (by_tma) {
+        if (lane == 0) tma_stage_block<C, D>(sV, &map_v, v_col, key_row0, &bar_v, C * D * 2);
+      } else {
+        dense_cp_async<T, D / 8, C, 32>(lane, sV, kKBlock, vbase, p.v_rs, keys_valid);
+        cp_async_wait_all();
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_v);
+      }
       more = scout_item(n + 1);
     }
   } else if (warp == kFwdIssuerWarp) {
@@ -545,7 +574,8 @@ __device__ __forceinline__ void bwd_decode_item(const TcParams& p, int item, int
 }
 
 template <typename T, int C, int D>
-__global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
+__global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap map_k,
+                                                                  const __grid_constant__ CUtensorMap map_v) {
   static_assert(C == 128, "tensor-core backward keeps one key per TMEM lane");
   constexpr uint32_t kKBlock = C * 128;
   constexpr uint32_t kQBlock = kTcM * 128;
@@ -762,12 +792,19 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_main_tc_kernel(TcParams p) {
       if (!skip) {
         const T* kbase = static_cast<const T*>(p.k) + (int64_t)(I.k0 + I.key0) * p.k_rs + (int64_t)I.hk * p.k_hs;
         const T* vbase = static_cast<const T*>(p.v) + (int64_t)(I.k0 + I.key0) * p.v_rs + (int64_t)I.hk * p.v_hs;
-        dense_cp_async<T, D / 8, C, 32>(lane, sK, kKBlock, kbase, p.k_rs, I.keys_valid);
-        dense_cp_async<T, D / 8, C, 32>(lane, sV, kKBlock, vbase, p.v_rs, I.keys_valid);
-        cp_async_wait_all();
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bar_kv);
+        if (p.kv_tma && I.keys_valid == C) {   // warp-uniform
+          if (lane == 0) {
+            tma_stage_block<C, D>(sK, &map_k, (int64_t)I.hk * p.k_hs, I.k0 + I.key0, &bar_kv, 2 * C * D * 2);
+            tma_stage_block<C, D>(sV, &map_v, (int64_t)I.hk * p.v_hs, I.k0 + I.key0, &bar_kv, 0);
+          }
+        } else {
+          dense_cp_async<T, D / 8, C, 32>(lane, sK, kKBlock, kbase, p.k_rs, I.keys_valid);
+          dense_cp_async<T, D / 8, C, 32>(lane, sV, kKBlock, vbase, p.v_rs, I.keys_valid);
+          cp_async_wait_all();
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bar_kv);
+        }
       }
       more = scout_item(n + 1);
       if (!skip) {                   // every GEMM of item n has completed: its K and V tiles are free
@@ -1148,92 +1185,6 @@ int launch_selftest_umma(const void* a, const void* b, float* d, int b_mn_major,
   return FMB_OK;
 }
 
-// Self test of the TMA row gather: A' = rows `idx` of a (T x 128) matrix a (idx -1 or >= T reads
-// zeros), fetched with tile::gather4 into the swizzled UMMA tile; then d = A' . b^T as above.
-template <typename T>
-__global__ void __launch_bounds__(128) selftest_gather_kernel(const __grid_constant__ CUtensorMap map_a,
-                                                              const int* idx, int nrows_total, const T* b,
-                                                              float* d, int* status) {
-  extern __shared__ unsigned char smem_raw[];
-  __shared__ uint64_t bar, bar_full;
-  __shared__ uint32_t tmem_base_s;
-  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  unsigned char* sA = smem;
-  unsigned char* sB = smem + 128 * 128 * 2;
-  const int tid = threadIdx.x, warp = tid >> 5;
-  if (warp == 0) tmem_alloc(&tmem_base_s, 128);
-  if (tid == 0) {
-    mbar_init(&bar, 1);
-    mbar_init(&bar_full, 1);
-    mbar_fence_init();
-  }
-  stage_tile_sw128<T, 16>(sB, 128 * 128, b, 128, 128, [](int r) { return (int64_t)r; });
-  fence_async_smem();
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  if (warp == 1) {   // one warp issues the gathers: lane l fetches rows 4l..4l+3, both 64-column halves
-    const int lane = tid & 31;
-    if (lane == 0) mbar_expect_tx(&bar_full, 128 * 128 * 2);
-    __syncwarp();
-    int y[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int r = idx[lane * 4 + i];
-      y[i] = (r < 0 || r >= nrows_total) ? nrows_total : r;   // out of range -> zero fill
-    }
-    tma_gather4(sA + lane * 512, &map_a, 0, y[0], y[1], y[2], y[3], &bar_full);
-    tma_gather4(sA + 16384 + lane * 512, &map_a, 64, y[0], y[1], y[2], y[3], &bar_full);
-  }
-  bool ok = mbar_wait(&bar_full, 0, status, 8);
-  ok = __syncthreads_and(ok);
-  const uint32_t tD = tmem_base_s;
-  if (ok) {
-    if (tid == 0) {
-      tc_fence_after_sync();
-      const uint32_t idesc = make_idesc(FmtOf<T>::v, 128, 128, 0, 0);
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint32_t o = (ks >> 2) * 16384 + (ks & 3) * 32;
-        umma_ss(tD, make_desc_sw128(smem_u32(sA) + o, 16, 1024), make_desc_sw128(smem_u32(sB) + o, 16, 1024), idesc,
-                ks > 0);
-      }
-      umma_commit(&bar);
-    }
-    ok = mbar_wait(&bar, 0, status, 9);
-    if (__syncthreads_and(ok)) {
-      tc_fence_after_sync();
-      for (int i = 0; i < 4; ++i) {
-        float o[32];
-        tmem_ld32(tD + ((uint32_t)(warp * 32) << 16) + i * 32, o);
-        tmem_ld_wait();
-        for (int j = 0; j < 32; ++j) d[tid * 128 + i * 32 + j] = o[j];
-      }
-      tc_fence_before_sync();
-    }
-  }
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tD, 128);
-}
-
-int launch_selftest_gather(const void* a, int a_rows, const int* idx, const void* b, float* d, int dtype,
-                           int* status, cudaStream_t s) {
-  CUtensorMap map;
-  int rc = make_tmap_2d(&map, a, dtype, 128, (uint64_t)a_rows, 256, 64, 1);
-  if (rc) return rc;
-  const size_t smem = 2 * 128 * 128 * 2 + 1024;
-  if (dtype == FMB_BF16) {
-    auto kern = selftest_gather_kernel<__nv_bfloat16>;
-    FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<1, 128, smem, s>>>(map, idx, a_rows, (const __nv_bfloat16*)b, d, status);
-  } else {
-    auto kern = selftest_gather_kernel<__half>;
-    FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<1, 128, smem, s>>>(map, idx, a_rows, (const __half*)b, d, status);
-  }
-  FMB_LAUNCH_CHECK("selftest_gather_kernel");
-  return FMB_OK;
-}
-
 // ------------------------------------------------------------------ launchers
 static TcParams make_tc_params(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps) {
   TcParams p;
@@ -1259,9 +1210,30 @@ static bool rows_fit_l2(const AttnArgs& a, const PassParams& ps) {
   return (int64_t)a.total_q * a.d * 2 * 2 * ps.nh <= (int64_t)160 << 20;
 }
 
+// Tensor maps of K and V for the key-block loads: one 2-D map per tensor over (columns of a token
+// row, token rows), box 64 columns x C rows, 128-byte swizzle.  Possible when all kv heads of a
+// token lie inside its row stride; the row extent is left open because only blocks that lie wholly
+// inside their sequence are loaded this way.  Tensor maps over this GPU's own memory only, plain
+// per-CTA loads (no multicast: the kernels also run in multi-GPU jobs).
+static int make_kv_maps(const AttnArgs& a, int C, CUtensorMap* mk, CUtensorMap* mv, int* usable) {
+  *usable = 0;
+  memset(mk, 0, sizeof(*mk));
+  memset(mv, 0, sizeof(*mv));
+  auto fits = [&](int64_t rs, int64_t hs) { return hs >= 0 && rs > 0 && (int64_t)(a.heads_k - 1) * hs + a.d <= rs; };
+  if (a.k == nullptr || a.v == nullptr || !fits(a.k_rs, a.k_hs) || !fits(a.v_rs, a.v_hs)) return FMB_OK;
+  const uint64_t rows = (uint64_t)1 << 31;
+  int rc = make_tmap_2d(mk, a.k, a.dtype, (uint64_t)((a.heads_k - 1) * a.k_hs + a.d), rows, (uint64_t)a.k_rs * 2, 64, C);
+  if (rc == FMB_OK) rc = make_tmap_2d(mv, a.v, a.dtype, (uint64_t)((a.heads_k - 1) * a.v_hs + a.d), rows, (uint64_t)a.v_rs * 2, 64, C);
+  if (rc != FMB_OK) return FMB_OK;     // no driver support for tensor maps: the cp.async path serves every block
+  *usable = 1;
+  return FMB_OK;
+}
+
 template <typename T, int C, int D>
 static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   TcParams p = make_tc_params(a, w, ps);
+  CUtensorMap map_k, map_v;
+  make_kv_maps(a, C, &map_k, &map_v, &p.kv_tma);
   constexpr int QP = (C > D ? C : D);
   // K, V, and per compute group a Q tile and a P / O-staging tile; one CTA per SM by size
   // (all 512 TMEM columns are allocated)
@@ -1275,7 +1247,7 @@ static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassPa
   p.items_heavy = !a.causal ? 0 : (rows_fit_l2(a, ps) ? p.items_x : min(p.items_x, 16 * ps.nsub));
   p.n_items = p.items_x * p.items_y * p.items_z;
   if (ps.h0 > 0) FMB_CUDA(cudaMemsetAsync(p.work, 0, sizeof(int), s));   // first pass: cleared with the status block
-  kern<<<min(p.n_items, sm_count()), kFwdThreads, smem, s>>>(p);
+  kern<<<min(p.n_items, sm_count()), kFwdThreads, smem, s>>>(p, map_k, map_v);
   FMB_LAUNCH_CHECK("fwd_main_tc_kernel");
   return FMB_OK;
 }
@@ -1283,6 +1255,8 @@ static int fwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassPa
 template <typename T, int C, int D>
 static int bwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   TcParams p = make_tc_params(a, w, ps);
+  CUtensorMap map_k, map_v;
+  make_kv_maps(a, C, &map_k, &map_v, &p.kv_tma);
   // K, V, two Q tiles, one dO tile, P and dS: with d = 128 that and the kernel's 3 KB of static shared
   // memory are exactly the 227 KB a CTA may have (the dynamic part is declared 1024-byte aligned)
   const size_t smem = (size_t)2 * C * D * 2 + (size_t)3 * kTcM * D * 2 + (size_t)2 * kTcM * C * 2;
@@ -1295,7 +1269,7 @@ static int bwd_tc_launch(const AttnArgs& a, const AttnWorkspace& w, const PassPa
   p.items_heavy = !a.causal ? 0 : (rows_fit_l2(a, ps) ? p.items_x : min(p.items_x, 16 * ps.nsub));
   p.n_items = p.items_x * p.items_y * p.items_z;
   if (ps.h0 > 0) FMB_CUDA(cudaMemsetAsync(p.work, 0, sizeof(int), s));   // first pass: cleared with the status block
-  kern<<<min(p.n_items, sm_count()), kBwdThreads, smem, s>>>(p);
+  kern<<<min(p.n_items, sm_count()), kBwdThreads, smem, s>>>(p, map_k, map_v);
   FMB_LAUNCH_CHECK("bwd_main_tc_kernel");
   return FMB_OK;
 }

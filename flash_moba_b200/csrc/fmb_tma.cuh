@@ -1,6 +1,6 @@
 // TMA (tensor-map) support: host-side descriptor builder and device-side issue wrappers.
-// Only plain per-CTA loads are used: tiled loads and tile::gather4 row gathers, completion
-// through an mbarrier's transaction count.
+// Only plain per-CTA tiled loads are used (the K / V key blocks of the attention kernels),
+// completion through an mbarrier's transaction count.  No multicast.
 #pragma once
 #include <cuda.h>
 
@@ -27,19 +27,6 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       :
       : "r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
-
-// four rows y0..y3 (each box_cols wide, starting at column x) -> four consecutive 128-byte
-// rows of shared memory.  The tensor map's box must be box_cols x 1.
-__device__ __forceinline__ void tma_gather4(void* dst, const CUtensorMap* map, int x, int y0, int y1, int y2,
-                                            int y3, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-      :
-      : "r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y0), "r"(y1),
-        "r"(y2), "r"(y3)
       : "memory");
 }
 

@@ -210,19 +210,6 @@ def selftest_umma(a: torch.Tensor, b: torch.Tensor, b_mn_major: bool) -> torch.T
     return d
 
 
-def selftest_gather(a: torch.Tensor, idx: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """(a[idx] with out-of-range rows = 0) @ b.T on the TMA-gather + tcgen05 path (see fmb_selftest_gather)."""
-    _require_cuda(a, idx, b)
-    a, b, idx = a.contiguous(), b.contiguous(), idx.to(torch.int32).contiguous()
-    with torch.cuda.device(a.device):
-        d = torch.empty((128, 128), dtype=torch.float32, device=a.device)
-        status = torch.zeros((1,), dtype=torch.int32, device=a.device)
-        check(lib.fmb_selftest_gather(ptr(a), a.shape[0], ptr(idx), ptr(b), ptr(d), _dtype_code(a), ptr(status), _stream()))
-        if int(status.item()) != 0:
-            raise RuntimeError(f"selftest_gather: bounded wait expired (code {int(status.item())})")
-    return d
-
-
 def selftest_wait_expiry(device=None) -> Tuple[int, float]:
     """Runs the library's bounded wait on an mbarrier nobody arrives at (see fmb_selftest_wait_expiry).
     Returns (status code written by the kernel, seconds the wait lasted before it gave up)."""

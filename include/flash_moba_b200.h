@@ -257,12 +257,6 @@ int fmb_attn_status(const void* workspace, int* host_status, fmb_stream_t stream
 int fmb_selftest_umma(const void* a, const void* b, float* d, int b_mn_major, int dtype, int* status,
                       fmb_stream_t stream);
 
-/* Self test of the TMA row gather (tile::gather4), no counterpart in the reference:
- * d[128][128] (float) = A' . b^T where A'[i] = a[idx[i]] (a is a_rows x 128, contiguous; an
- * index < 0 or >= a_rows gives a zero row) and b is [128][128]; idx is a device int[128]. */
-int fmb_selftest_gather(const void* a, int a_rows, const int* idx, const void* b, float* d, int dtype,
-                        int* status, fmb_stream_t stream);
-
 /* Self test of the bounded wait every kernel of this library uses: one warp waits on an mbarrier
  * that nobody arrives at, gives up, records code 5 in *status (device int, set to 0 by the call
  * first) and the nanoseconds the wait lasted in *elapsed_ns (device uint64), and exits normally.
