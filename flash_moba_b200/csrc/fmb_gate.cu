@@ -234,12 +234,16 @@ __global__ void __launch_bounds__(kGateThreads) gate_topk_kernel(GateParams p) {
 // Tensor-core variant (head_dim 64 or 128, top-k <= 32).  The score tile is a tcgen05 MMA
 // with the accumulator in TMEM; TMEM lane = query row, so thread t reads row t's scores
 // straight from TMEM (no shared-memory staging of scores) and keeps that row's top-k list
-// in registers as 64-bit keys: (order-preserving image of the fp32 score) << 32 | chunk id.
-// One unsigned compare then implements the reference's order — descending score, higher
-// chunk id first on ties — and the empty slot (-inf, id 0xffffffff) can never be displaced
-// by a -inf or NaN score.  Q is staged once; centroid tiles and TMEM accumulators are
-// double-buffered so the MMA of tile n+1 runs under the selection of tile n; two CTAs share
-// an SM.  All waits are bounded (status word g_gate_status).
+// in registers: val[] = order-preserving 32-bit images of the fp32 scores, descending, and
+// idx[] = their chunk ids.  A thread meets its candidates in ascending chunk order, so "the
+// higher chunk id ranks first on equal scores" (the reference's rule) is simply: a candidate
+// goes ahead of every entry it is greater than OR EQUAL to, one 32-bit compare per slot; the
+// values move with a min/max pair, the ids with two selects.  Slots that must never be
+// displaced (the row's own chunk, and the unused head of a list shorter than KMAX) hold the image
+// 0xffffffff, which no score that passes the "> -inf" test can reach; the empty slot holds the
+// image of -inf.  Q is staged once; centroid tiles and TMEM accumulators are double-buffered so
+// the MMA of tile n+1 runs under the selection of tile n; two CTAs share an SM.  All waits are
+// bounded (status word g_gate_status).
 // ---------------------------------------------------------------------------------------
 __device__ int g_gate_status = 0;
 
@@ -286,13 +290,31 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
   int nlim = nchunks;                          // candidate chunks of the row: n < nlim
   if (p.causal) nlim = pos < 0 ? 0 : min(nchunks, pos / p.chunk);
   if (!row_ok) nlim = 0;
-  constexpr uint64_t kEmpty = ((uint64_t)0x007fffffu << 32) | 0xffffffffu;   // (-inf, id -1)
+  constexpr uint32_t kFixed = 0xffffffffu;     // image of a slot no candidate may displace
+  constexpr uint32_t kEmptyVal = 0x007fffffu;  // image of -inf: the empty slot
+  constexpr int kBlockedId = -2;               // id of the unused head of a list shorter than KMAX
   const bool own = p.causal && row_ok && pos >= 0 && nchunks > 0 && qd == 0;
-  const uint64_t own_key = ((uint64_t)score_to_ordered(CUDART_INF_F) << 32) | (uint32_t)(own ? pos / p.chunk : 0);
-  uint64_t key[KMAX];
+  uint32_t val[KMAX];
+  int idx[KMAX];
 #pragma unroll
-  for (int j = 0; j < KMAX; ++j)   // static indices only: the list must stay in registers
-    key[j] = (j < KMAX - topk) ? ~0ull : ((j == KMAX - topk && own) ? own_key : kEmpty);
+  for (int j = 0; j < KMAX; ++j) {   // static indices only: the list must stay in registers
+    const bool blocked = j < KMAX - topk, is_own = (j == KMAX - topk) && own;
+    val[j] = (blocked || is_own) ? kFixed : kEmptyVal;
+    idx[j] = blocked ? kBlockedId : (is_own ? pos / p.chunk : -1);
+  }
+  // candidate (image ox, chunk n) into the list; every entry already there has a lower chunk id
+  auto insert = [&](uint32_t ox, int n) {
+    bool ge[KMAX];
+#pragma unroll
+    for (int y = 0; y < KMAX; ++y) ge[y] = ox >= val[y];
+#pragma unroll
+    for (int y = KMAX - 1; y > 0; --y) {
+      idx[y] = ge[y - 1] ? idx[y - 1] : (ge[y] ? n : idx[y]);
+      val[y] = min(val[y - 1], max(val[y], ox));
+    }
+    idx[0] = ge[0] ? n : idx[0];
+    val[0] = max(val[0], ox);
+  };
 
   int n_end = nchunks;
   if (p.causal) {
@@ -361,6 +383,49 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
       // works through ITS OWN marked scores, so the (long) insertion code runs max-over-lanes of
       // the marked counts times per step instead of once per position that any lane marked.
       const bool tail = n0 + kGateN > nlim;     // this tile crosses the row's candidate limit
+      // A list that is still empty lets every score in.  For the first tile of a row the thread
+      // therefore first finds a floor for its k-th best: the maxima of its 16 groups of 4 scores
+      // are 16 different candidates, so their 8th largest cannot exceed the 8th largest score.
+      // Only the dozen scores that reach the floor are then looked at one by one, instead of
+      // some forty while the list fills (the scores are read from TMEM a second time for it).
+      float floor_thr = -CUDART_INF_F;
+      if (KMAX == 8 && kCols == 64 && t == 0) {
+        float gm[16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float w[16];
+          tmem_ld16(taddr + i * 16, w);
+          tmem_ld_wait();
+          if (tail) {
+            const int left = nlim - (n0 + qd * kCols + i * 16);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) w[j] = j < left ? w[j] : -CUDART_INF_F;
+          }
+#pragma unroll
+          for (int g4 = 0; g4 < 4; ++g4)
+            gm[i * 4 + g4] = fmaxf(fmaxf(fmaxf(w[g4 * 4], w[g4 * 4 + 1]), fmaxf(w[g4 * 4 + 2], w[g4 * 4 + 3])),
+                                   -CUDART_INF_F);   // (a group of NaNs counts as -inf: fmaxf drops NaN operands)
+        }
+        // 8th largest of 16: both halves sorted descending (19 compare-exchanges each), then
+        // min over i of max(a[i], b[7 - i])
+        auto sort8 = [](float* x) {
+#define FMB_CE(i, j) { const float hi_ = fmaxf(x[i], x[j]), lo_ = fminf(x[i], x[j]); x[i] = hi_; x[j] = lo_; }
+          FMB_CE(0, 1) FMB_CE(2, 3) FMB_CE(4, 5) FMB_CE(6, 7)
+          FMB_CE(0, 2) FMB_CE(1, 3) FMB_CE(4, 6) FMB_CE(5, 7)
+          FMB_CE(1, 2) FMB_CE(5, 6) FMB_CE(0, 4) FMB_CE(3, 7)
+          FMB_CE(1, 5) FMB_CE(2, 6)
+          FMB_CE(1, 4) FMB_CE(3, 6)
+          FMB_CE(2, 4) FMB_CE(3, 5)
+          FMB_CE(3, 4)
+#undef FMB_CE
+        };
+        sort8(gm);
+        sort8(gm + 8);
+        float kth = CUDART_INF_F;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) kth = fminf(kth, fmaxf(gm[i], gm[15 - i]));
+        floor_thr = kth;
+      }
       float v[2][16];
       tmem_ld16(taddr, v[0]);
 #pragma unroll 1
@@ -370,7 +435,7 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
           tmem_ld_wait();
           if (i + half + 1 < kCols / 16) tmem_ld16(taddr + (i + half + 1) * 16, v[half ^ 1]);
           const int nb = n0 + qd * kCols + (i + half) * 16;
-          const float thr = ordered_to_score((uint32_t)(key[KMAX - 1] >> 32));
+          const float thr = val[KMAX - 1] == kFixed ? CUDART_INF_F : fmaxf(floor_thr, ordered_to_score(val[KMAX - 1]));
           uint32_t m = 0;
 #pragma unroll
           for (int j = 0; j < 16; ++j) m |= (v[half][j] >= thr) ? (1u << j) : 0u;
@@ -390,18 +455,8 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
               for (int e = 0; e < 4; ++e) a4[e] = (j & 4) ? a8[4 + e] : a8[e];
               const float a2a = (j & 2) ? a4[2] : a4[0], a2b = (j & 2) ? a4[3] : a4[1];
               const float x = (j & 1) ? a2b : a2a;
-              const uint64_t cand = ((uint64_t)score_to_ordered(x) << 32) | (uint32_t)(nb + j);
-              if (x > -CUDART_INF_F && cand > key[KMAX - 1]) {
-                // insertion with independent compares and selects (no dependent swap chain):
-                // slot y takes its upper neighbour if the candidate outranks that one, else the
-                // candidate if it outranks the slot, else keeps its key
-                bool gt[KMAX];
-#pragma unroll
-                for (int y = 0; y < KMAX; ++y) gt[y] = cand > key[y];
-#pragma unroll
-                for (int y = KMAX - 1; y > 0; --y) key[y] = gt[y - 1] ? key[y - 1] : (gt[y] ? cand : key[y]);
-                key[0] = gt[0] ? cand : key[0];
-              }
+              const uint32_t ox = score_to_ordered(x);
+              if (x > -CUDART_INF_F && ox >= val[KMAX - 1]) insert(ox, nb + j);
             }
           }
         }
@@ -424,20 +479,27 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
       uint64_t* sMerge = reinterpret_cast<uint64_t*>(sKM);
       if (qd > 0) {
 #pragma unroll
-        for (int j = 0; j < KMAX; ++j) sMerge[((qd - 1) * KMAX + j) * 128 + lt] = key[j];
+        for (int j = 0; j < KMAX; ++j) sMerge[((qd - 1) * KMAX + j) * 128 + lt] = ((uint64_t)val[j] << 32) | (uint32_t)idx[j];
       }
       __syncthreads();
       if (qd == 0) {
         for (int e = 0; e < (NQ - 1) * KMAX; ++e) {
           const uint64_t cand = sMerge[e * 128 + lt];
-          // sentinels of the other lists (~0) are skipped; empty slots never outrank anything
-          if (cand != ~0ull && cand > key[KMAX - 1]) {
+          const uint32_t ox = (uint32_t)(cand >> 32);
+          const int n = (int)(uint32_t)cand;
+          // blocked and empty slots of the other lists are skipped.  The lists meet in no particular
+          // chunk order, so the order is the full one here: score first, then the higher chunk id.
+          if (n >= 0 && (ox > val[KMAX - 1] || (ox == val[KMAX - 1] && n > idx[KMAX - 1]))) {
             bool gt[KMAX];
 #pragma unroll
-            for (int y = 0; y < KMAX; ++y) gt[y] = cand > key[y];
+            for (int y = 0; y < KMAX; ++y) gt[y] = ox > val[y] || (ox == val[y] && n > idx[y]);
 #pragma unroll
-            for (int y = KMAX - 1; y > 0; --y) key[y] = gt[y - 1] ? key[y - 1] : (gt[y] ? cand : key[y]);
-            key[0] = gt[0] ? cand : key[0];
+            for (int y = KMAX - 1; y > 0; --y) {
+              idx[y] = gt[y - 1] ? idx[y - 1] : (gt[y] ? n : idx[y]);
+              val[y] = gt[y - 1] ? val[y - 1] : (gt[y] ? ox : val[y]);
+            }
+            idx[0] = gt[0] ? n : idx[0];
+            val[0] = gt[0] ? ox : val[0];
           }
         }
       }
@@ -449,8 +511,8 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
     for (int j = 0; j < KMAX; ++j) {
       const int slot = j - (KMAX - topk);
       if (slot >= 0) {
-        p.topk_idx[o + slot] = (int)(uint32_t)key[j];
-        if (p.topk_val) p.topk_val[o + slot] = ordered_to_score((uint32_t)(key[j] >> 32));
+        p.topk_idx[o + slot] = idx[j];
+        if (p.topk_val) p.topk_val[o + slot] = val[j] == kFixed ? CUDART_INF_F : ordered_to_score(val[j]);
       }
     }
   }
