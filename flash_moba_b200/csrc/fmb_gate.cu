@@ -266,6 +266,8 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ uint64_t bar[2];
   __shared__ uint32_t tmem_base_s;
+  // the two threads of a row tell each other the eight best images they hold (NQ == 2)
+  __shared__ uint32_t sX[NQ == 2 ? 2 : 1][NQ == 2 ? 8 : 1][NQ == 2 ? 128 : 1];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* sQ = smem;
   unsigned char* sKM = sQ + kTile;             // two buffers
@@ -302,6 +304,14 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
     val[j] = (blocked || is_own) ? kFixed : kEmptyVal;
     idx[j] = blocked ? kBlockedId : (is_own ? pos / p.chunk : -1);
   }
+  // val[j] for a j that depends on the run-time top-k (selects: the list must stay in registers)
+  auto val_at = [&](int j) {
+    if (topk == KMAX) return val[j < KMAX ? j : 0];   // (callers pass compile-time j: no selects in the common case)
+    uint32_t x = val[0];
+#pragma unroll
+    for (int y = 1; y < KMAX; ++y) x = (j == y) ? val[y] : x;
+    return x;
+  };
   // candidate (image ox, chunk n) into the list; every entry already there has a lower chunk id
   auto insert = [&](uint32_t ox, int n) {
     bool ge[KMAX];
@@ -365,6 +375,7 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
       if (ntiles > 1) issue(1);
     }
     uint32_t phases = 0;   // bit b = parity to wait for on bar[b]
+    float floor_thr_row = -CUDART_INF_F;   // what the k-th best of the row is known to reach
     for (int t = 0; t < ntiles; ++t) {
       const int buf = t & 1;
       const int n0 = t * kGateN;
@@ -388,7 +399,7 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
       // are 16 different candidates, so their 8th largest cannot exceed the 8th largest score.
       // Only the dozen scores that reach the floor are then looked at one by one, instead of
       // some forty while the list fills (the scores are read from TMEM a second time for it).
-      float floor_thr = -CUDART_INF_F;
+      float floor_thr = floor_thr_row;
       if (KMAX == 8 && kCols == 64 && t == 0) {
         float gm[16];
 #pragma unroll
@@ -421,10 +432,21 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
         };
         sort8(gm);
         sort8(gm + 8);
+        // this thread's eight largest group maxima, sorted, then the same eight of the row's other
+        // thread: the 8th largest of the 32 groups of the whole tile is the floor for both
+        float c8[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) c8[i] = fmaxf(gm[i], gm[15 - i]);
+        sort8(c8);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sX[qd][i][lt] = __float_as_uint(c8[i]);
+        bar_sync(1 + (warp & 3), 64);           // warps w and w + 4 hold the same rows
         float kth = CUDART_INF_F;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) kth = fminf(kth, fmaxf(gm[i], gm[15 - i]));
+        for (int i = 0; i < 8; ++i) kth = fminf(kth, fmaxf(c8[i], __uint_as_float(sX[qd ^ 1][7 - i][lt])));
+        bar_sync(1 + (warp & 3), 64);           // both have read before the buffer is written again
         floor_thr = kth;
+        floor_thr_row = kth;
       }
       float v[2][16];
       tmem_ld16(taddr, v[0]);
@@ -462,6 +484,10 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
         }
       }
       if (ahead) {             // CTA-uniform
+        if (NQ == 2 && KMAX == 8) {   // this thread's list without the slots of a list shorter than KMAX
+#pragma unroll
+          for (int j = 0; j < 8; ++j) sX[qd][j][lt] = (j + (KMAX - topk) < KMAX) ? val_at(j + (KMAX - topk)) : kEmptyVal;
+        }
         cp_async_wait_all();
         fence_async_smem();
         tc_fence_before_sync();
@@ -469,6 +495,19 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
         if (tid == 0) {
           tc_fence_after_sync();
           issue(buf);
+        }
+        if (NQ == 2 && KMAX == 8) {
+          // The k-th best of the row so far is at least the k-th largest of the two threads' lists
+          // together (both sorted: min over i of max(a[i], b[k - 1 - i])): a floor for the next tiles
+          // that roughly halves the scores each thread still has to look at one by one.  (The
+          // barrier at the top of the next tile separates these reads from the next writes.)
+          uint32_t kth = kFixed;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t mine = (i + (KMAX - topk) < KMAX) ? val_at(i + (KMAX - topk)) : kEmptyVal;
+            kth = min(kth, max(mine, sX[qd ^ 1][7 - i][lt]));
+          }
+          if (kth != kFixed) floor_thr_row = fmaxf(floor_thr_row, ordered_to_score(kth));
         }
       }
     }
