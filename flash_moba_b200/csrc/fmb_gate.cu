@@ -395,15 +395,18 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
       // the marked counts times per step instead of once per position that any lane marked.
       const bool tail = n0 + kGateN > nlim;     // this tile crosses the row's candidate limit
       // A list that is still empty lets every score in.  For the first tile of a row the thread
-      // therefore first finds a floor for its k-th best: the maxima of its 16 groups of 4 scores
-      // are 16 different candidates, so their 8th largest cannot exceed the 8th largest score.
-      // Only the dozen scores that reach the floor are then looked at one by one, instead of
-      // some forty while the list fills (the scores are read from TMEM a second time for it).
+      // therefore first finds a floor for its k-th best: the maxima of its groups of 4 scores are
+      // different candidates, so their k-th largest cannot exceed the k-th largest score (lists of
+      // 8 with 16 or 32 groups, lists of 16 with 32 groups).  Only the scores that reach the floor
+      // are then looked at one by one, a dozen instead of some forty while a list of 8 fills (the
+      // scores are read from TMEM a second time for it).
       float floor_thr = floor_thr_row;
-      if (KMAX == 8 && kCols == 64 && t == 0) {
-        float gm[16];
+      constexpr int kGroups = kCols / 4;
+      constexpr bool kColdFloor = (KMAX == 8 && kGroups == 16) || (KMAX == 16 && kGroups == 32);
+      if (kColdFloor && t == 0) {
+        float gm[kGroups];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < kCols / 16; ++i) {
           float w[16];
           tmem_ld16(taddr + i * 16, w);
           tmem_ld_wait();
@@ -417,34 +420,63 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
             gm[i * 4 + g4] = fmaxf(fmaxf(fmaxf(w[g4 * 4], w[g4 * 4 + 1]), fmaxf(w[g4 * 4 + 2], w[g4 * 4 + 3])),
                                    -CUDART_INF_F);   // (a group of NaNs counts as -inf: fmaxf drops NaN operands)
         }
-        // 8th largest of 16: both halves sorted descending (19 compare-exchanges each), then
-        // min over i of max(a[i], b[7 - i])
+        // descending sorting networks on registers: 8 values in 19 compare-exchanges; 16 values as
+        // two sorted eights and a bitonic merge
+#define FMB_CE(x, i, j) { const float hi_ = fmaxf(x[i], x[j]), lo_ = fminf(x[i], x[j]); x[i] = hi_; x[j] = lo_; }
         auto sort8 = [](float* x) {
-#define FMB_CE(i, j) { const float hi_ = fmaxf(x[i], x[j]), lo_ = fminf(x[i], x[j]); x[i] = hi_; x[j] = lo_; }
-          FMB_CE(0, 1) FMB_CE(2, 3) FMB_CE(4, 5) FMB_CE(6, 7)
-          FMB_CE(0, 2) FMB_CE(1, 3) FMB_CE(4, 6) FMB_CE(5, 7)
-          FMB_CE(1, 2) FMB_CE(5, 6) FMB_CE(0, 4) FMB_CE(3, 7)
-          FMB_CE(1, 5) FMB_CE(2, 6)
-          FMB_CE(1, 4) FMB_CE(3, 6)
-          FMB_CE(2, 4) FMB_CE(3, 5)
-          FMB_CE(3, 4)
-#undef FMB_CE
+          FMB_CE(x, 0, 1) FMB_CE(x, 2, 3) FMB_CE(x, 4, 5) FMB_CE(x, 6, 7)
+          FMB_CE(x, 0, 2) FMB_CE(x, 1, 3) FMB_CE(x, 4, 6) FMB_CE(x, 5, 7)
+          FMB_CE(x, 1, 2) FMB_CE(x, 5, 6) FMB_CE(x, 0, 4) FMB_CE(x, 3, 7)
+          FMB_CE(x, 1, 5) FMB_CE(x, 2, 6)
+          FMB_CE(x, 1, 4) FMB_CE(x, 3, 6)
+          FMB_CE(x, 2, 4) FMB_CE(x, 3, 5)
+          FMB_CE(x, 3, 4)
         };
-        sort8(gm);
-        sort8(gm + 8);
-        // this thread's eight largest group maxima, sorted, then the same eight of the row's other
-        // thread: the 8th largest of the 32 groups of the whole tile is the floor for both
-        float c8[8];
+        auto sort16 = [&](float* x) {
+          sort8(x);
+          sort8(x + 8);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) c8[i] = fmaxf(gm[i], gm[15 - i]);
-        sort8(c8);
+          for (int i = 0; i < 8; ++i) FMB_CE(x, i, 15 - i)
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sX[qd][i][lt] = __float_as_uint(c8[i]);
-        bar_sync(1 + (warp & 3), 64);           // warps w and w + 4 hold the same rows
+          for (int h8 = 0; h8 < 16; h8 += 8) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) FMB_CE(x, h8 + i, h8 + i + 4)
+#pragma unroll
+            for (int i = 0; i < 8; i += 4) { FMB_CE(x, h8 + i, h8 + i + 2) FMB_CE(x, h8 + i + 1, h8 + i + 3) }
+#pragma unroll
+            for (int i = 0; i < 8; i += 2) FMB_CE(x, h8 + i, h8 + i + 1)
+          }
+        };
         float kth = CUDART_INF_F;
+        if constexpr (KMAX == 8) {
+          // 8th largest of the 16 group maxima: both halves sorted, then min over i of max(a[i], b[7 - i]);
+          // those eight maxima, sorted, are also what the row's other thread needs
+          sort8(gm);
+          sort8(gm + 8);
+          float c8[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) kth = fminf(kth, fmaxf(c8[i], __uint_as_float(sX[qd ^ 1][7 - i][lt])));
-        bar_sync(1 + (warp & 3), 64);           // both have read before the buffer is written again
+          for (int i = 0; i < 8; ++i) c8[i] = fmaxf(gm[i], gm[15 - i]);
+          if constexpr (NQ == 2) {
+            // the 8th largest of the 32 groups of the whole tile is the floor for both threads
+            sort8(c8);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sX[qd][i][lt] = __float_as_uint(c8[i]);
+            bar_sync(1 + (warp & 3), 64);         // warps w and w + 4 hold the same rows
+#pragma unroll
+            for (int i = 0; i < 8; ++i) kth = fminf(kth, fmaxf(c8[i], __uint_as_float(sX[qd ^ 1][7 - i][lt])));
+            bar_sync(1 + (warp & 3), 64);         // both have read before the buffer is written again
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) kth = fminf(kth, c8[i]);
+          }
+        } else {
+          // 16th largest of the 32 group maxima
+          sort16(gm);
+          sort16(gm + 16);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) kth = fminf(kth, fmaxf(gm[i], gm[31 - i]));
+        }
+#undef FMB_CE
         floor_thr = kth;
         floor_thr_row = kth;
       }
