@@ -58,7 +58,7 @@ def _load_accounting():
 
 
 ACC = _load_accounting()
-BWD_MAIN_DRAM_BYTES_PER_ENTRY = 653.7
+BWD_MAIN_DRAM_BYTES_PER_ENTRY = 575.2
 
 
 class ClockSampler:
@@ -446,10 +446,11 @@ def main():
     dom = "bwd_main" if backward else "fwd_main"
     dom_flops = (bwd_f if backward else fwd_f) * (1.0 / world if by_range else h_loc / H)      # rank 0's launch (about, under the range split)
     roof = None
-    # DRAM bytes per (row, chunk) entry of the dominant kernel, from one ncu capture of a 16K-token,
-    # 16-head case of this build (profiles/bwd_main_tc_kernel_16k.md: dram__bytes_read.sum +
-    # dram__bytes_write.sum over its 2,039,808 entries); the traffic is per-entry work (gathered
-    # rows in, partial rows out), so it scales with the entries.
+    # DRAM bytes per (row, chunk) entry of the dominant kernel, from one ncu capture of this build on
+    # 32K tokens x 32 heads (profiles/main_kernels_traffic_32k.md: dram__bytes_read.sum +
+    # dram__bytes_write.sum = 4,759.1 MB over its 8,273,920 entries; the same head-by-head order of
+    # work items as the 64K workload); the traffic is per-entry work (gathered rows in, partial rows
+    # out), so it scales with the entries.
     entry_bytes = {"bwd_main": BWD_MAIN_DRAM_BYTES_PER_ENTRY}.get(dom) if (d == 128 and chunk == 128) else None
     entries = ACC.selected_entries(seqlens, chunk, topk) * h_loc / (world if by_range else 1)
     if kern_ms.get(dom):
@@ -457,7 +458,7 @@ def main():
         roof = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s",
                 "frac": ach / peak_tf, "frac_of_burst": ach / peak_burst, "frac_of_sustained": ach / peak_sust,
                 "traffic": (entry_bytes * entries if entry_bytes else None),
-                "traffic_source": "ncu dram bytes of a 16K-token case, scaled by (row, chunk) entries" if entry_bytes else None,
+                "traffic_source": "ncu dram bytes of a 32K-token x 32-head case of this build, scaled by (row, chunk) entries" if entry_bytes else None,
                 "peak_source": peak_src,
                 "launch_ms": kern_ms[dom], "flops_per_launch": dom_flops,
                 "other_kernels_ms": {k_: v_ for k_, v_ in kern_ms.items() if k_ != dom}}
