@@ -84,6 +84,9 @@ class HostPipeline:
                 res = [out.detach()]
                 if self.backward:
                     res += list(torch.autograd.grad(out, (qg, kg, vg), self.do[:, h0:h1]))
+                # results of a zero-padded head dimension (d not 64 or 128) are slices of wider rows:
+                # the strided copy wants dense (heads, d) rows
+                res = [t if t.stride(1) == t.shape[2] else t.contiguous() for t in res]
                 done.record(self.s_comp)
             self.s_out.wait_event(done)
             _copy_heads(out_h[:, h0:h1], res[0], 1, self.s_out)

@@ -12,12 +12,13 @@ sys.path.insert(0, ROOT)
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("heads,heads_k,groups,backward", [(8, 8, 4, True), (8, 2, 8, True), (6, 6, 4, False)])
-def test_pipeline_matches_resident_call(heads, heads_k, groups, backward):
+@pytest.mark.parametrize("heads,heads_k,groups,backward,d", [(8, 8, 4, True, 128), (8, 2, 8, True, 128),
+                                                             (6, 6, 4, False, 128), (4, 4, 2, True, 96)])
+def test_pipeline_matches_resident_call(heads, heads_k, groups, backward, d):
     import flash_moba_b200 as F
     from flash_moba_b200.host_pipeline import HostPipeline
     lens = [1500, 700, 300]
-    T, d, chunk, topk = sum(lens), 128, 128, 3
+    T, chunk, topk = sum(lens), 128, 3
     g = torch.Generator().manual_seed(9)
     mk = lambda h: torch.randn(T, h, d, generator=g).bfloat16().pin_memory()
     q_h, k_h, v_h, do_h = mk(heads), mk(heads_k), mk(heads_k), mk(heads)
