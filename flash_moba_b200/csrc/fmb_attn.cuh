@@ -56,6 +56,8 @@ struct PassParams {
   const uint32_t* slot_base;
   int heads, ncol, h0, nh, nsub, kb, chunk;
   int64_t cap;
+  int64_t slot_shift;   // without a slot table: slot = position in `indices` - slot_shift (the first position
+                        // of the pass's heads; single sequences only, whose heads are contiguous in `indices`)
   int* status;
 };
 struct ColRef {
@@ -72,8 +74,9 @@ __device__ __forceinline__ ColRef column_of(const PassParams& r, int b, int h, i
   if (nnz <= 0 || off < 0 || off + nnz > r.n_indices) return o;   // malformed: ignored, never read
   // no slot table: the pattern builder vouches for columns that do not overlap, and an entry's
   // slot is simply its position in `indices`
-  const int64_t slot = r.slot_base ? (int64_t)r.slot_base[((int64_t)b * r.nh + (h - r.h0)) * r.ncol + c] : off;
-  if (slot + nnz > r.cap) {          // cannot happen for a pattern whose columns do not overlap
+  const int64_t slot = r.slot_base ? (int64_t)r.slot_base[((int64_t)b * r.nh + (h - r.h0)) * r.ncol + c]
+                                   : off - r.slot_shift;
+  if (slot < 0 || slot + nnz > r.cap) {          // cannot happen for a pattern whose columns do not overlap
     atomicCAS(r.status, 0, 7);
     return o;
   }

@@ -70,6 +70,7 @@ PassParams make_pass(const AttnArgs& a, const AttnWorkspace& w, int h0, int nh) 
   r.slot_base = w.slot_base;
   r.heads = a.heads; r.ncol = a.ncol; r.h0 = h0; r.nh = nh; r.nsub = w.nsub; r.kb = w.kb; r.chunk = a.chunk;
   r.cap = w.cap; r.status = w.status;
+  r.slot_shift = w.fixed_k > 0 ? (int64_t)h0 * a.total_q * w.fixed_k : 0;
   return r;
 }
 
@@ -239,6 +240,7 @@ struct CombineParams {
   int h0, nh, nsub, d;
   int fixed_k;     // > 0: row lists handed over by the pattern builder: row `rid` owns the fixed_k places
                    // row_pos[rid*fixed_k ..], empty places hold 0xffffffff; row_ptr is not used
+  int64_t slot_shift;               // handed-over rows hold positions in `indices`: slot = position - slot_shift
   const int* status; int* mirror;   // mirror != nullptr: the first combine kernel of the call's last pass copies
                                     // the call's status word there (see attn_status_mirror)
 };
@@ -297,7 +299,7 @@ __device__ __forceinline__ void fwd_combine_body(int64_t vblock, const T* __rest
   float m = -CUDART_INF_F;
   for (int sb = 0; sb < c.nsub; ++sb)
     for (int j = lane; j < n; j += 32)
-      if (rp[j] != kNoSlot) m = fmaxf(m, part_lse[(int64_t)sb * c.cap + rp[j]]);
+      if (rp[j] != kNoSlot) m = fmaxf(m, part_lse[(int64_t)sb * c.cap + rp[j] - c.slot_shift]);
 #pragma unroll
   for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   float2 acc[4];
@@ -308,9 +310,10 @@ __device__ __forceinline__ void fwd_combine_body(int64_t vblock, const T* __rest
     for (int sb = 0; sb < c.nsub; ++sb) {
       int64_t last = -1;
       for (int r = 0; r < n; ++r) {
-        const int64_t slot = next_slot(rp, n, last, lane);
-        if (slot >= (int64_t)kNoSlot) break;     // the remaining places of the row are empty
-        last = slot;
+        const int64_t raw = next_slot(rp, n, last, lane);
+        if (raw >= (int64_t)kNoSlot) break;      // the remaining places of the row are empty
+        last = raw;
+        const int64_t slot = raw - c.slot_shift;
         const int64_t pp = (int64_t)sb * c.cap + slot;
         const float wgt = __expf(part_lse[pp] - m);
         ssum += wgt;
@@ -369,9 +372,10 @@ __device__ __forceinline__ void bwd_combine_body(int64_t vblock, const T* __rest
   for (int sb = 0; sb < c.nsub; ++sb) {
     int64_t last = -1;
     for (int r = 0; r < n; ++r) {
-      const int64_t slot = next_slot(rp, n, last, lane);
-      if (slot >= (int64_t)kNoSlot) break;       // the remaining places of the row are empty
-      last = slot;
+      const int64_t raw = next_slot(rp, n, last, lane);
+      if (raw >= (int64_t)kNoSlot) break;        // the remaining places of the row are empty
+      last = raw;
+      const int64_t slot = raw - c.slot_shift;
       const T* src = part_dq + ((int64_t)sb * c.cap + slot) * c.d;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -439,6 +443,7 @@ __device__ __forceinline__ GroupRow group_row(int64_t vblock, const CombineParam
   g.valid = gl < g.n;
   g.slot = g.valid ? c.row_pos[p0 + gl / c.nsub] : 0u;
   if (g.slot == kNoSlot) g.valid = false;      // an empty place of a handed-over row list
+  else g.slot -= (uint32_t)c.slot_shift;
   g.pos = g.valid ? (uint32_t)((gl % c.nsub) * c.cap) + g.slot : 0xffffffffu;
   return g;
 }
@@ -776,6 +781,8 @@ static CombineParams make_combine(const AttnArgs& a, const AttnWorkspace& w, con
   c.row_ptr = w.row_ptr; c.row_pos = w.row_pos; c.total_q = a.total_q; c.cap = w.cap; c.heads_out = a.heads;
   c.h0 = ps.h0; c.nh = ps.nh; c.nsub = w.nsub; c.d = a.d;
   c.fixed_k = w.fixed_k;
+  c.slot_shift = ps.slot_shift;
+  if (w.fixed_k > 0) c.row_pos = w.row_pos + (int64_t)ps.h0 * a.total_q * w.fixed_k;   // the pass's heads
   c.status = w.status;
   c.mirror = (ps.h0 + ps.nh >= a.heads) ? w.mirror : nullptr;   // the call's last pass
   return c;
@@ -960,13 +967,14 @@ static thread_local RowsTicket g_rows = {nullptr, 0, 0, 0, false};
 void attn_rows_offer(const uint32_t* row_slots, int64_t total_q, int heads, int topk) {
   g_rows = RowsTicket{row_slots, total_q, heads, topk, row_slots != nullptr && topk > 0};
 }
-// Consumes the ticket; true if this call (one pass over all heads, matching geometry) runs on it:
-// slots are positions in `indices`, the row lists are the builder's.
+// Consumes the ticket; true if this call (matching geometry; one pass over all heads, or a single
+// sequence, whose heads lie one after the other in `indices`) runs on it: slots are positions in
+// `indices` (less the pass's first), the row lists are the builder's.
 static bool take_rows(const AttnArgs& a, AttnWorkspace& w) {
   const RowsTicket t = g_rows;
   g_rows.armed = false;
   w.fixed_k = 0;
-  if (!t.armed || t.total_q != a.total_q || t.heads != a.heads || w.nh < a.heads ||
+  if (!t.armed || t.total_q != a.total_q || t.heads != a.heads || (w.nh < a.heads && a.batch != 1) ||
       (int64_t)t.total_q * t.heads * t.topk != a.n_indices || a.n_indices >= (int64_t)0xffffffffll)
     return false;
   w.fixed_k = t.topk;

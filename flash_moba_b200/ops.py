@@ -119,10 +119,10 @@ def _rows_offer(col_offsets, col_nnz, indices, total_q, h) -> bool:
 
 def _workspace(query, total_q, h, hk, d, n_indices, batch, max_seqlen_k, chunk, device):
     """Workspace for one attention call: the single-pass size if it fits the cap
-    (FMB_WORKSPACE_GB, default 24 GiB), otherwise the largest pass of whole kv-head groups that
+    (FMB_WORKSPACE_GB, default 64 GiB of the 180), otherwise the largest pass of whole kv-head groups that
     does; the library then walks the heads in passes of that size."""
     import os
-    cap = int(float(os.environ.get("FMB_WORKSPACE_GB", "24")) * (1 << 30))
+    cap = int(float(os.environ.get("FMB_WORKSPACE_GB", "64")) * (1 << 30))
     group = h // hk
     nh = h
     nbytes = query(total_q, h, hk, d, n_indices, batch, int(max_seqlen_k), int(chunk), nh)
