@@ -1,9 +1,10 @@
 // CUDA-core ("SIMT") engine of the block-sparse attention: a plain fp32-FMA implementation
-// of the key-chunk-major main kernels.  It exists to validate the tensor-core engine on the
-// GPU (same workspace contract, same combine kernels) and to serve shapes the tensor-core
-// engine does not cover.  Mathematics follows the reference kernels
-// (csrc/flash_moba/src/flash_fwd_kernel.h:535-640, flash_bwd_kernel.h:552-803,
-//  softmax.h:259-319, mask.h:139-176); the tiling is this library's own.
+// of the key-chunk-major main kernels for the same shapes as the tensor-core engine (key blocks
+// of 64 / 128 keys, head dims 64 / 128).  It is a cross-check, not a fallback: the GPU tests run
+// both engines (fmb_set_engine(0) selects this one) against the CPU oracle and against each other
+// through the same workspace contract and the same merge kernels.  Mathematics follows the
+// reference kernels (csrc/flash_moba/src/flash_fwd_kernel.h:535-640, flash_bwd_kernel.h:552-803,
+// softmax.h:259-319, mask.h:139-176); the tiling is this library's own.
 #include "fmb_attn.cuh"
 
 namespace fmb {
