@@ -69,3 +69,36 @@ def test_static_scratch_builder_rejects_oversize():
                                        torch.cuda.current_stream().cuda_stream)
     assert rc == 3
     assert b"built-in array" in _lib.lib.fmb_last_error()
+
+
+def test_static_scratch_builder_at_its_capacity():
+    """The largest problem the built-in array holds: exactly 2,097,152 counters (one sequence of
+    65,536 rows x 8 heads = 128 tiles, 2,048 columns), the last counter of the array in use.  Same
+    pattern as the workspace-taking builder, and no device memory is taken or returned by the call
+    (outputs allocated beforehand).  One column more is refused."""
+    from flash_moba_b200 import _lib, ops
+    rows, heads, topk, ncol = 65536, 8, 2, 2048
+    assert heads * (rows // 512) * ncol * 4 == 8 << 20
+    g = torch.Generator().manual_seed(21)
+    idx = torch.randint(0, ncol, (rows, heads, topk), generator=g, dtype=torch.int32)
+    idx[:, :, 1] = torch.where(idx[:, :, 1] == idx[:, :, 0], (idx[:, :, 0] + 1) % ncol, idx[:, :, 1])
+    idx = idx.cuda()
+    cu = cu_of([rows]).cuda()
+    want = ops.build_csc(idx, cu, rows, ncol)
+    col_offsets = torch.empty((1, heads, ncol), dtype=torch.int64, device="cuda")
+    col_nnz = torch.empty((1, heads, ncol), dtype=torch.int32, device="cuda")
+    indices = torch.empty((rows * heads * topk,), dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    rc = _lib.lib.fmb_build_csc_static(idx.data_ptr(), idx.stride(0), idx.stride(1), cu.data_ptr(),
+                                       col_offsets.data_ptr(), col_nnz.data_ptr(), indices.data_ptr(),
+                                       1, heads, topk, rows, ncol, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, _lib.lib.fmb_last_error()
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    for a, b in zip((col_offsets, col_nnz, indices), want):
+        assert torch.equal(a, b)
+    rc = _lib.lib.fmb_build_csc_static(idx.data_ptr(), idx.stride(0), idx.stride(1), cu.data_ptr(),
+                                       col_offsets.data_ptr(), col_nnz.data_ptr(), indices.data_ptr(),
+                                       1, heads, topk, rows, ncol + 1, torch.cuda.current_stream().cuda_stream)
+    assert rc == 3
