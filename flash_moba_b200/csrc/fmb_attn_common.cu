@@ -17,7 +17,9 @@ static size_t layout(AttnWorkspace& w, void* base, const AttnArgs& a, size_t par
   w.nh = nh;
   w.fixed_k = 0;
   w.mirror = nullptr;
-  w.kb = (a.chunk % 128 == 0) ? 128 : 64;
+  // key block: 128 keys when the chunk is a multiple of 128; head dims above 128 always take 64-key
+  // blocks (the CUDA-core kernels that serve them hold K, V and the row tiles in shared memory)
+  w.kb = (a.chunk % 128 == 0 && a.d <= 128) ? 128 : 64;
   w.nsub = a.chunk / w.kb;
   // one pass over all heads can never need more slots than the pattern has entries; a pass over a
   // share of the heads is given that share (exact for the top-k packing), rounded up

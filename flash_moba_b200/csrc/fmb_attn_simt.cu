@@ -1,15 +1,19 @@
 // CUDA-core ("SIMT") engine of the block-sparse attention: a plain fp32-FMA implementation
-// of the key-chunk-major main kernels for the same shapes as the tensor-core engine (key blocks
-// of 64 / 128 keys, head dims 64 / 128).  It is a cross-check, not a fallback: the GPU tests run
-// both engines (fmb_set_engine(0) selects this one) against the CPU oracle and against each other
-// through the same workspace contract and the same merge kernels.  Mathematics follows the
+// of the key-chunk-major main kernels.  Two uses.  (1) Head dims above 128 (192 and 256; the
+// host pads 160 and 224 up to them): the tensor-core kernels keep dK and dV of one key block in
+// the SM's 512 TMEM columns, which d = 128 already fills, so these head dims run here, on key
+// blocks of 64 keys (forward tiles of 64 rows, backward tiles of 32).  (2) A cross-check of the
+// tensor-core engine at its own shapes (key blocks of 64 / 128 keys, head dims 64 / 128): the GPU
+// tests run both engines (fmb_set_engine(0) selects this one) against the CPU oracle and against
+// each other through the same workspace contract and the same merge kernels.  Mathematics follows the
 // reference kernels (csrc/flash_moba/src/flash_fwd_kernel.h:535-640, flash_bwd_kernel.h:552-803,
 // softmax.h:259-319, mask.h:139-176); the tiling is this library's own.
 #include "fmb_attn.cuh"
 
 namespace fmb {
 
-constexpr int kSimtM = 64;          // gathered query rows per tile
+// gathered query rows per tile: 16 row groups x M/16 rows per thread (M = 64, or 32 where the
+// backward's tiles would not fit in shared memory otherwise)
 constexpr int kSimtThreads = 256;
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -26,25 +30,25 @@ struct SimtParams {
 };
 
 // stage `rows_valid` gathered rows (ids in sRow, -1 = padding) transposed: dst[dd][m]
-template <typename T, int D>
+template <typename T, int D, int M>
 __device__ __forceinline__ void stage_rows_transposed(T* dst, const T* base, int64_t row_stride,
                                                       const int* sRow, int rows_valid) {
   constexpr int G = D / 8;
-  for (int e = threadIdx.x; e < kSimtM * G; e += blockDim.x) {
-    const int r = e % kSimtM, g = e / kSimtM;
+  for (int e = threadIdx.x; e < M * G; e += blockDim.x) {
+    const int r = e % M, g = e / M;
     uint4 u = make_uint4(0, 0, 0, 0);
     if (r < rows_valid && sRow[r] >= 0) u = ldg_nc_16(base + (int64_t)sRow[r] * row_stride + g * 8);
     const T* x = reinterpret_cast<const T*>(&u);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) dst[(g * 8 + i) * kSimtM + r] = x[i];
+    for (int i = 0; i < 8; ++i) dst[(g * 8 + i) * M + r] = x[i];
   }
 }
 // natural layout dst[m][D]
-template <typename T, int D>
+template <typename T, int D, int M>
 __device__ __forceinline__ void stage_rows(T* dst, const T* base, int64_t row_stride, const int* sRow,
                                            int rows_valid) {
   constexpr int G = D / 8;
-  for (int e = threadIdx.x; e < kSimtM * G; e += blockDim.x) {
+  for (int e = threadIdx.x; e < M * G; e += blockDim.x) {
     const int r = e / G, g = e % G;
     uint4 u = make_uint4(0, 0, 0, 0);
     if (r < rows_valid && sRow[r] >= 0) u = ldg_nc_16(base + (int64_t)sRow[r] * row_stride + g * 8);
@@ -68,36 +72,36 @@ __device__ __forceinline__ void stage_keys(T* dst, T* dstT, const T* base, int64
   }
 }
 
-// acc[4][C/16] += At^T Bt : rows ty*4.., cols tx*(C/16)..   (At [D][64], Bt [D][C])
-template <typename T, int C, int D>
-__device__ __forceinline__ void gemm_rows_keys(const T* At, const T* Bt, float (&acc)[4][C / 16]) {
-  constexpr int TN = C / 16;
+// acc[M/16][C/16] += At^T Bt : rows ty*(M/16).., cols tx*(C/16)..   (At [D][M], Bt [D][C])
+template <typename T, int C, int D, int M>
+__device__ __forceinline__ void gemm_rows_keys(const T* At, const T* Bt, float (&acc)[M / 16][C / 16]) {
+  constexpr int TN = C / 16, RM = M / 16;
   const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
 #pragma unroll 4
   for (int dd = 0; dd < D; ++dd) {
-    float a[4], b[TN];
+    float a[RM], b[TN];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) a[i] = Elem<T>::to_f(At[dd * kSimtM + ty * 4 + i]);
+    for (int i = 0; i < RM; ++i) a[i] = Elem<T>::to_f(At[dd * M + ty * RM + i]);
 #pragma unroll
     for (int j = 0; j < TN; ++j) b[j] = Elem<T>::to_f(Bt[dd * C + tx * TN + j]);
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < RM; ++i)
 #pragma unroll
       for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
   }
 }
 
 // ======================================================================== forward
-template <typename T, int C, int D>
+template <typename T, int C, int D, int M>
 __global__ void __launch_bounds__(kSimtThreads) fwd_main_simt_kernel(SimtParams p) {
-  constexpr int TN = C / 16, TD = D / 16, SS = C + 4;
+  constexpr int TN = C / 16, TD = D / 16, SS = C + 4, RM = M / 16;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* sKt = reinterpret_cast<T*>(smem_raw);          // [D][C]
   T* sV = sKt + D * C;                              // [C][D]
-  T* sQt = sV + C * D;                              // [D][64]
-  float* sS = reinterpret_cast<float*>(sQt + D * kSimtM);   // [64][C+4]
-  int* sRow = reinterpret_cast<int*>(sS + kSimtM * SS);     // [64]
-  float* sInv = reinterpret_cast<float*>(sRow + kSimtM);    // [64]
+  T* sQt = sV + C * D;                              // [D][M]
+  float* sS = reinterpret_cast<float*>(sQt + D * M);   // [M][C+4]
+  int* sRow = reinterpret_cast<int*>(sS + M * SS);     // [M]
+  float* sInv = reinterpret_cast<float*>(sRow + M);    // [M]
 
   // C is the key block: chunk c of the pattern is covered by nsub blocks of C keys
   const int c = blockIdx.x / p.ps.nsub, sb = blockIdx.x % p.ps.nsub, h = p.ps.h0 + blockIdx.y, b = blockIdx.z;
@@ -123,10 +127,10 @@ __global__ void __launch_bounds__(kSimtThreads) fwd_main_simt_kernel(SimtParams 
   stage_keys<T, C, D>(sV, nullptr, vbase, p.v_rs, keys_valid);
   T* part_o = static_cast<T*>(p.part_o);
 
-  for (int t0 = 0; t0 < nnz; t0 += kSimtM) {
-    const int rows = min(kSimtM, nnz - t0);
+  for (int t0 = 0; t0 < nnz; t0 += M) {
+    const int rows = min(M, nnz - t0);
     __syncthreads();
-    if (threadIdx.x < kSimtM) {
+    if (threadIdx.x < M) {
       int r = -1;
       if (threadIdx.x < rows) {
         r = p.ps.indices[off + t0 + threadIdx.x];
@@ -135,22 +139,22 @@ __global__ void __launch_bounds__(kSimtThreads) fwd_main_simt_kernel(SimtParams 
       sRow[threadIdx.x] = r;
     }
     __syncthreads();
-    stage_rows_transposed<T, D>(sQt, qbase, p.q_rs, sRow, rows);
+    stage_rows_transposed<T, D, M>(sQt, qbase, p.q_rs, sRow, rows);
     __syncthreads();
-    float acc[4][TN];
+    float acc[RM][TN];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < RM; ++i)
 #pragma unroll
       for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
-    gemm_rows_keys<T, C, D>(sQt, sKt, acc);
+    gemm_rows_keys<T, C, D, M>(sQt, sKt, acc);
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < RM; ++i)
 #pragma unroll
-      for (int j = 0; j < TN; ++j) sS[(ty * 4 + i) * SS + tx * TN + j] = acc[i][j];
+      for (int j = 0; j < TN; ++j) sS[(ty * RM + i) * SS + tx * TN + j] = acc[i][j];
     __syncthreads();
-    // chunk-local softmax: warp w owns rows w*8..w*8+7
-    for (int rr = 0; rr < 8; ++rr) {
-      const int m = warp * 8 + rr;
+    // chunk-local softmax: warp w owns rows w*(M/8)..
+    for (int rr = 0; rr < M / 8; ++rr) {
+      const int m = warp * (M / 8) + rr;
       const int r = sRow[m];
       const int lim = p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid;  // visible keys: j < lim
       float mx = -CUDART_INF_F;
@@ -176,25 +180,25 @@ __global__ void __launch_bounds__(kSimtThreads) fwd_main_simt_kernel(SimtParams 
     }
     __syncthreads();
     // partial O = P.V / l
-    float o[4][TD];
+    float o[RM][TD];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < RM; ++i)
 #pragma unroll
       for (int j = 0; j < TD; ++j) o[i][j] = 0.f;
     for (int j = 0; j < C; ++j) {
-      float pr[4], vv[TD];
+      float pr[RM], vv[TD];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) pr[i] = sS[(ty * 4 + i) * SS + j];
+      for (int i = 0; i < RM; ++i) pr[i] = sS[(ty * RM + i) * SS + j];
 #pragma unroll
       for (int x = 0; x < TD; ++x) vv[x] = Elem<T>::to_f(sV[j * D + tx * TD + x]);
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < RM; ++i)
 #pragma unroll
         for (int x = 0; x < TD; ++x) o[i][x] = fmaf(pr[i], vv[x], o[i][x]);
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int m = ty * 4 + i;
+    for (int i = 0; i < RM; ++i) {
+      const int m = ty * RM + i;
       if (m < rows) {
         const float inv = sInv[m];
         const int64_t slot = slot0 + t0 + m;
@@ -207,22 +211,22 @@ __global__ void __launch_bounds__(kSimtThreads) fwd_main_simt_kernel(SimtParams 
 }
 
 // ======================================================================== backward
-template <typename T, int C, int D>
+template <typename T, int C, int D, int M>
 __global__ void __launch_bounds__(kSimtThreads) bwd_main_simt_kernel(SimtParams p) {
-  constexpr int TN = C / 16, TD = D / 16, SS = C + 4;
+  constexpr int TN = C / 16, TD = D / 16, SS = C + 4, RM = M / 16;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* sKt = reinterpret_cast<T*>(smem_raw);          // [D][C]
   T* sVt = sKt + D * C;                             // [D][C]
   T* sK = sVt + D * C;                              // [C][D]
-  T* sQt = sK + C * D;                              // [D][64]
-  T* sdOt = sQt + D * kSimtM;                       // [D][64]
-  T* sQ = sdOt + D * kSimtM;                        // [64][D]
-  T* sdO = sQ + kSimtM * D;                         // [64][D]
-  float* sP = reinterpret_cast<float*>(sdO + kSimtM * D);   // [64][C+4]
-  float* sdS = sP + kSimtM * SS;                            // [64][C+4]
-  int* sRow = reinterpret_cast<int*>(sdS + kSimtM * SS);    // [64]
-  float* sLse = reinterpret_cast<float*>(sRow + kSimtM);    // [64]
-  float* sD = sLse + kSimtM;                                // [64]
+  T* sQt = sK + C * D;                              // [D][M]
+  T* sdOt = sQt + D * M;                       // [D][M]
+  T* sQ = sdOt + D * M;                        // [M][D]
+  T* sdO = sQ + M * D;                         // [M][D]
+  float* sP = reinterpret_cast<float*>(sdO + M * D);   // [M][C+4]
+  float* sdS = sP + M * SS;                            // [M][C+4]
+  int* sRow = reinterpret_cast<int*>(sdS + M * SS);    // [M]
+  float* sLse = reinterpret_cast<float*>(sRow + M);    // [M]
+  float* sD = sLse + M;                                // [M]
 
   const int group = p.heads / p.heads_k;
   const int c = blockIdx.x / p.ps.nsub, sb = blockIdx.x % p.ps.nsub, hk = p.ps.h0 / group + blockIdx.y, b = blockIdx.z;
@@ -263,10 +267,10 @@ __global__ void __launch_bounds__(kSimtThreads) bwd_main_simt_kernel(SimtParams 
     const float* lse = p.lse + (int64_t)h * p.total_q + q0;
     const float* dsum = p.softmax_d + (int64_t)h * p.total_q + q0;
 
-    for (int t0 = 0; t0 < nnz; t0 += kSimtM) {
-      const int rows = min(kSimtM, nnz - t0);
+    for (int t0 = 0; t0 < nnz; t0 += M) {
+      const int rows = min(M, nnz - t0);
       __syncthreads();
-      if (threadIdx.x < kSimtM) {
+      if (threadIdx.x < M) {
         int r = -1;
         float l = CUDART_INF_F, dd = 0.f;
         if (threadIdx.x < rows) {
@@ -277,22 +281,22 @@ __global__ void __launch_bounds__(kSimtThreads) bwd_main_simt_kernel(SimtParams 
         sRow[threadIdx.x] = r; sLse[threadIdx.x] = l; sD[threadIdx.x] = dd;
       }
       __syncthreads();
-      stage_rows_transposed<T, D>(sQt, qbase, p.q_rs, sRow, rows);
-      stage_rows_transposed<T, D>(sdOt, dobase, p.do_rs, sRow, rows);
-      stage_rows<T, D>(sQ, qbase, p.q_rs, sRow, rows);
-      stage_rows<T, D>(sdO, dobase, p.do_rs, sRow, rows);
+      stage_rows_transposed<T, D, M>(sQt, qbase, p.q_rs, sRow, rows);
+      stage_rows_transposed<T, D, M>(sdOt, dobase, p.do_rs, sRow, rows);
+      stage_rows<T, D, M>(sQ, qbase, p.q_rs, sRow, rows);
+      stage_rows<T, D, M>(sdO, dobase, p.do_rs, sRow, rows);
       __syncthreads();
       {
-        float s[4][TN], dp[4][TN];
+        float s[RM][TN], dp[RM][TN];
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < RM; ++i)
 #pragma unroll
           for (int j = 0; j < TN; ++j) { s[i][j] = 0.f; dp[i][j] = 0.f; }
-        gemm_rows_keys<T, C, D>(sQt, sKt, s);
-        gemm_rows_keys<T, C, D>(sdOt, sVt, dp);
+        gemm_rows_keys<T, C, D, M>(sQt, sKt, s);
+        gemm_rows_keys<T, C, D, M>(sdOt, sVt, dp);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int m = ty * 4 + i;
+        for (int i = 0; i < RM; ++i) {
+          const int m = ty * RM + i;
           const int r = sRow[m];
           const int lim = p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid;
           const float l2 = sLse[m] * kLog2e, dd = sD[m];
@@ -308,7 +312,7 @@ __global__ void __launch_bounds__(kSimtThreads) bwd_main_simt_kernel(SimtParams 
       }
       __syncthreads();
       // dV += P^T dO ; dK += dS^T Q        (keys ty*TN.., dims tx*TD..)
-      for (int m = 0; m < kSimtM; ++m) {
+      for (int m = 0; m < M; ++m) {
         float pv[TN], ds[TN], dov[TD], qv[TD];
 #pragma unroll
         for (int i = 0; i < TN; ++i) { pv[i] = sP[m * SS + ty * TN + i]; ds[i] = sdS[m * SS + ty * TN + i]; }
@@ -327,25 +331,25 @@ __global__ void __launch_bounds__(kSimtThreads) bwd_main_simt_kernel(SimtParams 
       }
       // partial dQ = dS . K  (rows ty*4.., dims tx*TD..), unscaled
       {
-        float dq[4][TD];
+        float dq[RM][TD];
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < RM; ++i)
 #pragma unroll
           for (int j = 0; j < TD; ++j) dq[i][j] = 0.f;
         for (int key = 0; key < C; ++key) {
-          float ds[4], kv[TD];
+          float ds[RM], kv[TD];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) ds[i] = sdS[(ty * 4 + i) * SS + key];
+          for (int i = 0; i < RM; ++i) ds[i] = sdS[(ty * RM + i) * SS + key];
 #pragma unroll
           for (int j = 0; j < TD; ++j) kv[j] = Elem<T>::to_f(sK[key * D + tx * TD + j]);
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
+          for (int i = 0; i < RM; ++i)
 #pragma unroll
             for (int j = 0; j < TD; ++j) dq[i][j] = fmaf(ds[i], kv[j], dq[i][j]);
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int m = ty * 4 + i;
+        for (int i = 0; i < RM; ++i) {
+          const int m = ty * RM + i;
           if (m < rows) {
             const int64_t slot = slot0 + t0 + m;
             T* dst = part_dq + (plane + slot) * D;
@@ -389,8 +393,9 @@ static SimtParams make_params(const AttnArgs& a, const AttnWorkspace& w, const P
 template <typename T, int C, int D>
 static int fwd_launch(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   SimtParams p = make_params(a, w, ps);
-  const size_t smem = (size_t)(2 * C * D + D * kSimtM) * sizeof(T) + (size_t)kSimtM * (C + 4) * 4 + kSimtM * 8;
-  auto kern = fwd_main_simt_kernel<T, C, D>;
+  constexpr int M = 64;
+  const size_t smem = (size_t)(2 * C * D + D * M) * sizeof(T) + (size_t)M * (C + 4) * 4 + M * 8;
+  auto kern = fwd_main_simt_kernel<T, C, D, M>;
   FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<dim3(a.ncol * ps.nsub, ps.nh, a.batch), kSimtThreads, smem, s>>>(p);
   FMB_LAUNCH_CHECK("fwd_main_simt_kernel");
@@ -399,9 +404,10 @@ static int fwd_launch(const AttnArgs& a, const AttnWorkspace& w, const PassParam
 template <typename T, int C, int D>
 static int bwd_launch(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   SimtParams p = make_params(a, w, ps);
-  const size_t smem = (size_t)(3 * C * D + 4 * D * kSimtM) * sizeof(T) + (size_t)2 * kSimtM * (C + 4) * 4 +
-                      kSimtM * 12;
-  auto kern = bwd_main_simt_kernel<T, C, D>;
+  constexpr int M = D > 128 ? 32 : 64;    // 64-row tiles of d = 256 would need 264 KB of shared memory
+  const size_t smem = (size_t)(3 * C * D + 4 * D * M) * sizeof(T) + (size_t)2 * M * (C + 4) * 4 +
+                      M * 12;
+  auto kern = bwd_main_simt_kernel<T, C, D, M>;
   FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int nchunk = max(a.ncol, ceil_div(a.max_k, a.chunk));
   kern<<<dim3(nchunk * ps.nsub, ps.nh / (a.heads / a.heads_k), a.batch), kSimtThreads, smem, s>>>(p);
@@ -415,14 +421,18 @@ static int bwd_launch(const AttnArgs& a, const AttnWorkspace& w, const PassParam
     if (w.kb == 64 && a.d == 128) return FN<__nv_bfloat16, 64, 128>(a, w, ps, s);           \
     if (w.kb == 128 && a.d == 64) return FN<__nv_bfloat16, 128, 64>(a, w, ps, s);           \
     if (w.kb == 128 && a.d == 128) return FN<__nv_bfloat16, 128, 128>(a, w, ps, s);         \
+    if (w.kb == 64 && a.d == 192) return FN<__nv_bfloat16, 64, 192>(a, w, ps, s);           \
+    if (w.kb == 64 && a.d == 256) return FN<__nv_bfloat16, 64, 256>(a, w, ps, s);           \
   } else {                                                                                  \
     if (w.kb == 64 && a.d == 64) return FN<__half, 64, 64>(a, w, ps, s);                    \
     if (w.kb == 64 && a.d == 128) return FN<__half, 64, 128>(a, w, ps, s);                  \
     if (w.kb == 128 && a.d == 64) return FN<__half, 128, 64>(a, w, ps, s);                  \
     if (w.kb == 128 && a.d == 128) return FN<__half, 128, 128>(a, w, ps, s);                \
+    if (w.kb == 64 && a.d == 192) return FN<__half, 64, 192>(a, w, ps, s);                  \
+    if (w.kb == 64 && a.d == 256) return FN<__half, 64, 256>(a, w, ps, s);                  \
   }                                                                                         \
   return fail(FMB_ERR_UNSUPPORTED, "attention (CUDA-core engine): head_dim %d not built "  \
-              "(head_dim in {64,128})", a.d);
+              "(head_dim in {64,128,192,256})", a.d);
 
 int launch_fwd_main_simt(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   if (a.ncol == 0 || a.batch == 0 || a.heads == 0) return FMB_OK;

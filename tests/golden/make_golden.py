@@ -116,6 +116,7 @@ def make_attn(utils, out):
         ([130, 64], [130, 64], 4, 4, 64, 64, 3, True),
         ([200, 77], [200, 77], 4, 2, 32, 64, 2, False),
         ([50, 128], [190, 128], 2, 1, 64, 64, 2, True),    # len_q < len_k, bottom-right causal
+        ([140, 64], [140, 64], 2, 1, 160, 64, 2, True),    # a head dim above 128 (tests/test_moba_attn.py:48)
     ]
     for i, (lq, lk, H, Hk, d, c, kk, causal) in enumerate(cases):
         torch.manual_seed(300 + i)

@@ -234,7 +234,7 @@ def _attn_check(q, k, v, do, cq, ck, mask, chunk, causal, engine, pattern=None, 
 
 
 @pytest.mark.parametrize("engine", [0, 1])
-@pytest.mark.parametrize("case", [0, 1, 2])
+@pytest.mark.parametrize("case", [0, 1, 2, 3])
 def test_attention_golden_patterns(case, engine):
     g = load_golden("attn")
     i = case
@@ -249,8 +249,6 @@ def test_attention_golden_patterns(case, engine):
     q, k, v, do = unpad(q, lq), unpad(k, lk), unpad(v, lk), unpad(do, lq)
     mask = torch.from_numpy(g[f"attn{i}_mask"])
     pattern = tuple(torch.from_numpy(g[f"attn{i}_{n}"]) for n in ("col_offsets", "col_nnz", "indices"))
-    if d > 128:
-        pytest.skip("head_dim above 128 is not built")
     _attn_check(q, k, v, do, cu_of(lq), cu_of(lk), mask, c, bool(causal), engine, pattern=pattern)
     # the reference's golden outputs themselves
     import flash_moba_b200 as F
@@ -440,6 +438,27 @@ def test_attention_head_dims_padded_to_64_or_128(d):
     _attn_check(q, k, v, do, cq, cq, mask, chunk, True, 1, pattern=(co, cn, ind))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d,chunk,causal,hk", [(160, 64, True, 2), (192, 128, True, 4), (224, 128, False, 1),
+                                               (256, 64, True, 1), (256, 256, True, 4), (136, 192, True, 2)])
+def test_attention_head_dims_above_128(d, chunk, causal, hk, dtype):
+    """Head dimensions above 128 (the reference dispatches up to 256 and tests 160,
+    tests/test_moba_attn.py:48): run on the CUDA-core kernels at 192 / 256, zero-padded where they
+    fall between; ragged sequences, len_q != len_k, GQA / MQA, chunks of 1 to 4 key blocks."""
+    torch.manual_seed(d + chunk)
+    lens_q, lens_k = [190, 77, 300], [250, 77, 300]
+    H = 4
+    q = torch.randn(sum(lens_q), H, d).to(dtype)
+    k = torch.randn(sum(lens_k), hk, d).to(dtype)
+    v = torch.randn(sum(lens_k), hk, d).to(dtype)
+    do = torch.randn(sum(lens_q), H, d).to(dtype)
+    cq, ck = cu_of(lens_q), cu_of(lens_k)
+    mask = _random_mask(lens_q, lens_k, H, chunk, causal, 3, seed=d)
+    from flash_moba_b200 import _lib
+    assert _lib.lib.fmb_attn_engine(chunk, 256 if d > 192 else 192, 0) == 0     # not the tensor-core engine
+    _attn_check(q, k, v, do, cq, ck, mask, chunk, causal, 1)
+
+
 # ----------------------------------------------------------------------------- whole path
 def test_c1_end_to_end():
     """The reference's CPU-runnable configuration (sequences of 1024 and 2048 tokens, 8 heads, d 64, chunk 128, top-k 4) through the public API: top-k indices against the reference's
@@ -577,6 +596,41 @@ def test_determinism_and_autograd_through_public_api():
         res.append((out.detach().clone(), *[x.clone() for x in grads]))
     for a, b in zip(*res):
         assert torch.equal(a, b)          # bit-identical run to run (no floating-point atomics)
+
+
+def test_public_api_at_head_dim_160():
+    """The whole path (pool, gating, pattern, attention forward and backward) at a head dimension
+    above 128, through the fused public function: the pattern against the oracle on the same
+    inputs, O and the gradients against the dense fp32 evaluation of that pattern; two runs
+    bit-identical; in passes over 2 heads as well."""
+    import flash_moba_b200 as F
+    torch.manual_seed(5)
+    lens = [700, 333]
+    T, H, Hk, d, c, kk = sum(lens), 4, 2, 160, 128, 3
+    q, k, v, do = [torch.randn(T, h, d).bfloat16() for h in (H, Hk, Hk, H)]
+    cs = cu_of(lens)
+    co, cn, ind = F.flash_topk_varlen_func(q.to(DEV), k.to(DEV), cs.to(DEV), cs.to(DEV), max(lens), max(lens), kk, c,
+                                           causal=True)
+    idx_ref, co_ref, cn_ref, ind_ref = O.moba_pattern(q.float(), k.float(), cs, cs, max(lens), kk, c, True)
+    mine = O.csc_to_mask(co.cpu(), cn.cpu(), ind.cpu(), cs, max(lens))
+    want = O.csc_to_mask(co_ref, cn_ref, ind_ref, cs, max(lens))
+    assert (mine != want).float().mean().item() < 0.005 * kk / mine.shape[-1] * 2   # < 0.5 % of the selections
+    res = []
+    for _ in range(2):
+        qd, kd, vd = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+        out = F.flash_moba_varlen_func(qd, kd, vd, cs.to(DEV), cs.to(DEV), max(lens), max(lens), c, kk, causal=True)
+        res.append((out.detach(), *torch.autograd.grad(out, (qd, kd, vd), do.to(DEV))))
+    for a, b in zip(*res):
+        assert torch.equal(a, b)
+    refs = {}
+    for tag, lowp in (("fp32", False), ("lowp", True)):
+        qq, kk_, vv = [t.clone().requires_grad_(True) for t in (q, k, v)]
+        o, _ = O.attention_dense(qq, kk_, vv, cs, cs, mine, c, True, lowp=lowp)
+        refs[tag] = (o.detach().float(), *[g.float() for g in torch.autograd.grad(o, (qq, kk_, vv), do)])
+    for j, bar in ((0, 2), (1, 3), (2, 3), (3, 3)):
+        e_pt = (refs["lowp"][j] - refs["fp32"][j]).abs().max().item()
+        e = (res[0][j].cpu().float() - refs["fp32"][j]).abs().max().item()
+        assert e <= bar * e_pt + 1e-4, (j, e, e_pt)
 
 
 def test_reference_argument_checks():

@@ -43,7 +43,7 @@ def test_gate_topk_and_csc_match_reference():
         assert int(mask.sum()) == int(cn.sum())
 
 
-@pytest.mark.parametrize("case", [0, 1, 2])
+@pytest.mark.parametrize("case", [0, 1, 2, 3])
 def test_attention_matches_reference(case):
     g = load_golden("attn")
     i = case
