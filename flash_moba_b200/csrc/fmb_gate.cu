@@ -619,10 +619,7 @@ template <typename T, int D>
 static int gate_tc_pick(const GateParams& p, int batch, int max_q, cudaStream_t s) {
   // threads per row (each scans its share of a tile's columns with its own list, merged at the
   // end).  Measured at 64K tokens, top-k 8: 1.77 ms with one, 1.67 ms with two, 2.68 ms with four.
-#ifndef FMB_GATE_NQ
-#define FMB_GATE_NQ 2
-#endif
-  if (p.topk <= 8) return gate_tc_launch<T, D, 8, FMB_GATE_NQ>(p, batch, max_q, s);
+  if (p.topk <= 8) return gate_tc_launch<T, D, 8, 2>(p, batch, max_q, s);
   if (p.topk <= 16) return gate_tc_launch<T, D, 16, 1>(p, batch, max_q, s);
   return gate_tc_launch<T, D, 32, 1>(p, batch, max_q, s);
 }
