@@ -14,7 +14,10 @@ value   : device-timed, inputs resident in HBM.   e2e: the same through the publ
 N > 1   : query heads are split across ranks (no collective on the data path); value is the
           whole job's FLOPs / max-over-ranks time ("strong": the 64K problem is fixed).
 --impl reference : the reference's pure-PyTorch MoBA restated in oracle/ (the reference has
-          no CPU build of its CUDA path), timed on the host cores over a bounded sample.
+          no CPU build of its CUDA path), timed on the host cores over a bounded sample; that is the
+          line's value.  Where oracle/build_ref.sh has built the reference's own CUDA extension for
+          sm_100 (oracle/_ref/), the line also carries "reference_cuda": those kernels on the full
+          workload on this GPU (1-GPU runs).
 """
 import argparse
 import json
@@ -221,6 +224,71 @@ def config_of(wl, seqlens, H, Hk, d, chunk, topk, backward):
             "topk": topk, "causal": True, "step": "pattern(pool+gate+csc) + fwd" + (" + bwd" if backward else "")}
 
 
+def reference_cuda_leg(seqlens, H, Hk, d, chunk, topk, backward, scale, steps):
+    """The reference's own CUDA extension (built for sm_100 from its sources by oracle/build_ref.sh,
+    present as oracle/_ref/flash_moba_cuda.so) on the full workload on this GPU: gating top-k +
+    column sort, forward, backward, each timed with CUDA events.  The reference's mean pool is a
+    Triton kernel of its Python package, not part of the extension: the centroids are made with
+    plain torch outside the timed region.  None when the extension or a GPU is missing."""
+    from oracle import ref_cuda
+    if not ref_cuda.available() or not torch.cuda.is_available():
+        return None
+    try:
+        torch.manual_seed(0)
+        T, S = sum(seqlens), max(seqlens)
+        dev = "cuda"
+        q = (torch.randn(T, H, d, device=dev) * scale).bfloat16()
+        k = (torch.randn(T, Hk, d, device=dev) * scale).bfloat16()
+        v = (torch.randn(T, Hk, d, device=dev) * scale).bfloat16()
+        do = torch.randn(T, H, d, device=dev).bfloat16()
+        cu = [0]
+        for n in seqlens:
+            cu.append(cu[-1] + n)
+        cs = torch.tensor(cu, dtype=torch.int32, device=dev)
+        cm = [0]
+        pooled = []
+        for b, n in enumerate(seqlens):      # per-chunk means, the last chunk over its true length
+            kb = k[cu[b]:cu[b + 1]].float()
+            full = n // chunk
+            if full:
+                pooled.append(kb[:full * chunk].view(full, chunk, Hk, d).mean(1))
+            if n % chunk:
+                pooled.append(kb[full * chunk:].mean(0, keepdim=True))
+            cm.append(cm[-1] + (n + chunk - 1) // chunk)
+        km = torch.cat(pooled, 0).bfloat16().contiguous()
+        cu_km = torch.tensor(cm, dtype=torch.int32, device=dev)
+        from flash_moba_b200.interface import decide_lg_block_m     # the reference's own table of five thresholds
+        lg_m = decide_lg_block_m(topk, chunk, S, True)
+        sm_scale = d ** -0.5
+
+        def timed(fn):
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / steps
+
+        pat = ref_cuda.fused_topk(q, km, cs, cs, cu_km, S, S, topk, chunk, True)
+        out, lse = ref_cuda.attn_fwd(q, k, v, cs, cs, S, S, *pat, lg_m, chunk, sm_scale)
+        ms = {"topk_and_sort": timed(lambda: ref_cuda.fused_topk(q, km, cs, cs, cu_km, S, S, topk, chunk, True)),
+              "fwd": timed(lambda: ref_cuda.attn_fwd(q, k, v, cs, cs, S, S, *pat, lg_m, chunk, sm_scale))}
+        if backward:
+            ms["bwd"] = timed(lambda: ref_cuda.attn_bwd(do, q, k, v, out, lse, cs, cs, S, S, *pat, lg_m, chunk, sm_scale))
+        fwd, bwd, both = ACC.attention_flops(seqlens, H, d, chunk, topk)
+        total = sum(ms.values())
+        return {"ms_per_step": total, "ms": ms, "value": (both if backward else fwd) / total / 1e9, "unit": "TFLOP/s",
+                "lg_block_m": lg_m, "steps": steps,
+                "what": "the reference's CUDA extension compiled for sm_100 (its own sources, trimmed to the head-dim 64/128 "
+                        "bf16 causal instantiations), same workload on this GPU, inputs resident; its Triton mean pool is not timed"}
+    except Exception as e:      # reported, never fatal: the line's own numbers do not depend on it
+        return {"error": repr(e)[:300]}
+
+
 def run_reference(args, wl):
     seqlens, H, Hk, d, chunk, topk, backward, scale = workload_of(args)
     rank = int(os.environ.get("RANK", "0"))
@@ -245,6 +313,8 @@ def run_reference(args, wl):
                                    "fp32 PyTorch oracle (oracle/moba_oracle.py), per step"},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+    if args.gpus == 1 and not args.no_reference_cuda:
+        line["reference_cuda"] = reference_cuda_leg(seqlens, H, Hk, d, chunk, topk, backward, scale, max(1, min(args.steps, 5)))
     emit(json.dumps(line))
 
 
@@ -282,6 +352,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="single-sequence workloads: this many tokens instead")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-reference-cuda", action="store_true",
+                    help="--impl reference: do not also time the reference's CUDA extension (oracle/_ref) on the GPU")
     ap.add_argument("--e2e-groups", type=int, default=8, help="head groups of the host pipeline")
     ap.add_argument("--engine", type=int, default=1)
     ap.add_argument("--shard", default="heads", choices=["heads", "query-range"],
