@@ -111,7 +111,7 @@ int fmb_attn_engine(int chunk, int head_dim, int backward) {
   memset(&a, 0, sizeof(a));
   a.chunk = chunk; a.d = head_dim; a.heads = 1;
   a.q_rs = a.do_rs = head_dim; a.q_hs = a.do_hs = head_dim;   // a packed layout
-  return (g_engine == 1 && tc_supported(a, backward != 0)) ? 1 : 0;
+  return (g_engine == 1 && (tc_supported(a, backward != 0) || tc_wide_supported(a, backward != 0))) ? 1 : 0;
 }
 
 int fmb_selftest_umma(const void* a, const void* b, float* d, int b_mn_major, int dtype, int* status,

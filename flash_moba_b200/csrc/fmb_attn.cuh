@@ -143,6 +143,10 @@ int launch_bwd_main_simt(const AttnArgs& a, const AttnWorkspace& w, const PassPa
 int launch_fwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s);
 int launch_bwd_main_tc(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s);
 bool tc_supported(const AttnArgs& a, bool backward);
+// tcgen05 kernels for head dims 192 and 256 (fmb_attn_tc_wide.cu)
+int launch_fwd_main_tc_wide(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s);
+int launch_bwd_main_tc_wide(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s);
+bool tc_wide_supported(const AttnArgs& a, bool backward);
 int sm_count();   // SMs of the current device
 int launch_selftest_wait_expiry(int* status, unsigned long long* elapsed_ns, cudaStream_t s);
 int launch_selftest_umma(const void* a, const void* b, float* d, int b_mn_major, int dtype, int* status,

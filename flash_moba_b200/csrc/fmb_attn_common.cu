@@ -1006,6 +1006,7 @@ int launch_attn_fwd(const AttnArgs& a, int engine, cudaStream_t s) {
     if (!rows_given && (rc = build_row_lists(a, w, ps, s))) return rc;
     prof_begin(0, s);
     if (engine == 1 && tc_supported(a, false)) rc = launch_fwd_main_tc(a, w, ps, s);
+    else if (engine == 1 && tc_wide_supported(a, false)) rc = launch_fwd_main_tc_wide(a, w, ps, s);
     else rc = launch_fwd_main_simt(a, w, ps, s);
     prof_end(0, s);
     if (rc) return rc;
@@ -1069,6 +1070,7 @@ int launch_attn_bwd(const AttnArgs& a, int engine, cudaStream_t s) {
     if (!lists_given && !rows_given && (rc = build_row_lists(a, w, ps, s))) return rc;
     prof_begin(1, s);
     if (engine == 1 && tc_supported(a, true)) rc = launch_bwd_main_tc(a, w, ps, s);
+    else if (engine == 1 && tc_wide_supported(a, true)) rc = launch_bwd_main_tc_wide(a, w, ps, s);
     else rc = launch_bwd_main_simt(a, w, ps, s);
     prof_end(1, s);
     if (rc) return rc;

@@ -1,11 +1,10 @@
 // CUDA-core ("SIMT") engine of the block-sparse attention: a plain fp32-FMA implementation
-// of the key-chunk-major main kernels.  Two uses.  (1) Head dims above 128 (192 and 256; the
-// host pads 160 and 224 up to them): the tensor-core kernels keep dK and dV of one key block in
-// the SM's 512 TMEM columns, which d = 128 already fills, so these head dims run here, on key
-// blocks of 64 keys (forward tiles of 64 rows, backward tiles of 32).  (2) A cross-check of the
-// tensor-core engine at its own shapes (key blocks of 64 / 128 keys, head dims 64 / 128): the GPU
-// tests run both engines (fmb_set_engine(0) selects this one) against the CPU oracle and against
-// each other through the same workspace contract and the same merge kernels.  Mathematics follows the
+// of the key-chunk-major main kernels for every shape the tensor-core engines serve (key blocks
+// of 64 / 128 keys with head dims 64 / 128; key blocks of 64 keys with head dim 256, where the
+// backward tiles are 32 rows so that K, V and the row tiles fit in shared memory).  It is a
+// cross-check, not a fallback: the GPU tests run both engines (fmb_set_engine(0) selects this
+// one) against the CPU oracle and against each other through the same workspace contract and the
+// same merge kernels.  Mathematics follows the
 // reference kernels (csrc/flash_moba/src/flash_fwd_kernel.h:535-640, flash_bwd_kernel.h:552-803,
 // softmax.h:259-319, mask.h:139-176); the tiling is this library's own.
 #include "fmb_attn.cuh"
@@ -421,18 +420,16 @@ static int bwd_launch(const AttnArgs& a, const AttnWorkspace& w, const PassParam
     if (w.kb == 64 && a.d == 128) return FN<__nv_bfloat16, 64, 128>(a, w, ps, s);           \
     if (w.kb == 128 && a.d == 64) return FN<__nv_bfloat16, 128, 64>(a, w, ps, s);           \
     if (w.kb == 128 && a.d == 128) return FN<__nv_bfloat16, 128, 128>(a, w, ps, s);         \
-    if (w.kb == 64 && a.d == 192) return FN<__nv_bfloat16, 64, 192>(a, w, ps, s);           \
     if (w.kb == 64 && a.d == 256) return FN<__nv_bfloat16, 64, 256>(a, w, ps, s);           \
   } else {                                                                                  \
     if (w.kb == 64 && a.d == 64) return FN<__half, 64, 64>(a, w, ps, s);                    \
     if (w.kb == 64 && a.d == 128) return FN<__half, 64, 128>(a, w, ps, s);                  \
     if (w.kb == 128 && a.d == 64) return FN<__half, 128, 64>(a, w, ps, s);                  \
     if (w.kb == 128 && a.d == 128) return FN<__half, 128, 128>(a, w, ps, s);                \
-    if (w.kb == 64 && a.d == 192) return FN<__half, 64, 192>(a, w, ps, s);                  \
     if (w.kb == 64 && a.d == 256) return FN<__half, 64, 256>(a, w, ps, s);                  \
   }                                                                                         \
   return fail(FMB_ERR_UNSUPPORTED, "attention (CUDA-core engine): head_dim %d not built "  \
-              "(head_dim in {64,128,192,256})", a.d);
+              "(head_dim in {64,128,256})", a.d);
 
 int launch_fwd_main_simt(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   if (a.ncol == 0 || a.batch == 0 || a.heads == 0) return FMB_OK;

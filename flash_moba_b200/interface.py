@@ -192,11 +192,10 @@ def _flash_moba_attn_varlen_backward_fake(dout, q, k, v, out, softmax_lse, dq, d
 
 
 def _attention_head_dim(d: int) -> int:
-    """Head dimension the attention kernels run at: 64 and 128 on the tensor-core engine, 192 and
-    256 on the CUDA-core kernels; anything else is zero-padded up to the next of them (the
-    reference pads to a multiple of 8 and dispatches on 32 ... 256,
+    """Head dimension the attention kernels run at: 64, 128 or 256; anything else is zero-padded up
+    to the next of them (the reference pads to a multiple of 8 and dispatches on 32 ... 256,
     flash_moba/flash_moba_interface.py:433-436)."""
-    for built in (64, 128, 192, 256):
+    for built in (64, 128, 256):
         if d <= built:
             return built
     return d + (-d) % 8          # above 256: rejected by the library with its message

@@ -182,7 +182,7 @@ size_t fmb_attn_bwd_workspace_bytes(int64_t total_q, int heads, int heads_k, int
  * sequence is visible iff chunk col/chunk is in the row's pattern, col < len_k and, if
  * causal, col <= row + len_k - len_q.  lse float (heads, total_q) = log-sum-exp of the
  * scaled scores; rows without visible keys give out = 0, lse = +inf.
- * head_dim: 64 or 128 (tcgen05 kernels), 192 or 256 (CUDA-core kernels); chunk: a multiple of 64.
+ * head_dim: 64, 128 or 256 (the Python layer zero-pads anything else up to the next); chunk: a multiple of 64.
  * Replaces moba_varlen_fwd, csrc/flash_moba/flash_moba_api.cpp:375-596 and
  * csrc/flash_moba/src/flash_fwd_kernel.h:232-769. */
 int fmb_attn_fwd(const void* q, int64_t q_row_stride, int64_t q_head_stride,
@@ -226,9 +226,8 @@ int fmb_attn_bwd(const void* dout, int64_t do_row_stride, int64_t do_head_stride
                  int max_seqlen_k, int chunk, float softmax_scale, int causal, int dtype,
                  fmb_stream_t stream);
 
-/* Selects the engine of the attention and gating kernels for this process: 0 = CUDA-core kernels at
- * every shape, 1 = tcgen05 tensor-core kernels wherever they are built (the default; attention head
- * dims 192 and 256 always run on CUDA cores).  Testing aid; returns the engine now in use. */
+/* Selects the engine of the attention and gating kernels for this process: 0 = CUDA-core kernels,
+ * 1 = tcgen05 tensor-core kernels (the default).  Testing aid; returns the engine now in use. */
 int fmb_set_engine(int engine);
 
 /* Which engine fmb_attn_fwd (backward = 0) or fmb_attn_bwd (backward = 1) will use for this

@@ -1,7 +1,7 @@
 #!/bin/bash
 # Builds the reference's own CUDA extension (module name flash_moba_cuda) for sm_100 from its
-# sources WHERE THEY LIE in a reference checkout, trimmed to the translation units that the bf16 /
-# fp16, head-dim 64 / 128 configurations use; nothing of the reference is copied.  Test
+# sources WHERE THEY LIE in a reference checkout, trimmed to the translation units that the bf16
+# causal configurations of head dims 64, 128 and 256 use; nothing of the reference is copied.  Test
 # infrastructure: the result (oracle/_ref/flash_moba_cuda.so, git-ignored) is only loaded by
 # oracle/ref_cuda.py for parity checks and for timing the reference's kernels beside this
 # library's.  The other instantiations that the reference's dispatch names stay undefined; the
@@ -9,6 +9,8 @@
 #
 #   bash oracle/build_ref.sh /path/to/reference [jobs]
 #
+# Objects are kept in oracle/_ref/obj/ (git-ignored, and left out of GPU-box snapshots) so that a
+# rerun only compiles what is missing.
 # Needs nvcc, the PyTorch headers of the running interpreter and a CUTLASS 3.x / 4.x header tree
 # (the reference's csrc/cutlass submodule; when that is empty, the tree that ships inside the
 # flashinfer package is used).
@@ -41,10 +43,14 @@ csrc/flash_topk/src/flash_topk16_hdim128_bf16_causal_sm80.cu
 csrc/flash_moba/src/flash_moba_fwd_hdim64_bf16_causal_sm80.cu
 csrc/flash_moba/src/flash_moba_bwd_hdim64_bf16_causal_sm80.cu
 csrc/flash_topk/src/flash_topk16_hdim64_bf16_causal_sm80.cu
+csrc/flash_moba/src/flash_moba_fwd_hdim256_bf16_causal_sm80.cu
+csrc/flash_moba/src/flash_moba_bwd_hdim256_bf16_causal_sm80.cu
+csrc/flash_topk/src/flash_topk16_hdim256_bf16_causal_sm80.cu
 "
 compile_one() {
   src=$1
   obj=$OUT/obj/$(basename "${src%.*}").o
+  if [ -f "$obj" ] && [ "$obj" -nt "$REF/$src" ]; then echo "$(date +%T) $src up to date"; return; fi
   if [ "${src##*.}" = "cu" ]; then
     nvcc $NVCC_FLAGS $DEFS $INC -c "$REF/$src" -o "$obj" > "$obj.log" 2>&1
   else
@@ -57,5 +63,4 @@ export OUT REF NVCC_FLAGS DEFS INC
 echo $SRCS | tr ' ' '\n' | xargs -P "$JOBS" -I{} bash -c 'compile_one {}'
 g++ -shared -o "$OUT/flash_moba_cuda.so" "$OUT"/obj/*.o -L"$TORCH_LIB" -ltorch -ltorch_cpu -ltorch_cuda -ltorch_python -lc10 -lc10_cuda \
     -L/usr/local/cuda/lib64 -lcudart -Wl,-rpath,"$TORCH_LIB"
-rm -r "$OUT/obj"
 echo "built $OUT/flash_moba_cuda.so"

@@ -438,13 +438,14 @@ def test_attention_head_dims_padded_to_64_or_128(d):
     _attn_check(q, k, v, do, cq, cq, mask, chunk, True, 1, pattern=(co, cn, ind))
 
 
+@pytest.mark.parametrize("engine", [0, 1])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("d,chunk,causal,hk", [(160, 64, True, 2), (192, 128, True, 4), (224, 128, False, 1),
                                                (256, 64, True, 1), (256, 256, True, 4), (136, 192, True, 2)])
-def test_attention_head_dims_above_128(d, chunk, causal, hk, dtype):
+def test_attention_head_dims_above_128(d, chunk, causal, hk, dtype, engine):
     """Head dimensions above 128 (the reference dispatches up to 256 and tests 160,
-    tests/test_moba_attn.py:48): run on the CUDA-core kernels at 192 / 256, zero-padded where they
-    fall between; ragged sequences, len_q != len_k, GQA / MQA, chunks of 1 to 4 key blocks."""
+    tests/test_moba_attn.py:48): run at 192 / 256, zero-padded where they fall between, on both
+    engines; ragged sequences, len_q != len_k, GQA / MQA, chunks of 1 to 4 key blocks."""
     torch.manual_seed(d + chunk)
     lens_q, lens_k = [190, 77, 300], [250, 77, 300]
     H = 4
@@ -454,9 +455,7 @@ def test_attention_head_dims_above_128(d, chunk, causal, hk, dtype):
     do = torch.randn(sum(lens_q), H, d).to(dtype)
     cq, ck = cu_of(lens_q), cu_of(lens_k)
     mask = _random_mask(lens_q, lens_k, H, chunk, causal, 3, seed=d)
-    from flash_moba_b200 import _lib
-    assert _lib.lib.fmb_attn_engine(chunk, 256 if d > 192 else 192, 0) == 0     # not the tensor-core engine
-    _attn_check(q, k, v, do, cq, ck, mask, chunk, causal, 1)
+    _attn_check(q, k, v, do, cq, ck, mask, chunk, causal, engine)
 
 
 # ----------------------------------------------------------------------------- whole path
