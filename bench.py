@@ -283,7 +283,7 @@ def reference_cuda_leg(seqlens, H, Hk, d, chunk, topk, backward, scale, steps):
         total = sum(ms.values())
         return {"ms_per_step": total, "ms": ms, "value": (both if backward else fwd) / total / 1e9, "unit": "TFLOP/s",
                 "lg_block_m": lg_m, "steps": steps,
-                "what": "the reference's CUDA extension compiled for sm_100 (its own sources, trimmed to the head-dim 64/128 "
+                "what": "the reference's CUDA extension compiled for sm_100 (its own sources, trimmed to the head-dim 64/128/256 "
                         "bf16 causal instantiations), same workload on this GPU, inputs resident; its Triton mean pool is not timed"}
     except Exception as e:      # reported, never fatal: the line's own numbers do not depend on it
         return {"error": repr(e)[:300]}

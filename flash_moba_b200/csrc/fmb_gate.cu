@@ -231,7 +231,7 @@ __global__ void __launch_bounds__(kGateThreads) gate_topk_kernel(GateParams p) {
 }
 
 // ---------------------------------------------------------------------------------------
-// Tensor-core variant (head_dim 64 or 128, top-k <= 32).  The score tile is a tcgen05 MMA
+// Tensor-core variant (head_dim 64, 128 or 256, top-k <= 32).  The score tile is a tcgen05 MMA
 // with the accumulator in TMEM; TMEM lane = query row, so thread t reads row t's scores
 // straight from TMEM (no shared-memory staging of scores) and keeps that row's top-k list
 // in registers: val[] = order-preserving 32-bit images of the fp32 scores, descending, and
@@ -591,7 +591,7 @@ __global__ void __launch_bounds__(128 * NQ) gate_topk_tc_kernel(GateParams p) {
 
 static int g_gate_engine = 1;
 void set_gate_engine(int e) { g_gate_engine = e; }
-bool gate_tc_supported(int d, int topk) { return (d == 64 || d == 128) && topk <= 32; }
+bool gate_tc_supported(int d, int topk) { return (d == 64 || d == 128 || d == 256) && topk <= 32; }
 
 // reads the word (synchronising) and clears it, so that one expired wait is reported once
 int read_gate_status(int* out) {
@@ -630,7 +630,9 @@ static int gate_dispatch(const GateParams& p, int batch, int max_q, cudaStream_t
                       (size_t)kGateM * kGateSStride * sizeof(float) + (size_t)kGateM * p.topk * 8;
   dim3 grid(ceil_div(max_q, kGateM), p.heads, batch);
   if (g_gate_engine == 1 && gate_tc_supported(p.d, p.topk)) {
-    return p.d == 64 ? gate_tc_pick<T, 64>(p, batch, max_q, s) : gate_tc_pick<T, 128>(p, batch, max_q, s);
+    if (p.d == 64) return gate_tc_pick<T, 64>(p, batch, max_q, s);
+    if (p.d == 128) return gate_tc_pick<T, 128>(p, batch, max_q, s);
+    return gate_tc_pick<T, 256>(p, batch, max_q, s);     // one CTA per SM: Q and two centroid tiles are 192 KB
   }
   if (p.topk > 32) {
     auto kern = gate_topk_kernel<T, true>;

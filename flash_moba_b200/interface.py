@@ -271,8 +271,9 @@ def flash_topk_varlen_func(q, k, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_s
     q: (total_q, nheads, d); k: (total_k, nheads_k, d); cu_seqlens_*: int32 (batch+1,).
     Note the argument order (top-k, then chunk size), as in the reference."""
     d_og = q.size(2)
-    if d_og % 8 != 0:
-        pad = [0, 8 - d_og % 8]
+    d_pad = _attention_head_dim(d_og)      # zero columns change no score; 64 / 128 / 256 run on tensor cores
+    if d_pad != d_og:
+        pad = [0, d_pad - d_og]
         q, k = torch.nn.functional.pad(q, pad), torch.nn.functional.pad(k, pad)
     km, cu_seqlens_km = ops.mean_pool(_fix_last_stride(k), cu_seqlens_k, max_seqlen_k, moba_chunk_size)
     return torch.ops.flash_moba._moba_fused_topk(q, km, cu_seqlens_q, cu_seqlens_k, cu_seqlens_km, max_seqlen_q,

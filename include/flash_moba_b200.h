@@ -235,7 +235,7 @@ int fmb_set_engine(int engine);
  * 0 = CUDA cores. */
 int fmb_attn_engine(int chunk, int head_dim, int backward);
 
-/* Same for fmb_gate_topk (tcgen05 for head_dim 64/128 and topk <= 32). */
+/* Same for fmb_gate_topk (tcgen05 for head_dim 64/128/256 and topk <= 32). */
 int fmb_gate_engine(int head_dim, int topk);
 
 /* Synchronising read of the gating kernel's device-side status word of the current device into

@@ -1,7 +1,7 @@
 """Loader of the reference's own CUDA extension, built by oracle/build_ref.sh (test infrastructure).
 
 The extension (module flash_moba_cuda, oracle/_ref/flash_moba_cuda.so) is the reference's
-unmodified C++/CUDA, trimmed to the head-dim 64 / 128 bf16 causal instantiations; this file only
+unmodified C++/CUDA, trimmed to the head-dim 64 / 128 / 256 bf16 causal instantiations; this file only
 opens it and calls its four bound functions the way the reference's Python layer does
 (flash_moba/flash_moba_interface.py:86-111, 148-160, 200-224, 312-342).  Mean pooling in the
 reference is a Triton kernel of its Python package, which is not part of the extension: callers

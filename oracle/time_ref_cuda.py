@@ -1,7 +1,7 @@
 """Times the reference's own CUDA kernels (oracle/_ref, built by oracle/build_ref.sh for sm_100)
 beside this library's on one GPU, same inputs, CUDA events, L2-exceeding inputs.
 
-    python oracle/time_ref_cuda.py [--tokens 65536] [--heads 32] [--chunk 128] [--topk 8] [--steps 5]
+    python oracle/time_ref_cuda.py [--tokens 65536] [--heads 32] [--head-dim 128] [--chunk 128] [--topk 8] [--steps 5]
 
 Prints one JSON line.  The reference's mean pool is a Triton kernel of its Python package (not part
 of the extension): both sides get the centroids from this library's pool, and the pool is timed
@@ -37,6 +37,7 @@ def main():
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--chunk", type=int, default=128)
     ap.add_argument("--topk", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128, 256])
     ap.add_argument("--steps", type=int, default=5)
     a = ap.parse_args()
     if not ref_cuda.available():
@@ -46,7 +47,7 @@ def main():
     from flash_moba_b200 import ops
     from flash_moba_b200.interface import decide_lg_block_m
     torch.manual_seed(0)
-    T, H, d, C, K = a.tokens, a.heads, 128, a.chunk, a.topk
+    T, H, d, C, K = a.tokens, a.heads, a.head_dim, a.chunk, a.topk
     q, k, v, do = (torch.randn(T, H, d, device="cuda", dtype=torch.bfloat16) for _ in range(4))
     cs = torch.tensor([0, T], dtype=torch.int32, device="cuda")
     scale = d ** -0.5

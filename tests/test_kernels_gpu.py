@@ -105,6 +105,8 @@ def test_gate_topk_vs_oracle(topk, chunk, causal):
     dict(B=1, H=4, Hk=2, S=1000, d=128, chunk=64, topk=8, causal=True),
     dict(B=2, H=2, Hk=1, S=300, d=128, chunk=16, topk=40, causal=False),
     dict(B=1, H=2, Hk=2, S=512, d=256, chunk=32, topk=3, causal=True),
+    dict(B=1, H=4, Hk=2, S=2500, d=256, chunk=8, topk=8, causal=True),      # three score tiles at head dim 256
+    dict(B=2, H=2, Hk=2, S=1100, d=256, chunk=4, topk=16, causal=False),    # lists of 16
     dict(B=3, H=2, Hk=2, S=0, d=64, chunk=64, topk=4, causal=True, lens_q=[10, 200, 64], lens_k=[300, 200, 70]),
     dict(B=2, H=2, Hk=2, S=0, d=64, chunk=32, topk=4, causal=True, lens_q=[200, 64], lens_k=[100, 64]),
 ])

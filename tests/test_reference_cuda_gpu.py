@@ -1,7 +1,7 @@
 """This library against the reference's own CUDA kernels on the same GPU.
 
 Runs only where oracle/build_ref.sh has built the reference's extension (oracle/_ref/,
-head dims 64 / 128, bf16, causal).  Same inputs to both: the pattern (pool -> gate -> CSC) is
+head dims 64 / 128 / 256, bf16, causal).  Same inputs to both: the pattern (pool -> gate -> CSC) is
 compared entry by entry, attention forward and backward are compared on one common pattern, and
 both are measured against the dense fp32 evaluation of that pattern: the reference's own error is
 the yardstick ("no worse than twice the reference's error").
@@ -36,6 +36,7 @@ def _inputs(lens, H, Hk, d, seed):
     ([1024, 2048], 8, 8, 64, 128, 4),          # the reference's CPU-runnable configuration, in bf16
     ([4096], 4, 4, 128, 128, 8),
     ([1500, 700, 333], 4, 2, 128, 64, 3),
+    ([2048, 900], 4, 2, 256, 128, 4),          # the wide-head kernels
 ])
 def test_pattern_and_attention_against_reference_kernels(lens, H, Hk, d, chunk, topk):
     import flash_moba_b200 as F
