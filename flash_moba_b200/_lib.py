@@ -6,8 +6,7 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-# FLASH_MOBA_B200_LIB names another build of the same library (e.g. one compiled with other tuning macros)
-LIB_PATH = os.environ.get("FLASH_MOBA_B200_LIB") or os.path.join(HERE, "libflashmoba_b200.so")
+LIB_PATH = os.path.join(HERE, "libflashmoba_b200.so")
 
 c_i32p = ctypes.c_void_p
 c_ptr = ctypes.c_void_p
