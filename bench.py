@@ -289,6 +289,28 @@ def reference_cuda_leg(seqlens, H, Hk, d, chunk, topk, backward, scale, steps):
         return {"error": repr(e)[:300]}
 
 
+def reference_cuda_in_child(args):
+    """reference_cuda_leg in a process of its own: the extension is the reference's code, and whatever it
+    does (an instantiation left out of the trimmed build, a fault) must not take this arm's line with it."""
+    from oracle import ref_cuda
+    if not ref_cuda.available() or not torch.cuda.is_available():
+        return None
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference-cuda-leg", "--workload", args.workload,
+           "--steps", str(max(1, min(args.steps, 5)))]
+    if args.heads:
+        cmd += ["--heads", str(args.heads)]
+    if args.tokens:
+        cmd += ["--tokens", str(args.tokens)]
+    try:
+        r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=900)
+        last = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+        if r.returncode != 0 or not last:
+            return {"error": f"child exited {r.returncode}: {r.stderr[-300:]}"}
+        return json.loads(last[-1])
+    except Exception as e:
+        return {"error": repr(e)[:300]}
+
+
 def run_reference(args, wl):
     seqlens, H, Hk, d, chunk, topk, backward, scale = workload_of(args)
     rank = int(os.environ.get("RANK", "0"))
@@ -314,7 +336,7 @@ def run_reference(args, wl):
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     if args.gpus == 1 and not args.no_reference_cuda:
-        line["reference_cuda"] = reference_cuda_leg(seqlens, H, Hk, d, chunk, topk, backward, scale, max(1, min(args.steps, 5)))
+        line["reference_cuda"] = reference_cuda_in_child(args)
     emit(json.dumps(line))
 
 
@@ -346,7 +368,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda-leg"])
     ap.add_argument("--workload", default="64k", choices=sorted(WORKLOADS))
     ap.add_argument("--heads", type=int, default=0, help="run this many of the workload's q heads (same q:kv ratio)")
     ap.add_argument("--tokens", type=int, default=0, help="single-sequence workloads: this many tokens instead")
@@ -364,6 +386,9 @@ def main():
     wl = args.workload
     if args.impl == "reference":
         return run_reference(args, wl)
+    if args.impl == "reference-cuda-leg":     # the child of reference_cuda_in_child
+        seqlens, H, Hk, d, chunk, topk, backward, scale = workload_of(args)
+        return emit(json.dumps(reference_cuda_leg(seqlens, H, Hk, d, chunk, topk, backward, scale, args.steps)))
 
     seqlens, H, Hk, d, chunk, topk, backward, scale = workload_of(args)
     rank = int(os.environ.get("RANK", "0"))
