@@ -17,9 +17,9 @@ static size_t layout(AttnWorkspace& w, void* base, const AttnArgs& a, size_t par
   w.nh = nh;
   w.fixed_k = 0;
   w.mirror = nullptr;
-  // key block: 128 keys when the chunk is a multiple of 128; head dims above 128 always take 64-key
-  // blocks (the CUDA-core kernels that serve them hold K, V and the row tiles in shared memory)
-  w.kb = (a.chunk % 128 == 0 && a.d <= 128) ? 128 : 64;
+  // key block: 128 keys when the chunk is a multiple of 128, except in the backward pass of head
+  // dim 256, whose dK and dV accumulators for 128 keys would not fit in TMEM (with_lse = forward)
+  w.kb = (a.chunk % 128 == 0 && (a.d <= 128 || with_lse)) ? 128 : 64;
   w.nsub = a.chunk / w.kb;
   // one pass over all heads can never need more slots than the pattern has entries; a pass over a
   // share of the heads is given that share (exact for the top-k packing), rounded up
@@ -800,7 +800,10 @@ static int fwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const
   const int64_t nb8 = group_grid(rows, 8), nbw = warp_grid(rows);
   if (c.fixed_k > 0) {   // every row has fixed_k * nsub places: the stage is known on the host, one launch
     const int places = c.fixed_k * c.nsub;
-    if (places <= 8) {   // (16 lanes per row instead of 8 for these rows: 1.57 ms against 1.21 ms at 64K)
+    // 8 lanes per row while a lane's share of a partial row is at most 32 bytes (at d = 128, 16 lanes
+    // for these rows: 1.57 ms against 1.21 ms at 64K; at d = 256, 8 lanes would hold 128 registers of
+    // loads in flight each: 3.5 ms against the 16-lane form's time for the same bytes)
+    if (places <= 8 && D <= 128) {
       fwd_combine_group_kernel<T, 8, D / 8><<<first_grid(nb8), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse,
                                                                           0, nullptr, ovf, nb8);
       FMB_LAUNCH_CHECK("fwd_combine_group_kernel<8>");
@@ -821,15 +824,21 @@ static int fwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const
     }
     return FMB_OK;
   }
-  fwd_combine_group_kernel<T, 8, D / 8><<<first_grid(nb8), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, 0,
-                                                                      nullptr, ovf, nb8);
-  FMB_LAUNCH_CHECK("fwd_combine_group_kernel<8>");
   int* left = ovf;            // flag set by the stage before; rows of at least min_n partials are left
   int min_n = 9;
+  if constexpr (D <= 128) {
+    fwd_combine_group_kernel<T, 8, D / 8><<<first_grid(nb8), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs, a.lse, 0,
+                                                                        nullptr, ovf, nb8);
+    FMB_LAUNCH_CHECK("fwd_combine_group_kernel<8>");
+  }
   if constexpr (D >= 128) {   // 16 lanes of a row own whole 16-byte chunks: two rows per warp
     const int64_t nb16 = group_grid(rows, 16);
-    fwd_combine_group_kernel<T, 16, D / 16><<<late_grid(nb16), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs,
-                                                                           a.lse, 9, ovf, ovf + 1, nb16);
+    if constexpr (D <= 128)
+      fwd_combine_group_kernel<T, 16, D / 16><<<late_grid(nb16), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs,
+                                                                             a.lse, 9, ovf, ovf + 1, nb16);
+    else                      // d = 256: the first stage
+      fwd_combine_group_kernel<T, 16, D / 16><<<first_grid(nb16), 256, 0, s>>>(po, w.part_lse, c, out, a.o_rs, a.o_hs,
+                                                                              a.lse, 0, nullptr, ovf + 1, nb16);
     FMB_LAUNCH_CHECK("fwd_combine_group_kernel<16>");
     left = ovf + 1;
     min_n = 17;
@@ -869,7 +878,7 @@ static int bwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const
   const int64_t nb8 = group_grid(rows, 8), nbw = warp_grid(rows);
   if (c.fixed_k > 0) {   // every row has fixed_k * nsub places: the stage is known on the host, one launch
     const int places = c.fixed_k * c.nsub;
-    if (places <= 8) {
+    if (places <= 8 && D <= 128) {
       bwd_combine_group_kernel<T, 8, D / 8><<<first_grid(nb8), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 0, nullptr, ovf, nb8);
       FMB_LAUNCH_CHECK("bwd_combine_group_kernel<8>");
     } else if (D >= 128 && places <= 16) {
@@ -889,14 +898,20 @@ static int bwd_combine_dispatch(const AttnArgs& a, const AttnWorkspace& w, const
     }
     return FMB_OK;
   }
-  bwd_combine_group_kernel<T, 8, D / 8><<<first_grid(nb8), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 0, nullptr, ovf, nb8);
-  FMB_LAUNCH_CHECK("bwd_combine_group_kernel<8>");
   int* left = ovf;
   int min_n = 9;
+  if constexpr (D <= 128) {
+    bwd_combine_group_kernel<T, 8, D / 8><<<first_grid(nb8), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 0, nullptr, ovf, nb8);
+    FMB_LAUNCH_CHECK("bwd_combine_group_kernel<8>");
+  }
   if constexpr (D >= 128) {
     const int64_t nb16 = group_grid(rows, 16);
-    bwd_combine_group_kernel<T, 16, D / 16><<<late_grid(nb16), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 9, ovf, ovf + 1,
-                                                                           nb16);
+    if constexpr (D <= 128)
+      bwd_combine_group_kernel<T, 16, D / 16><<<late_grid(nb16), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 9, ovf, ovf + 1,
+                                                                             nb16);
+    else
+      bwd_combine_group_kernel<T, 16, D / 16><<<first_grid(nb16), 256, 0, s>>>(pd, c, dq, a.dq_rs, a.dq_hs, 0, nullptr,
+                                                                              ovf + 1, nb16);
     FMB_LAUNCH_CHECK("bwd_combine_group_kernel<16>");
     left = ovf + 1;
     min_n = 17;

@@ -414,30 +414,32 @@ static int bwd_launch(const AttnArgs& a, const AttnWorkspace& w, const PassParam
   return FMB_OK;
 }
 
-#define FMB_SIMT_DISPATCH(FN)                                                               \
+#define FMB_SIMT_DISPATCH(FN, FWD)                                                             \
   if (a.dtype == FMB_BF16) {                                                                \
     if (w.kb == 64 && a.d == 64) return FN<__nv_bfloat16, 64, 64>(a, w, ps, s);             \
     if (w.kb == 64 && a.d == 128) return FN<__nv_bfloat16, 64, 128>(a, w, ps, s);           \
     if (w.kb == 128 && a.d == 64) return FN<__nv_bfloat16, 128, 64>(a, w, ps, s);           \
     if (w.kb == 128 && a.d == 128) return FN<__nv_bfloat16, 128, 128>(a, w, ps, s);         \
     if (w.kb == 64 && a.d == 256) return FN<__nv_bfloat16, 64, 256>(a, w, ps, s);           \
+    if (FWD && w.kb == 128 && a.d == 256) return fwd_launch<__nv_bfloat16, 128, 256>(a, w, ps, s);   \
   } else {                                                                                  \
     if (w.kb == 64 && a.d == 64) return FN<__half, 64, 64>(a, w, ps, s);                    \
     if (w.kb == 64 && a.d == 128) return FN<__half, 64, 128>(a, w, ps, s);                  \
     if (w.kb == 128 && a.d == 64) return FN<__half, 128, 64>(a, w, ps, s);                  \
     if (w.kb == 128 && a.d == 128) return FN<__half, 128, 128>(a, w, ps, s);                \
     if (w.kb == 64 && a.d == 256) return FN<__half, 64, 256>(a, w, ps, s);                  \
+    if (FWD && w.kb == 128 && a.d == 256) return fwd_launch<__half, 128, 256>(a, w, ps, s);          \
   }                                                                                         \
   return fail(FMB_ERR_UNSUPPORTED, "attention (CUDA-core engine): head_dim %d not built "  \
               "(head_dim in {64,128,256})", a.d);
 
 int launch_fwd_main_simt(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   if (a.ncol == 0 || a.batch == 0 || a.heads == 0) return FMB_OK;
-  FMB_SIMT_DISPATCH(fwd_launch)
+  FMB_SIMT_DISPATCH(fwd_launch, true)
 }
 int launch_bwd_main_simt(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   if (a.batch == 0 || a.heads == 0) return FMB_OK;
-  FMB_SIMT_DISPATCH(bwd_launch)
+  FMB_SIMT_DISPATCH(bwd_launch, false)
 }
 
 }  // namespace fmb

@@ -2,15 +2,16 @@
 //
 // The kernels of fmb_attn_tc.cu keep dK and dV of a 128-key block in the SM's 512 TMEM columns,
 // which a head dim of 128 already fills, and their shared-memory tiles assume d <= 128.  Wider heads
-// run here, on key blocks of 64 keys, in a simpler shape: one CTA of 256 threads per work item (key
-// block, head or kv head, sequence), every thread takes part in every phase, one thread issues the
-// MMAs, and the only overlap is the cp.async gather of the next tile's rows under the current
-// tile's work.  Same workspace contract (slots, per-entry partials) and the same merge kernels as
+// run here (forward: key blocks of 128 keys where the chunk allows, else 64; backward: 64), in a
+// simpler shape: one CTA of 256 threads per work item (key block, head or kv head, sequence), every
+// thread takes part in every phase, one thread issues the MMAs, and the only overlap is the
+// forward's cp.async gather of the next tile's rows under the current tile's work.  Same workspace contract (slots, per-entry partials) and the same merge kernels as
 // the other engines.  Every mbarrier wait is bounded (status word of the workspace).
 //
 // Forward, per tile of 128 gathered query rows:
-//     S = Q.K^T (K dimension d, 64 keys)  ->  chunk-local softmax, P (I/O dtype) to shared memory
-//     O = P.V  (N = d)                    ->  O / l staged over the consumed Q tile, bulk copies
+//     S = Q.K^T (K dimension d)  ->  the Q tile is refilled with the next tile's rows
+//     chunk-local softmax in one pass (32 or 64 scores per thread), P (I/O dtype) to shared memory
+//     O = P.V  (N = d)           ->  O / l written from registers (256 contiguous bytes per thread)
 // Backward (head dim 256), work item = key block of one kv head, tiles = the q heads of its group
 // times the 128-row tiles of each head's column.  dK and dV are accumulated TRANSPOSED (TMEM lane =
 // head-dim index, two halves of 128; column = key), which takes 2 x 128 columns instead of the
@@ -47,28 +48,32 @@ struct WideParams {
 // threads that take part in the 16-byte copies of rows of D elements: eight rows per pass
 template <int D> struct Copiers { static constexpr int n = (D / 8) * 8; };
 
-template <typename T, int D>
+template <typename T, int C, int D>
 __global__ void __launch_bounds__(kThreads) fwd_wide_tc_kernel(WideParams p) {
   constexpr int NCH = D / 8;                    // 16-byte chunks of a row
   constexpr int NT = Copiers<D>::n;             // copying threads
-  constexpr uint32_t kKBlock = kC * 128;        // bytes between 64-element blocks of the K / V tiles
-  constexpr uint32_t kQBlock = kM * 128;        // same for the 128-row Q tiles
-  constexpr uint32_t kQTile = kM * D * 2;
-  constexpr int DH = D / 2;                     // head-dim columns per thread in the epilogue
-  static_assert(D == 256, "head dim 256");
-  extern __shared__ unsigned char smem_raw[];
+  constexpr uint32_t kKBlock = C * 128;         // bytes between 64-element blocks of the K / V tiles
+  constexpr uint32_t kQBlock = kM * 128;        // same for the 128-row Q and P tiles
+  constexpr int CH = C / 2, DH = D / 2;         // keys / head-dim columns per thread
+  static_assert(D == 256 && (C == 64 || C == 128), "head dim 256, key blocks of 64 or 128");
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ uint64_t bar_s, bar_o;
   __shared__ uint32_t tmem_base_s;
-  __shared__ int sRow[2][kM];
+  __shared__ int sRow[kM];
   __shared__ float sMax[2][kM], sSum[2][kM];
 
-  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  unsigned char* sK = smem;                     // [64][D]
-  unsigned char* sV = sK + kC * D * 2;          // [64][D]
-  unsigned char* sQ = sV + kC * D * 2;          // 2 x [128][D]; a consumed tile stages the tile's O
-  unsigned char* sP = sQ + 2 * kQTile;          // [128][64]
+  // with 128-key blocks the tiles and the arrays above fill the 227 KB: no room for alignment padding
+  unsigned char* smem = smem_raw;
+  if ((smem_u32(smem_raw) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, 9);
+    return;
+  }
+  unsigned char* sK = smem;                     // [C][D]
+  unsigned char* sV = sK + C * D * 2;           // [C][D]
+  unsigned char* sQ = sV + C * D * 2;           // [128][D]: refilled as soon as the tile's S has been computed
+  unsigned char* sP = sQ + kM * D * 2;          // [128][C]
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = tid >> 5;
   const int lt = tid & (kM - 1), hf = tid >> 7;
   const int c = blockIdx.x / p.ps.nsub, sb = blockIdx.x % p.ps.nsub, h = p.ps.h0 + blockIdx.y, b = blockIdx.z;
   const ColRef col = column_of(p.ps, b, h, c);
@@ -76,8 +81,8 @@ __global__ void __launch_bounds__(kThreads) fwd_wide_tc_kernel(WideParams p) {
   const int64_t slot0 = (int64_t)sb * p.ps.cap + col.slot;
   const int q0 = p.cu_q[b], len_q = p.cu_q[b + 1] - q0;
   const int k0 = p.k_begin[b], len_k = p.k_end[b] - k0;
-  const int key0 = c * p.ps.chunk + sb * kC;
-  const int keys_valid = max(0, min(kC, len_k - key0));
+  const int key0 = c * p.ps.chunk + sb * C;
+  const int keys_valid = max(0, min(C, len_k - key0));
   const int hk = h / (p.heads / p.heads_k);
   const int shift = len_k - len_q;
   const float scale_log2 = p.scale * kLog2e;
@@ -91,7 +96,7 @@ __global__ void __launch_bounds__(kThreads) fwd_wide_tc_kernel(WideParams p) {
     mbar_init(&bar_o, 1);
     mbar_fence_init();
   }
-  // row ids of tile t (-1 = none) into sRow[t & 1]
+  // row ids of tile t (-1 = none)
   auto load_rows = [&](int t) {
     if (tid < kM) {
       int r = -1;
@@ -99,66 +104,63 @@ __global__ void __launch_bounds__(kThreads) fwd_wide_tc_kernel(WideParams p) {
         r = p.ps.indices[col.off + t * kM + tid];
         if (r < 0 || r >= len_q) r = -1;
       }
-      sRow[t & 1][tid] = r;
+      sRow[tid] = r;
     }
   };
   load_rows(0);
   if (tid < NT) {
     const T* kbase = static_cast<const T*>(p.k) + (int64_t)(k0 + key0) * p.k_rs + (int64_t)hk * p.k_hs;
     const T* vbase = static_cast<const T*>(p.v) + (int64_t)(k0 + key0) * p.v_rs + (int64_t)hk * p.v_hs;
-    dense_cp_async<T, NCH, kC, NT>(tid, sK, kKBlock, kbase, p.k_rs, keys_valid);
-    dense_cp_async<T, NCH, kC, NT>(tid, sV, kKBlock, vbase, p.v_rs, keys_valid);
+    dense_cp_async<T, NCH, C, NT>(tid, sK, kKBlock, kbase, p.k_rs, keys_valid);
+    dense_cp_async<T, NCH, C, NT>(tid, sV, kKBlock, vbase, p.v_rs, keys_valid);
   }
   tc_fence_before_sync();
   __syncthreads();                              // row ids of tile 0, the TMEM base, the barriers
   tc_fence_after_sync();
-  if (tid < NT) gather_cp_async<T, NCH, NT>(tid, sQ, kQBlock, qbase, p.q_rs, sRow[0]);
+  if (tid < NT) gather_cp_async<T, NCH, NT>(tid, sQ, kQBlock, qbase, p.q_rs, sRow);
   const uint32_t tmem_base = tmem_base_s;
   const uint32_t tS = tmem_base, tO = tmem_base + 256;
   const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
-  constexpr uint32_t idesc_s = make_idesc(FmtOf<T>::v, kM, kC, 0, 0);
+  constexpr uint32_t idesc_s = make_idesc(FmtOf<T>::v, kM, C, 0, 0);
   constexpr uint32_t idesc_o = make_idesc(FmtOf<T>::v, kM, D, 0, 1);
   const uint32_t hi = desc_hi_sw128(1024);
-  const uint32_t k_km = desc_lo_sw128(smem_u32(sK), 16), v_mn = desc_lo_sw128(smem_u32(sV), kKBlock);
-  const uint32_t p_km = desc_lo_sw128(smem_u32(sP), 16);
+  const uint32_t q_km = desc_lo_sw128(smem_u32(sQ), 16), k_km = desc_lo_sw128(smem_u32(sK), 16);
+  const uint32_t v_mn = desc_lo_sw128(smem_u32(sV), kKBlock), p_km = desc_lo_sw128(smem_u32(sP), 16);
   bool good = true;
 
 #pragma unroll 1
   for (int i = 0; i < ntiles && good; ++i) {
-    unsigned char* sQi = sQ + (i & 1) * kQTile;
     const int t0 = i * kM;
     const int rows = min(kM, col.nnz - t0);
-    // Q(i) (with K and V on the first tile) has landed; the next tile's row ids are on their way
-    load_rows(i + 1);
+    // Q(i) (with K and V on the first tile) has landed
+    const int r = sRow[lt];                     // this tile's row, before the next tile's ids replace it
     cp_async_wait_all();
     fence_async_smem();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     if (tid == 0) {
-      umma_gemm<D / 16>(tS, desc_lo_sw128(smem_u32(sQi), 16), hi, 2, kQBlock >> 4, k_km, hi, 2, kKBlock >> 4, idesc_s, 0);
+      umma_gemm<D / 16>(tS, q_km, hi, 2, kQBlock >> 4, k_km, hi, 2, kKBlock >> 4, idesc_s, 0);
       umma_commit(&bar_s);
     }
-    // the next tile's rows are gathered under this tile's work.  Its buffer staged the O of tile
-    // i - 1: the bulk copies must have read it
-    if (i + 1 < ntiles) {
-      if (warp < 4 && lane == 0) bulk_wait_read();
-      __syncthreads();
-      if (tid < NT) gather_cp_async<T, NCH, NT>(tid, sQ + ((i + 1) & 1) * kQTile, kQBlock, qbase, p.q_rs, sRow[(i + 1) & 1]);
-    }
+    load_rows(i + 1);                           // (every thread has read its row id above)
     good = mbar_wait(&bar_s, i & 1, p.status, 1);
+    __syncthreads();                            // the next tile's row ids
     tc_fence_after_sync();
+    // S is complete, so the Q tile is free: the next tile's rows are gathered under the rest of this
+    // tile's work (the row gather, not the arithmetic, is what bounds these kernels)
+    if (i + 1 < ntiles && tid < NT) gather_cp_async<T, NCH, NT>(tid, sQ, kQBlock, qbase, p.q_rs, sRow);
 
-    // ---- chunk-local softmax of row `lt`, this thread's 32 keys, in one pass over the scores
-    const int r = sRow[i & 1][lt];
+    // ---- chunk-local softmax of row `lt`, this thread's half of the keys, in one pass over the scores
     const int lim = r < 0 ? 0 : (p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid);
-    float s[32];
-    tmem_ld32(tS + lane_sel + hf * 32, s);
+    float s[CH];
+#pragma unroll
+    for (int q4 = 0; q4 < CH / 32; ++q4) tmem_ld32(tS + lane_sel + hf * CH + q4 * 32, s + q4 * 32);
     tmem_ld_wait();
     tc_fence_before_sync();
     float mx = -CUDART_INF_F;
 #pragma unroll
-    for (int jj = 0; jj < 32; ++jj) mx = fmaxf(mx, hf * 32 + jj < lim ? s[jj] : -CUDART_INF_F);
+    for (int jj = 0; jj < CH; ++jj) mx = fmaxf(mx, hf * CH + jj < lim ? s[jj] : -CUDART_INF_F);
     sMax[hf][lt] = mx;
     good = __syncthreads_and(good);
     if (!good) break;
@@ -166,21 +168,21 @@ __global__ void __launch_bounds__(kThreads) fwd_wide_tc_kernel(WideParams p) {
     const float mref = lim > 0 ? mx * scale_log2 : 0.f;
     float sum = 0.f;
 #pragma unroll
-    for (int jj = 0; jj < 32; ++jj) {
+    for (int jj = 0; jj < CH; ++jj) {
       const float e = exp2f(s[jj] * scale_log2 - mref);
-      s[jj] = (hf * 32 + jj < lim) ? e : 0.f;
+      s[jj] = (hf * CH + jj < lim) ? e : 0.f;
       sum += s[jj];
     }
 #pragma unroll
-    for (int jj = 0; jj < 4; ++jj)
-      *reinterpret_cast<uint4*>(sP + sw128_offset(lt, hf * 4 + jj, kQBlock)) = pack8<T>(s + jj * 8);
+    for (int jj = 0; jj < CH / 8; ++jj)
+      *reinterpret_cast<uint4*>(sP + sw128_offset(lt, hf * (CH / 8) + jj, kQBlock)) = pack8<T>(s + jj * 8);
     sSum[hf][lt] = sum;
     fence_async_smem();
     tc_fence_before_sync();
     __syncthreads();                            // P complete; S has been read by every thread
     tc_fence_after_sync();
     if (tid == 0) {
-      umma_gemm<kC / 16>(tO, p_km, hi, 2, 0, v_mn, hi, 128, 512, idesc_o, 0);
+      umma_gemm<C / 16>(tO, p_km, hi, 2, kQBlock >> 4, v_mn, hi, 128, 512, idesc_o, 0);
       umma_commit(&bar_o);
     }
     sum += sSum[hf ^ 1][lt];
@@ -189,36 +191,30 @@ __global__ void __launch_bounds__(kThreads) fwd_wide_tc_kernel(WideParams p) {
     good = mbar_wait(&bar_o, i & 1, p.status, 2);
     tc_fence_after_sync();
 
-    // ---- normalised partial O of row `lt`, this thread's half of the head dim, staged over the Q
-    // tile (its MMA has completed), 16-byte chunks permuted like every partial; one bulk copy per 32 rows
+    // ---- normalised partial O of row `lt`, this thread's half of the head dim (256 contiguous
+    // bytes of the row's slot), written from registers; 16-byte chunks permuted like every partial
     {
       const int key = (int)((slot0 + t0 + lt) & 7);
-      unsigned char* srow = sQi + lt * (D * 2);
+      T* dst = part_o + (slot0 + t0 + lt) * D;
 #pragma unroll
       for (int q4 = 0; q4 < DH / 32; ++q4) {
         float o[32];
         tmem_ld32(tO + lane_sel + hf * DH + q4 * 32, o);
         tmem_ld_wait();
+        if (lt < rows) {
 #pragma unroll
-        for (int jj = 0; jj < 32; ++jj) o[jj] *= inv;
+          for (int jj = 0; jj < 4; ++jj) {
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj)
-          *reinterpret_cast<uint4*>(srow + (((hf * (DH / 8) + q4 * 4 + jj) ^ key) << 4)) = pack8<T>(o + jj * 8);
+            for (int e = 0; e < 8; ++e) o[jj * 8 + e] *= inv;
+            *reinterpret_cast<uint4*>(dst + (((hf * (DH / 8) + q4 * 4 + jj) ^ key) << 3)) = pack8<T>(o + jj * 8);
+          }
+        }
       }
       tc_fence_before_sync();
-      fence_async_smem();
     }
-    good = __syncthreads_and(good);
-    if (!good) break;
-    if (warp < 4 && lane == 0) {
-      const int wrows = min(32, rows - warp * 32);   // a warp's rows are contiguous in the workspace
-      if (wrows > 0) {
-        bulk_store(part_o + (slot0 + t0 + warp * 32) * D, sQi + warp * 32 * (D * 2), (uint32_t)wrows * D * 2);
-        bulk_commit();
-      }
-    }
+    // (the barrier at the top of the next tile keeps its P.V, which overwrites O, behind these reads)
   }
-  if (warp < 4 && lane == 0) bulk_wait_read();
+  cp_async_wait_all();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -478,11 +474,11 @@ WideParams make_wide_params(const AttnArgs& a, const AttnWorkspace& w, const Pas
   return p;
 }
 
-template <typename T, int D>
+template <typename T, int C, int D>
 int fwd_wide_launch(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   const WideParams p = make_wide_params(a, w, ps);
-  const size_t smem = (size_t)2 * kC * D * 2 + (size_t)2 * kM * D * 2 + (size_t)kM * kC * 2 + 1024;
-  auto kern = fwd_wide_tc_kernel<T, D>;
+  const size_t smem = (size_t)2 * C * D * 2 + (size_t)kM * D * 2 + (size_t)kM * C * 2;   // K, V, Q, P
+  auto kern = fwd_wide_tc_kernel<T, C, D>;
   FMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<dim3(a.ncol * ps.nsub, ps.nh, a.batch), kThreads, smem, s>>>(p);
   FMB_LAUNCH_CHECK("fwd_wide_tc_kernel");
@@ -519,10 +515,13 @@ int launch_bwd_main_tc_wide(const AttnArgs& a, const AttnWorkspace& w, const Pas
 
 int launch_fwd_main_tc_wide(const AttnArgs& a, const AttnWorkspace& w, const PassParams& ps, cudaStream_t s) {
   if (a.ncol == 0 || a.batch == 0 || a.heads == 0) return FMB_OK;
-  if (w.kb != kC) return fail(FMB_ERR_UNSUPPORTED, "wide-head forward: key block %d (64 expected)", w.kb);
-  if (a.d == 256)
-    return a.dtype == FMB_BF16 ? fwd_wide_launch<__nv_bfloat16, 256>(a, w, ps, s) : fwd_wide_launch<__half, 256>(a, w, ps, s);
-  return fail(FMB_ERR_UNSUPPORTED, "wide-head forward: head_dim %d not built", a.d);
+  if (a.d == 256 && w.kb == 128)
+    return a.dtype == FMB_BF16 ? fwd_wide_launch<__nv_bfloat16, 128, 256>(a, w, ps, s)
+                               : fwd_wide_launch<__half, 128, 256>(a, w, ps, s);
+  if (a.d == 256 && w.kb == 64)
+    return a.dtype == FMB_BF16 ? fwd_wide_launch<__nv_bfloat16, 64, 256>(a, w, ps, s)
+                               : fwd_wide_launch<__half, 64, 256>(a, w, ps, s);
+  return fail(FMB_ERR_UNSUPPORTED, "wide-head forward: key block %d / head_dim %d not built", w.kb, a.d);
 }
 
 }  // namespace fmb

@@ -329,7 +329,8 @@ def _random_mask(lens_q, lens_k, H, chunk, causal, picks, seed=1):
     return mask
 
 
-@pytest.mark.parametrize("chunk,d,max_picks", [(64, 64, 31), (64, 128, 31), (128, 128, 20), (256, 128, 15), (256, 64, 15)])
+@pytest.mark.parametrize("chunk,d,max_picks", [(64, 64, 31), (64, 128, 31), (128, 128, 20), (256, 128, 15), (256, 64, 15),
+                                               (64, 256, 31), (128, 256, 20)])
 def test_attention_rows_with_9_to_32_partials(chunk, d, max_picks):
     """Rows with every count of selected chunks from 1 to max_picks + 1 next to each other: the merge
     of a row's partials goes through the 8-lane stage, the warp-per-row stage (9..32 partials; a
