@@ -19,6 +19,8 @@
 // computed and written one after the other:
 //     S = Q.K^T, dP = dO.V^T -> P = exp2(S.scale - LSE), dS = P o (dP - D) to shared memory
 //     dV^T += dO^T.P, dK^T += Q^T.dS (Q, dO as M-major A operands), dQ = dS.K per half
+//     once those have completed the Q and dO tiles are refilled with the next tile's rows while the
+//     dQ halves are read out and written from registers
 #include "fmb_attn.cuh"
 #include "fmb_tc.cuh"
 
@@ -243,12 +245,12 @@ __global__ void __launch_bounds__(kThreads) bwd_wide_tc_kernel(WideParams p) {
   }
   unsigned char* sK = smem;                     // [64][D]
   unsigned char* sV = sK + kC * D * 2;          // [64][D]
-  unsigned char* sQ = sV + kC * D * 2;          // [128][D]; stages the tile's dQ once dK^T has read it
+  unsigned char* sQ = sV + kC * D * 2;          // [128][D]
   unsigned char* sdO = sQ + kQTile;             // [128][D]
   unsigned char* sP = sdO + kQTile;             // [128][64]
   unsigned char* sdS = sP + kM * kC * 2;        // [128][64]
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = tid >> 5;
   const int lt = tid & (kM - 1), hf = tid >> 7;
   const int group = p.heads / p.heads_k;
   const int c = blockIdx.x / p.ps.nsub, sb = blockIdx.x % p.ps.nsub, hk = p.ps.h0 / group + blockIdx.y, b = blockIdx.z;
@@ -296,133 +298,157 @@ __global__ void __launch_bounds__(kThreads) bwd_wide_tc_kernel(WideParams p) {
   bool good = true;
   uint32_t g = 0;                               // tiles so far (phase of the three barriers)
 
-#pragma unroll 1
-  for (int hg = 0; hg < group && good; ++hg) {
-    const int h = hk * group + hg;
-    const ColRef col = column_of(p.ps, b, h, c);
-    if (col.nnz <= 0) continue;                 // CTA-uniform
-    const T* qbase = static_cast<const T*>(p.q) + (int64_t)q0 * p.q_rs + (int64_t)h * p.q_hs;
-    const T* dobase = static_cast<const T*>(p.dout) + (int64_t)q0 * p.do_rs + (int64_t)h * p.do_hs;
-    const float* lse = p.lse + (int64_t)h * p.total_q + q0;
-    const float* dsum = p.softmax_d + (int64_t)h * p.total_q + q0;
-#pragma unroll 1
-    for (int t0 = 0; t0 < col.nnz && good; t0 += kM, ++g) {
-      const int rows = min(kM, col.nnz - t0);
-      const int64_t slot0 = plane + col.slot + t0;
-      // ---- the tile's rows: ids, log-sum-exps, dO.O sums; then its Q and dO rows
-      if (warp < 4 && lane == 0) bulk_wait_read();   // the dQ staging of the tile before has been read out
-      if (tid < kM) {
-        int r = -1;
-        float l = CUDART_INF_F, dd = 0.f;
-        if (tid < rows) {
-          r = p.ps.indices[col.off + t0 + tid];
-          if (r < 0 || r >= len_q) r = -1;
-          else { l = lse[r]; dd = dsum[r]; }
+  // The item's tiles as one sequence over the q heads of the group and the 128-row tiles of each
+  // head's column: `cur` is the tile being worked on, `nxt` the one whose rows are gathered under
+  // the end of it.
+  struct Tile { int hg, t0, nnz; int64_t off, slot; bool valid; };
+  auto seek = [&](Tile& t) {                    // first head >= t.hg with a column; t.t0 = 0
+    t.valid = false;
+    for (; t.hg < group; ++t.hg) {
+      const ColRef col = column_of(p.ps, b, hk * group + t.hg, c);
+      if (col.nnz > 0) { t.nnz = col.nnz; t.off = col.off; t.slot = col.slot; t.t0 = 0; t.valid = true; return; }
+    }
+  };
+  auto advance = [&](Tile t) {
+    t.t0 += kM;
+    if (t.t0 >= t.nnz) { ++t.hg; seek(t); }
+    return t;
+  };
+  // row ids, log-sum-exps and dO.O sums of a tile into shared memory (the first 128 threads)
+  auto load_rows = [&](const Tile& t) {
+    if (tid < kM) {
+      int r = -1;
+      float l = CUDART_INF_F, dd = 0.f;
+      if (t.valid && t.t0 + tid < t.nnz) {
+        r = p.ps.indices[t.off + t.t0 + tid];
+        if (r < 0 || r >= len_q) r = -1;
+        else {
+          const int64_t at = (int64_t)(hk * group + t.hg) * p.total_q + q0 + r;
+          l = p.lse[at];
+          dd = p.softmax_d[at];
         }
-        sRow[tid] = r; sLse[tid] = l; sDsum[tid] = dd;
       }
-      __syncthreads();
-      if (tid < NT) {
-        gather_cp_async<T, NCH, NT>(tid, sQ, kQBlock, qbase, p.q_rs, sRow);
-        gather_cp_async<T, NCH, NT>(tid, sdO, kQBlock, dobase, p.do_rs, sRow);
-      }
-      cp_async_wait_all();                      // (and K, V on the item's first tile)
-      fence_async_smem();
-      tc_fence_before_sync();
-      __syncthreads();
-      tc_fence_after_sync();
-      if (tid == 0) {
-        umma_gemm<D / 16>(tS, q_km, hi, 2, kQBlock >> 4, k_km, hi, 2, kKBlock >> 4, idesc_s, 0);
-        umma_gemm<D / 16>(tdP, do_km, hi, 2, kQBlock >> 4, v_km, hi, 2, kKBlock >> 4, idesc_s, 0);
-        umma_commit(&bar_a);
-      }
-      good = mbar_wait(&bar_a, g & 1, p.status, 3);
-      tc_fence_after_sync();
+      sRow[tid] = r; sLse[tid] = l; sDsum[tid] = dd;
+    }
+  };
+  auto gather = [&](const Tile& t) {
+    if (tid < NT) {
+      const int h = hk * group + t.hg;
+      gather_cp_async<T, NCH, NT>(tid, sQ, kQBlock, static_cast<const T*>(p.q) + (int64_t)q0 * p.q_rs + (int64_t)h * p.q_hs,
+                                  p.q_rs, sRow);
+      gather_cp_async<T, NCH, NT>(tid, sdO, kQBlock,
+                                  static_cast<const T*>(p.dout) + (int64_t)q0 * p.do_rs + (int64_t)h * p.do_hs, p.do_rs, sRow);
+    }
+  };
+  Tile cur{0, 0, 0, 0, 0, false};
+  seek(cur);
+  if (cur.valid) {
+    load_rows(cur);
+    __syncthreads();
+    gather(cur);
+  }
+#pragma unroll 1
+  for (; cur.valid; ++g) {
+    const int rows = min(kM, cur.nnz - cur.t0);
+    const int64_t slot0 = plane + cur.slot + cur.t0;
+    cp_async_wait_all();                        // Q and dO rows of the tile (and K, V on the item's first)
+    fence_async_smem();
+    tc_fence_before_sync();
+    good = __syncthreads_and(good);             // (a wait that gave up in the tile before ends the loop for every thread)
+    if (!good) break;
+    tc_fence_after_sync();
+    if (tid == 0) {
+      umma_gemm<D / 16>(tS, q_km, hi, 2, kQBlock >> 4, k_km, hi, 2, kKBlock >> 4, idesc_s, 0);
+      umma_gemm<D / 16>(tdP, do_km, hi, 2, kQBlock >> 4, v_km, hi, 2, kKBlock >> 4, idesc_s, 0);
+      umma_commit(&bar_a);
+    }
+    const Tile nxt = advance(cur);              // (global loads of the next column's header, under the MMAs)
+    good = mbar_wait(&bar_a, g & 1, p.status, 3);
+    tc_fence_after_sync();
 
-      // ---- P and dS of row `lt`, this thread's 32 keys
-      {
-        const int r = sRow[lt];
-        const float lse2 = sLse[lt] * kLog2e, dd = sDsum[lt];
-        const int lim = r < 0 ? 0 : (p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid);
-        float pr[32], dp[32];
-        tmem_ld32(tS + lane_sel + hf * 32, pr);
-        tmem_ld32(tdP + lane_sel + hf * 32, dp);
-        tmem_ld_wait();
-        tc_fence_before_sync();
-#pragma unroll
-        for (int jj = 0; jj < 32; ++jj) {
-          pr[jj] = (hf * 32 + jj < lim) ? exp2f(pr[jj] * scale_log2 - lse2) : 0.f;
-          dp[jj] = pr[jj] * (dp[jj] - dd);
-        }
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          *reinterpret_cast<uint4*>(sP + sw128_offset(lt, hf * 4 + jj, kQBlock)) = pack8<T>(pr + jj * 8);
-          *reinterpret_cast<uint4*>(sdS + sw128_offset(lt, hf * 4 + jj, kQBlock)) = pack8<T>(dp + jj * 8);
-        }
-      }
-      fence_async_smem();
+    // ---- P and dS of row `lt`, this thread's 32 keys
+    {
+      const int r = sRow[lt];
+      const float lse2 = sLse[lt] * kLog2e, dd = sDsum[lt];
+      const int lim = r < 0 ? 0 : (p.causal ? min(keys_valid, r + shift - key0 + 1) : keys_valid);
+      float pr[32], dp[32];
+      tmem_ld32(tS + lane_sel + hf * 32, pr);
+      tmem_ld32(tdP + lane_sel + hf * 32, dp);
+      tmem_ld_wait();
       tc_fence_before_sync();
-      good = __syncthreads_and(good);           // P, dS complete; S and dP have been read by every thread
-      if (!good) break;
-      tc_fence_after_sync();
-      if (tid == 0) {
-        const uint32_t acc = g > 0 ? 1u : 0u;   // the item's first tile starts the accumulators
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          // dV^T[half] += dO^T.P, dK^T[half] += Q^T.dS : M = 128 head-dim columns, N = keys, K = the rows
-          umma_gemm<kM / 16>(tdV + hh * 64, desc_lo_sw128(smem_u32(sdO) + hh * 2 * kQBlock, kQBlock), hi, 128, 512,
-                             p_mn, hi, 128, 512, idesc_t, acc);
-          umma_gemm<kM / 16>(tdK + hh * 64, desc_lo_sw128(smem_u32(sQ) + hh * 2 * kQBlock, kQBlock), hi, 128, 512,
-                             ds_mn, hi, 128, 512, idesc_t, acc);
-        }
-        // dQ[first half of the head dim] = dS.K over the columns S and dP occupied
-        umma_gemm<kC / 16>(tdQ, ds_km, hi, 2, 0, desc_lo_sw128(smem_u32(sK), kKBlock), hi, 128, 512, idesc_dq, 0);
-        umma_commit(&bar_b);
+      for (int jj = 0; jj < 32; ++jj) {
+        pr[jj] = (hf * 32 + jj < lim) ? exp2f(pr[jj] * scale_log2 - lse2) : 0.f;
+        dp[jj] = pr[jj] * (dp[jj] - dd);
       }
-      good = mbar_wait(&bar_b, g & 1, p.status, 4);
-      tc_fence_after_sync();
-      // ---- dQ partial of row `lt`: per head-dim half, this thread's 64 columns: scaled, rounded,
-      // staged over the Q tile (dK^T has read it), 16-byte chunks permuted like every partial
-      const int key = (int)((slot0 + lt) & 7);
-      unsigned char* srow = sQ + lt * (D * 2);
-#pragma unroll 1
-      for (int hh = 0; hh < 2; ++hh) {
 #pragma unroll
-        for (int i2 = 0; i2 < 2; ++i2) {
-          float o[32];
-          tmem_ld32(tdQ + lane_sel + hf * 64 + i2 * 32, o);
-          tmem_ld_wait();
+      for (int jj = 0; jj < 4; ++jj) {
+        *reinterpret_cast<uint4*>(sP + sw128_offset(lt, hf * 4 + jj, kQBlock)) = pack8<T>(pr + jj * 8);
+        *reinterpret_cast<uint4*>(sdS + sw128_offset(lt, hf * 4 + jj, kQBlock)) = pack8<T>(dp + jj * 8);
+      }
+    }
+    fence_async_smem();
+    tc_fence_before_sync();
+    good = __syncthreads_and(good);             // P, dS complete; S, dP and the row data have been read by every thread
+    if (!good) break;
+    tc_fence_after_sync();
+    if (tid == 0) {
+      const uint32_t acc = g > 0 ? 1u : 0u;     // the item's first tile starts the accumulators
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        // dV^T[half] += dO^T.P, dK^T[half] += Q^T.dS : M = 128 head-dim columns, N = keys, K = the rows
+        umma_gemm<kM / 16>(tdV + hh * 64, desc_lo_sw128(smem_u32(sdO) + hh * 2 * kQBlock, kQBlock), hi, 128, 512,
+                           p_mn, hi, 128, 512, idesc_t, acc);
+        umma_gemm<kM / 16>(tdK + hh * 64, desc_lo_sw128(smem_u32(sQ) + hh * 2 * kQBlock, kQBlock), hi, 128, 512,
+                           ds_mn, hi, 128, 512, idesc_t, acc);
+      }
+      // dQ[first half of the head dim] = dS.K over the columns S and dP occupied
+      umma_gemm<kC / 16>(tdQ, ds_km, hi, 2, 0, desc_lo_sw128(smem_u32(sK), kKBlock), hi, 128, 512, idesc_dq, 0);
+      umma_commit(&bar_b);
+    }
+    load_rows(nxt);                             // the next tile's row data, under these MMAs
+    good = mbar_wait(&bar_b, g & 1, p.status, 4);
+    good = __syncthreads_and(good);             // (also publishes the row data)
+    if (!good) break;
+    tc_fence_after_sync();
+    // dV^T, dK^T and the first dQ half are complete: the Q and dO tiles are free, and the next
+    // tile's rows are gathered while dQ is read out (the gathers bound this kernel)
+    if (nxt.valid) gather(nxt);
+    // ---- dQ partial of row `lt`: per head-dim half, this thread's 64 columns (128 contiguous bytes
+    // of the row's slot): scaled, rounded, written from registers, 16-byte chunks permuted like every partial
+    const int key = (int)((slot0 + lt) & 7);
+    T* dst = part_dq + (slot0 + lt) * D;
+#pragma unroll 1
+    for (int hh = 0; hh < 2; ++hh) {
+#pragma unroll
+      for (int i2 = 0; i2 < 2; ++i2) {
+        float o[32];
+        tmem_ld32(tdQ + lane_sel + hf * 64 + i2 * 32, o);
+        tmem_ld_wait();
+        if (lt < rows) {
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) {
 #pragma unroll
             for (int e = 0; e < 8; ++e) o[jj * 8 + e] *= p.scale;
-            *reinterpret_cast<uint4*>(srow + (((hh * 16 + hf * 8 + i2 * 4 + jj) ^ key) << 4)) = pack8<T>(o + jj * 8);
+            *reinterpret_cast<uint4*>(dst + (((hh * 16 + hf * 8 + i2 * 4 + jj) ^ key) << 3)) = pack8<T>(o + jj * 8);
           }
-        }
-        tc_fence_before_sync();
-        fence_async_smem();
-        good = __syncthreads_and(good);         // the half has been read out of TMEM (and staged)
-        if (!good) break;
-        if (hh == 0) {
-          tc_fence_after_sync();
-          if (tid == 0) {
-            umma_gemm<kC / 16>(tdQ, ds_km, hi, 2, 0, desc_lo_sw128(smem_u32(sK) + 2 * kKBlock, kKBlock), hi, 128, 512,
-                               idesc_dq, 0);
-            umma_commit(&bar_c);
-          }
-          good = mbar_wait(&bar_c, g & 1, p.status, 4);
-          tc_fence_after_sync();
         }
       }
-      if (!good) break;
-      if (warp < 4 && lane == 0) {
-        const int wrows = min(32, rows - warp * 32);
-        if (wrows > 0) {
-          bulk_store(part_dq + (slot0 + warp * 32) * D, sQ + warp * 32 * (D * 2), (uint32_t)wrows * D * 2);
-          bulk_commit();
+      tc_fence_before_sync();
+      if (hh == 0) {
+        __syncthreads();                        // the first half has been read out of TMEM
+        tc_fence_after_sync();
+        if (tid == 0) {
+          umma_gemm<kC / 16>(tdQ, ds_km, hi, 2, 0, desc_lo_sw128(smem_u32(sK) + 2 * kKBlock, kKBlock), hi, 128, 512,
+                             idesc_dq, 0);
+          umma_commit(&bar_c);
         }
+        good = mbar_wait(&bar_c, g & 1, p.status, 4);
+        tc_fence_after_sync();
       }
     }
+    cur = nxt;
+    // (the barrier at the top of the next tile keeps its S and dP, which overwrite dQ, behind these reads)
   }
   cp_async_wait_all();                          // (K and V of an item without tiles)
   // ---- dK (scaled) and dV of this key block: TMEM lane = head-dim index of this thread's half,
@@ -452,7 +478,6 @@ __global__ void __launch_bounds__(kThreads) bwd_wide_tc_kernel(WideParams p) {
       }
     }
   }
-  if (warp < 4 && lane == 0) bulk_wait_read();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
