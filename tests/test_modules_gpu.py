@@ -21,14 +21,15 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
+@pytest.mark.parametrize("d", [128, 256])
 @pytest.mark.parametrize("engine", [0, 1])
-def test_leftpad_and_seqused_equal_packed_keys(engine):
+def test_leftpad_and_seqused_equal_packed_keys(engine, d):
     import flash_moba_b200 as F
     from flash_moba_b200 import ops
     ops.set_engine(engine)
     try:
         torch.manual_seed(4)
-        H, Hk, d, chunk, topk = 4, 2, 128, 128, 3
+        H, Hk, chunk, topk = 4, 2, 128, 3
         lens_q, lens_k, pad, slack = [200, 77], [520, 333], [64, 8], [40, 0]
         q = torch.randn(sum(lens_q), H, d, device=DEV).bfloat16()
         ks = [torch.randn(n, Hk, d, device=DEV).bfloat16() for n in lens_k]
