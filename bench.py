@@ -445,6 +445,11 @@ def main():
         barrier()
         launches0 = _lib.lib.fmb_launch_count()
         _lib.lib.fmb_profile_enable(1)
+        # a collection pause of the interpreter in the middle of a short timed region (15 ms at 8 GPUs)
+        # would stall one rank's launches, and the slowest rank is the result
+        import gc
+        gc.collect()
+        gc.disable()
         barrier()
         clk.mark("start")
         ev0.record()
@@ -453,7 +458,10 @@ def main():
         ev1.record()
         barrier()
         clk.mark("end")
+        gc.enable()
     ms = ev0.elapsed_time(ev1) / args.steps
+    if os.environ.get("FMB_BENCH_VERBOSE") == "1":
+        print(f"[rank {rank}] {ms:.4f} ms per step over {args.steps} steps", file=sys.stderr, flush=True)
     launches = _lib.lib.fmb_launch_count() - launches0
     # device-side status words of every attention call so far, and of the gating launches
     status = 0

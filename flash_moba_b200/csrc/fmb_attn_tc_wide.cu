@@ -5,8 +5,10 @@
 // run here (forward: key blocks of 128 keys where the chunk allows, else 64; backward: 64), in a
 // simpler shape: one CTA of 256 threads per work item (key block, head or kv head, sequence), every
 // thread takes part in every phase, one thread issues the MMAs, and the only overlap is the
-// forward's cp.async gather of the next tile's rows under the current tile's work.  Same workspace contract (slots, per-entry partials) and the same merge kernels as
-// the other engines.  Every mbarrier wait is bounded (status word of the workspace).
+// cp.async gather of the next tile's rows under the rest of the current tile's work (the row
+// gathers, 512 bytes per row, bound these kernels).  Same workspace contract (slots, per-entry
+// partials) and the same merge kernels as the other engines.  Every mbarrier wait is bounded
+// (status word of the workspace).
 //
 // Forward, per tile of 128 gathered query rows:
 //     S = Q.K^T (K dimension d)  ->  the Q tile is refilled with the next tile's rows
