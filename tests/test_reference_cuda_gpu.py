@@ -37,6 +37,7 @@ def _inputs(lens, H, Hk, d, seed):
     ([4096], 4, 4, 128, 128, 8),
     ([1500, 700, 333], 4, 2, 128, 64, 3),
     ([2048, 900], 4, 2, 256, 128, 4),          # the wide-head kernels
+    ([3000, 1536], 8, 2, 128, 64, 16),         # configuration 4 in miniature: GQA 4:1, chunk 64, lists of 16
 ])
 def test_pattern_and_attention_against_reference_kernels(lens, H, Hk, d, chunk, topk):
     import flash_moba_b200 as F
