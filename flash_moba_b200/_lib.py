@@ -40,6 +40,7 @@ _SIGS = {
     "fmb_launch_count": (ctypes.c_ulonglong, []),
     "fmb_profile_enable": (i32, [i32]),
     "fmb_profile_read": (i32, [i32, c_ptr, i32]),
+    "fmb_profile_kinds": (i32, [ctypes.c_uint]),
     "fmb_copy_rows_async": (i32, [c_ptr, sz, c_ptr, sz, sz, sz, i32, c_ptr]),
     "fmb_chunk_offsets": (i32, [c_ptr, i32, i32, c_ptr, c_ptr]),
     "fmb_mean_pool": (i32, [c_ptr, i64, i64, c_ptr, c_ptr, c_ptr, i32, i32, i32, i32, i32, i32, c_ptr]),

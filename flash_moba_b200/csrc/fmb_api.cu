@@ -25,18 +25,19 @@ void note_launch() { __atomic_fetch_add(&g_launches, 1ull, __ATOMIC_RELAXED); }
 constexpr int kProfKinds = 8, kProfRing = 256;
 struct ProfState {
   bool on = false;
+  unsigned kinds = ~0u;       // bit k: launches of kind k are bracketed
   cudaEvent_t ev[kProfKinds][kProfRing][2] = {};
   int count[kProfKinds] = {};
 };
 static ProfState g_prof;
 void prof_begin(int kind, cudaStream_t s) {
-  if (!g_prof.on || g_prof.count[kind] >= kProfRing) return;
+  if (!g_prof.on || !((g_prof.kinds >> kind) & 1u) || g_prof.count[kind] >= kProfRing) return;
   cudaEvent_t& e = g_prof.ev[kind][g_prof.count[kind]][0];
   if (!e) cudaEventCreate(&e);
   cudaEventRecord(e, s);
 }
 void prof_end(int kind, cudaStream_t s) {
-  if (!g_prof.on || g_prof.count[kind] >= kProfRing) return;
+  if (!g_prof.on || !((g_prof.kinds >> kind) & 1u) || g_prof.count[kind] >= kProfRing) return;
   cudaEvent_t& e = g_prof.ev[kind][g_prof.count[kind]][1];
   if (!e) cudaEventCreate(&e);
   cudaEventRecord(e, s);
@@ -79,7 +80,13 @@ unsigned long long fmb_launch_count(void) { return __atomic_load_n(&g_launches, 
 
 int fmb_profile_enable(int on) {
   g_prof.on = on != 0;
+  g_prof.kinds = ~0u;
   for (int k = 0; k < kProfKinds; ++k) g_prof.count[k] = 0;
+  return FMB_OK;
+}
+
+int fmb_profile_kinds(unsigned mask) {
+  g_prof.kinds = mask;
   return FMB_OK;
 }
 

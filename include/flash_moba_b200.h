@@ -312,6 +312,10 @@ unsigned long long fmb_launch_count(void);
  * the elapsed milliseconds of each recorded launch and returns how many (or -1). */
 int fmb_profile_enable(int on);
 int fmb_profile_read(int kind, float* ms, int max_entries);
+/* Restricts the bracketing to the kinds whose bit is set in `mask` (bit k = kind k; all kinds after
+ * fmb_profile_enable): two event records per launch between short kernels are not free, and a
+ * caller that times whole steps may want only the dominant kernel bracketed meanwhile. */
+int fmb_profile_kinds(unsigned mask);
 
 /* Strided host<->device copy of a head range: `rows` rows of `width_bytes` bytes, `src_pitch` /
  * `dst_pitch` bytes apart, enqueued on `stream` (cudaMemcpy2DAsync; the host side should be
