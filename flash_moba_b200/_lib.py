@@ -44,6 +44,7 @@ _SIGS = {
     "fmb_copy_rows_async": (i32, [c_ptr, sz, c_ptr, sz, sz, sz, i32, c_ptr]),
     "fmb_chunk_offsets": (i32, [c_ptr, i32, i32, c_ptr, c_ptr]),
     "fmb_mean_pool": (i32, [c_ptr, i64, i64, c_ptr, c_ptr, c_ptr, i32, i32, i32, i32, i32, i32, c_ptr]),
+    "fmb_mean_pool_offsets": (i32, [c_ptr, i64, i64, c_ptr, c_ptr, c_ptr, i32, i32, i32, i32, i32, i32, c_ptr]),
     "fmb_gate_topk": (i32, [c_ptr, i64, i64, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, i64, i64,
                             i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, c_ptr]),
     "fmb_build_csc_workspace_bytes": (sz, [i32, i32, i32, i32]),

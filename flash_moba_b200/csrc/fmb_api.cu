@@ -188,8 +188,24 @@ int fmb_mean_pool(const void* k, int64_t k_row_stride, int64_t k_head_stride, co
   if ((rc = check_tensor("mean_pool: k", k, k_row_stride, k_head_stride, head_dim))) return rc;
   FMB_CHECK_ARG(km && aligned16(km), "mean_pool: km must be non-null and 16-byte aligned");
   FMB_CHECK_ARG(heads_k <= 65535 && batch <= 65535, "mean_pool: heads_k and batch must be <= 65535");
-  return launch_mean_pool(k, k_row_stride, k_head_stride, cu_seqlens_k, cu_seqlens_km, km, batch, heads_k,
-                          head_dim, max_seqlen_k, chunk, dtype, (cudaStream_t)stream);
+  return launch_mean_pool(k, k_row_stride, k_head_stride, cu_seqlens_k, const_cast<int32_t*>(cu_seqlens_km), km, batch,
+                          heads_k, head_dim, max_seqlen_k, chunk, dtype, (cudaStream_t)stream);
+}
+
+int fmb_mean_pool_offsets(const void* k, int64_t k_row_stride, int64_t k_head_stride, const int32_t* cu_seqlens_k,
+                          int32_t* cu_seqlens_km, void* km, int batch, int heads_k, int head_dim,
+                          int max_seqlen_k, int chunk, int dtype, fmb_stream_t stream) {
+  int rc = check_common("mean_pool", heads_k, heads_k, head_dim, dtype);
+  if (rc) return rc;
+  FMB_CHECK_ARG(chunk > 0 && batch >= 0 && max_seqlen_k >= 0, "mean_pool: bad sizes");
+  FMB_CHECK_ARG(cu_seqlens_k && cu_seqlens_km, "mean_pool: null cu_seqlens");
+  if (batch == 0 || max_seqlen_k == 0)     // nothing to pool: the offsets alone
+    return launch_chunk_offsets(cu_seqlens_k, batch, chunk, cu_seqlens_km, (cudaStream_t)stream);
+  if ((rc = check_tensor("mean_pool: k", k, k_row_stride, k_head_stride, head_dim))) return rc;
+  FMB_CHECK_ARG(km && aligned16(km), "mean_pool: km must be non-null and 16-byte aligned");
+  FMB_CHECK_ARG(heads_k <= 65535 && batch <= 65535, "mean_pool: heads_k and batch must be <= 65535");
+  return launch_mean_pool(k, k_row_stride, k_head_stride, cu_seqlens_k, cu_seqlens_km, km, batch, heads_k, head_dim,
+                          max_seqlen_k, chunk, dtype, (cudaStream_t)stream, true);
 }
 
 int fmb_gate_topk(const void* q, int64_t q_row_stride, int64_t q_head_stride, const void* km,

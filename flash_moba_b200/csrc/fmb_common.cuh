@@ -102,9 +102,9 @@ __host__ __device__ __forceinline__ size_t align_up(size_t x, size_t a) { return
 
 // ---- launchers implemented in the .cu files, called from fmb_api.cu ------------------
 int launch_chunk_offsets(const int32_t* cu_k, int batch, int chunk, int32_t* cu_km, cudaStream_t s);
-int launch_mean_pool(const void* k, int64_t rs, int64_t hs, const int32_t* cu_k, const int32_t* cu_km,
+int launch_mean_pool(const void* k, int64_t rs, int64_t hs, const int32_t* cu_k, int32_t* cu_km,
                      void* km, int batch, int heads_k, int d, int max_seqlen_k, int chunk, int dtype,
-                     cudaStream_t s);
+                     cudaStream_t s, bool offsets = false);
 
 struct GateArgs {
   const void* q; int64_t q_rs, q_hs;

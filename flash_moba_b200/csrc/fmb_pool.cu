@@ -38,11 +38,17 @@ int launch_chunk_offsets(const int32_t* cu_k, int batch, int chunk, int32_t* cu_
 
 constexpr int kPoolWarps = 4;
 
+// batches up to this many sequences have their chunk offsets computed inside the pool kernel
+// (every warp sums the chunk counts of the sequences before its own: two rounds of loads at most)
+constexpr int kPoolInlineOffsets = 64;
+
 // LPR = lanes per row (power of two >= d/8), RPI = rows per warp iteration = 32 / LPR.
-template <typename T, int LPR>
+// OFFS: cu_km is an OUTPUT: the warp derives its sequence's first centroid row from cu_k itself and
+// the first warp of every sequence publishes it (no separate offsets launch).
+template <typename T, int LPR, bool OFFS>
 __global__ void __launch_bounds__(kPoolWarps * 32)
 mean_pool_kernel(const T* __restrict__ k, int64_t row_stride, int64_t head_stride,
-                 const int32_t* __restrict__ cu_k, const int32_t* __restrict__ cu_km,
+                 const int32_t* __restrict__ cu_k, int32_t* cu_km,
                  T* __restrict__ km, int heads_k, int d, int chunk) {
   constexpr int RPI = 32 / LPR;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -50,6 +56,23 @@ mean_pool_kernel(const T* __restrict__ k, int64_t row_stride, int64_t head_strid
   const int hk = blockIdx.y, b = blockIdx.z;
   const int seq0 = cu_k[b];
   const int len = cu_k[b + 1] - seq0;
+  int km_row0;                                   // first centroid row of this sequence
+  if (OFFS) {
+    int sum = 0;
+    for (int b0 = 0; b0 < b; b0 += 32) {
+      const int bb = b0 + lane;
+      sum += bb < b ? (cu_k[bb + 1] - cu_k[bb] + chunk - 1) / chunk : 0;
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    km_row0 = sum;
+    if (n == 0 && hk == 0 && lane == 0) {
+      if (b == 0) cu_km[0] = 0;
+      cu_km[b + 1] = sum + (len + chunk - 1) / chunk;
+    }
+  } else {
+    km_row0 = cu_km[b];
+  }
   const int row0 = n * chunk;
   if (row0 >= len) return;
   const int rows = min(chunk, len - row0);
@@ -102,22 +125,26 @@ mean_pool_kernel(const T* __restrict__ k, int64_t row_stride, int64_t head_strid
     const float inv = 1.0f / (float)rows;
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] *= inv;
-    T* dst = km + ((int64_t)(cu_km[b] + n) * heads_k + hk) * d + col * 8;
+    T* dst = km + ((int64_t)(km_row0 + n) * heads_k + hk) * d + col * 8;
     *reinterpret_cast<uint4*>(dst) = pack8<T>(acc);
   }
 }
 
 template <typename T>
-static int pool_dispatch(const void* k, int64_t rs, int64_t hs, const int32_t* cu_k, const int32_t* cu_km,
+static int pool_dispatch(const void* k, int64_t rs, int64_t hs, const int32_t* cu_k, int32_t* cu_km,
                          void* km, int batch, int heads_k, int d, int max_seqlen_k, int chunk,
-                         cudaStream_t s) {
+                         bool offsets, cudaStream_t s) {
   const int nchunk = ceil_div(max_seqlen_k, chunk);
   if (nchunk == 0 || batch == 0) return FMB_OK;
   dim3 grid(ceil_div(nchunk, kPoolWarps), heads_k, batch), block(kPoolWarps * 32);
   const int lanes = d / 8;
   const T* kp = static_cast<const T*>(k);
   T* kmp = static_cast<T*>(km);
-#define FMB_POOL(L) mean_pool_kernel<T, L><<<grid, block, 0, s>>>(kp, rs, hs, cu_k, cu_km, kmp, heads_k, d, chunk)
+#define FMB_POOL(L)                                                                                              \
+  do {                                                                                                           \
+    if (offsets) mean_pool_kernel<T, L, true><<<grid, block, 0, s>>>(kp, rs, hs, cu_k, cu_km, kmp, heads_k, d, chunk);   \
+    else mean_pool_kernel<T, L, false><<<grid, block, 0, s>>>(kp, rs, hs, cu_k, cu_km, kmp, heads_k, d, chunk);  \
+  } while (0)
   if (lanes <= 1) FMB_POOL(1);
   else if (lanes <= 2) FMB_POOL(2);
   else if (lanes <= 4) FMB_POOL(4);
@@ -129,13 +156,23 @@ static int pool_dispatch(const void* k, int64_t rs, int64_t hs, const int32_t* c
   return FMB_OK;
 }
 
-int launch_mean_pool(const void* k, int64_t rs, int64_t hs, const int32_t* cu_k, const int32_t* cu_km,
+// offsets: cu_km is written (by the pool kernel itself for small batches, by the offsets kernel
+// first otherwise) instead of read
+int launch_mean_pool(const void* k, int64_t rs, int64_t hs, const int32_t* cu_k, int32_t* cu_km,
                      void* km, int batch, int heads_k, int d, int max_seqlen_k, int chunk, int dtype,
-                     cudaStream_t s) {
+                     cudaStream_t s, bool offsets) {
   prof_begin(3, s);
-  const int rc = dtype == FMB_BF16
-      ? pool_dispatch<__nv_bfloat16>(k, rs, hs, cu_k, cu_km, km, batch, heads_k, d, max_seqlen_k, chunk, s)
-      : pool_dispatch<__half>(k, rs, hs, cu_k, cu_km, km, batch, heads_k, d, max_seqlen_k, chunk, s);
+  bool inline_offsets = false;
+  int rc = FMB_OK;
+  if (offsets) {
+    // a batch without keys launches no pool kernel: the offsets kernel then writes the zeros
+    inline_offsets = batch <= kPoolInlineOffsets && ceil_div(max_seqlen_k, chunk) > 0;
+    if (!inline_offsets) rc = launch_chunk_offsets(cu_k, batch, chunk, cu_km, s);
+  }
+  if (rc == FMB_OK)
+    rc = dtype == FMB_BF16
+        ? pool_dispatch<__nv_bfloat16>(k, rs, hs, cu_k, cu_km, km, batch, heads_k, d, max_seqlen_k, chunk, inline_offsets, s)
+        : pool_dispatch<__half>(k, rs, hs, cu_k, cu_km, km, batch, heads_k, d, max_seqlen_k, chunk, inline_offsets, s);
   prof_end(3, s);
   return rc;
 }

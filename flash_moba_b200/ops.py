@@ -241,9 +241,8 @@ def mean_pool(k: torch.Tensor, cu_seqlens_k: torch.Tensor, max_seqlen_k: int, ch
     with torch.cuda.device(k.device):
         km = torch.empty((rows_ub, hk, d), dtype=k.dtype, device=k.device)
         cu_km = torch.empty((batch + 1,), dtype=torch.int32, device=k.device)
-        check(lib.fmb_chunk_offsets(ptr(cu_seqlens_k), batch, chunk, ptr(cu_km), _stream()))
-        check(lib.fmb_mean_pool(ptr(k), k.stride(0), k.stride(1), ptr(cu_seqlens_k), ptr(cu_km), ptr(km),
-                                batch, hk, d, int(max_seqlen_k), chunk, _dtype_code(k), _stream()))
+        check(lib.fmb_mean_pool_offsets(ptr(k), k.stride(0), k.stride(1), ptr(cu_seqlens_k), ptr(cu_km), ptr(km),
+                                        batch, hk, d, int(max_seqlen_k), chunk, _dtype_code(k), _stream()))
     return km, cu_km
 
 

@@ -78,6 +78,14 @@ int fmb_mean_pool(const void* k, int64_t k_row_stride, int64_t k_head_stride,
                   int batch, int heads_k, int head_dim, int max_seqlen_k, int chunk,
                   int dtype, fmb_stream_t stream);
 
+/* fmb_chunk_offsets and fmb_mean_pool in one call: cu_seqlens_km is an OUTPUT here.  For batches of
+ * at most 64 sequences it is one launch (every warp of the pool kernel derives its sequence's first
+ * centroid row from cu_seqlens_k itself); larger batches take the two launches above. */
+int fmb_mean_pool_offsets(const void* k, int64_t k_row_stride, int64_t k_head_stride,
+                          const int32_t* cu_seqlens_k, int32_t* cu_seqlens_km, void* km,
+                          int batch, int heads_k, int head_dim, int max_seqlen_k, int chunk,
+                          int dtype, fmb_stream_t stream);
+
 /* ------------------------------------------------------------------ stage G: gating top-k
  * For every query row and q head: scores q . km (fp32, unscaled) against the centroids of
  * its sequence (kv head = h / (heads/heads_k)), causal chunk rule, top-k.

@@ -25,6 +25,7 @@ def _ops():
 @pytest.mark.parametrize("batch,max_seqlen,heads,d,chunk", [
     (1, 512, 4, 64, 32), (8, 512, 4, 128, 128), (8, 2048, 12, 128, 256), (1, 2048, 4, 256, 512),
     (8, 512, 12, 64, 64), (4, 128, 4, 32, 256), (16, 8, 4, 32, 4), (3, 700, 2, 96, 128),
+    (64, 300, 2, 64, 64), (65, 300, 2, 64, 64), (200, 90, 2, 128, 32),   # chunk offsets inside the pool kernel up to 64 sequences, by their own launch above
 ])
 def test_mean_pool_vs_oracle(batch, max_seqlen, heads, d, chunk, dtype):
     # tolerance of the reference test: atol 1e-2, rtol 0 (tests/test_triton_mean_pool.py:63-64)
@@ -580,7 +581,7 @@ def test_lists_of_a_caller_built_pattern_and_launch_counts(monkeypatch):
     out = F.flash_moba_varlen_func(qd, kd, vd, cu, cu, mx, mx, chunk, topk, causal=True)
     torch.autograd.grad(out, (qd, kd, vd), do)
     torch.cuda.synchronize()
-    assert _lib.lib.fmb_launch_count() - n0 <= 12
+    assert _lib.lib.fmb_launch_count() - n0 <= 10
 
 
 def test_determinism_and_autograd_through_public_api():
