@@ -1,4 +1,5 @@
-"""Parity at the headline sequence length (65,536 tokens, chunk 128, top-k 8, d 128, bf16).
+"""Parity at the headline sequence length (65,536 tokens, chunk 128, top-k 8, bf16; d 128 with
+four heads, and d 256 with two: the wide-head kernels).
 
 The dense oracle cannot hold a 64K x 64K score matrix, so the checks are the size-independent
 ones: run-to-run bit identity, and sampled rows / key blocks recomputed on the CPU from the
@@ -22,12 +23,13 @@ from oracle import moba_oracle as O  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
-S, H, D, CHUNK, TOPK = 65536, 4, 128, 128, 8
+S, CHUNK, TOPK = 65536, 128, 8
 
 
-@pytest.fixture(scope="module")
-def run64k():
+@pytest.fixture(scope="module", params=[(4, 128), (2, 256)], ids=["d128", "d256"])
+def run64k(request):
     import flash_moba_b200 as F
+    H, D = request.param
     g = torch.Generator(device=DEV).manual_seed(2024)
     mk = lambda: torch.randn(S, H, D, generator=g, device=DEV, dtype=torch.float32).to(torch.bfloat16)
     q, k, v, do = mk(), mk(), mk(), mk()
@@ -40,7 +42,7 @@ def run64k():
                                                     return_attn_probs=True)
         dq, dk, dv = torch.autograd.grad(out, (qd, kd, vd), do)
         outs.append((out.detach(), lse.detach(), dq, dk, dv))
-    return dict(q=q, k=k, v=v, do=do, cu=cu, pattern=(co, cn, ind), runs=outs)
+    return dict(q=q, k=k, v=v, do=do, cu=cu, pattern=(co, cn, ind), runs=outs, H=H, D=D)
 
 
 def test_two_runs_bit_identical(run64k):
@@ -56,7 +58,7 @@ def _rows_of_column(pattern, h, c):
 
 
 def test_pattern_of_sampled_rows(run64k):
-    q, k = run64k["q"], run64k["k"]
+    q, k, H = run64k["q"], run64k["k"], run64k["H"]
     pattern = tuple(t.cpu() for t in run64k["pattern"])
     km, cu_km = O.mean_pool(k.cpu(), run64k["cu"].cpu(), CHUNK)
     g = torch.Generator().manual_seed(1)
@@ -86,6 +88,7 @@ def test_sampled_rows_outputs_and_dq(run64k):
     q, k, v, do = (run64k[n] for n in ("q", "k", "v", "do"))
     co, cn, ind = (t.cpu() for t in run64k["pattern"])
     out, lse, dq, _, _ = run64k["runs"][0]
+    H, D = run64k["H"], run64k["D"]
     scale = 1.0 / math.sqrt(D)
     # row -> chunks from the CSC itself (the pattern the GPU used): scan the columns of a few heads
     g = torch.Generator().manual_seed(3)
@@ -128,10 +131,11 @@ def test_sampled_key_blocks_dk_dv(run64k):
     q, k, v, do = (run64k[n] for n in ("q", "k", "v", "do"))
     pattern = tuple(t.cpu() for t in run64k["pattern"])
     out, lse, _, dk, dv = run64k["runs"][0]
+    H, D = run64k["H"], run64k["D"]
     scale = 1.0 / math.sqrt(D)
     worst_k = worst_v = 0.0
     scale_ref = 0.0
-    for h, c in ((0, 0), (1, 7), (2, 255), (3, 511), (0, 300)):
+    for h, c in ((0, 0), (1, 7), (2 % H, 255), (3 % H, 511), (0, 300)):
         rows = _rows_of_column(pattern, h, c)
         keys = torch.arange(c * CHUNK, (c + 1) * CHUNK)
         qf = q[rows, h].cpu().float()
